@@ -1,0 +1,84 @@
+// Shared helpers for the engine's CUDA kernels (sm_100a).
+//
+// Every exported launcher is `extern "C"`, takes raw device pointers plus a `cudaStream_t` and returns a
+// status: 0 on success, a negative CVB_E_* code when it refuses its arguments (the Python wrapper turns the
+// code into an exception with the text from cvb_error_string), or the positive cudaError_t of a failed launch.
+// Activations come in two element types selected by an integer code: 0 = float (the true 32-bit path),
+// 1 = __nv_bfloat16.  All arithmetic between loads and stores is float; `rnd<T>` rounds to the activation
+// type and back where the reference rounds (kernels/fused_ops.cu:27).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define CVB_OK 0
+#define CVB_E_DTYPE (-1)      // element type code is neither 0 (float) nor 1 (bf16)
+#define CVB_E_SIZE (-2)       // a size is zero/negative where it must be positive, or beyond a kernel's limit
+#define CVB_E_ALIGN (-3)      // a pointer or row length breaks the kernel's alignment rule
+#define CVB_E_SHAPE (-4)      // sizes are inconsistent with one another (heads vs groups, rotary width, ...)
+#define CVB_E_UNSUPPORTED (-5)  // this specialised kernel does not cover the configuration; use the general one
+#define CVB_E_SCRATCH (-6)    // scratch memory is missing or too small
+
+#define CVB_DTYPE_F32 0
+#define CVB_DTYPE_BF16 1
+
+namespace cvb {
+
+__device__ __forceinline__ float to_float(float x) { return x; }
+__device__ __forceinline__ float to_float(__nv_bfloat16 x) { return __bfloat162float(x); }
+
+template <typename T> __device__ __forceinline__ T from_float(float x);
+template <> __device__ __forceinline__ float from_float<float>(float x) { return x; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
+
+// Round to the activation type and come back: identity in the 32-bit path.
+template <typename T> __device__ __forceinline__ float rnd(float x) { return to_float(from_float<T>(x)); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over the block; every thread receives the result.  `scratch` holds at least 32 floats.  The partial
+// sums are added in warp order so that the result does not depend on scheduling.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+    v = warp_sum(v);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = (blockDim.x + 31) >> 5;
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float r = 0.f;
+    for (int i = 0; i < n_warps; ++i) r += scratch[i];
+    __syncthreads();
+    return r;
+}
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+    v = warp_max(v);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n_warps = (blockDim.x + 31) >> 5;
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float r = scratch[0];
+    for (int i = 1; i < n_warps; ++i) r = fmaxf(r, scratch[i]);
+    __syncthreads();
+    return r;
+}
+
+inline int launch_status() {
+    cudaError_t e = cudaGetLastError();
+    return e == cudaSuccess ? CVB_OK : static_cast<int>(e);
+}
+
+}  // namespace cvb
+
+// Dispatch on the element type code.  `CALL` is a macro taking the C++ type.
+#define CVB_DISPATCH_DTYPE(code, CALL)                       \
+    do {                                                     \
+        if ((code) == CVB_DTYPE_F32) { CALL(float); }        \
+        else if ((code) == CVB_DTYPE_BF16) { CALL(__nv_bfloat16); } \
+        else return CVB_E_DTYPE;                             \
+    } while (0)

@@ -1,0 +1,145 @@
+// Embedding gather, RMSNorm, residual-add + RMSNorm, residual add, SwiGLU and row gather.
+// General kernels: any row length, float or bf16 activations, float norm weights.
+//
+// Formulas (reference kernels/fused_ops.cu):
+//   rms_norm      :61-88   out = T( rnd(x * rsqrt(mean(x^2) + eps)) * w )
+//   add_rms_norm  :70-87   resid = T(resid + x) first, then the norm of the new residual
+//   swiglu        :210-220 out = T( rnd(g / (1 + exp(-g))) * u ),  g = gu[r, i], u = gu[r, I + i]
+// Sums of squares, rsqrt, the residual sum and the activation are float in both paths.
+#include "common.cuh"
+
+namespace cvb {
+
+template <typename T>
+__global__ void embed_kernel(T* __restrict__ out, const T* __restrict__ table, const int* __restrict__ tokens,
+                             int D, int V, int* __restrict__ err) {
+    const int64_t t = blockIdx.x;
+    int tok = tokens[t];
+    if (tok < 0 || tok >= V) {           // never read outside the table: record and clamp
+        if (threadIdx.x == 0) atomicExch(err, 1);
+        tok = tok < 0 ? 0 : V - 1;
+    }
+    const T* src = table + static_cast<int64_t>(tok) * D;
+    T* dst = out + t * D;
+    for (int i = threadIdx.x; i < D; i += blockDim.x) dst[i] = src[i];
+}
+
+template <typename T, bool ADD>
+__global__ void rmsnorm_kernel(T* __restrict__ out, T* resid, const T* __restrict__ x, const float* __restrict__ w,
+                               int D, float eps) {
+    __shared__ float scratch[32];
+    const int64_t row = blockIdx.x;
+    const T* xin = x + row * D;
+    T* res = ADD ? resid + row * D : nullptr;
+    T* o = out + row * D;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < D; i += blockDim.x) {
+        float v;
+        if constexpr (ADD) {
+            v = rnd<T>(to_float(res[i]) + to_float(xin[i]));
+            res[i] = from_float<T>(v);
+        } else {
+            v = to_float(xin[i]);
+        }
+        ss += v * v;
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = rsqrtf(ss / static_cast<float>(D) + eps);
+    for (int i = threadIdx.x; i < D; i += blockDim.x) {
+        const float v = ADD ? to_float(res[i]) : to_float(xin[i]);
+        o[i] = from_float<T>(rnd<T>(v * inv) * w[i]);
+    }
+}
+
+template <typename T>
+__global__ void add_kernel(T* __restrict__ resid, const T* __restrict__ x, int64_t n) {
+    const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i < n) resid[i] = from_float<T>(to_float(resid[i]) + to_float(x[i]));
+}
+
+template <typename T>
+__global__ void swiglu_kernel(T* __restrict__ out, const T* __restrict__ gu, int64_t n, int I) {
+    const int64_t k = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (k >= n) return;
+    const int64_t r = k / I;
+    const int i = static_cast<int>(k - r * I);
+    const float g = to_float(gu[r * 2 * I + i]);
+    const float u = to_float(gu[r * 2 * I + I + i]);
+    const float silu = rnd<T>(g / (1.f + expf(-g)));
+    out[k] = from_float<T>(silu * u);
+}
+
+template <typename T>
+__global__ void gather_rows_kernel(T* __restrict__ out, const T* __restrict__ in, const int* __restrict__ rows,
+                                   int D, int n_in) {
+    const int64_t r = blockIdx.x;
+    int src = rows[r];
+    if (src < 0) src = 0;
+    if (src >= n_in) src = n_in - 1;
+    for (int i = threadIdx.x; i < D; i += blockDim.x) out[r * D + i] = in[static_cast<int64_t>(src) * D + i];
+}
+
+}  // namespace cvb
+
+using namespace cvb;
+
+extern "C" int cvb_embed(void* out, const void* table, const int* tokens, int T, int D, int V, int dtype,
+                         int* err_flag, cudaStream_t stream) {
+    if (T == 0) return CVB_OK;
+    if (T < 0 || D <= 0 || V <= 0) return CVB_E_SIZE;
+#define CALL(TY) embed_kernel<TY><<<T, 128, 0, stream>>>((TY*)out, (const TY*)table, tokens, D, V, err_flag)
+    CVB_DISPATCH_DTYPE(dtype, CALL);
+#undef CALL
+    return launch_status();
+}
+
+extern "C" int cvb_rmsnorm(void* out, const void* x, const float* w, int T, int D, float eps, int dtype,
+                           cudaStream_t stream) {
+    if (T == 0) return CVB_OK;
+    if (T < 0 || D <= 0) return CVB_E_SIZE;
+#define CALL(TY) rmsnorm_kernel<TY, false><<<T, 256, 0, stream>>>((TY*)out, nullptr, (const TY*)x, w, D, eps)
+    CVB_DISPATCH_DTYPE(dtype, CALL);
+#undef CALL
+    return launch_status();
+}
+
+extern "C" int cvb_add_rmsnorm(void* out, void* resid, const void* x, const float* w, int T, int D, float eps,
+                               int dtype, cudaStream_t stream) {
+    if (T == 0) return CVB_OK;
+    if (T < 0 || D <= 0) return CVB_E_SIZE;
+#define CALL(TY) rmsnorm_kernel<TY, true><<<T, 256, 0, stream>>>((TY*)out, (TY*)resid, (const TY*)x, w, D, eps)
+    CVB_DISPATCH_DTYPE(dtype, CALL);
+#undef CALL
+    return launch_status();
+}
+
+extern "C" int cvb_add(void* resid, const void* x, int64_t n, int dtype, cudaStream_t stream) {
+    if (n == 0) return CVB_OK;
+    if (n < 0) return CVB_E_SIZE;
+    const unsigned blocks = static_cast<unsigned>((n + 255) / 256);
+#define CALL(TY) add_kernel<TY><<<blocks, 256, 0, stream>>>((TY*)resid, (const TY*)x, n)
+    CVB_DISPATCH_DTYPE(dtype, CALL);
+#undef CALL
+    return launch_status();
+}
+
+extern "C" int cvb_swiglu(void* out, const void* gate_up, int T, int I, int dtype, cudaStream_t stream) {
+    if (T == 0) return CVB_OK;
+    if (T < 0 || I <= 0) return CVB_E_SIZE;
+    const int64_t n = static_cast<int64_t>(T) * I;
+    const unsigned blocks = static_cast<unsigned>((n + 255) / 256);
+#define CALL(TY) swiglu_kernel<TY><<<blocks, 256, 0, stream>>>((TY*)out, (const TY*)gate_up, n, I)
+    CVB_DISPATCH_DTYPE(dtype, CALL);
+#undef CALL
+    return launch_status();
+}
+
+extern "C" int cvb_gather_rows(void* out, const void* in, const int* rows, int R, int D, int n_in, int dtype,
+                               cudaStream_t stream) {
+    if (R == 0) return CVB_OK;
+    if (R < 0 || D <= 0 || n_in <= 0) return CVB_E_SIZE;
+#define CALL(TY) gather_rows_kernel<TY><<<R, 128, 0, stream>>>((TY*)out, (const TY*)in, rows, D, n_in)
+    CVB_DISPATCH_DTYPE(dtype, CALL);
+#undef CALL
+    return launch_status();
+}

@@ -1,0 +1,299 @@
+"""Python faces of the CUDA launchers: argument checks, pointer passing, status codes turned into errors.
+
+Every function works on CUDA tensors only and launches on the current stream of PyTorch, so the launches
+are ordered with PyTorch's own work and are captured by ``torch.cuda.graph``.  There is no CPU path: a
+tensor that is not on a CUDA device, or a missing compiler, raises.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_int, c_int64, c_float, c_void_p
+from typing import Optional
+
+import torch
+
+from .build import load_library
+
+_ERRORS = {
+    -1: "element type must be float32 or bfloat16",
+    -2: "a size is zero, negative or beyond what the kernel takes",
+    -3: "a pointer or a row length breaks the kernel's alignment rule",
+    -4: "sizes are inconsistent with one another",
+    -5: "this specialised kernel does not cover the configuration",
+    -6: "scratch memory is missing or too small",
+}
+
+DEVICE_ERRORS = {
+    1: "a token id lies outside the embedding table",
+    2: "a cache slot lies outside the page pool",
+    3: "a position lies outside the rotary tables (beyond max_position_embeddings)",
+    4: "attention needed a key whose page is missing from the block table",
+    5: "a bounded wait in a kernel ran out",
+}
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def _check(status: int, what: str) -> None:
+    if status == 0:
+        return
+    if status < 0:
+        raise KernelError(f"{what}: refused: {_ERRORS.get(status, f'code {status}')}")
+    raise KernelError(f"{what}: CUDA launch failed with cudaError {status}")
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    if dt == torch.float32:
+        return 0
+    if dt == torch.bfloat16:
+        return 1
+    raise KernelError(f"element type must be float32 or bfloat16, got {dt}")
+
+
+def _cuda(*tensors) -> None:
+    for t in tensors:
+        if t is not None and not t.is_cuda:
+            raise KernelError("the kernels run on CUDA tensors only; got a tensor on " + str(t.device))
+
+
+def _contig(*tensors) -> None:
+    for t in tensors:
+        if t is not None and not t.is_contiguous():
+            raise KernelError("kernel arguments must be contiguous")
+
+
+def _ptr(t: Optional[torch.Tensor]):
+    return c_void_p(t.data_ptr()) if t is not None else c_void_p(0)
+
+
+def _stream():
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+_core = None
+
+
+def core():
+    global _core
+    if _core is None:
+        lib = load_library("core")
+        for name in ("cvb_embed", "cvb_rmsnorm", "cvb_add_rmsnorm", "cvb_add", "cvb_swiglu", "cvb_gather_rows",
+                     "cvb_qk_norm_rope_kv", "cvb_paged_attention_general", "cvb_sample", "cvb_feed_tokens"):
+            getattr(lib, name).restype = c_int
+        _core = lib
+    return _core
+
+
+_err_flags = {}
+
+
+def error_flag(device) -> torch.Tensor:
+    """One int32 per device that kernels set when they meet an index they refuse to follow."""
+    device = torch.device(device)
+    key = device.index if device.index is not None else torch.cuda.current_device()
+    f = _err_flags.get(key)
+    if f is None:
+        f = torch.zeros(1, dtype=torch.int32, device=device)
+        _err_flags[key] = f
+    return f
+
+
+def check_device_errors(device) -> None:
+    """Read the device error flag (synchronises) and raise if a kernel recorded a refused index."""
+    f = error_flag(device)
+    v = int(f.item())
+    if v != 0:
+        f.zero_()
+        raise KernelError(f"a kernel reported: {DEVICE_ERRORS.get(v, f'error {v}')}")
+
+
+# ---- elementwise ------------------------------------------------------------------------------------------
+
+def embed(out: torch.Tensor, table: torch.Tensor, tokens: torch.Tensor) -> torch.Tensor:
+    _cuda(out, table, tokens); _contig(out, table, tokens)
+    T, D = out.shape
+    if tokens.dtype != torch.int32 or tokens.numel() != T or table.shape[1] != D or table.dtype != out.dtype:
+        raise KernelError("embed: tokens must be int32 [T]; table [V, D] and out [T, D] of one element type")
+    _check(core().cvb_embed(_ptr(out), _ptr(table), _ptr(tokens), c_int(T), c_int(D), c_int(table.shape[0]),
+                            c_int(dtype_code(out.dtype)), _ptr(error_flag(out.device)), _stream()), "embed")
+    return out
+
+
+def rmsnorm(out: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    _cuda(out, x, weight); _contig(out, x, weight)
+    T, D = x.shape
+    if weight.dtype != torch.float32 or weight.numel() != D or out.shape != x.shape or out.dtype != x.dtype:
+        raise KernelError("rmsnorm: weight must be float32 [D]; out like x")
+    _check(core().cvb_rmsnorm(_ptr(out), _ptr(x), _ptr(weight), c_int(T), c_int(D), c_float(eps),
+                              c_int(dtype_code(x.dtype)), _stream()), "rmsnorm")
+    return out
+
+
+def add_rmsnorm(out: torch.Tensor, resid: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    """resid <- T(resid + x) in place; out <- rmsnorm(resid)."""
+    _cuda(out, resid, x, weight); _contig(out, resid, x, weight)
+    T, D = x.shape
+    if (weight.dtype != torch.float32 or weight.numel() != D or out.shape != x.shape or resid.shape != x.shape
+            or out.dtype != x.dtype or resid.dtype != x.dtype):
+        raise KernelError("add_rmsnorm: weight must be float32 [D]; out, resid like x")
+    _check(core().cvb_add_rmsnorm(_ptr(out), _ptr(resid), _ptr(x), _ptr(weight), c_int(T), c_int(D), c_float(eps),
+                                  c_int(dtype_code(x.dtype)), _stream()), "add_rmsnorm")
+    return out
+
+
+def add_(resid: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
+    _cuda(resid, x); _contig(resid, x)
+    if resid.shape != x.shape or resid.dtype != x.dtype:
+        raise KernelError("add_: operands must match")
+    _check(core().cvb_add(_ptr(resid), _ptr(x), c_int64(x.numel()), c_int(dtype_code(x.dtype)), _stream()), "add_")
+    return resid
+
+
+def swiglu(out: torch.Tensor, gate_up: torch.Tensor) -> torch.Tensor:
+    _cuda(out, gate_up); _contig(out, gate_up)
+    T, I = out.shape
+    if gate_up.shape != (T, 2 * I) or gate_up.dtype != out.dtype:
+        raise KernelError("swiglu: gate_up must be [T, 2I] for out [T, I]")
+    _check(core().cvb_swiglu(_ptr(out), _ptr(gate_up), c_int(T), c_int(I), c_int(dtype_code(out.dtype)), _stream()),
+           "swiglu")
+    return out
+
+
+def gather_rows(out: torch.Tensor, src: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
+    _cuda(out, src, rows); _contig(out, src, rows)
+    R, D = out.shape
+    if rows.dtype != torch.int32 or rows.numel() < R or src.shape[1] != D or src.dtype != out.dtype:
+        raise KernelError("gather_rows: rows must be int32 [R]; src [N, D], out [R, D] of one element type")
+    _check(core().cvb_gather_rows(_ptr(out), _ptr(src), _ptr(rows), c_int(R), c_int(D), c_int(src.shape[0]),
+                                  c_int(dtype_code(out.dtype)), _stream()), "gather_rows")
+    return out
+
+
+# ---- projection epilogue: per-head norm, rotary, cache write --------------------------------------------------
+
+def qk_norm_rope_kv(q_out: torch.Tensor, qkv: torch.Tensor, q_weight: Optional[torch.Tensor],
+                    k_weight: Optional[torch.Tensor], cos: Optional[torch.Tensor], sin: Optional[torch.Tensor],
+                    positions: Optional[torch.Tensor], slots: Optional[torch.Tensor],
+                    cache: Optional[torch.Tensor], num_heads: int, num_kv_heads: int, head_dim: int,
+                    page_size: int, eps: float, rotary_dim: Optional[int] = None, interleaved: bool = False) -> torch.Tensor:
+    """q_out[T, H, hd] <- rotate(norm(q)); k -> rotate(norm(k)) and v into `cache` [pages, 2, KV, page, hd]."""
+    _cuda(q_out, qkv, q_weight, k_weight, cos, sin, positions, slots, cache)
+    _contig(q_out, qkv, q_weight, k_weight, cos, sin, positions, slots, cache)
+    T = qkv.shape[0]
+    H, KV, hd = num_heads, num_kv_heads, head_dim
+    if qkv.shape[1] != (H + 2 * KV) * hd or q_out.numel() != T * H * hd or q_out.dtype != qkv.dtype:
+        raise KernelError("qk_norm_rope_kv: qkv must be [T, (H + 2 KV) hd] and q_out [T, H, hd]")
+    for w in (q_weight, k_weight):
+        if w is not None and (w.dtype != torch.float32 or w.numel() != hd):
+            raise KernelError("qk_norm_rope_kv: per-head norm weights must be float32 [hd]")
+    rot = head_dim if rotary_dim is None else int(rotary_dim)
+    max_pos = 0
+    if cos is not None:
+        if cos.dtype != torch.float32 or sin is None or sin.shape != cos.shape or cos.shape[1] != rot // 2:
+            raise KernelError("qk_norm_rope_kv: cos/sin tables must be float32 [max_pos, rotary_dim / 2]")
+        max_pos = cos.shape[0]
+        if positions is None or positions.dtype != torch.int32 or positions.numel() < T:
+            raise KernelError("qk_norm_rope_kv: positions must be int32 [T]")
+    if slots is not None and (slots.dtype != torch.int32 or slots.numel() < T):
+        raise KernelError("qk_norm_rope_kv: slots must be int32 [T]")
+    cache_elems = 0
+    if cache is not None:
+        if cache.dtype != qkv.dtype:
+            raise KernelError("qk_norm_rope_kv: cache pages must have the activations' element type")
+        cache_elems = cache.numel()
+    _check(core().cvb_qk_norm_rope_kv(
+        _ptr(q_out), _ptr(qkv), _ptr(q_weight), _ptr(k_weight), _ptr(cos), _ptr(sin), _ptr(positions), _ptr(slots),
+        _ptr(cache), c_int(T), c_int(H), c_int(KV), c_int(hd), c_int(rot), c_int(1 if interleaved else 0),
+        c_int(page_size), c_int(max_pos), c_float(eps), c_int64(cache_elems), c_int(dtype_code(qkv.dtype)),
+        _ptr(error_flag(qkv.device)), _stream()), "qk_norm_rope_kv")
+    return q_out
+
+
+# ---- attention ---------------------------------------------------------------------------------------------
+
+def paged_attention_general(out: torch.Tensor, q: torch.Tensor, cache: torch.Tensor, block_tables: torch.Tensor,
+                            seq_of_token: torch.Tensor, positions: torch.Tensor, num_heads: int, num_kv_heads: int,
+                            head_dim: int, page_size: int, scale: float, window: int = 0,
+                            num_tokens: Optional[int] = None) -> torch.Tensor:
+    _cuda(out, q, cache, block_tables, seq_of_token, positions)
+    _contig(out, q, cache, block_tables, seq_of_token, positions)
+    T = q.shape[0] if num_tokens is None else num_tokens
+    if q.dtype != cache.dtype or out.dtype != q.dtype:
+        raise KernelError("paged_attention: q, out and the cache pages must share one element type")
+    if block_tables.dtype != torch.int32 or block_tables.dim() != 2:
+        raise KernelError("paged_attention: block_tables must be int32 [S, W]")
+    if seq_of_token.dtype != torch.int32 or positions.dtype != torch.int32:
+        raise KernelError("paged_attention: seq_of_token and positions must be int32")
+    if num_heads % num_kv_heads:
+        raise KernelError(f"paged_attention: {num_heads} query heads are not a multiple of {num_kv_heads} kv heads")
+    page_elems = 2 * num_kv_heads * page_size * head_dim
+    num_pages = cache.numel() // page_elems
+    _check(core().cvb_paged_attention_general(
+        _ptr(out), _ptr(q), _ptr(cache), _ptr(block_tables), c_int(block_tables.shape[1]), _ptr(seq_of_token),
+        _ptr(positions), c_int(T), c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), c_int(page_size),
+        c_int(window), c_float(scale), c_int(num_pages), c_int(dtype_code(q.dtype)),
+        _ptr(error_flag(q.device)), _stream()), "paged_attention_general")
+    return out
+
+
+# ---- sampling ----------------------------------------------------------------------------------------------
+
+def sample(out: torch.Tensor, logits: torch.Tensor, rows: Optional[torch.Tensor], temps: torch.Tensor,
+           seeds: torch.Tensor, out_positions: torch.Tensor, num_rows: Optional[int] = None) -> torch.Tensor:
+    _cuda(out, logits, rows, temps, seeds, out_positions); _contig(out, logits, rows, temps, seeds, out_positions)
+    R = out.numel() if num_rows is None else num_rows
+    if (logits.dtype != torch.float32 or logits.dim() != 2 or out.dtype != torch.int32 or temps.dtype != torch.float32
+            or seeds.dtype != torch.int64 or out_positions.dtype != torch.int32
+            or (rows is not None and rows.dtype != torch.int32)):
+        raise KernelError("sample: logits float32 [N, V]; out, rows, out_positions int32; temps float32; seeds int64")
+    _check(core().cvb_sample(_ptr(out), _ptr(logits), _ptr(rows), _ptr(temps), _ptr(seeds), _ptr(out_positions),
+                             c_int(R), c_int(logits.shape[1]), c_int(logits.shape[0]), _stream()), "sample")
+    return out
+
+
+def feed_tokens(tokens: torch.Tensor, src: torch.Tensor, sampled: torch.Tensor, n: int) -> torch.Tensor:
+    _cuda(tokens, src, sampled); _contig(tokens, src, sampled)
+    if tokens.dtype != torch.int32 or src.dtype != torch.int32 or sampled.dtype != torch.int32:
+        raise KernelError("feed_tokens: all arguments must be int32")
+    _check(core().cvb_feed_tokens(_ptr(tokens), _ptr(src), _ptr(sampled), c_int(n), c_int(sampled.numel()), _stream()),
+           "feed_tokens")
+    return tokens
+
+
+# ---- library matrix products ---------------------------------------------------------------------------------
+
+def linear(x: torch.Tensor, weight: torch.Tensor, out: Optional[torch.Tensor] = None,
+           out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """y = x @ weight^T through cuBLAS, as the reference does with at::linear (model_architecture.cpp:155,178,
+    182,185,224).  float32 operands use full float32 arithmetic (no TF32); bf16 operands accumulate in
+    float32.  `out_dtype=torch.float32` with bf16 operands returns the float32 accumulators unrounded."""
+    _cuda(x, weight)
+    if x.dtype != weight.dtype:
+        if weight.dtype == torch.float32 and x.dtype == torch.bfloat16:
+            # a weight stored in 32-bit stays so: the product runs in float32 and is rounded once at the end
+            y = torch.mm(x.float(), weight.t())
+            want = out_dtype or x.dtype
+            if out is not None:
+                out.copy_(y)
+                return out
+            return y.to(want)
+        raise KernelError(f"linear: activations are {x.dtype} but the weight is {weight.dtype}")
+    if out_dtype is not None and out_dtype != x.dtype:
+        if out is not None:
+            return torch.mm(x, weight.t(), out_dtype=out_dtype, out=out)
+        return torch.mm(x, weight.t(), out_dtype=out_dtype)
+    if out is not None:
+        return torch.mm(x, weight.t(), out=out)
+    return torch.mm(x, weight.t())
+
+
+def configure_library_matmul() -> None:
+    """Pin cuBLAS to exact modes: float32 products in true float32 (no TF32), bf16 products with float32
+    accumulation and no reduced-precision split-K reduction."""
+    torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
+    try:
+        torch.backends.cuda.matmul.fp32_precision = "ieee"
+    except (AttributeError, RuntimeError):
+        torch.backends.cuda.matmul.allow_tf32 = False

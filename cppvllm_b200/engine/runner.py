@@ -1,0 +1,359 @@
+"""The step function: one flattened batch of (request, its next tokens) through the model, from the cache.
+
+``ModelRunner`` owns the model, the device storage of the cache (pages per group, state tensors per slot), the
+host-side ``CacheManager`` and the staging buffers.  ``step(entries)`` takes any mix of prompt portions and single
+decoded tokens, cut anywhere, runs exactly those tokens as ONE forward pass (the reference runs up to three
+separate passes per step, engine/model_runner.cpp:181-196), and returns float32 logits for the wanted tokens.
+
+Per step the host fills one pinned int32 staging block (tokens, positions, request index per token, cumulative
+lengths, lengths after the step, state slots, wanted rows and, per cache group, the slot of every token and
+the block tables; the reference stages the same arrays, model_runner.cpp:290-320, but derives slots on the
+device, model_architecture.cpp:137-141) and copies it with one asynchronous transfer.  Steps that consist only
+of single decoded tokens replay a CUDA graph captured per batch-size bucket (reference model_runner.cpp:371-428);
+rows that pad a bucket read and write a scratch page that no request owns (model_runner.cpp:69,329,346).
+"""
+from __future__ import annotations
+
+import json
+import os
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..cache.manager import CacheManager, GroupConfig
+from ..config.model_config import read_config_json
+from ..config.registry import resolve_architecture
+from ..csrc import ops
+from ..parts.base import Runtime, Workspace
+from ..parts.context import CacheUnitView, GroupStepView, StepContext
+from ..parts.model import CausalLM
+from ..weights.loader import load_weights
+from .. import models as _models  # noqa: F401  (registers the architectures)
+from .. import parts as _parts  # noqa: F401
+
+
+@dataclass
+class StepEntry:
+    """One request's share of a step: its next tokens, the absolute position of the first of them, and the
+    indices (within these tokens) at which logits are wanted."""
+    request_id: object
+    tokens: Sequence[int]
+    start: int
+    want: Sequence[int] = ()
+
+
+def _align(n: int, a: int = 4) -> int:
+    return (n + a - 1) // a * a
+
+
+GRAPH_BUCKETS = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256)
+
+
+class ModelRunner:
+    def __init__(self, model_dir: str, dtype=torch.bfloat16, device="cuda:0", page_size: int = 16,
+                 num_pages: Optional[int] = None, max_step_tokens: int = 4096, max_seqs: int = 256,
+                 max_model_len: int = 4096, gpu_memory_utilization: float = 0.90, enforce_eager: bool = False,
+                 num_state_slots: Optional[int] = None):
+        if not torch.cuda.is_available():
+            raise RuntimeError("cppvllm_b200 runs on a CUDA device only; torch.cuda.is_available() is False")
+        self.device = torch.device(device)
+        torch.cuda.set_device(self.device)
+        ops.configure_library_matmul()
+        ops.core()                                           # compile/load the kernels now; fails loudly
+        self.dtype = dtype
+        self.page_size = page_size
+        self.max_step_tokens = int(max_step_tokens)
+        self.max_seqs = int(max_seqs)
+        self.enforce_eager = enforce_eager
+
+        cfg_dict = read_config_json(model_dir)
+        self.arch = resolve_architecture(cfg_dict)
+        self.config = self.arch.parse_config(cfg_dict)
+        spec = self.arch.build_spec(self.config)
+        self.max_model_len = int(min(max_model_len, spec.max_positions) if spec.max_positions else max_model_len)
+        self.workspace = Workspace(self.device, self.max_step_tokens)
+        self.rt = Runtime(self.device, dtype, self.workspace)
+        self.model = CausalLM(spec, self.rt)
+        self.model.bind(load_weights(self.model, model_dir, self.device, dtype))
+        self.vocab_size = self.model.vocab_size
+
+        # ---- cache groups: units with equal needs share a pool of pages -----------------------------------
+        units = self.model.cache_units()                      # unit id -> CacheSpec
+        self.group_specs = []
+        self.unit_location: Dict[int, tuple] = {}             # unit id -> (group, index in group)
+        for uid in sorted(units):
+            cs = units[uid]
+            for g, (gs, members) in enumerate(self.group_specs):
+                if gs == cs:
+                    self.unit_location[uid] = (g, len(members))
+                    members.append(uid)
+                    break
+            else:
+                self.unit_location[uid] = (len(self.group_specs), 0)
+                self.group_specs.append((cs, [uid]))
+        elem = torch.empty((), dtype=dtype).element_size()
+        self.page_bytes = [len(m) * 2 * cs.num_kv_heads * page_size * cs.head_dim * elem for cs, m in self.group_specs]
+        self.table_width = (self.max_model_len + page_size - 1) // page_size
+        if num_pages is None:
+            num_pages = self._pages_from_free_memory(gpu_memory_utilization)
+        self.num_pages = int(num_pages)
+        self.storage = [torch.zeros((len(m), self.num_pages + 1, 2, cs.num_kv_heads, page_size, cs.head_dim),
+                                    dtype=dtype, device=self.device) for cs, m in self.group_specs]
+        self.scratch_page = self.num_pages                    # the extra page: padding rows of captured graphs
+        n_slots = int(num_state_slots if num_state_slots is not None else max_seqs)
+        self.cache = CacheManager([GroupConfig(self.num_pages, cs.window, tuple(m)) for cs, m in self.group_specs],
+                                  page_size, n_slots)
+        self.scratch_slot = n_slots
+        self.state_specs = self.model.state_specs()
+        self.states = {i: torch.zeros((n_slots + 1,) + tuple(ss.shape), dtype=ss.dtype, device=self.device)
+                       for i, ss in enumerate(self.state_specs) if ss is not None}
+        self.cache_views: Dict[int, CacheUnitView] = {}
+        for i, e in enumerate(self.model.run_order):
+            cs = self.model.blocks[e.layer].mixer.cache_spec()
+            if cs is None:
+                continue
+            g, idx = self.unit_location[e.cache]
+            self.cache_views[i] = CacheUnitView(self.storage[g][idx], g, cs, e.writes_cache)
+
+        # ---- staging ----------------------------------------------------------------------------------
+        G = max(1, len(self.group_specs))
+        cap = (4 * _align(self.max_step_tokens) + 3 * _align(self.max_seqs + 1)
+               + G * (_align(self.max_step_tokens) + _align(self.max_seqs * self.table_width)) + 64)
+        self._stage_capacity = cap
+        self._stage_host = [torch.empty(cap, dtype=torch.int32, pin_memory=True) for _ in range(4)]
+        self._stage_np = [t.numpy() for t in self._stage_host]
+        self._stage_events = [None] * 4
+        self._stage_turn = 0
+        self._stage_dev = torch.zeros(cap, dtype=torch.int32, device=self.device)
+        self._logits = torch.empty((self.max_seqs, self.vocab_size), dtype=torch.float32, device=self.device)
+        self._graphs: Dict[int, tuple] = {}
+        self.stats = {"steps": 0, "graph_steps": 0, "tokens": 0}
+
+    # ---- sizing -----------------------------------------------------------------------------------------
+    def _pages_from_free_memory(self, utilization: float) -> int:
+        """Pages that fit into `utilization` of the device after weights and a reserve for activations
+        (the reference sizes its pool the same way from cudaMemGetInfo, engine/model_runner.cpp:116-145)."""
+        torch.cuda.synchronize(self.device)
+        free_b, total_b = torch.cuda.mem_get_info(self.device)
+        used = total_b - free_b
+        cfg = self.model
+        act_reserve = self.max_step_tokens * (16 * cfg.hidden_size) * 4 + self.max_seqs * cfg.vocab_size * 4 * 2 + (1 << 30)
+        budget = total_b * utilization - used - act_reserve
+        per_page = sum(self.page_bytes) or 1
+        n = int(budget // per_page)
+        if n <= 0:
+            raise RuntimeError("no memory is left for cache pages: lower max_num_batched_tokens or raise gpu_memory_utilization")
+        # no request can use more than max_model_len tokens; cap the pool where more would never be used
+        return min(n, self.max_seqs * self.table_width)
+
+    def kv_bytes_per_token(self) -> int:
+        return sum(pb // self.page_size for pb in self.page_bytes)
+
+    # ---- staging ----------------------------------------------------------------------------------------
+    def _layout(self, T: int, S: int, R: int, W: int):
+        off, lay = 0, {}
+        for name, n in (("tokens", T), ("positions", T), ("seq_of_token", T), ("logit_rows", max(R, 1)),
+                        ("cu_seqlens", S + 1), ("kv_lens", S), ("state_slots", S)):
+            lay[name] = (off, n)
+            off += _align(n)
+        for g in range(len(self.group_specs)):
+            lay[f"slots{g}"] = (off, T)
+            off += _align(T)
+            lay[f"tables{g}"] = (off, S * W)
+            off += _align(S * W)
+        lay["_end"] = (off, 0)
+        return lay
+
+    def _next_stage(self):
+        i = self._stage_turn
+        self._stage_turn = (i + 1) % len(self._stage_host)
+        ev = self._stage_events[i]
+        if ev is not None:
+            ev.synchronize()                                  # the copy that last read this buffer is done
+        return i, self._stage_np[i]
+
+    def _fill(self, entries: Sequence[StepEntry], T: int, S: int, R: int, W: int, pad_to: int = 0):
+        """Write the step's index arrays into a pinned buffer and start its copy to the device."""
+        S_pad = max(S, pad_to)
+        T_pad = T + (S_pad - S)
+        R_pad = R + (S_pad - S) if pad_to else R
+        lay = self._layout(T_pad, S_pad, R_pad, W)
+        idx, buf = self._next_stage()
+        ps = self.page_size
+
+        def reg(name):
+            o, n = lay[name]
+            return buf[o:o + n]
+
+        tokens, positions, seq_of = reg("tokens"), reg("positions"), reg("seq_of_token")
+        cu, kvl, sts, rows = reg("cu_seqlens"), reg("kv_lens"), reg("state_slots"), reg("logit_rows")
+        slots = [reg(f"slots{g}") for g in range(len(self.group_specs))]
+        tables = [reg(f"tables{g}").reshape(S_pad, W) for g in range(len(self.group_specs))]
+        for tb in tables:
+            tb.fill(-1)
+        t = r = 0
+        cu[0] = 0
+        for s, e in enumerate(entries):
+            n = len(e.tokens)
+            lease = self.cache.lease(e.request_id)
+            tokens[t:t + n] = e.tokens
+            positions[t:t + n] = np.arange(e.start, e.start + n, dtype=np.int32)
+            seq_of[t:t + n] = s
+            cu[s + 1] = t + n
+            kvl[s] = e.start + n
+            sts[s] = lease.state_slot
+            for w in e.want:
+                rows[r] = t + w
+                r += 1
+            for g in range(len(self.group_specs)):
+                tab = lease.tables[g]
+                if len(tab) > W:
+                    raise ValueError("a request's block table is wider than the staged width")
+                if e.start + n > len(tab) * ps:
+                    raise RuntimeError(f"request {e.request_id!r}: pages for positions up to {e.start + n - 1} were "
+                                       f"not reserved in group {g}")
+                tables[g][s, :len(tab)] = tab
+                pos = positions[t:t + n]
+                page_of = np.asarray(tab, dtype=np.int32)[pos // ps]
+                if (page_of < 0).any():
+                    raise RuntimeError(f"request {e.request_id!r}: a token of this step has no page in group {g}")
+                slots[g][t:t + n] = page_of * ps + pos % ps
+            t += n
+        for s in range(S, S_pad):                             # padding rows of a captured graph
+            tokens[t] = 0
+            positions[t] = 0
+            seq_of[t] = s
+            cu[s + 1] = t + 1
+            kvl[s] = 1
+            sts[s] = self.scratch_slot
+            rows[r] = t
+            r += 1
+            for g in range(len(self.group_specs)):
+                tables[g][s, 0] = self.scratch_page
+                slots[g][t] = self.scratch_page * ps
+            t += 1
+        if R == 0 and not pad_to:
+            rows[0] = 0
+        end = lay["_end"][0]
+        self._stage_dev[:end].copy_(self._stage_host[idx][:end], non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self._stage_events[idx] = ev
+        return lay, T_pad, S_pad, R_pad
+
+    def _context(self, lay, T: int, S: int, R: int, W: int, q_lens, max_kv: int) -> StepContext:
+        d = self._stage_dev
+
+        def reg(name):
+            o, n = lay[name]
+            return d[o:o + n]
+
+        groups = []
+        for g in range(len(self.group_specs)):
+            groups.append(GroupStepView(reg(f"tables{g}").view(S, W), reg(f"slots{g}"), self.page_size, self.num_pages + 1))
+        return StepContext(
+            num_tokens=T, num_seqs=S, tokens=reg("tokens"), positions=reg("positions"), seq_of_token=reg("seq_of_token"),
+            cu_seqlens=reg("cu_seqlens"), kv_lens=reg("kv_lens"), state_slots=reg("state_slots"), groups=groups,
+            logit_rows=reg("logit_rows"), num_logit_rows=R, q_lens=q_lens, max_q_len=max(q_lens) if q_lens else 1,
+            max_kv_len=max_kv, all_decode=all(q == 1 for q in q_lens) if q_lens else True)
+
+    # ---- the step ---------------------------------------------------------------------------------------
+    def _validate(self, entries: Sequence[StepEntry]) -> None:
+        seen = set()
+        for e in entries:
+            if e.request_id in seen:
+                raise ValueError(f"request {e.request_id!r} occurs twice in one step")
+            seen.add(e.request_id)
+            n = len(e.tokens)
+            if n == 0:
+                raise ValueError(f"request {e.request_id!r} brings no tokens")
+            lease = self.cache.lease(e.request_id)
+            if e.start != lease.computed:
+                raise ValueError(f"request {e.request_id!r}: step starts at position {e.start} but {lease.computed} "
+                                 "tokens are in the cache")
+            if e.start + n > self.max_model_len:
+                raise ValueError(f"request {e.request_id!r} would reach {e.start + n} tokens; max_model_len is {self.max_model_len}")
+            for w in e.want:
+                if not (0 <= w < n):
+                    raise ValueError(f"request {e.request_id!r}: wanted index {w} outside its {n} tokens")
+
+    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """Run one step.  Pages for every entry's tokens must have been reserved with ``cache.reserve``.
+        Returns float32 logits [R, vocab] on the device, rows in the order of the entries and of their ``want``;
+        the tensor is valid until the next step."""
+        entries = list(entries)
+        if not entries:
+            raise ValueError("a step needs at least one entry")
+        self._validate(entries)
+        q_lens = [len(e.tokens) for e in entries]
+        T, S = sum(q_lens), len(entries)
+        R = sum(len(e.want) for e in entries)
+        if T > self.max_step_tokens:
+            raise ValueError(f"a step of {T} tokens exceeds max_num_batched_tokens = {self.max_step_tokens}")
+        if S > self.max_seqs:
+            raise ValueError(f"a step of {S} requests exceeds max_num_seqs = {self.max_seqs}")
+        fresh = self.cache.take_fresh_slots()
+        if fresh and self.states:
+            idx = torch.tensor(fresh, dtype=torch.long, device=self.device)
+            for st in self.states.values():
+                st.index_fill_(0, idx, 0)
+        max_kv = max(e.start + len(e.tokens) for e in entries)
+
+        use_graph = (not self.enforce_eager and T == S and S <= GRAPH_BUCKETS[-1]
+                     and all(len(e.want) == 1 for e in entries))
+        if use_graph:
+            logits = self._step_graph(entries, S, max_kv)
+        else:
+            W = max(1, max(len(self.cache.lease(e.request_id).tables[g]) for e in entries
+                           for g in range(len(self.group_specs))) if self.group_specs else 1)
+            lay, T_, S_, R_ = self._fill(entries, T, S, R, W)
+            ctx = self._context(lay, T, S, R, W, q_lens, max_kv)
+            out = self._logits if R <= self._logits.shape[0] else torch.empty(
+                (R, self.vocab_size), dtype=torch.float32, device=self.device)
+            logits = self.model.forward(ctx, self.cache_views, self.states, out)[:R] if R > 0 else \
+                self._forward_no_logits(ctx)
+        for e in entries:
+            self.cache.advance(e.request_id, e.start + len(e.tokens))
+        self.stats["steps"] += 1
+        self.stats["tokens"] += T
+        return logits
+
+    def _forward_no_logits(self, ctx) -> torch.Tensor:
+        self.model.forward_hidden(ctx, self.cache_views, self.states)
+        return self._logits[:0]
+
+    # ---- CUDA graphs for decode-only steps -------------------------------------------------------------
+    def _bucket(self, S: int) -> int:
+        for b in GRAPH_BUCKETS:
+            if b >= S and b <= self.max_seqs:
+                return b
+        return 0
+
+    def _step_graph(self, entries, S: int, max_kv: int) -> torch.Tensor:
+        B = self._bucket(S)
+        if B == 0:
+            B = S
+        W = self.table_width
+        lay, T_pad, S_pad, R_pad = self._fill(entries, S, S, S, W, pad_to=B)
+        g = self._graphs.get(B)
+        if g is None:
+            ctx = self._context(lay, B, B, B, W, [1] * B, self.max_model_len)
+            ctx.extras["captured"] = True
+            # warm-up outside capture: lazy initialisation (cuBLAS handles, kernel loading) must not be captured
+            self.model.forward(ctx, self.cache_views, self.states, self._logits)
+            torch.cuda.synchronize(self.device)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                self.model.forward(ctx, self.cache_views, self.states, self._logits)
+            self._graphs[B] = (graph, ctx)
+            g = self._graphs[B]
+        g[0].replay()
+        self.stats["graph_steps"] += 1
+        return self._logits[:S]
+
+    # ---- bookkeeping helpers ----------------------------------------------------------------------------
+    def check_errors(self) -> None:
+        """Raise if a kernel of an earlier step recorded an index it refused to follow (synchronises)."""
+        ops.check_device_errors(self.device)

@@ -1,0 +1,93 @@
+"""Grouped-query attention over the paged cache, with optional per-head RMSNorm of q and k and optional
+rotary position encoding (reference model/model_architecture.cpp:155-178):
+
+    qkv = x Wqkv^T                      Wqkv = rows(q_proj) over rows(k_proj) over rows(v_proj), no bias
+    q, k <- rotate(headnorm(q)), rotate(headnorm(k));  k, v written to this step's slots of the cache pages
+    att_t = softmax_j(scale * q_t . k_j) v_j  over the request's positions lo..p_t   (causal; lo = 0 or window edge)
+    y = att Wo^T
+
+Prompt portions and decoded tokens run through the same code: every token attends to its request's pages,
+which already hold the step's own keys.  All sizes are parameters; `scale` defaults to 1/sqrt(head_dim)
+(model_architecture.cpp:134).  The part does not know how many layers exist or which model it serves.
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict, Optional
+
+import torch
+
+from ..csrc import ops
+from .base import CacheSpec, Mixer, WeightSpec, register_part
+
+
+@register_part("mixer", "paged_attention")
+class PagedAttention(Mixer):
+    def __init__(self, runtime, prefix="", names=None, *, hidden_size: int, num_heads: int, num_kv_heads: int,
+                 head_dim: int, qk_norm: bool = True, qk_norm_eps: float = 1e-6, window: int = 0,
+                 scale: Optional[float] = None, position=None):
+        super().__init__(runtime, prefix, names)
+        if num_heads % num_kv_heads:
+            raise ValueError(f"{num_heads} query heads are not a multiple of {num_kv_heads} key/value heads")
+        self.hidden_size, self.num_heads, self.num_kv_heads, self.head_dim = map(int, (hidden_size, num_heads, num_kv_heads, head_dim))
+        self.qk_norm, self.qk_norm_eps, self.window = bool(qk_norm), float(qk_norm_eps), int(window)
+        self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(self.head_dim)
+        self.position = position            # a RotaryEmbedding part or None
+        if self.position is not None and self.position.rotary_dim > self.head_dim:
+            raise ValueError("rotary_dim exceeds head_dim")
+        self.w_qkv = self.w_o = self.q_norm_w = self.k_norm_w = None
+
+    # ---- declarations ----
+    def cache_spec(self) -> CacheSpec:
+        return CacheSpec(self.num_kv_heads, self.head_dim, self.window)
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        D, H, KV, hd = self.hidden_size, self.num_heads, self.num_kv_heads, self.head_dim
+        specs = {
+            self.full_name("q_proj.weight"): WeightSpec((H * hd, D)),
+            self.full_name("k_proj.weight"): WeightSpec((KV * hd, D)),
+            self.full_name("v_proj.weight"): WeightSpec((KV * hd, D)),
+            self.full_name("o_proj.weight"): WeightSpec((D, H * hd)),
+        }
+        if self.qk_norm:
+            specs[self.full_name("q_norm.weight")] = WeightSpec((hd,), role="vector", init="norm")
+            specs[self.full_name("k_norm.weight")] = WeightSpec((hd,), role="vector", init="norm")
+        return specs
+
+    def bind(self, tensors) -> None:
+        parts = [tensors[self.full_name(n)] for n in ("q_proj.weight", "k_proj.weight", "v_proj.weight")]
+        if len({p.dtype for p in parts}) > 1:
+            parts = [p.float() for p in parts]
+        self.w_qkv = torch.cat(parts, dim=0).contiguous()
+        self.w_o = tensors[self.full_name("o_proj.weight")]
+        if self.qk_norm:
+            self.q_norm_w = tensors[self.full_name("q_norm.weight")]
+            self.k_norm_w = tensors[self.full_name("k_norm.weight")]
+
+    def weight_bytes(self) -> int:
+        return sum(w.numel() * w.element_size() for w in (self.w_qkv, self.w_o, self.q_norm_w, self.k_norm_w) if w is not None)
+
+    # ---- step ----
+    def forward(self, x, ctx, cache, state):
+        T = x.shape[0]
+        H, KV, hd = self.num_heads, self.num_kv_heads, self.head_dim
+        ws = self.rt.workspace
+        g = ctx.groups[cache.group]
+        qkv = ops.linear(x, self.w_qkv, out=ws.rows("attn_qkv", T, (H + 2 * KV) * hd, x.dtype))
+        q = ws.rows("attn_q", T, H * hd, x.dtype)
+        pos = self.position
+        ops.qk_norm_rope_kv(
+            q, qkv, self.q_norm_w, self.k_norm_w,
+            pos.cos if pos is not None else None, pos.sin if pos is not None else None, ctx.positions,
+            g.slot_mapping if cache.writes else None, cache.pages if cache.writes else None,
+            H, KV, hd, g.page_size, self.qk_norm_eps,
+            rotary_dim=pos.rotary_dim if pos is not None else 0,
+            interleaved=pos.interleaved if pos is not None else False)
+        att = ws.rows("attn_out", T, H * hd, x.dtype)
+        self.attend(att, q, ctx, cache, g)
+        return ops.linear(att, self.w_o, out=ws.rows("attn_proj", T, self.hidden_size, x.dtype))
+
+    def attend(self, att, q, ctx, cache, g):
+        ops.paged_attention_general(att, q, cache.pages, g.block_tables, ctx.seq_of_token, ctx.positions,
+                                    self.num_heads, self.num_kv_heads, self.head_dim, g.page_size, self.scale,
+                                    window=self.window, num_tokens=ctx.num_tokens)

@@ -1,0 +1,182 @@
+"""Interfaces of the parts a layer is put together from, and the registry that maps a kind to a class.
+
+Categories: ``mixer`` (token mixing: attention here), ``ffn`` (feed-forward), ``norm``, ``position``
+(position encoding), ``block`` (arrangement of mixer, feed-forward and norms with the residual stream),
+``embedding`` and ``head``.  A part
+
+* is constructed as ``cls(runtime, prefix=..., names=..., **params)``: all sizes and constants arrive as
+  parameters; a part never looks at a model configuration and does not know which model it is in;
+* declares its tensors with ``weight_specs()`` (full tensor name -> ``WeightSpec``); the loader checks the
+  checkpoint against these and ``bind()`` hands the tensors over; the random-weights writer draws them;
+* runs with ``forward`` on the tokens of one step (see each category's class below).
+
+A mixer additionally declares what it keeps between steps: ``cache_spec()`` for keys and values that grow
+with the sequence (paged, optionally windowed) and ``state_spec()`` for per-request state of fixed size.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Dict, Optional, Tuple
+
+import torch
+
+# ---- registry ------------------------------------------------------------------------------------------
+
+_REGISTRY: Dict[str, Dict[str, type]] = {c: {} for c in
+                                         ("mixer", "ffn", "norm", "position", "block", "embedding", "head")}
+
+
+def register_part(category: str, kind: str, cls: type = None, replace: bool = False):
+    """Register `cls` under (category, kind); usable as a decorator: ``@register_part("mixer", "my_kind")``."""
+    if category not in _REGISTRY:
+        raise ValueError(f"unknown part category '{category}'; categories: {sorted(_REGISTRY)}")
+
+    def deco(c):
+        if kind in _REGISTRY[category] and not replace:
+            raise ValueError(f"{category} kind '{kind}' is already registered")
+        _REGISTRY[category][kind] = c
+        return c
+
+    return deco(cls) if cls is not None else deco
+
+
+def unregister_part(category: str, kind: str) -> None:
+    _REGISTRY[category].pop(kind, None)
+
+
+def part_class(category: str, kind: str) -> type:
+    try:
+        return _REGISTRY[category][kind]
+    except KeyError:
+        raise ValueError(f"no {category} of kind '{kind}' is registered; registered: "
+                         f"{sorted(_REGISTRY.get(category, {}))}") from None
+
+
+def build_part(category: str, spec, runtime, **extra):
+    cls = part_class(category, spec.kind)
+    return cls(runtime, prefix=spec.prefix, names=dict(spec.names), **spec.params, **extra)
+
+
+# ---- declarations ----------------------------------------------------------------------------------------
+
+@dataclass(frozen=True)
+class WeightSpec:
+    shape: Tuple[int, ...]
+    role: str = "matrix"      # "matrix": operand of a matrix product / embedding table (engine dtype, or float32
+                              #           if stored so); "vector": norm weights and the like (always float32);
+                              # "int_table": integer look-up table (int32)
+    init: str = "normal"      # random weights: "normal" = N(0, std), "norm" = 1 + U(-spread, spread)
+
+
+@dataclass(frozen=True)
+class CacheSpec:
+    """Keys and values that grow by one entry per token.  Units with equal specs form one group of pages."""
+    num_kv_heads: int
+    head_dim: int
+    window: int = 0           # 0 = all keys; w > 0 = only the last w positions are ever read
+
+
+@dataclass(frozen=True)
+class StateSpec:
+    """Per-request state of fixed size: one tensor of this shape and dtype per slot, zeroed at admission."""
+    shape: Tuple[int, ...]
+    dtype: torch.dtype = torch.float32
+
+
+class Workspace:
+    """Named activation buffers with fixed addresses, sized once for the largest step (`max_tokens` rows).
+    Fixed addresses let decode steps be captured in CUDA graphs; sharing names between layers keeps the
+    footprint at one layer's worth."""
+
+    def __init__(self, device, max_tokens: int):
+        self.device = device
+        self.max_tokens = max_tokens
+        self._buffers: Dict[str, torch.Tensor] = {}
+
+    def rows(self, name: str, n_rows: int, width, dtype: torch.dtype) -> torch.Tensor:
+        widths = tuple(width) if isinstance(width, (tuple, list)) else (width,)
+        key = f"{name}|{widths}|{dtype}"
+        buf = self._buffers.get(key)
+        if buf is None:
+            buf = torch.empty((self.max_tokens,) + widths, dtype=dtype, device=self.device)
+            self._buffers[key] = buf
+        if n_rows > self.max_tokens:
+            raise ValueError(f"a step of {n_rows} tokens exceeds the workspace of {self.max_tokens}")
+        return buf[:n_rows]
+
+
+@dataclass
+class Runtime:
+    """What parts are built against: the device, the activation element type and the shared workspace."""
+    device: torch.device
+    dtype: torch.dtype
+    workspace: Workspace
+
+
+class Part:
+    category = ""
+
+    def __init__(self, runtime: Runtime, prefix: str = "", names: Optional[Dict[str, str]] = None):
+        self.rt = runtime
+        self.prefix = prefix
+        self.names = names or {}
+
+    def full_name(self, local: str) -> str:
+        return self.names.get(local, self.prefix + local)
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        return {}
+
+    def bind(self, tensors: Dict[str, torch.Tensor]) -> None:
+        """Receive the tensors named by weight_specs() (already on the device, in their final dtype)."""
+
+    def weight_bytes(self) -> int:
+        """Bytes of weights a decode step reads from this part (for the roofline)."""
+        return 0
+
+
+class Norm(Part):
+    category = "norm"
+
+    def forward(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        raise NotImplementedError
+
+    def add_forward(self, residual: torch.Tensor, delta: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """residual += delta (in place, rounded to the activation type), then the norm of the new residual."""
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    category = "position"
+
+
+class Mixer(Part):
+    category = "mixer"
+
+    def cache_spec(self) -> Optional[CacheSpec]:
+        return None
+
+    def state_spec(self) -> Optional[StateSpec]:
+        return None
+
+    def forward(self, x: torch.Tensor, ctx, cache, state) -> torch.Tensor:
+        """x: [T, D] normed activations of this step's tokens.  ctx: StepContext.  cache: a CacheUnitView or
+        None.  state: the [num_slots, *shape] tensor of this run entry's per-request state or None (index it
+        with ctx.state_slots).  Returns [T, D]."""
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    category = "ffn"
+
+    def forward(self, x: torch.Tensor, ctx) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class Block(Part):
+    """An arrangement of a mixer, a feed-forward and their norms around the residual stream."""
+    category = "block"
+
+    def forward(self, h, pending, ctx, cache, state):
+        """h: residual stream [T, D]; pending: a delta not yet added to h, or None.  Returns (h, pending)."""
+        raise NotImplementedError

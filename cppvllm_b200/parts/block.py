@@ -1,0 +1,28 @@
+"""Pre-norm decoder block (reference model/model_architecture.cpp:150-188):
+
+    h <- h + mixer(norm_m(h));   h <- h + ffn(norm_f(h))
+
+The reference fuses every residual add with the norm that follows it (kernels/fused_ops.cu:70-87,
+model_architecture.cpp:180,187).  The block keeps that fusion without knowing its neighbours: it receives the
+residual stream `h` together with a `pending` delta that has not been added yet, folds it into its first
+norm, and hands its own feed-forward output on as the next pending delta."""
+from __future__ import annotations
+
+from .base import Block, build_part, register_part
+
+
+@register_part("block", "prenorm")
+class PreNormBlock(Block):
+    def __init__(self, runtime, prefix="", names=None, *, mixer, ffn, mixer_norm, ffn_norm):
+        super().__init__(runtime, prefix, names)
+        self.mixer, self.ffn, self.mixer_norm, self.ffn_norm = mixer, ffn, mixer_norm, ffn_norm
+
+    def parts(self):
+        return (self.mixer_norm, self.mixer, self.ffn_norm, self.ffn)
+
+    def forward(self, h, pending, ctx, cache, state):
+        x = self.mixer_norm.forward(h) if pending is None else self.mixer_norm.add_forward(h, pending)
+        a = self.mixer.forward(x, ctx, cache, state)
+        x = self.ffn_norm.add_forward(h, a)
+        m = self.ffn.forward(x, ctx)
+        return h, m

@@ -1,0 +1,44 @@
+"""Dense gated feed-forward (reference model/model_architecture.cpp:106-112,182-185; kernels/fused_ops.cu:210-220):
+gu = x Wgu^T with Wgu = rows(gate_proj) over rows(up_proj); act = T( rnd(silu(g)) * u ); y = act Wdown^T; no biases."""
+from __future__ import annotations
+
+from typing import Dict
+
+import torch
+
+from ..csrc import ops
+from .base import FeedForward, WeightSpec, register_part
+
+
+@register_part("ffn", "swiglu")
+class SwiGLUMLP(FeedForward):
+    def __init__(self, runtime, prefix="", names=None, *, hidden_size: int, intermediate_size: int):
+        super().__init__(runtime, prefix, names)
+        self.hidden_size, self.intermediate_size = int(hidden_size), int(intermediate_size)
+        self.w_gate_up = None
+        self.w_down = None
+
+    def weight_specs(self) -> Dict[str, WeightSpec]:
+        D, I = self.hidden_size, self.intermediate_size
+        return {
+            self.full_name("gate_proj.weight"): WeightSpec((I, D)),
+            self.full_name("up_proj.weight"): WeightSpec((I, D)),
+            self.full_name("down_proj.weight"): WeightSpec((D, I)),
+        }
+
+    def bind(self, tensors) -> None:
+        g, u = tensors[self.full_name("gate_proj.weight")], tensors[self.full_name("up_proj.weight")]
+        if g.dtype != u.dtype:
+            g, u = g.float(), u.float()
+        self.w_gate_up = torch.cat([g, u], dim=0).contiguous()
+        self.w_down = tensors[self.full_name("down_proj.weight")]
+
+    def weight_bytes(self) -> int:
+        return sum(w.numel() * w.element_size() for w in (self.w_gate_up, self.w_down))
+
+    def forward(self, x, ctx):
+        T = x.shape[0]
+        ws = self.rt.workspace
+        gu = ops.linear(x, self.w_gate_up, out=ws.rows("ffn_gate_up", T, 2 * self.intermediate_size, x.dtype))
+        act = ops.swiglu(ws.rows("ffn_act", T, self.intermediate_size, x.dtype), gu)
+        return ops.linear(act, self.w_down, out=ws.rows("ffn_out", T, self.hidden_size, x.dtype))
