@@ -1,0 +1,173 @@
+"""The engine's public face, in the reference's manner (engine/llm_engine.h:34-69, example.cpp, bench.cpp):
+
+    engine = LLMEngine(EngineConfig(model_path=..., dtype="bfloat16"))
+    outs = engine.generate([[1, 2, 3], [4, 5]], SamplingParams(temperature=0.6, max_tokens=64))
+
+``add_request`` / ``step`` / ``is_finished`` / ``generate`` / ``take_finished`` / ``stats`` / ``num_kv_blocks`` keep the
+reference's names and meanings.  Token ids go in and come out; there is no tokenizer.  ``LLM`` is the same class
+under the name a Python user expects.
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence as Seq, Union
+
+import torch
+
+from ..config.engine_config import EngineConfig
+from ..sampling.params import SamplingParams
+from ..sampling.sampler import Sampler, mix_seed
+from .runner import ModelRunner, StepEntry
+from .scheduler import FINISHED, ScheduledBatch, Scheduler, SchedulerConfig, Sequence
+
+
+@dataclass
+class GenerationOutput:
+    request_id: int = 0
+    prompt_ids: List[int] = field(default_factory=list)
+    token_ids: List[int] = field(default_factory=list)
+    stopped_on_eos: bool = False
+
+
+@dataclass
+class StepInfo:
+    num_seqs: int = 0
+    num_tokens: int = 0
+    num_sampled: int = 0
+    num_finished: int = 0
+
+
+@dataclass
+class EngineStats:
+    steps: int = 0
+    tokens_processed: int = 0
+    tokens_generated: int = 0
+    preemptions: int = 0
+    seconds: float = 0.0
+
+    def generated_per_second(self) -> float:
+        return self.tokens_generated / self.seconds if self.seconds > 0 else 0.0
+
+
+class LLMEngine:
+    def __init__(self, config: Union[EngineConfig, str, None] = None, **kwargs):
+        if isinstance(config, str):
+            config = EngineConfig(model_path=config, **kwargs)
+        elif config is None:
+            config = EngineConfig(**kwargs)
+        elif kwargs:
+            raise TypeError("pass either an EngineConfig or keyword options, not both")
+        self.config = config
+        self.runner = ModelRunner(
+            config.model_path, dtype=config.dtype, device=config.device, page_size=config.block_size,
+            num_pages=config.num_kv_blocks if config.num_kv_blocks > 0 else None,
+            max_step_tokens=config.max_num_batched_tokens, max_seqs=config.max_num_seqs,
+            max_model_len=config.max_model_len, gpu_memory_utilization=config.gpu_memory_utilization,
+            enforce_eager=config.enforce_eager)
+        eos = tuple(getattr(self.runner.config, "eos_token_ids", ()) or ())
+        self.scheduler = Scheduler(SchedulerConfig(
+            max_num_batched_tokens=config.max_num_batched_tokens, max_num_seqs=config.max_num_seqs,
+            max_chunk_tokens=config.max_chunk_tokens, max_model_len=self.runner.max_model_len,
+            eos_token_ids=eos), self.runner.cache)
+        self.sampler = Sampler(self.runner.device, config.max_num_seqs)
+        self._live: Dict[int, Sequence] = {}
+        self._finished: Dict[int, GenerationOutput] = {}
+        self._next_id = 0
+        self._stats = EngineStats()
+        self._empty_steps = 0
+
+    # ---- requests ------------------------------------------------------------------------------------
+    def add_request(self, prompt: Seq[int], params: Optional[SamplingParams] = None) -> int:
+        params = params or SamplingParams()
+        vocab = self.runner.vocab_size
+        for t in prompt:
+            if not (0 <= int(t) < vocab):
+                raise ValueError(f"prompt token {t} lies outside the vocabulary of {vocab}")
+        rid = self._next_id
+        seq = Sequence(rid, prompt, params)
+        seq.row_seed = mix_seed(self.config.seed, params.seed if params.seed is not None else rid)
+        self.scheduler.add_request(seq)
+        self._next_id += 1
+        self._live[rid] = seq
+        return rid
+
+    def is_finished(self) -> bool:
+        return self.scheduler.is_finished()
+
+    @property
+    def num_kv_blocks(self) -> int:
+        return self.runner.num_pages
+
+    def stats(self) -> EngineStats:
+        return self._stats
+
+    # ---- one step -------------------------------------------------------------------------------------
+    def step(self) -> StepInfo:
+        info = StepInfo()
+        if self.scheduler.is_finished():
+            return info
+        t0 = time.perf_counter()
+        batch = self.scheduler.schedule()
+        self._stats.preemptions = self.scheduler.num_preemptions
+        if not batch.seqs:
+            self._empty_steps += 1
+            if self._empty_steps > 2:
+                raise RuntimeError("the scheduler produced no work although requests are pending")
+            return info
+        self._empty_steps = 0
+        entries = []
+        for seq in batch.seqs:
+            c, n = seq.num_cached_tokens, seq.num_scheduled_tokens
+            entries.append(StepEntry(seq.seq_id, seq.token_ids[c:c + n], c, (n - 1,) if seq.samples_this_step() else ()))
+        logits = self.runner.step(entries)
+        flags = self.scheduler.on_launched(batch)
+        samplers = [s for s, f in zip(batch.seqs, flags) if f]
+        tokens = self.sampler.sample(
+            logits, [s.params.temperature for s in samplers], [s.row_seed for s in samplers],
+            [s.num_completion_tokens for s in samplers]) if samplers else []
+        finished = self.scheduler.postprocess(batch, flags, tokens)
+        for seq in finished:
+            self._harvest(seq)
+        info.num_seqs, info.num_tokens = len(batch.seqs), batch.total_tokens
+        info.num_sampled, info.num_finished = len(tokens), len(finished)
+        self._stats.steps += 1
+        self._stats.tokens_processed += batch.total_tokens
+        self._stats.tokens_generated += len(tokens)
+        self._stats.seconds += time.perf_counter() - t0
+        return info
+
+    def _harvest(self, seq: Sequence) -> None:
+        out = GenerationOutput(seq.seq_id, seq.token_ids[:seq.num_prompt_tokens], seq.token_ids[seq.num_prompt_tokens:],
+                               seq.stopped_on_eos)
+        if out.stopped_on_eos and out.token_ids:
+            out.token_ids.pop()                              # the end-of-sequence token itself is not returned
+        self._finished[seq.seq_id] = out
+        self._live.pop(seq.seq_id, None)
+
+    def take_finished(self) -> List[GenerationOutput]:
+        outs = [self._finished[k] for k in sorted(self._finished)]
+        self._finished.clear()
+        return outs
+
+    # ---- whole requests ---------------------------------------------------------------------------------
+    def generate(self, prompts: Seq[Seq[int]], params: Union[SamplingParams, Seq[SamplingParams], None] = None) -> List[GenerationOutput]:
+        if params is None or isinstance(params, SamplingParams):
+            plist = [params or SamplingParams()] * len(prompts)
+        else:
+            plist = list(params)
+            if len(plist) != len(prompts):
+                raise ValueError("one SamplingParams per prompt is needed")
+        ids = [self.add_request(p, sp) for p, sp in zip(prompts, plist)]
+        while not self.is_finished():
+            self.step()
+        self.runner.check_errors()
+        outs = []
+        for rid in ids:
+            if rid not in self._finished:
+                raise RuntimeError(f"generate: request {rid} never finished")
+            outs.append(self._finished.pop(rid))
+        return outs
+
+
+LLM = LLMEngine

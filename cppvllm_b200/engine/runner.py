@@ -14,8 +14,8 @@ rows that pad a bucket read and write a scratch page that no request owns (model
 """
 from __future__ import annotations
 
-import json
 import os
+import sys
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence
 
@@ -301,11 +301,11 @@ class ModelRunner:
                 st.index_fill_(0, idx, 0)
         max_kv = max(e.start + len(e.tokens) for e in entries)
 
-        use_graph = (not self.enforce_eager and T == S and S <= GRAPH_BUCKETS[-1]
-                     and all(len(e.want) == 1 for e in entries))
-        if use_graph:
+        logits = None
+        if (not self.enforce_eager and self.model.capturable and T == S and self._bucket(S)
+                and all(len(e.want) == 1 for e in entries)):
             logits = self._step_graph(entries, S, max_kv)
-        else:
+        if logits is None:
             W = max(1, max(len(self.cache.lease(e.request_id).tables[g]) for e in entries
                            for g in range(len(self.group_specs))) if self.group_specs else 1)
             lay, T_, S_, R_ = self._fill(entries, T, S, R, W)
@@ -326,30 +326,43 @@ class ModelRunner:
 
     # ---- CUDA graphs for decode-only steps -------------------------------------------------------------
     def _bucket(self, S: int) -> int:
+        """The smallest captured batch size that holds S rows; 0 if S is beyond the largest bucket."""
         for b in GRAPH_BUCKETS:
-            if b >= S and b <= self.max_seqs:
-                return b
+            if b >= S:
+                return min(b, max(self.max_seqs, S))
         return 0
 
-    def _step_graph(self, entries, S: int, max_kv: int) -> torch.Tensor:
-        B = self._bucket(S)
-        if B == 0:
-            B = S
+    def _capture(self, B: int) -> bool:
+        """Capture the graph of a decode-only step of B rows.  Warm-up and capture run on padding rows only (they
+        read and write the scratch page and the scratch state slot), so no request's cache or state is touched
+        before the real replay.  Returns False, and switches graphs off, if the model cannot be captured."""
         W = self.table_width
-        lay, T_pad, S_pad, R_pad = self._fill(entries, S, S, S, W, pad_to=B)
-        g = self._graphs.get(B)
-        if g is None:
-            ctx = self._context(lay, B, B, B, W, [1] * B, self.max_model_len)
-            ctx.extras["captured"] = True
-            # warm-up outside capture: lazy initialisation (cuBLAS handles, kernel loading) must not be captured
+        lay, _, _, _ = self._fill([], 0, 0, 0, W, pad_to=B)
+        ctx = self._context(lay, B, B, B, W, [1] * B, self.max_model_len)
+        ctx.extras["captured"] = True
+        try:
+            # lazy initialisation (cuBLAS handles, kernel loading, workspace buffers) must happen outside capture
             self.model.forward(ctx, self.cache_views, self.states, self._logits)
             torch.cuda.synchronize(self.device)
             graph = torch.cuda.CUDAGraph()
             with torch.cuda.graph(graph):
                 self.model.forward(ctx, self.cache_views, self.states, self._logits)
-            self._graphs[B] = (graph, ctx)
-            g = self._graphs[B]
-        g[0].replay()
+        except Exception as ex:                               # a part that synchronises or allocates on the host
+            torch.cuda.synchronize(self.device)
+            self.enforce_eager = True
+            print(f"[cppvllm_b200] decode steps cannot be captured in a CUDA graph ({type(ex).__name__}: "
+                  f"{str(ex).splitlines()[0][:120]}); running eagerly", file=sys.stderr, flush=True)
+            return False
+        self._graphs[B] = (graph, ctx)
+        return True
+
+    def _step_graph(self, entries, S: int, max_kv: int):
+        """Replay the captured graph of the bucket that fits S rows; None if graphs turned out to be unusable."""
+        B = self._bucket(S)
+        if B not in self._graphs and not self._capture(B):
+            return None
+        self._fill(entries, S, S, S, self.table_width, pad_to=B)
+        self._graphs[B][0].replay()
         self.stats["graph_steps"] += 1
         return self._logits[:S]
 

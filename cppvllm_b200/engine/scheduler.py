@@ -1,0 +1,205 @@
+"""Continuous batching above the step function: admission, prompt portions under a token budget, decoding,
+finishing and freeing, and what happens when pages run out.
+
+Policy after the reference's ``Scheduler`` (engine/scheduler.cpp):
+
+* a step has a token budget ``max_num_batched_tokens``; a request gets ``min(tokens not yet in the cache, budget
+  left, max_chunk_tokens)`` tokens (:43-44,68,99); ``max_chunk_tokens = 0`` means no cap; a prompt longer than
+  that runs as portions over several steps and samples only in the step that ends with its last known token
+  (scheduler.h:29-31);
+* running requests come first, in order, decodes being portions of one token (:55-90); then waiting requests
+  are admitted first-come-first-served while budget, ``max_num_seqs`` and pages allow; admission stops at the
+  first request that does not fit, and no admission happens in a step that preempted (:91-100);
+* admission reserves pages for the whole current sequence; before each later step the reservation is topped up
+  to the sequence's length (engine/block_manager.cpp:80-126);
+* pages run out: the request that cannot grow preempts the LAST running request that this step has not looked
+  at yet, or itself if there is none (:74-85).  A preempted request gives back all pages and its state slot,
+  keeps the tokens it has generated, and goes to the FRONT of the waiting queue; on re-admission its whole
+  sequence is run again as a prompt (:28-34; engine/sequence.h:82-89);
+* a request whose prompt plus ``max_tokens`` can never fit the pool, or exceeds ``max_model_len``, is refused at
+  ``add_request`` (:18-26);
+* a request finishes on an end-of-sequence token (unless ``ignore_eos``) or at ``max_tokens`` new tokens, and
+  its pages are freed at once (:123-155).
+"""
+from __future__ import annotations
+
+from collections import deque
+from dataclasses import dataclass, field
+from typing import Deque, List, Optional, Sequence as Seq
+
+from ..cache.manager import CacheManager
+from ..sampling.params import SamplingParams
+
+WAITING, RUNNING, FINISHED = "waiting", "running", "finished"
+
+
+class Sequence:
+    """One request: its tokens (prompt, then generated), how many are in the cache, and its options."""
+    __slots__ = ("seq_id", "token_ids", "num_prompt_tokens", "num_cached_tokens", "num_scheduled_tokens",
+                 "params", "status", "stopped_on_eos", "row_seed", "num_preemptions")
+
+    def __init__(self, seq_id: int, prompt: Seq[int], params: Optional[SamplingParams] = None):
+        if len(prompt) == 0:
+            raise ValueError("a request needs at least one prompt token")
+        self.seq_id = seq_id
+        self.token_ids: List[int] = [int(t) for t in prompt]
+        self.num_prompt_tokens = len(self.token_ids)
+        self.num_cached_tokens = 0
+        self.num_scheduled_tokens = 0
+        self.params = params or SamplingParams()
+        self.status = WAITING
+        self.stopped_on_eos = False
+        self.row_seed = 0
+        self.num_preemptions = 0
+
+    def __len__(self) -> int:
+        return len(self.token_ids)
+
+    @property
+    def num_completion_tokens(self) -> int:
+        return len(self.token_ids) - self.num_prompt_tokens
+
+    @property
+    def num_uncached_tokens(self) -> int:
+        return len(self.token_ids) - self.num_cached_tokens
+
+    def samples_this_step(self) -> bool:
+        return self.num_cached_tokens + self.num_scheduled_tokens == len(self.token_ids)
+
+
+@dataclass
+class SchedulerConfig:
+    max_num_batched_tokens: int = 4096
+    max_num_seqs: int = 256
+    max_chunk_tokens: int = 1024
+    max_model_len: int = 4096
+    eos_token_ids: tuple = ()
+
+
+@dataclass
+class ScheduledBatch:
+    seqs: List[Sequence] = field(default_factory=list)
+    total_tokens: int = 0
+    preempted: List[Sequence] = field(default_factory=list)
+
+    @property
+    def all_single_token(self) -> bool:
+        return bool(self.seqs) and all(s.num_scheduled_tokens == 1 for s in self.seqs)
+
+
+class Scheduler:
+    def __init__(self, config: SchedulerConfig, cache: CacheManager):
+        self.cfg = config
+        self.cache = cache
+        self.waiting: Deque[Sequence] = deque()
+        self.running: List[Sequence] = []
+        self.num_preemptions = 0
+
+    # ---- queue ---------------------------------------------------------------------------------------
+    def add_request(self, seq: Sequence) -> None:
+        max_len = seq.num_prompt_tokens + max(seq.params.max_tokens, 0)
+        if max_len > self.cfg.max_model_len:
+            raise ValueError(f"request needs {max_len} tokens (prompt {seq.num_prompt_tokens} + max_tokens "
+                             f"{seq.params.max_tokens}) but max_model_len is {self.cfg.max_model_len}")
+        need = self.cache.num_pages_for(max_len)
+        smallest = min(p.num_pages for p in self.cache.pools) if self.cache.pools else need
+        if need > smallest:
+            raise ValueError(f"request needs {need} cache pages but the pool only has {smallest}")
+        seq.status = WAITING
+        self.waiting.append(seq)
+
+    def is_finished(self) -> bool:
+        return not self.waiting and not self.running
+
+    def _preempt(self, seq: Sequence) -> None:
+        self.cache.release(seq.seq_id)
+        seq.status = WAITING
+        seq.num_cached_tokens = 0
+        seq.num_scheduled_tokens = 0
+        seq.num_preemptions += 1
+        self.waiting.appendleft(seq)
+        self.num_preemptions += 1
+
+    # ---- one step's decisions --------------------------------------------------------------------------
+    def schedule(self) -> ScheduledBatch:
+        out = ScheduledBatch()
+        budget = self.cfg.max_num_batched_tokens
+        cap = self.cfg.max_chunk_tokens if self.cfg.max_chunk_tokens > 0 else 1 << 62
+        pending: Deque[Sequence] = deque(self.running)
+        kept: List[Sequence] = []
+        preempted_now = False
+
+        def push(seq: Sequence, n: int) -> None:
+            nonlocal budget
+            seq.num_scheduled_tokens = n
+            out.seqs.append(seq)
+            out.total_tokens += n
+            budget -= n
+
+        while pending:
+            seq = pending.popleft()
+            want = min(seq.num_uncached_tokens, budget, cap)
+            if want <= 0 or len(out.seqs) >= self.cfg.max_num_seqs:
+                kept.append(seq)
+                continue
+            yielded = False
+            while not self.cache.can_reserve(seq.seq_id, len(seq)):
+                if pending:
+                    victim = pending.pop()
+                else:
+                    victim, yielded = seq, True
+                self._preempt(victim)
+                out.preempted.append(victim)
+                preempted_now = True
+                if yielded:
+                    break
+            if yielded:
+                continue
+            self.cache.reserve(seq.seq_id, len(seq))
+            push(seq, want)
+            kept.append(seq)
+        self.running = kept
+
+        while (not preempted_now and self.waiting and budget > 0 and len(self.running) < self.cfg.max_num_seqs
+               and len(out.seqs) < self.cfg.max_num_seqs):
+            seq = self.waiting[0]
+            if self.cache.slots.num_free == 0 or not self.cache.can_reserve(seq.seq_id, len(seq)):
+                break
+            self.waiting.popleft()
+            self.cache.admit(seq.seq_id)
+            self.cache.reserve(seq.seq_id, len(seq))
+            seq.status = RUNNING
+            self.running.append(seq)
+            push(seq, min(seq.num_uncached_tokens, budget, cap))
+        return out
+
+    # ---- after the step ----------------------------------------------------------------------------------
+    def on_launched(self, batch: ScheduledBatch) -> List[bool]:
+        """The step ran: its tokens are in the cache.  Returns, per sequence, whether it sampled this step."""
+        sampled = []
+        for seq in batch.seqs:
+            sampled.append(seq.samples_this_step())
+            seq.num_cached_tokens += seq.num_scheduled_tokens
+            seq.num_scheduled_tokens = 0
+        return sampled
+
+    def postprocess(self, batch: ScheduledBatch, sampled_flags: List[bool], tokens: List[int]) -> List[Sequence]:
+        """Append the sampled tokens (`tokens` holds one per sampling sequence, in batch order); finish and free.
+        Returns the sequences that finished."""
+        finished = []
+        it = iter(tokens)
+        for seq, did in zip(batch.seqs, sampled_flags):
+            if not did:
+                continue
+            tok = int(next(it))
+            seq.token_ids.append(tok)
+            hit_eos = (not seq.params.ignore_eos) and tok in self.cfg.eos_token_ids
+            hit_len = seq.num_completion_tokens >= seq.params.max_tokens
+            if hit_eos or hit_len:
+                seq.stopped_on_eos = hit_eos
+                seq.status = FINISHED
+                self.cache.release(seq.seq_id)
+                finished.append(seq)
+        if finished:
+            self.running = [s for s in self.running if s.status != FINISHED]
+        return finished

@@ -115,6 +115,9 @@ class Runtime:
 
 class Part:
     category = ""
+    # False for a part whose forward synchronises with the host or allocates per call: a model that holds such a
+    # part runs its decode steps eagerly instead of replaying CUDA graphs.
+    capturable = True
 
     def __init__(self, runtime: Runtime, prefix: str = "", names: Optional[Dict[str, str]] = None):
         self.rt = runtime

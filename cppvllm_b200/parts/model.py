@@ -44,6 +44,10 @@ class CausalLM:
         self.run_order: List[RunEntry] = spec.resolved_run_order()
         self._check_shared_caches()
 
+    @property
+    def capturable(self) -> bool:
+        return all(p.capturable for p in self.all_parts())
+
     # ---- what the model keeps between steps ------------------------------------------------------------
     def cache_units(self) -> Dict[int, CacheSpec]:
         """cache unit id -> spec, taken from the mixer of the entry that writes the unit."""

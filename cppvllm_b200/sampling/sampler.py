@@ -1,0 +1,59 @@
+"""Sampling of next tokens from float32 logits rows on the device (kernel: csrc/sampling.cu).
+
+Greedy for temperature <= 0, else Gumbel-max at the given temperature, as the reference samples
+(kernels/fused_ops.cu:285-378).  The random stream of a row is a function of (row seed, output position, vocab
+index) only, so what a request draws does not depend on the batch it is in; the reference keys its generator
+by the row's index in the batch and a call counter (fused_ops.cu:330-335; engine/model_runner.cpp:259-260).
+"""
+from __future__ import annotations
+
+from typing import List, Sequence
+
+import numpy as np
+import torch
+
+from ..csrc import ops
+
+_MASK = (1 << 64) - 1
+
+
+def mix_seed(engine_seed: int, request_key: int) -> int:
+    """A 64-bit row seed from the engine's seed and a request's key (splitmix64 finaliser)."""
+    z = (engine_seed * 0x9E3779B97F4A7C15 + request_key + 0x632BE59BD9B4E019) & _MASK
+    z = ((z ^ (z >> 30)) * 0xBF58476D1CE4E5B9) & _MASK
+    z = ((z ^ (z >> 27)) * 0x94D049BB133111EB) & _MASK
+    return z ^ (z >> 31)
+
+
+class Sampler:
+    def __init__(self, device, max_rows: int):
+        self.device = torch.device(device)
+        self.max_rows = max_rows
+        # one pinned block: temps (float32 bits), out positions, seeds lo/hi interleaved as int64
+        self._host_f = torch.empty(max_rows, dtype=torch.float32, pin_memory=True)
+        self._host_p = torch.empty(max_rows, dtype=torch.int32, pin_memory=True)
+        self._host_s = torch.empty(max_rows, dtype=torch.int64, pin_memory=True)
+        self._temps = torch.zeros(max_rows, dtype=torch.float32, device=self.device)
+        self._pos = torch.zeros(max_rows, dtype=torch.int32, device=self.device)
+        self._seeds = torch.zeros(max_rows, dtype=torch.int64, device=self.device)
+        self._out = torch.zeros(max_rows, dtype=torch.int32, device=self.device)
+        self._out_host = torch.empty(max_rows, dtype=torch.int32, pin_memory=True)
+
+    def sample(self, logits: torch.Tensor, temps: Sequence[float], seeds: Sequence[int],
+               out_positions: Sequence[int]) -> List[int]:
+        """logits: [R, V] float32 on the device, one row per entry of the sequences.  Returns R token ids."""
+        R = logits.shape[0]
+        if R == 0:
+            return []
+        if R > self.max_rows or len(temps) != R or len(seeds) != R or len(out_positions) != R:
+            raise ValueError("sampler: row count does not match its arguments or exceeds its capacity")
+        self._host_f.numpy()[:R] = temps
+        self._host_p.numpy()[:R] = out_positions
+        self._host_s.numpy()[:R] = np.asarray([s if s < (1 << 63) else s - (1 << 64) for s in seeds], dtype=np.int64)
+        self._temps[:R].copy_(self._host_f[:R], non_blocking=True)
+        self._pos[:R].copy_(self._host_p[:R], non_blocking=True)
+        self._seeds[:R].copy_(self._host_s[:R], non_blocking=True)
+        ops.sample(self._out[:R], logits, None, self._temps, self._seeds, self._pos, num_rows=R)
+        self._out_host[:R].copy_(self._out[:R], non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        return self._out_host[:R].tolist()

@@ -1,0 +1,326 @@
+"""Each CUDA kernel alone against a plain PyTorch float32 restatement of the same formula, at sizes other than
+the engine's tiny models (odd widths, head sizes in steps of 16, groups of 1, 3, 5 and 7, windows, page edges)."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def dev():
+    return torch.device("cuda:0")
+
+
+def rnd(x, dt):
+    return x.to(dt).float()
+
+
+def tol(dt):
+    return dict(atol=2e-6, rtol=2e-6) if dt == torch.float32 else dict(atol=1e-2, rtol=1.6e-2)
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from cppvllm_b200.csrc import ops as o
+    o.core()
+    return o
+
+
+@pytest.mark.parametrize("dt", DTYPES)
+@pytest.mark.parametrize("T,D", [(1, 7), (5, 100), (33, 1000), (3, 4104)])
+def test_rmsnorm_and_add_rmsnorm(ops, dt, T, D):
+    g = torch.Generator(device="cpu").manual_seed(T * 1000 + D)
+    x = (torch.randn(T, D, generator=g) * 3).to(dt).to(dev())
+    r = torch.randn(T, D, generator=g).to(dt).to(dev())
+    w = (1 + 0.3 * torch.randn(D, generator=g)).to(dev())
+    eps = 3e-5
+    out = torch.empty_like(x)
+    ops.rmsnorm(out, x, w, eps)
+    xf = x.float()
+    ref = rnd(rnd(xf * torch.rsqrt((xf * xf).mean(-1, keepdim=True) + eps), dt) * w, dt)
+    torch.testing.assert_close(out.float(), ref, **tol(dt))
+    res = r.clone()
+    ops.add_rmsnorm(out, res, x, w, eps)
+    s = rnd(r.float() + xf, dt)
+    torch.testing.assert_close(res.float(), s, atol=0, rtol=0)
+    ref = rnd(rnd(s * torch.rsqrt((s * s).mean(-1, keepdim=True) + eps), dt) * w, dt)
+    torch.testing.assert_close(out.float(), ref, **tol(dt))
+    ops.add_(res, x)
+    torch.testing.assert_close(res.float(), rnd(s + xf, dt), atol=0, rtol=0)
+
+
+@pytest.mark.parametrize("dt", DTYPES)
+def test_swiglu_embed_gather(ops, dt):
+    g = torch.Generator().manual_seed(0)
+    gu = (torch.randn(9, 2 * 37, generator=g) * 4).to(dt).to(dev())
+    out = torch.empty(9, 37, dtype=dt, device=dev())
+    ops.swiglu(out, gu)
+    gate, up = gu[:, :37].float(), gu[:, 37:].float()
+    torch.testing.assert_close(out.float(), rnd(rnd(gate / (1 + torch.exp(-gate)), dt) * up, dt), **tol(dt))
+    table = torch.randn(50, 13, generator=g).to(dt).to(dev())
+    toks = torch.tensor([3, 49, 0, 3, 17], dtype=torch.int32, device=dev())
+    e = torch.empty(5, 13, dtype=dt, device=dev())
+    ops.embed(e, table, toks)
+    assert torch.equal(e, table[toks.long()])
+    rows = torch.tensor([4, 0, 0, 2], dtype=torch.int32, device=dev())
+    o = torch.empty(4, 13, dtype=dt, device=dev())
+    ops.gather_rows(o, e, rows)
+    assert torch.equal(o, e[rows.long()])
+
+
+def test_embed_reports_a_token_outside_the_table(ops):
+    table = torch.randn(10, 4, device=dev())
+    out = torch.empty(2, 4, device=dev())
+    ops.embed(out, table, torch.tensor([1, 10], dtype=torch.int32, device=dev()))
+    with pytest.raises(ops.KernelError, match="outside the embedding table"):
+        ops.check_device_errors(dev())
+    ops.check_device_errors(dev())          # the flag was cleared
+
+
+def test_wrong_arguments_are_refused(ops):
+    x = torch.randn(4, 8, device=dev())
+    with pytest.raises(ops.KernelError, match="float32"):
+        ops.rmsnorm(torch.empty_like(x), x, torch.ones(8, device=dev(), dtype=torch.bfloat16), 1e-6)
+    with pytest.raises(ops.KernelError, match="CUDA tensors only"):
+        ops.rmsnorm(torch.empty(4, 8), torch.randn(4, 8), torch.ones(8), 1e-6)
+    with pytest.raises(ops.KernelError, match="float32 or bfloat16"):
+        ops.rmsnorm(x.half(), x.half(), torch.ones(8, device=dev()), 1e-6)
+    with pytest.raises(ops.KernelError, match="multiple"):
+        ops.paged_attention_general(torch.empty(1, 5 * 16, device=dev()), torch.empty(1, 5 * 16, device=dev()),
+                                    torch.zeros(2, 2, 2, 16, 16, device=dev()), torch.zeros(1, 1, dtype=torch.int32, device=dev()),
+                                    torch.zeros(1, dtype=torch.int32, device=dev()), torch.zeros(1, dtype=torch.int32, device=dev()),
+                                    5, 2, 16, 16, 0.25)
+
+
+def rope_ref(n, cos, sin, pos, rot, interleaved):
+    out = n.clone()
+    half = rot // 2
+    c, s = cos[pos][:, None, :], sin[pos][:, None, :]
+    if interleaved:
+        a, b = n[..., 0:rot:2], n[..., 1:rot:2]
+        out[..., 0:rot:2] = a * c - b * s
+        out[..., 1:rot:2] = b * c + a * s
+    else:
+        a, b = n[..., :half], n[..., half:rot]
+        out[..., :half] = a * c - b * s
+        out[..., half:rot] = b * c + a * s
+    return out
+
+
+@pytest.mark.parametrize("dt", DTYPES)
+@pytest.mark.parametrize("H,KV,hd,rot,inter,norm", [(5, 5, 16, 16, False, True), (6, 2, 48, 48, False, True),
+                                                    (7, 1, 80, 32, True, True), (3, 3, 144, 144, False, False),
+                                                    (8, 4, 256, 128, False, True)])
+def test_qk_norm_rope_kv_write(ops, dt, H, KV, hd, rot, inter, norm):
+    T, page, pages, max_pos, eps = 23, 16, 9, 300, 2e-5
+    g = torch.Generator().manual_seed(hd)
+    qkv = torch.randn(T, (H + 2 * KV) * hd, generator=g).to(dt).to(dev())
+    qw = (1 + 0.2 * torch.randn(hd, generator=g)).to(dev()) if norm else None
+    kw = (1 + 0.2 * torch.randn(hd, generator=g)).to(dev()) if norm else None
+    ang = torch.outer(torch.arange(max_pos, dtype=torch.float64), 1.0 / (5000.0 ** (torch.arange(0, rot, 2, dtype=torch.float64) / rot)))
+    cos, sin = ang.cos().float().to(dev()), ang.sin().float().to(dev())
+    pos = torch.randint(0, max_pos, (T,), generator=g).int().to(dev())
+    slots = torch.randperm(pages * page, generator=g)[:T].int().to(dev())
+    cache = torch.zeros(pages, 2, KV, page, hd, dtype=dt, device=dev())
+    q = torch.empty(T, H * hd, dtype=dt, device=dev())
+    ops.qk_norm_rope_kv(q, qkv, qw, kw, cos, sin, pos, slots, cache, H, KV, hd, page, eps, rotary_dim=rot, interleaved=inter)
+    ops.check_device_errors(dev())
+    x = qkv.float().view(T, H + 2 * KV, hd)
+    def headnorm(v, w):
+        if w is None:
+            return v
+        return rnd(rnd(v * torch.rsqrt((v * v).mean(-1, keepdim=True) + eps), dt) * w, dt)
+    qr = rnd(rope_ref(headnorm(x[:, :H], qw), cos, sin, pos.long(), rot, inter), dt)
+    kr = rnd(rope_ref(headnorm(x[:, H:H + KV], kw), cos, sin, pos.long(), rot, inter), dt)
+    torch.testing.assert_close(q.float().view(T, H, hd), qr, **tol(dt))
+    sl = slots.long()
+    torch.testing.assert_close(cache[sl // page, 0, :, sl % page].float(), kr, **tol(dt))
+    assert torch.equal(cache[sl // page, 1, :, sl % page], qkv.view(T, H + 2 * KV, hd)[:, H + KV:])
+    untouched = torch.ones(pages * page, dtype=torch.bool)
+    untouched[sl.cpu()] = False
+    flat = cache.permute(0, 3, 1, 2, 4).reshape(pages * page, -1)
+    assert flat[untouched.to(dev())].abs().max() == 0          # nothing but the step's slots was written
+    # a layer that only reads another layer's cache writes nothing
+    cache2 = torch.zeros_like(cache)
+    q2 = torch.empty_like(q)
+    ops.qk_norm_rope_kv(q2, qkv, qw, kw, cos, sin, pos, None, None, H, KV, hd, page, eps, rotary_dim=rot, interleaved=inter)
+    assert torch.equal(q2, q) and cache2.abs().max() == 0
+
+
+def attention_ref(q, k_all, v_all, kv_lens_per_token, positions, H, KV, hd, scale, window):
+    """q: [T, H, hd]; k_all/v_all: list per token of that token's sequence keys [len, KV, hd]."""
+    out = torch.zeros_like(q)
+    for t in range(q.shape[0]):
+        p = int(positions[t])
+        lo = max(0, p - window + 1) if window > 0 else 0
+        for h in range(H):
+            g = h // (H // KV)
+            k = k_all[t][lo:p + 1, g].float()
+            v = v_all[t][lo:p + 1, g].float()
+            s = (k @ q[t, h].float()) * scale
+            out[t, h] = torch.softmax(s, 0) @ v
+    return out
+
+
+def build_paged(seqs_k, seqs_v, page, pages_total, KV, hd, dt, g):
+    """Scatter per-sequence K/V [len, KV, hd] into shuffled pages; returns cache and block tables."""
+    cache = torch.randn(pages_total, 2, KV, page, hd, generator=g).to(dt)       # garbage where nothing is stored
+    perm = torch.randperm(pages_total, generator=g).tolist()
+    W = max((k.shape[0] + page - 1) // page for k in seqs_k)
+    tables = torch.full((len(seqs_k), W), -1, dtype=torch.int32)
+    for s, (k, v) in enumerate(zip(seqs_k, seqs_v)):
+        for i in range((k.shape[0] + page - 1) // page):
+            pg = perm.pop()
+            tables[s, i] = pg
+            n = min(page, k.shape[0] - i * page)
+            cache[pg, 0, :, :n] = k[i * page:i * page + n].transpose(0, 1)
+            cache[pg, 1, :, :n] = v[i * page:i * page + n].transpose(0, 1)
+    return cache, tables
+
+
+@pytest.mark.parametrize("dt", DTYPES)
+@pytest.mark.parametrize("H,KV,hd,page,window", [(4, 4, 16, 16, 0), (6, 2, 32, 32, 0), (5, 1, 64, 16, 0), (7, 7, 48, 16, 37),
+                                                 (8, 2, 128, 64, 0), (3, 1, 160, 16, 130), (14, 2, 96, 16, 0)])
+def test_paged_attention_general(ops, dt, H, KV, hd, page, window):
+    g = torch.Generator().manual_seed(H * 100 + hd)
+    lens = [1, 17, page, page + 1, 300, 129]
+    seqs_k = [torch.randn(n, KV, hd, generator=g).to(dt) for n in lens]
+    seqs_v = [torch.randn(n, KV, hd, generator=g).to(dt) for n in lens]
+    cache, tables = build_paged(seqs_k, seqs_v, page, 64, KV, hd, dt, g)
+    # queries: the last tokens of each sequence (a portion), plus some in the middle
+    seq_of, positions = [], []
+    for s, n in enumerate(lens):
+        for p in sorted(set([0, n // 2, max(0, n - 3), max(0, n - 2), n - 1])):
+            seq_of.append(s)
+            positions.append(p)
+    T = len(seq_of)
+    q = (torch.randn(T, H, hd, generator=g) * 2).to(dt)
+    scale = 1 / math.sqrt(hd)
+    out = torch.empty(T, H * hd, dtype=dt, device=dev())
+    ops.paged_attention_general(out, q.view(T, -1).to(dev()), cache.to(dev()), tables.to(dev()),
+                                torch.tensor(seq_of, dtype=torch.int32, device=dev()),
+                                torch.tensor(positions, dtype=torch.int32, device=dev()), H, KV, hd, page, scale, window=window)
+    ops.check_device_errors(dev())
+    ref = attention_ref(q, [seqs_k[s] for s in seq_of], [seqs_v[s] for s in seq_of], None, positions, H, KV, hd, scale, window)
+    torch.testing.assert_close(out.float().cpu().view(T, H, hd), rnd(ref, dt), **tol(dt))
+
+
+@pytest.mark.parametrize("dt", DTYPES)
+def test_attention_finds_one_far_key_and_respects_the_window_edge(ops, dt):
+    """One key far back among hundreds is made to dominate; the output must be its value.  With a window that
+    just excludes it, the output must not contain it."""
+    H = KV = 2
+    hd, page, n = 32, 16, 700
+    g = torch.Generator().manual_seed(1)
+    k = torch.randn(n, KV, hd, generator=g) * 0.1
+    v = torch.randn(n, KV, hd, generator=g)
+    q = torch.randn(1, H, hd, generator=g)
+    far = 37
+    k[far] = q[0] * 4.0                                           # score ~ 4 |q|^2 / sqrt(hd): dominates the softmax
+    cache, tables = build_paged([k.to(dt)], [v.to(dt)], page, 50, KV, hd, dt, g)
+    args = (torch.zeros(1, dtype=torch.int32, device=dev()), torch.tensor([n - 1], dtype=torch.int32, device=dev()))
+    out = torch.empty(1, H * hd, dtype=dt, device=dev())
+    ops.paged_attention_general(out, q.view(1, -1).to(dt).to(dev()), cache.to(dev()), tables.to(dev()), *args,
+                                H, KV, hd, page, 1 / math.sqrt(hd))
+    torch.testing.assert_close(out.float().cpu().view(H, hd), v[far].to(dt).float(), atol=2e-2, rtol=2e-2)
+    for window, sees in ((n - far, True), (n - far - 1, False)):      # the edge of the window, to the key
+        ops.paged_attention_general(out, q.view(1, -1).to(dt).to(dev()), cache.to(dev()), tables.to(dev()), *args,
+                                    H, KV, hd, page, 1 / math.sqrt(hd), window=window)
+        close = torch.allclose(out.float().cpu().view(H, hd), v[far].to(dt).float(), atol=2e-2, rtol=2e-2)
+        assert close == sees
+    ops.check_device_errors(dev())
+
+
+def test_attention_reports_a_missing_page(ops):
+    cache = torch.zeros(4, 2, 1, 16, 16, device=dev())
+    tables = torch.tensor([[0, -1]], dtype=torch.int32, device=dev())
+    out = torch.empty(1, 16, device=dev())
+    ops.paged_attention_general(out, torch.zeros(1, 16, device=dev()), cache, tables, torch.zeros(1, dtype=torch.int32, device=dev()),
+                                torch.tensor([20], dtype=torch.int32, device=dev()), 1, 1, 16, 16, 0.25)
+    with pytest.raises(ops.KernelError, match="page is missing"):
+        ops.check_device_errors(dev())
+
+
+# ---- sampling ----------------------------------------------------------------------------------------------
+
+def philox(c, k):
+    c = [np.uint32(x) for x in c]
+    k = [np.uint32(k[0]), np.uint32(k[1])]
+    for _ in range(10):
+        p0 = np.uint64(0xD2511F53) * np.uint64(c[0])
+        p1 = np.uint64(0xCD9E8D57) * np.uint64(c[2])
+        c = [np.uint32(p1 >> np.uint64(32)) ^ c[1] ^ k[0], np.uint32(p1 & np.uint64(0xFFFFFFFF)),
+             np.uint32(p0 >> np.uint64(32)) ^ c[3] ^ k[1], np.uint32(p0 & np.uint64(0xFFFFFFFF))]
+        k = [np.uint32((int(k[0]) + 0x9E3779B9) & 0xFFFFFFFF), np.uint32((int(k[1]) + 0xBB67AE85) & 0xFFFFFFFF)]
+    return c
+
+
+def sample_ref(row, temp, seed, opos):
+    if temp <= 0:
+        return int(np.argmax(row))
+    inv_t = np.float32(1.0) / max(np.float32(temp), np.float32(1e-5))
+    best, best_i = -np.inf, -1
+    for base in range(0, len(row), 4):
+        r = philox([base >> 2, opos, 0x53414D50, 0], [seed & 0xFFFFFFFF, (seed >> 32) & 0xFFFFFFFF])
+        for j in range(4):
+            if base + j >= len(row):
+                break
+            u = (np.float32(int(r[j]) >> 8) + np.float32(0.5)) * np.float32(1.0 / 16777216.0)
+            e = max(-np.log(u, dtype=np.float32), np.float32(1e-10))
+            s = np.float32(row[base + j]) * inv_t - np.log(e, dtype=np.float32)
+            if s > best:
+                best, best_i = s, base + j
+    return best_i
+
+
+def test_sampling_matches_its_formula_and_does_not_depend_on_the_batch(ops):
+    with np.errstate(over="ignore"):
+        V, R = 1003, 6
+        g = torch.Generator().manual_seed(3)
+        logits = (torch.randn(R, V, generator=g) * 2).to(dev())
+        logits[0, 500] = logits[0, 7] = 50.0                        # a tie: greedy takes the lower index
+        temps = torch.tensor([0.0, 0.7, 1.0, 0.0, 0.3, 5.0], device=dev())
+        seeds = torch.tensor([1, 2, 0x123456789ABCDEF, 4, 5, -7], dtype=torch.int64, device=dev())
+        opos = torch.tensor([0, 3, 100, 1, 0, 9], dtype=torch.int32, device=dev())
+        out = torch.zeros(R, dtype=torch.int32, device=dev())
+        ops.sample(out, logits, None, temps, seeds, opos)
+        got = out.tolist()
+        assert got[0] == 7 and got[3] == int(logits[3].argmax())
+        rows = logits.cpu().numpy()
+        for r in (1, 2, 4, 5):
+            sd = int(seeds[r]) & ((1 << 64) - 1)
+            assert got[r] == sample_ref(rows[r], float(temps[r]), sd, int(opos[r]))
+        # the same row alone, or at another place of another batch, draws the same token
+        order = torch.tensor([4, 1, 5], dtype=torch.int32, device=dev())
+        out2 = torch.zeros(3, dtype=torch.int32, device=dev())
+        ops.sample(out2, logits, order, temps[order.long()].contiguous(), seeds[order.long()].contiguous(), opos[order.long()].contiguous())
+        assert out2.tolist() == [got[4], got[1], got[5]]
+        # other output positions and other seeds give other draws (with overwhelming probability over 20 tries)
+        draws = set()
+        for p in range(20):
+            ops.sample(out, logits, None, temps, seeds, torch.full((R,), p, dtype=torch.int32, device=dev()))
+            draws.add(out[5].item())
+        assert len(draws) > 5
+
+
+def test_temperature_sampling_follows_the_distribution(ops):
+    V, N = 8, 4000
+    logits = torch.tensor([[2.0, 1.0, 0.0, -1.0, 0.5, -3.0, 1.5, 0.0]], device=dev()).repeat(N, 1).contiguous()
+    out = torch.zeros(N, dtype=torch.int32, device=dev())
+    ops.sample(out, logits, None, torch.full((N,), 0.8, device=dev()), torch.arange(N, dtype=torch.int64, device=dev()),
+               torch.zeros(N, dtype=torch.int32, device=dev()))
+    freq = torch.bincount(out.long(), minlength=V).float().cpu() / N
+    p = torch.softmax(logits[0].cpu() / 0.8, 0)
+    assert (freq - p).abs().max() < 0.03
+
+
+def test_feed_tokens(ops):
+    tokens = torch.tensor([5, 6, 7, 8], dtype=torch.int32, device=dev())
+    src = torch.tensor([-1, 1, -1, 0], dtype=torch.int32, device=dev())
+    sampled = torch.tensor([40, 41], dtype=torch.int32, device=dev())
+    ops.feed_tokens(tokens, src, sampled, 4)
+    assert tokens.tolist() == [5, 41, 7, 40]

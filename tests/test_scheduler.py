@@ -1,0 +1,130 @@
+"""The scheduler's decisions (CPU, no model): portions under a budget, admission, finishing, preemption.
+
+`golden/scheduler_golden.json` was printed by the reference's own scheduler and block manager, compiled on the
+CPU by `golden/scheduler_driver.cpp`; the same workloads must produce the same batches here."""
+import json
+import os
+
+import pytest
+
+from cppvllm_b200.cache.manager import CacheManager, GroupConfig
+from cppvllm_b200.engine.scheduler import FINISHED, Scheduler, SchedulerConfig, Sequence
+from cppvllm_b200.sampling.params import SamplingParams
+
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden", "scheduler_golden.json")
+
+
+def make(blocks, budget, chunk, max_seqs, page=16, max_model_len=4096, eos=()):
+    cache = CacheManager([GroupConfig(blocks)], page, max(8, max_seqs))
+    return Scheduler(SchedulerConfig(budget, max_seqs, chunk, max_model_len, tuple(eos)), cache), cache
+
+
+def run(sched, cache, seqs, token=lambda step, seq: 7, max_steps=2000):
+    """Drive the scheduler with a model that 'samples' `token`; returns per step [(id, n, samples)]."""
+    for s in seqs:
+        sched.add_request(s)
+    steps = []
+    while not sched.is_finished():
+        assert len(steps) < max_steps
+        b = sched.schedule()
+        cache.check_invariants()
+        steps.append([(s.seq_id, s.num_scheduled_tokens, int(s.samples_this_step())) for s in b.seqs])
+        for s in b.seqs:                                  # every scheduled token has a page
+            cache.slots_for(s.seq_id, 0, s.num_cached_tokens, s.num_scheduled_tokens)
+            cache.advance(s.seq_id, s.num_cached_tokens + s.num_scheduled_tokens)
+        flags = sched.on_launched(b)
+        toks = [token(len(steps), s) for s, f in zip(b.seqs, flags) if f]
+        sched.postprocess(b, flags, toks)
+    cache.check_invariants()
+    return steps
+
+
+@pytest.mark.parametrize("case", json.load(open(GOLDEN)), ids=lambda c: f"blocks{c['blocks']}")
+def test_same_batches_as_the_reference_scheduler(case):
+    sched, cache = make(case["blocks"], case["budget"], case["chunk"], case["max_seqs"])
+    seqs = [Sequence(i, list(range(n)), SamplingParams(max_tokens=case["max_tokens"], ignore_eos=True))
+            for i, n in enumerate(case["prompts"])]
+    steps = [[list(x) for x in st] for st in run(sched, cache, seqs)]
+    if case["preemptions"] == 0:
+        assert steps == case["steps"]
+    else:
+        # The reference re-admits a preempted request with its first full blocks still found by its prefix cache
+        # (engine/block_manager.cpp:80-116), so it recomputes fewer tokens; this engine recomputes all of them.
+        # Up to the first re-admission, victims included, the decisions are the same.
+        gone = set()
+        for n, (mine, ref) in enumerate(zip(steps, case["steps"])):
+            back = [x[0] for x in ref if x[0] in gone]
+            if back:
+                break
+            assert mine == ref, f"step {n}"
+            if n + 1 < len(case["steps"]):
+                nxt = {x[0] for x in case["steps"][n + 1]}
+                gone |= {x[0] for x in ref if x[0] not in nxt and x[2] == 1 and
+                         len([1 for st in case["steps"][:n + 1] for y in st if y[0] == x[0] and y[2]]) < case["max_tokens"]}
+        assert n >= 19 and gone
+    assert sched.num_preemptions == case["preemptions"]
+    assert all(s.status == FINISHED and s.num_completion_tokens == case["max_tokens"] for s in seqs)
+    assert cache.num_free_pages() == case["blocks"]
+
+
+def test_budget_and_chunk_cap_cut_prompts_into_portions():
+    sched, cache = make(64, budget=50, chunk=20, max_seqs=8)
+    a, b = Sequence(0, list(range(45)), SamplingParams(max_tokens=2)), Sequence(1, list(range(30)), SamplingParams(max_tokens=2))
+    steps = run(sched, cache, [a, b])
+    assert steps[0] == [(0, 20, 0), (1, 20, 0)]            # each capped at 20, 40 <= 50
+    assert steps[1] == [(0, 20, 0), (1, 10, 1)]            # b ends its prompt and samples
+    assert steps[2] == [(0, 5, 1), (1, 1, 1)]              # a's last portion beside b's decoded token
+    assert steps[3] == [(0, 1, 1)]
+    no_cap, c2 = make(64, budget=50, chunk=0, max_seqs=8)
+    assert run(no_cap, c2, [Sequence(0, list(range(45)), SamplingParams(max_tokens=1))])[0] == [(0, 45, 1)]
+
+
+def test_max_num_seqs_and_first_come_first_served():
+    sched, cache = make(64, budget=100, chunk=0, max_seqs=2)
+    seqs = [Sequence(i, [1, 2, 3], SamplingParams(max_tokens=2)) for i in range(4)]
+    steps = run(sched, cache, seqs)
+    assert steps[0] == [(0, 3, 1), (1, 3, 1)] and steps[1] == [(0, 1, 1), (1, 1, 1)]
+    assert steps[2] == [(2, 3, 1), (3, 3, 1)]
+
+
+def test_eos_finishes_unless_ignored_and_max_tokens_bounds():
+    sched, cache = make(16, 64, 0, 4, eos=(99,))
+    a = Sequence(0, [1, 2], SamplingParams(max_tokens=10))
+    b = Sequence(1, [1, 2], SamplingParams(max_tokens=3, ignore_eos=True))
+    run(sched, cache, [a, b], token=lambda step, s: 99 if step == 2 else 5)
+    assert a.token_ids == [1, 2, 5, 99] and a.stopped_on_eos
+    assert b.token_ids == [1, 2, 5, 99, 5] and not b.stopped_on_eos
+
+
+def test_oversize_requests_are_refused_at_admission():
+    sched, cache = make(4, 64, 0, 4, max_model_len=100)
+    with pytest.raises(ValueError, match="cache pages"):
+        sched.add_request(Sequence(0, list(range(60)), SamplingParams(max_tokens=10)))      # 5 pages > 4
+    with pytest.raises(ValueError, match="max_model_len"):
+        sched.add_request(Sequence(1, list(range(50)), SamplingParams(max_tokens=60)))
+    with pytest.raises(ValueError, match="at least one"):
+        Sequence(2, [], SamplingParams())
+
+
+def test_pages_run_out_last_running_request_is_preempted_and_recomputed():
+    # 4 pages of 16.  Two requests of 31 tokens fill them; when request 0 crosses into a third page, the last
+    # running request (1) is preempted: it gives back everything, keeps its tokens and later runs them again.
+    sched, cache = make(4, 64, 0, 4)
+    a = Sequence(0, list(range(31)), SamplingParams(max_tokens=8, ignore_eos=True))
+    b = Sequence(1, list(range(100, 131)), SamplingParams(max_tokens=8, ignore_eos=True))
+    steps = run(sched, cache, [a, b])
+    assert steps[0] == [(0, 31, 1), (1, 31, 1)] and steps[1] == [(0, 1, 1), (1, 1, 1)]
+    assert steps[2] == [(0, 1, 1)]                          # 0 needs a third page -> 1 is preempted
+    assert sched.num_preemptions >= 1 and b.num_preemptions >= 1
+    readmit = next(st for st in steps[3:] if any(x[0] == 1 for x in st))
+    n_again = [x for x in readmit if x[0] == 1][0][1]
+    assert n_again > 31                                     # prompt plus what it had generated, as one portion
+    assert a.num_completion_tokens == 8 and b.num_completion_tokens == 8
+    assert b.token_ids[:31] == list(range(100, 131))
+
+
+def test_a_request_alone_preempts_itself_only_if_it_cannot_fit():
+    sched, cache = make(3, 64, 0, 4)
+    a = Sequence(0, list(range(40)), SamplingParams(max_tokens=8, ignore_eos=True))       # 48 tokens = 3 pages: fits
+    run(sched, cache, [a])
+    assert sched.num_preemptions == 0 and a.num_completion_tokens == 8

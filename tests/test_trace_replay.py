@@ -1,0 +1,155 @@
+"""bin/trace_run against the plain implementation: the same requests whole, with the last 32 tokens one by one,
+in portions of changing size, and mixed with other requests in a pool so small that pages are used again; in
+float32 and in bfloat16, at both tiny configurations."""
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen3 as plain
+import tiny_models
+from trace_util import TraceBuilder, needed_max_tokens, portions, rows_by_position, run_trace, tail_one_by_one, whole
+
+pytestmark = pytest.mark.gpu
+
+# float32: the engine and the plain implementation differ only in the order of float32 sums.
+# bfloat16: against the plain implementation in its bfloat16 rounding mode (roundings at the same places), and
+# more loosely against true float32.  All relative to the largest logit of the sequence.
+TOL = {"float32": 1e-5, "bfloat16": 2e-2}
+TOL_BF16_VS_F32 = 4e-2
+
+
+def check_rows(rows, refs, dtype, refs32=None, noise=None):
+    """`noise[rid]`, for the models whose attention was sharpened on purpose: how far the plain implementation's own
+    bfloat16 mode lies from its float32 mode on that request.  Two bfloat16 implementations that sum in different
+    orders differ by about that much; a key read from a wrong page differs by the size of the logits."""
+    worst = 0.0
+    for (rid, pos), row in rows.items():
+        ref = refs[rid]
+        scale = max(1.0, float(ref.abs().max()))
+        err = float(np.abs(row - ref[pos].numpy()).max()) / scale
+        limit = max(TOL[dtype], noise[rid]) if noise else TOL[dtype]
+        assert err <= limit, f"request {rid} position {pos}: error {err:.3e} of scale exceeds {limit:.1e}"
+        if refs32 is not None:
+            e32 = float(np.abs(row - refs32[rid][pos].numpy()).max()) / scale
+            assert e32 <= TOL_BF16_VS_F32, f"request {rid} position {pos}: {e32:.3e} away from float32"
+        worst = max(worst, err)
+    return worst
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_b"])
+def test_one_request_in_three_cuttings(model_dirs, tmp_path, name, dtype):
+    d = model_dirs[name]
+    vocab = tiny_models.config(name)["vocab_size"]
+    toks = {"w": tiny_models.random_tokens(vocab, 100, 11), "t": tiny_models.random_tokens(vocab, 97, 12),
+            "p": tiny_models.random_tokens(vocab, 100, 11)}
+    tb = TraceBuilder()
+    whole(tb, "w", toks["w"])
+    tail_one_by_one(tb, "t", toks["t"])
+    portions(tb, "p", toks["p"])
+    out = run_trace(d, dtype, tb.steps, 128, str(tmp_path / "o"), ["--block-size", str(tiny_models.page_size(name))])
+    rows = rows_by_position(tb.steps, out)
+    assert len(rows) == 100 + 97 + 100
+    refs = {k: plain.forward(d, v, dtype) for k, v in toks.items()}
+    refs32 = {k: plain.forward(d, v, "float32") for k, v in toks.items()} if dtype == "bfloat16" else None
+    check_rows(rows, refs, dtype, refs32)
+    # the same tokens cut differently ("w" whole, "p" in portions) give the same logits beyond rounding
+    for pos in range(100):
+        a, b = rows[("w", pos)], rows[("p", pos)]
+        assert np.abs(a - b).max() <= TOL[dtype] * max(1.0, np.abs(a).max())
+
+
+def mixed_trace(reqs):
+    """Up to four live requests; portions of some beside single decoded tokens of others; requests pause for a
+    step now and then; finished requests give their pages to the next ones."""
+    order = list(reqs)
+    tb = TraceBuilder()
+    fed = {r: 0 for r in order}
+    live, waiting = [], list(order)
+    rng = np.random.RandomState(7)
+    prefill_sizes = [9, 2, 24, 5, 3, 17]
+    step = 0
+    while live or waiting:
+        while waiting and len(live) < 4:
+            live.append(waiting.pop(0))
+        entries, end = [], []
+        for i, r in enumerate(list(live)):
+            n_all = len(reqs[r])
+            if len(live) > 1 and rng.rand() < 0.15:
+                continue                                     # left out of this step, goes on later
+            prompt_part = n_all - 20                         # the last 20 tokens arrive one by one, as decoded
+            if fed[r] < prompt_part:
+                n = min(prefill_sizes[(step + i) % len(prefill_sizes)], prompt_part - fed[r])
+                if prompt_part - fed[r] - n == 1:
+                    n += 1
+            else:
+                n = 1
+            want = list(range(n)) if (n == 1 or rng.rand() < 0.7) else [n - 1]
+            entries.append((r, reqs[r][fed[r]:fed[r] + n], want))
+            fed[r] += n
+            if fed[r] == n_all:
+                end.append(r)
+                live.remove(r)
+        if entries:
+            tb.add(entries, end)
+        step += 1
+    return tb
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["tiny_a_sharp", "tiny_b_sharp", "tiny_b"])
+def test_mixed_requests_with_page_reuse(model_dirs, tmp_path, name, dtype):
+    d = model_dirs[name]
+    vocab = tiny_models.config(name)["vocab_size"]
+    lens = [70, 33, 100, 41, 64, 90, 22, 55]
+    reqs = {f"r{i}": tiny_models.random_tokens(vocab, n, 100 + i) for i, n in enumerate(lens)}
+    tb = mixed_trace(reqs)
+    assert max(len(s["entries"]) for s in tb.steps) == 4
+    assert any(len(e["tokens"]) == 1 for s in tb.steps for e in s["entries"]) and \
+        any(len(e["tokens"]) > 1 and any(len(f["tokens"]) == 1 for f in s["entries"]) for s in tb.steps for e in s["entries"])
+    # the pool holds exactly what the live requests need at the worst moment: 8 requests cannot all fit, so
+    # the pages of finished requests are used again
+    max_tokens = needed_max_tokens(tb.steps)
+    assert max_tokens < sum((n + 63) // 64 * 64 for n in lens)
+    out = run_trace(d, dtype, tb.steps, max_tokens, str(tmp_path / "o"), ["--block-size", str(tiny_models.page_size(name))])
+    rows = rows_by_position(tb.steps, out)
+    refs = {k: plain.forward(d, v, dtype) for k, v in reqs.items()}
+    for rid in reqs:
+        assert (rid, len(reqs[rid]) - 1) in rows
+    noise = None
+    if dtype == "bfloat16" and name.endswith("_sharp"):
+        noise = {}
+        for k, v in reqs.items():
+            r32 = plain.forward(d, v, "float32")
+            noise[k] = float((refs[k] - r32).abs().max()) / max(1.0, float(r32.abs().max()))
+        assert max(noise.values()) < 0.25                     # still far below the size of the logits
+    check_rows(rows, refs, dtype, noise=noise)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_and_first_tokens(model_dirs, tmp_path, dtype):
+    d = model_dirs["tiny_b"]
+    toks = tiny_models.random_tokens(320, 300, 5)
+    tb = TraceBuilder()
+    tb.add([("l", toks[:3], [0, 1, 2])])
+    for i in range(3, 300):
+        tb.add([("l", toks[i:i + 1], [0])], end=["l"] if i == 299 else [])
+    # the first tokens of a sequence: a one-token prompt, then single tokens
+    tb.add([("f", toks[:1], [0])])
+    tb.add([("f", toks[1:2], [0])])
+    tb.add([("f", toks[2:4], [0, 1])], end=["f"])
+    out = run_trace(d, dtype, tb.steps, 320, str(tmp_path / "o"), ["--block-size", "32"])
+    rows = rows_by_position(tb.steps, out)
+    ref = plain.forward(d, toks, dtype)
+    check_rows(rows, {"l": ref, "f": ref}, dtype)
+    assert len(rows) == 300 + 4
+
+
+def test_refusals_are_clear(model_dirs, tmp_path):
+    import json, subprocess, sys
+    from trace_util import TRACE_RUN
+    d = model_dirs["tiny_a"]
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": list(range(100)), "want": [0]}], "end": []}]
+    p = subprocess.run([sys.executable, TRACE_RUN, "--model", d, "--dtype", "float32", "--out", str(tmp_path / "o"),
+                        "--max-tokens", "64"], input=json.dumps(steps[0]) + "\n", capture_output=True, text=True)
+    assert p.returncode == 3 and "pages" in p.stderr and "done 0" not in p.stdout
