@@ -33,6 +33,7 @@ NVCC_FLAGS = [
 # library name -> source files
 LIBRARIES: Dict[str, List[str]] = {
     "core": ["elementwise.cu", "qk_rope_kv.cu", "attention_general.cu", "sampling.cu"],
+    "attn_bf16": ["attention_bf16.cu"],
 }
 
 _HEADERS = ["common.cuh"]

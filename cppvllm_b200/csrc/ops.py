@@ -238,6 +238,74 @@ def paged_attention_general(out: torch.Tensor, q: torch.Tensor, cache: torch.Ten
     return out
 
 
+_attn = None
+
+
+def attn_bf16():
+    global _attn
+    if _attn is None:
+        lib = load_library("attn_bf16")
+        lib.cvb_attn_prefill_bf16.restype = c_int
+        lib.cvb_attn_decode_bf16.restype = c_int
+        lib.cvb_attn_decode_scratch_floats.restype = c_int64
+        _attn = lib
+    return _attn
+
+
+def fast_attention_supported(dtype: torch.dtype, num_heads: int, num_kv_heads: int, head_dim: int) -> bool:
+    """The tensor-core kernels cover bf16, head sizes 64 and 128 and up to 16 query heads per kv head."""
+    return (dtype == torch.bfloat16 and head_dim in (64, 128) and num_heads % num_kv_heads == 0
+            and num_heads // num_kv_heads <= 16)
+
+
+def prefill_tiles(q_lens, num_heads: int, num_kv_heads: int, skip_single: bool = True) -> int:
+    """Tiles the prefill kernel's grid needs: per request ceil(tokens / (64 / group))."""
+    tpt = 64 // (num_heads // num_kv_heads)
+    return sum((n + tpt - 1) // tpt for n in q_lens if not (skip_single and n == 1))
+
+
+def _attn_common_checks(out, q, cache, block_tables, cu_seqlens, positions):
+    _cuda(out, q, cache, block_tables, cu_seqlens, positions)
+    _contig(out, q, cache, block_tables, cu_seqlens, positions)
+    if q.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
+        raise KernelError("tensor-core attention takes bf16 queries, pages and output")
+    if block_tables.dtype != torch.int32 or block_tables.dim() != 2 or cu_seqlens.dtype != torch.int32 \
+            or positions.dtype != torch.int32:
+        raise KernelError("tensor-core attention: block_tables [S, W], cu_seqlens and positions must be int32")
+
+
+def attn_prefill_bf16(out, q, cache, block_tables, cu_seqlens, positions, num_seqs: int, num_tiles: int,
+                      num_heads: int, num_kv_heads: int, head_dim: int, page_size: int, scale: float,
+                      window: int = 0, skip_single: bool = True):
+    _attn_common_checks(out, q, cache, block_tables, cu_seqlens, positions)
+    num_pages = cache.numel() // (2 * num_kv_heads * page_size * head_dim)
+    _check(attn_bf16().cvb_attn_prefill_bf16(
+        _ptr(out), _ptr(q), _ptr(cache), _ptr(block_tables), c_int(block_tables.shape[1]), _ptr(cu_seqlens),
+        _ptr(positions), c_int(num_seqs), c_int(num_tiles), c_int(num_heads), c_int(num_kv_heads), c_int(head_dim),
+        c_int(page_size), c_int(window), c_float(scale), c_int(num_pages), c_int(1 if skip_single else 0),
+        _ptr(error_flag(q.device)), _stream()), "attn_prefill_bf16")
+    return out
+
+
+def attn_decode_scratch_floats(num_seqs: int, num_kv_heads: int, head_dim: int, splits: int) -> int:
+    return int(attn_bf16().cvb_attn_decode_scratch_floats(c_int(num_seqs), c_int(num_kv_heads), c_int(head_dim), c_int(splits)))
+
+
+def attn_decode_bf16(out, q, cache, block_tables, cu_seqlens, positions, num_seqs: int, num_heads: int,
+                     num_kv_heads: int, head_dim: int, page_size: int, scale: float, splits: int,
+                     scratch: Optional[torch.Tensor], window: int = 0):
+    _attn_common_checks(out, q, cache, block_tables, cu_seqlens, positions)
+    if scratch is not None and (scratch.dtype != torch.float32 or not scratch.is_cuda or not scratch.is_contiguous()):
+        raise KernelError("attn_decode_bf16: scratch must be a contiguous float32 CUDA tensor")
+    num_pages = cache.numel() // (2 * num_kv_heads * page_size * head_dim)
+    _check(attn_bf16().cvb_attn_decode_bf16(
+        _ptr(out), _ptr(q), _ptr(cache), _ptr(block_tables), c_int(block_tables.shape[1]), _ptr(cu_seqlens),
+        _ptr(positions), c_int(num_seqs), c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), c_int(page_size),
+        c_int(window), c_float(scale), c_int(num_pages), c_int(splits), _ptr(scratch),
+        c_int64(scratch.numel() if scratch is not None else 0), _ptr(error_flag(q.device)), _stream()), "attn_decode_bf16")
+    return out
+
+
 # ---- sampling ----------------------------------------------------------------------------------------------
 
 def sample(out: torch.Tensor, logits: torch.Tensor, rows: Optional[torch.Tensor], temps: torch.Tensor,

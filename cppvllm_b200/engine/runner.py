@@ -73,7 +73,7 @@ class ModelRunner:
         self.config = self.arch.parse_config(cfg_dict)
         spec = self.arch.build_spec(self.config)
         self.max_model_len = int(min(max_model_len, spec.max_positions) if spec.max_positions else max_model_len)
-        self.workspace = Workspace(self.device, self.max_step_tokens)
+        self.workspace = Workspace(self.device, self.max_step_tokens, self.max_seqs)
         self.rt = Runtime(self.device, dtype, self.workspace)
         self.model = CausalLM(spec, self.rt)
         self.model.bind(load_weights(self.model, model_dir, self.device, dtype))

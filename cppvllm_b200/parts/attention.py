@@ -25,13 +25,14 @@ from .base import CacheSpec, Mixer, WeightSpec, register_part
 class PagedAttention(Mixer):
     def __init__(self, runtime, prefix="", names=None, *, hidden_size: int, num_heads: int, num_kv_heads: int,
                  head_dim: int, qk_norm: bool = True, qk_norm_eps: float = 1e-6, window: int = 0,
-                 scale: Optional[float] = None, position=None):
+                 scale: Optional[float] = None, position=None, force_general: bool = False):
         super().__init__(runtime, prefix, names)
         if num_heads % num_kv_heads:
             raise ValueError(f"{num_heads} query heads are not a multiple of {num_kv_heads} key/value heads")
         self.hidden_size, self.num_heads, self.num_kv_heads, self.head_dim = map(int, (hidden_size, num_heads, num_kv_heads, head_dim))
         self.qk_norm, self.qk_norm_eps, self.window = bool(qk_norm), float(qk_norm_eps), int(window)
         self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(self.head_dim)
+        self.force_general = bool(force_general)     # always use the general kernel (tests compare the two)
         self.position = position            # a RotaryEmbedding part or None
         if self.position is not None and self.position.rotary_dim > self.head_dim:
             raise ValueError("rotary_dim exceeds head_dim")
@@ -67,6 +68,12 @@ class PagedAttention(Mixer):
     def weight_bytes(self) -> int:
         return sum(w.numel() * w.element_size() for w in (self.w_qkv, self.w_o, self.q_norm_w, self.k_norm_w) if w is not None)
 
+    def scratch_floats(self) -> int:
+        """Upper bound of the split-KV scratch: requests * kv heads * splits never exceeds the larger of the block
+        target and requests * kv heads (one split), each with 16 rows of head_dim + 2 floats."""
+        most = max(self.DECODE_TARGET_BLOCKS, self.rt.workspace.max_seqs * self.num_kv_heads)
+        return most * 16 * (self.head_dim + 2)
+
     # ---- step ----
     def forward(self, x, ctx, cache, state):
         T = x.shape[0]
@@ -87,7 +94,34 @@ class PagedAttention(Mixer):
         self.attend(att, q, ctx, cache, g)
         return ops.linear(att, self.w_o, out=ws.rows("attn_proj", T, self.hidden_size, x.dtype))
 
+    # target number of blocks for the split-KV decode kernel: two per SM of a B200
+    DECODE_TARGET_BLOCKS = 296
+    MAX_SPLITS = 32
+
+    def decode_splits(self, num_seqs: int, max_kv_len: int) -> int:
+        per_seq = self.DECODE_TARGET_BLOCKS // max(1, num_seqs * self.num_kv_heads)
+        tiles = (max_kv_len + 63) // 64
+        return max(1, min(self.MAX_SPLITS, per_seq, tiles))
+
     def attend(self, att, q, ctx, cache, g):
+        H, KV, hd = self.num_heads, self.num_kv_heads, self.head_dim
+        if not self.force_general and ops.fast_attention_supported(q.dtype, H, KV, hd):
+            S = ctx.num_seqs
+            q_lens = ctx.q_lens if ctx.q_lens is not None else [1] * S
+            tiles = ops.prefill_tiles(q_lens, H, KV)
+            if tiles:
+                ops.attn_prefill_bf16(att, q, cache.pages, g.block_tables, ctx.cu_seqlens, ctx.positions, S, tiles,
+                                      H, KV, hd, g.page_size, self.scale, window=self.window, skip_single=True)
+            if any(n == 1 for n in q_lens):
+                splits = self.decode_splits(S, ctx.max_kv_len)
+                scratch = None
+                if splits > 1:
+                    n = ops.attn_decode_scratch_floats(S, KV, hd, splits)
+                    scratch = self.rt.workspace.flat("attn_decode_scratch", self.scratch_floats(), torch.float32)
+                    assert n <= scratch.numel()
+                ops.attn_decode_bf16(att, q, cache.pages, g.block_tables, ctx.cu_seqlens, ctx.positions, S, H, KV, hd,
+                                     g.page_size, self.scale, splits, scratch, window=self.window)
+            return
         ops.paged_attention_general(att, q, cache.pages, g.block_tables, ctx.seq_of_token, ctx.positions,
                                     self.num_heads, self.num_kv_heads, self.head_dim, g.page_size, self.scale,
                                     window=self.window, num_tokens=ctx.num_tokens)

@@ -88,9 +88,10 @@ class Workspace:
     Fixed addresses let decode steps be captured in CUDA graphs; sharing names between layers keeps the
     footprint at one layer's worth."""
 
-    def __init__(self, device, max_tokens: int):
+    def __init__(self, device, max_tokens: int, max_seqs: int = 0):
         self.device = device
         self.max_tokens = max_tokens
+        self.max_seqs = max_seqs or max_tokens
         self._buffers: Dict[str, torch.Tensor] = {}
 
     def rows(self, name: str, n_rows: int, width, dtype: torch.dtype) -> torch.Tensor:
@@ -103,6 +104,17 @@ class Workspace:
         if n_rows > self.max_tokens:
             raise ValueError(f"a step of {n_rows} tokens exceeds the workspace of {self.max_tokens}")
         return buf[:n_rows]
+
+    def flat(self, name: str, numel: int, dtype: torch.dtype) -> torch.Tensor:
+        """A named scratch buffer of a fixed number of elements (allocated once, at its first use)."""
+        key = f"{name}|flat|{dtype}"
+        buf = self._buffers.get(key)
+        if buf is None:
+            buf = torch.empty(numel, dtype=dtype, device=self.device)
+            self._buffers[key] = buf
+        elif buf.numel() < numel:           # never reallocated: captured graphs hold the address
+            raise ValueError(f"scratch buffer '{name}' was sized for {buf.numel()} elements, {numel} are asked for")
+        return buf
 
 
 @dataclass

@@ -324,3 +324,91 @@ def test_feed_tokens(ops):
     sampled = torch.tensor([40, 41], dtype=torch.int32, device=dev())
     ops.feed_tokens(tokens, src, sampled, 4)
     assert tokens.tolist() == [5, 41, 7, 40]
+
+
+# ---- tensor-core attention (bf16, head sizes 64 and 128) against the plain restatement -----------------------
+
+@pytest.mark.parametrize("H,KV,hd,page,window", [(4, 2, 128, 16, 0), (6, 2, 64, 16, 0), (8, 1, 128, 32, 0), (5, 5, 64, 64, 0),
+                                                 (16, 8, 128, 16, 0), (14, 2, 128, 16, 150), (3, 1, 64, 16, 70), (32, 2, 64, 16, 0)])
+def test_tensor_core_attention_mixed_portions_and_single_tokens(ops, H, KV, hd, page, window):
+    dt = torch.bfloat16
+    g = torch.Generator().manual_seed(H * 7 + hd + page)
+    # (tokens already in the cache, tokens in this step): portions at the start, in the middle, crossing tile and page
+    # edges, and single decoded tokens at short and long contexts
+    reqs = [(0, 70), (0, 1), (130, 1), (63, 2), (64, 64), (500, 1), (17, 130), (255, 1), (256, 1), (0, 5), (1000, 3), (777, 1)]
+    seqs_k = [torch.randn(c + n, KV, hd, generator=g).to(dt) for c, n in reqs]
+    seqs_v = [torch.randn(c + n, KV, hd, generator=g).to(dt) for c, n in reqs]
+    total_pages = sum((c + n + page - 1) // page for c, n in reqs) + 3
+    cache, tables = build_paged(seqs_k, seqs_v, page, total_pages, KV, hd, dt, g)
+    cu, positions, seq_of = [0], [], []
+    for s, (c, n) in enumerate(reqs):
+        cu.append(cu[-1] + n)
+        positions += list(range(c, c + n))
+        seq_of += [s] * n
+    T = cu[-1]
+    q = (torch.randn(T, H, hd, generator=g) * 1.5).to(dt)
+    scale = 1 / math.sqrt(hd)
+    d = dev()
+    out = torch.zeros(T, H * hd, dtype=dt, device=d)
+    q_lens = [n for _, n in reqs]
+    cu_t = torch.tensor(cu, dtype=torch.int32, device=d)
+    pos_t = torch.tensor(positions, dtype=torch.int32, device=d)
+    tiles = ops.prefill_tiles(q_lens, H, KV)
+    ops.attn_prefill_bf16(out, q.view(T, -1).to(d), cache.to(d), tables.to(d), cu_t, pos_t, len(reqs), tiles, H, KV, hd, page,
+                          scale, window=window)
+    results = {}
+    for splits in (1, 3, 7):
+        o2 = out.clone()
+        n = ops.attn_decode_scratch_floats(len(reqs), KV, hd, splits)
+        scratch = torch.full((max(n, 1),), float("nan"), device=d) if splits > 1 else None
+        ops.attn_decode_bf16(o2, q.view(T, -1).to(d), cache.to(d), tables.to(d), cu_t, pos_t, len(reqs), H, KV, hd, page,
+                             scale, splits, scratch, window=window)
+        results[splits] = o2.float().cpu().view(T, H, hd)
+    ops.check_device_errors(d)
+    ref = attention_ref(q, [seqs_k[s] for s in seq_of], [seqs_v[s] for s in seq_of], None, positions, H, KV, hd, scale, window)
+    for splits, got in results.items():
+        torch.testing.assert_close(got, rnd(ref, dt), atol=2e-2, rtol=2e-2)
+    # and against the general kernel of the package
+    gen = torch.empty_like(out)
+    ops.paged_attention_general(gen, q.view(T, -1).to(d), cache.to(d), tables.to(d), torch.tensor(seq_of, dtype=torch.int32, device=d),
+                                pos_t, H, KV, hd, page, scale, window=window)
+    torch.testing.assert_close(results[3], gen.float().cpu().view(T, H, hd), atol=2e-2, rtol=2e-2)
+
+
+def test_tensor_core_attention_finds_one_far_key(ops):
+    dt = torch.bfloat16
+    H, KV, hd, page = 4, 2, 128, 16
+    g = torch.Generator().manual_seed(5)
+    n = 1500
+    k = torch.randn(n, KV, hd, generator=g) * 0.1
+    v = torch.randn(n, KV, hd, generator=g)
+    q = torch.randn(2, H, hd, generator=g)          # token 0: single decoded token of request 0; token 1.. a portion of request 1
+    far = 70
+    k[far, 0] = q[0, 1] * 2.0                         # head 1 (kv head 0) of the decoded token must return v[far, 0]
+    cache, tables = build_paged([k.to(dt), k.to(dt)], [v.to(dt), v.to(dt)], page, 200, KV, hd, dt, g)
+    d = dev()
+    cu = torch.tensor([0, 1, 3], dtype=torch.int32, device=d)
+    qq = torch.cat([q[:1], q[1:2], q[:1]]).to(dt)     # request 1 brings two tokens at positions n-2, n-1; its last equals token 0
+    pos = torch.tensor([n - 1, n - 2, n - 1], dtype=torch.int32, device=d)
+    out = torch.zeros(3, H * hd, dtype=dt, device=d)
+    ops.attn_prefill_bf16(out, qq.view(3, -1).to(d), cache.to(d), tables.to(d), cu, pos, 2, ops.prefill_tiles([1, 2], H, KV), H, KV,
+                          hd, page, 1 / math.sqrt(hd))
+    scratch = torch.zeros(ops.attn_decode_scratch_floats(2, KV, hd, 5), device=d)
+    ops.attn_decode_bf16(out, qq.view(3, -1).to(d), cache.to(d), tables.to(d), cu, pos, 2, H, KV, hd, page, 1 / math.sqrt(hd), 5, scratch)
+    o = out.float().cpu().view(3, H, hd)
+    want = v[far, 0].to(dt).float()
+    torch.testing.assert_close(o[0, 1], want, atol=3e-2, rtol=3e-2)      # decode kernel
+    torch.testing.assert_close(o[2, 1], want, atol=3e-2, rtol=3e-2)      # prefill kernel, same query
+    ops.check_device_errors(d)
+
+
+def test_tensor_core_attention_refuses_what_it_does_not_cover(ops):
+    d = dev()
+    z = torch.zeros(1, 2 * 32, dtype=torch.bfloat16, device=d)
+    i = torch.zeros(2, dtype=torch.int32, device=d)
+    with pytest.raises(ops.KernelError, match="does not cover"):
+        ops.attn_prefill_bf16(z, z, torch.zeros(2, 2, 1, 16, 32, dtype=torch.bfloat16, device=d), i.view(1, 2), i, i, 1, 1, 2, 1, 32, 16, 0.1)
+    assert not ops.fast_attention_supported(torch.float32, 4, 2, 128) and not ops.fast_attention_supported(torch.bfloat16, 4, 2, 96)
+    z = torch.zeros(1, 2 * 64, dtype=torch.bfloat16, device=d)
+    with pytest.raises(ops.KernelError, match="scratch"):
+        ops.attn_decode_bf16(z, z, torch.zeros(2, 2, 1, 16, 64, dtype=torch.bfloat16, device=d), i.view(1, 2), i, i, 1, 2, 1, 64, 16, 0.1, 4, None)

@@ -19,10 +19,16 @@ TINY_B = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", hidden_siz
               rope_parameters={"rope_theta": 1000000.0}, rms_norm_eps=1e-5, tie_word_embeddings=False,
               max_position_embeddings=512)
 
+# head size 64 with a group of 3: the smallest shape that the tensor-core attention kernels take
+TINY_C = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", hidden_size=80, num_hidden_layers=2,
+              num_attention_heads=6, num_key_value_heads=2, head_dim=64, intermediate_size=144, vocab_size=200,
+              rope_theta=50000.0, rms_norm_eps=1e-6, tie_word_embeddings=False, max_position_embeddings=512)
+
 # name -> (config, seed, std, norm spread, page size)
 SETUPS = {
     "tiny_a": (TINY_A, 0, 0.02, 0.1, 16),
     "tiny_b": (TINY_B, 1, 0.03, 0.2, 32),
+    "tiny_c": (TINY_C, 2, 0.03, 0.1, 16),
 }
 
 
