@@ -36,8 +36,17 @@ class KernelError(RuntimeError):
     pass
 
 
-def _check(status: int, what: str) -> None:
+LAUNCHES = 0      # kernels of this package launched (or recorded into a graph being captured) so far
+
+
+def launches() -> int:
+    return LAUNCHES
+
+
+def _check(status: int, what: str, kernels: int = 1) -> None:
+    global LAUNCHES
     if status == 0:
+        LAUNCHES += kernels
         return
     if status < 0:
         raise KernelError(f"{what}: refused: {_ERRORS.get(status, f'code {status}')}")
@@ -302,7 +311,8 @@ def attn_decode_bf16(out, q, cache, block_tables, cu_seqlens, positions, num_seq
         _ptr(out), _ptr(q), _ptr(cache), _ptr(block_tables), c_int(block_tables.shape[1]), _ptr(cu_seqlens),
         _ptr(positions), c_int(num_seqs), c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), c_int(page_size),
         c_int(window), c_float(scale), c_int(num_pages), c_int(splits), _ptr(scratch),
-        c_int64(scratch.numel() if scratch is not None else 0), _ptr(error_flag(q.device)), _stream()), "attn_decode_bf16")
+        c_int64(scratch.numel() if scratch is not None else 0), _ptr(error_flag(q.device)), _stream()), "attn_decode_bf16",
+        kernels=2 if splits > 1 else 1)
     return out
 
 

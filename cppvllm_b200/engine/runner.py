@@ -119,7 +119,7 @@ class ModelRunner:
 
         # ---- staging ----------------------------------------------------------------------------------
         G = max(1, len(self.group_specs))
-        cap = (4 * _align(self.max_step_tokens) + 3 * _align(self.max_seqs + 1)
+        cap = (5 * _align(self.max_step_tokens) + 3 * _align(self.max_seqs + 1)
                + G * (_align(self.max_step_tokens) + _align(self.max_seqs * self.table_width)) + 64)
         self._stage_capacity = cap
         self._stage_host = [torch.empty(cap, dtype=torch.int32, pin_memory=True) for _ in range(4)]
@@ -129,6 +129,9 @@ class ModelRunner:
         self._stage_dev = torch.zeros(cap, dtype=torch.int32, device=self.device)
         self._logits = torch.empty((self.max_seqs, self.vocab_size), dtype=torch.float32, device=self.device)
         self._graphs: Dict[int, tuple] = {}
+        self._graph_launches: Dict[int, int] = {}
+        self._feed = None
+        self.h2d_bytes_last_step = 0
         self.stats = {"steps": 0, "graph_steps": 0, "tokens": 0}
 
     # ---- sizing -----------------------------------------------------------------------------------------
@@ -158,12 +161,16 @@ class ModelRunner:
                         ("cu_seqlens", S + 1), ("kv_lens", S), ("state_slots", S)):
             lay[name] = (off, n)
             off += _align(n)
+        lay["feed_src"] = (off, T)
+        off += _align(T)
         for g in range(len(self.group_specs)):
             lay[f"slots{g}"] = (off, T)
             off += _align(T)
             lay[f"tables{g}"] = (off, S * W)
             off += _align(S * W)
         lay["_end"] = (off, 0)
+        if off > self._stage_capacity:
+            raise ValueError("the step's index arrays exceed the staging buffer")
         return lay
 
     def _next_stage(self):
@@ -237,10 +244,21 @@ class ModelRunner:
         if R == 0 and not pad_to:
             rows[0] = 0
         end = lay["_end"][0]
+        feed = getattr(self, "_feed", None)
+        if feed is not None and entries:
+            o, n = lay["feed_src"]
+            src = buf[o:o + n]
+            src[:] = -1
+            src[:len(feed[1])] = feed[1]
         self._stage_dev[:end].copy_(self._stage_host[idx][:end], non_blocking=True)
         ev = torch.cuda.Event()
         ev.record()
         self._stage_events[idx] = ev
+        self.h2d_bytes_last_step = end * 4
+        if feed is not None and entries:
+            o, n = lay["tokens"]
+            fo, _ = lay["feed_src"]
+            ops.feed_tokens(self._stage_dev[o:o + n], self._stage_dev[fo:fo + n], feed[0], T)
         return lay, T_pad, S_pad, R_pad
 
     def _context(self, lay, T: int, S: int, R: int, W: int, q_lens, max_kv: int) -> StepContext:
@@ -279,10 +297,15 @@ class ModelRunner:
                 if not (0 <= w < n):
                     raise ValueError(f"request {e.request_id!r}: wanted index {w} outside its {n} tokens")
 
-    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+    def step(self, entries: Sequence[StepEntry], feed=None) -> torch.Tensor:
         """Run one step.  Pages for every entry's tokens must have been reserved with ``cache.reserve``.
         Returns float32 logits [R, vocab] on the device, rows in the order of the entries and of their ``want``;
-        the tensor is valid until the next step."""
+        the tensor is valid until the next step.
+
+        ``feed = (sampled, src)`` hands tokens over on the device: ``sampled`` is an int32 device tensor (the
+        previous step's samples, possibly still being computed) and ``src`` a list with one entry per token of
+        this step, the index into ``sampled`` whose value replaces that token, or -1 to keep the given one
+        (reference engine/model_runner.cpp:266-275, 299-303)."""
         entries = list(entries)
         if not entries:
             raise ValueError("a step needs at least one entry")
@@ -301,6 +324,7 @@ class ModelRunner:
                 st.index_fill_(0, idx, 0)
         max_kv = max(e.start + len(e.tokens) for e in entries)
 
+        self._feed = feed
         logits = None
         if (not self.enforce_eager and self.model.capturable and T == S and self._bucket(S)
                 and all(len(e.want) == 1 for e in entries)):
@@ -345,8 +369,11 @@ class ModelRunner:
             self.model.forward(ctx, self.cache_views, self.states, self._logits)
             torch.cuda.synchronize(self.device)
             graph = torch.cuda.CUDAGraph()
+            before = ops.launches()
             with torch.cuda.graph(graph):
                 self.model.forward(ctx, self.cache_views, self.states, self._logits)
+            self._graph_launches[B] = ops.launches() - before
+            ops.LAUNCHES = before                             # recorded, not run: replays count them
         except Exception as ex:                               # a part that synchronises or allocates on the host
             torch.cuda.synchronize(self.device)
             self.enforce_eager = True
@@ -363,6 +390,7 @@ class ModelRunner:
             return None
         self._fill(entries, S, S, S, self.table_width, pad_to=B)
         self._graphs[B][0].replay()
+        ops.LAUNCHES += self._graph_launches[B]
         self.stats["graph_steps"] += 1
         return self._logits[:S]
 

@@ -45,6 +45,19 @@ class Sampler:
         R = logits.shape[0]
         if R == 0:
             return []
+        self.sample_async(logits, temps, seeds, out_positions)
+        return self.collect(R)
+
+    def collect(self, R: int) -> List[int]:
+        """Wait for the last sample_async and return its R tokens."""
+        torch.cuda.current_stream().synchronize()
+        return self._out_host[:R].tolist()
+
+    def sample_async(self, logits: torch.Tensor, temps: Sequence[float], seeds: Sequence[int],
+                     out_positions: Sequence[int]) -> torch.Tensor:
+        """Enqueue the sampling of R rows and the copy of the tokens to pinned host memory; returns the device
+        tensor of tokens (int32 [R]) without waiting for it."""
+        R = logits.shape[0]
         if R > self.max_rows or len(temps) != R or len(seeds) != R or len(out_positions) != R:
             raise ValueError("sampler: row count does not match its arguments or exceeds its capacity")
         self._host_f.numpy()[:R] = temps
@@ -55,5 +68,5 @@ class Sampler:
         self._seeds[:R].copy_(self._host_s[:R], non_blocking=True)
         ops.sample(self._out[:R], logits, None, self._temps, self._seeds, self._pos, num_rows=R)
         self._out_host[:R].copy_(self._out[:R], non_blocking=True)
-        torch.cuda.current_stream().synchronize()
-        return self._out_host[:R].tolist()
+        self.h2d_bytes_last = R * (4 + 4 + 8)
+        return self._out[:R]
