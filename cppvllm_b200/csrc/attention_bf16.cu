@@ -12,10 +12,19 @@
 // second product, as flash attention does.  Formulas as in attention_general.cu (reference
 // kernels/paged_attention.cu:89-359: scale * q.k, keys lo..p, online softmax, o = sum p v / l).
 //
-// Tiles move with cp.async (16-byte chunks; rows beyond the request's length are zero-filled and never read from
-// memory); shared-memory rows are XOR-swizzled in 16-byte chunks so that ldmatrix is conflict-free.  The matrix
-// products are mma.sync.m16n8k16 (bf16 in, float accumulate).
+// Key and value tiles are fetched by TMA (cp.async.bulk.tensor.2d through a tensor map of the page pool seen as
+// rows of head_dim elements; one box per page and 64-column half, 128-byte swizzle, completion on an mbarrier
+// with a transaction count), issued by one thread per block into a ring of stages.  A box whose keys lie outside
+// the request's range is fetched from the nearest page inside it, so every tile brings the same number of
+// bytes and never touches a page the request does not own; such keys are excluded by the mask.  Waits on the
+// mbarrier are bounded: if one runs out, the block records error 5 and leaves without computing.  The query tile
+// comes by cp.async.  The matrix products are mma.sync.m16n8k16 (bf16 in, float accumulate); ldmatrix reads the
+// swizzled tiles without bank conflicts.
 #include "common.cuh"
+
+#include <cuda.h>
+#include <mutex>
+#include <unordered_map>
 
 namespace cvb {
 
@@ -50,17 +59,50 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
-// element offset of 16-byte chunk `c` of row `r` in a swizzled tile whose rows hold HD bf16
+// element offset of 16-byte chunk `c` of row `r` in the query tile (rows of HD bf16, chunks XOR-swizzled by row)
 template <int HD> __device__ __forceinline__ int swz(int r, int c) { return r * HD + ((c ^ (r & 7)) << 3); }
+
+// element offset of chunk `c` of key row `r` in a key/value tile as TMA lays it out: HD/64 halves of
+// [64 rows][64 columns], each 128-byte row with its 16-byte chunks XOR-ed by (row & 7) (the 128-byte swizzle)
+__device__ __forceinline__ int kv_off(int r, int c) { return ((c >> 3) << 12) + (r << 6) + (((c & 7) ^ (r & 7)) << 3); }
+
+// ---- mbarrier and TMA ------------------------------------------------------------------------------------
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%1], %0;\n" ::"r"(count), "r"(smem_u32(bar)));
+}
+__device__ __forceinline__ void mbar_fence_init() { asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory"); }
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%1], %0;\n" ::"r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n.reg .pred P1;\nmbarrier.try_wait.parity.shared::cta.b64 P1, [%1], %2;\nselp.b32 %0, 1, 0, P1;\n}\n"
+                 : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Bounded wait (about 20 ms of clock cycles): if the barrier does not complete, error 5 is recorded and the
+// caller goes on with whatever the stage holds.  No thread leaves early, so block-wide barriers stay matched
+// and the kernel always ends; the host sees the error flag and discards the step.
+__device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, int* err) {
+    if (mbar_try_wait(bar, parity)) return;
+    const long long t0 = clock64();
+    while (!mbar_try_wait(bar, parity)) {
+        if (clock64() - t0 > 40000000LL) { atomicExch(err, 5); return; }
+    }
+}
+__device__ __forceinline__ void tma_load_2d(void* smem, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
+                 ::"r"(smem_u32(smem)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
+}
 
 struct AttnParams {
     __nv_bfloat16* out;                 // [T, H, HD]
     const __nv_bfloat16* q;             // [T, H, HD]
-    const __nv_bfloat16* cache;         // [pages, 2, KV, page_size, HD]
     const int* block_tables;            // [S, table_width]
     const int* cu_seqlens;              // [S + 1]
     const int* positions;               // [T]
     int table_width, S, H, KV, page_size, window, num_pages;
+    int box_rows;                       // rows of one TMA box: min(page_size, 64)
     float scale_log2;                   // scale * log2(e)
     int* err;
     // decode only
@@ -69,31 +111,31 @@ struct AttnParams {
     int splits;
 };
 
-// Loads keys [key0, key0 + 64) of one kv head into a swizzled tile: `which` = 0 for K, 1 for V.
+// Issued by ONE thread: fetch keys [key0, key0 + 64) of one kv head, K then V, into a stage.  `stage` points at
+// the K tile; the V tile follows it.
 template <int HD>
-__device__ __forceinline__ void load_kv_tile(__nv_bfloat16* tile, const AttnParams& p, const int* table, int kvh,
-                                             int which, int key0, int key_lo, int key_hi) {
-    constexpr int CPR = HD / 8;                         // chunks per row
-    for (int i = threadIdx.x; i < kBN * CPR; i += kThreads) {
-        const int r = i / CPR, c = i % CPR;
-        const int j = key0 + r;
-        bool valid = j >= key_lo && j <= key_hi;
-        const __nv_bfloat16* src = p.cache;
-        if (valid) {
-            const int slot = j / p.page_size;
-            const int page = slot < p.table_width ? table[slot] : -1;
-            if (page < 0 || page >= p.num_pages) {
-                atomicExch(p.err, 4);
-                valid = false;
-            } else {
-                src = p.cache + ((((static_cast<int64_t>(page) * 2 + which) * p.KV + kvh) * p.page_size + j % p.page_size) * HD + c * 8);
-            }
+__device__ __forceinline__ void tma_issue_tile(__nv_bfloat16* stage, uint64_t* bar, const CUtensorMap* map,
+                                               const AttnParams& p, const int* table, int kvh, int key0,
+                                               int key_lo, int key_hi) {
+    constexpr int kTileElems = kBN * HD;
+    mbar_expect_tx(bar, 2u * kTileElems * sizeof(__nv_bfloat16));
+    for (int b0 = 0; b0 < kBN; b0 += p.box_rows) {
+        int key = min(max(key0 + b0, key_lo), key_hi);            // outside the range: the nearest key inside it
+        key -= key % p.box_rows;                                  // boxes start on multiples of their size
+        const int slot = key / p.page_size;
+        int page = slot < p.table_width ? table[slot] : -1;
+        if (page < 0 || page >= p.num_pages) { atomicExch(p.err, 4); page = 0; }
+        const int row_k = ((page * 2 + 0) * p.KV + kvh) * p.page_size + key % p.page_size;
+        const int row_v = row_k + p.KV * p.page_size;
+#pragma unroll
+        for (int half = 0; half < HD / 64; ++half) {
+            tma_load_2d(stage + half * 4096 + b0 * 64, map, bar, half * 64, row_k);
+            tma_load_2d(stage + kTileElems + half * 4096 + b0 * 64, map, bar, half * 64, row_v);
         }
-        cp_async16(tile + swz<HD>(r, c), src, valid);
     }
 }
 
-// One warp: S[16 x NK*8] = Q[16 x HD] * K^T over NK/2 groups of 16 keys starting at tile row `krow0`.
+// One warp: S[16 x NT*8] = Q[16 x HD] * K^T over NT/2 groups of 16 keys starting at tile row `krow0`.
 template <int HD, int NT>
 __device__ __forceinline__ void qk_product(float (&s)[NT][4], const uint32_t (&qf)[HD / 16][4],
                                            const __nv_bfloat16* sK, int krow0, int lane) {
@@ -106,7 +148,7 @@ __device__ __forceinline__ void qk_product(float (&s)[NT][4], const uint32_t (&q
             uint32_t b[4];
             const int r = krow0 + np * 16 + (lane & 7) + ((lane >> 4) << 3);
             const int c = ks * 2 + ((lane >> 3) & 1);
-            ldmatrix_x4(b, sK + swz<HD>(r, c));
+            ldmatrix_x4(b, sK + kv_off(r, c));
             mma_bf16(s[np * 2], qf[ks], b[0], b[1]);
             mma_bf16(s[np * 2 + 1], qf[ks], b[2], b[3]);
         }
@@ -129,16 +171,24 @@ __device__ __forceinline__ void pv_product(float (&o)[HD / 8][4], const float (&
             uint32_t b[4];
             const int r = krow0 + kk * 16 + (lane & 7) + (((lane >> 3) & 1) << 3);
             const int c = dp * 2 + (lane >> 4);
-            ldmatrix_x4_trans(b, sV + swz<HD>(r, c));
+            ldmatrix_x4_trans(b, sV + kv_off(r, c));
             mma_bf16(o[dp * 2], a, b[0], b[1]);
             mma_bf16(o[dp * 2 + 1], a, b[2], b[3]);
         }
     }
 }
 
-// Masks the score tile, updates the running max and sum of the warp's two rows per thread, rescales the output
-// accumulator and turns scores into probabilities.  Column n of the tile is key `key0 + n`.
-template <int HD, int NT>
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// Updates the running max and sum of the warp's two rows per thread, rescales the output accumulator and turns
+// raw scores into probabilities p = 2^(s * scale_log2 - m).  Column n of the tile is key `key0 + n`; with MASK,
+// keys outside [row_lo, row_hi] of their row are excluded (tiles that lie wholly inside every row's range skip
+// the comparisons).
+template <int HD, int NT, bool MASK>
 __device__ __forceinline__ void softmax_step(float (&s)[NT][4], float (&o)[HD / 8][4], float (&m)[2], float (&l)[2],
                                              int key0, const int (&row_lo)[2], const int (&row_hi)[2],
                                              float scale_log2, int lane) {
@@ -148,23 +198,21 @@ __device__ __forceinline__ void softmax_step(float (&s)[NT][4], float (&o)[HD / 
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
             const int half = e >> 1;
-            const int j = key0 + nt * 8 + ((lane & 3) << 1) + (e & 1);
-            const bool ok = j >= row_lo[half] && j <= row_hi[half];
-            s[nt][e] = ok ? s[nt][e] * scale_log2 : -INFINITY;
+            if (MASK) {
+                const int j = key0 + nt * 8 + ((lane & 3) << 1) + (e & 1);
+                if (j < row_lo[half] || j > row_hi[half]) s[nt][e] = -INFINITY;
+            }
             tile_max[half] = fmaxf(tile_max[half], s[nt][e]);
         }
     }
+    float corr[2], m_scaled[2];
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
         tile_max[half] = fmaxf(tile_max[half], __shfl_xor_sync(0xffffffffu, tile_max[half], 1));
         tile_max[half] = fmaxf(tile_max[half], __shfl_xor_sync(0xffffffffu, tile_max[half], 2));
-    }
-    float corr[2], m_use[2];
-#pragma unroll
-    for (int half = 0; half < 2; ++half) {
-        const float m_new = fmaxf(m[half], tile_max[half]);
-        m_use[half] = m_new == -INFINITY ? 0.f : m_new;
-        corr[half] = m[half] == -INFINITY ? 0.f : exp2f(m[half] - m_use[half]);
+        const float m_new = fmaxf(m[half], tile_max[half] * scale_log2);      // scale > 0 keeps the order
+        m_scaled[half] = m_new == -INFINITY ? 0.f : m_new;
+        corr[half] = fast_exp2(m[half] - m_scaled[half]);                    // 2^(-inf) = 0 at the first tile
         m[half] = m_new;
     }
     float tile_sum[2] = {0.f, 0.f};
@@ -173,7 +221,7 @@ __device__ __forceinline__ void softmax_step(float (&s)[NT][4], float (&o)[HD / 
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
             const int half = e >> 1;
-            const float pr = exp2f(s[nt][e] - m_use[half]);       // exp2(-inf) = 0 for excluded keys
+            const float pr = fast_exp2(fmaf(s[nt][e], scale_log2, -m_scaled[half]));   // excluded keys: 2^(-inf) = 0
             s[nt][e] = pr;
             tile_sum[half] += pr;
         }
@@ -187,15 +235,33 @@ __device__ __forceinline__ void softmax_step(float (&s)[NT][4], float (&o)[HD / 
     }
 }
 
+// Carves the dynamic shared memory: stages (1024-byte aligned for the swizzle), then the query tile, then barriers.
+template <int HD, int STAGES, int QROWS>
+struct SmemPlan {
+    static constexpr int kStageElems = 2 * kBN * HD;                      // K tile + V tile
+    static constexpr size_t kBytes = 1024 + static_cast<size_t>(STAGES) * kStageElems * 2 + static_cast<size_t>(QROWS) * HD * 2 + 8 * STAGES;
+    __nv_bfloat16* stages;
+    __nv_bfloat16* q;
+    uint64_t* bars;
+    __device__ explicit SmemPlan(unsigned char* raw) {
+        const uint32_t addr = smem_u32(raw);
+        unsigned char* base = raw + ((1024u - (addr & 1023u)) & 1023u);
+        stages = reinterpret_cast<__nv_bfloat16*>(base);
+        q = stages + STAGES * kStageElems;
+        bars = reinterpret_cast<uint64_t*>(q + QROWS * HD);
+    }
+};
+
 // ---- prefill ---------------------------------------------------------------------------------------------------
+
+constexpr int kPreStages = 2;
 
 template <int HD>
 __global__ void __launch_bounds__(kThreads)
-attn_prefill_bf16_kernel(const AttnParams p, const int skip_single) {
-    extern __shared__ __align__(128) unsigned char smem_raw[];
-    __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem_raw);       // [64][HD]
-    __nv_bfloat16* sK = sQ + 64 * HD;                                      // [2][64][HD]
-    __nv_bfloat16* sV = sK + 2 * kBN * HD;                                 // [2][64][HD]
+attn_prefill_bf16_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnParams p, const int skip_single) {
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    using Plan = SmemPlan<HD, kPreStages, 64>;
+    Plan sm(smem_raw);
     constexpr int CPR = HD / 8;
     const int g = p.H / p.KV;
     const int tok_per_tile = 64 / g;
@@ -221,67 +287,76 @@ attn_prefill_bf16_kernel(const AttnParams p, const int skip_single) {
     const int pos_last = p.positions[cu0 + q0 + n_tok - 1];
     const int key_lo = p.window > 0 ? max(0, pos_first - p.window + 1) : 0;
     const int key_hi = pos_last;
-    const int tile_begin = key_lo / kBN, tile_end = key_hi / kBN;
+    const int tile_begin = key_lo / kBN, n_tiles = key_hi / kBN - tile_begin + 1;
 
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < kPreStages; ++i) mbar_init(sm.bars + i, 1);
+        mbar_fence_init();
+    }
     // Q tile: row r = (token r / g, head kvh * g + r % g)
     for (int i = threadIdx.x; i < 64 * CPR; i += kThreads) {
         const int r = i / CPR, c = i % CPR;
         const int tok = r / g;
         const bool valid = tok < n_tok;
         const __nv_bfloat16* src = valid ? p.q + ((static_cast<int64_t>(cu0 + q0 + tok) * p.H + kvh * g + r % g) * HD + c * 8) : p.q;
-        cp_async16(sQ + swz<HD>(r, c), src, valid);
+        cp_async16(sm.q + swz<HD>(r, c), src, valid);
     }
-    load_kv_tile<HD>(sK, p, table, kvh, 0, tile_begin * kBN, key_lo, key_hi);
-    load_kv_tile<HD>(sV, p, table, kvh, 1, tile_begin * kBN, key_lo, key_hi);
     cp_async_commit();
+    __syncthreads();                                      // barriers are initialised
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < kPreStages - 1 && i < n_tiles; ++i)
+            tma_issue_tile<HD>(sm.stages + i * Plan::kStageElems, sm.bars + i, &kv_map, p, table, kvh, (tile_begin + i) * kBN, key_lo, key_hi);
+    }
 
-    // the two rows this thread owns in the warp's 16-row slab
+    // the two rows this thread owns in the warp's 16-row slab, and the warp's extremes
     int row_lo[2], row_hi[2];
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
         const int r = warp * 16 + (lane >> 2) + half * 8;
-        const int tok = r / g;
-        if (tok < n_tok) {
-            const int pos = p.positions[cu0 + q0 + tok];
-            row_hi[half] = pos;
-            row_lo[half] = p.window > 0 ? max(0, pos - p.window + 1) : 0;
-        } else {
-            row_hi[half] = -1;                          // no key passes lo <= j <= hi
-            row_lo[half] = 0;
-        }
+        const int tok = min(r / g, n_tok - 1);            // rows past the tile's tokens repeat the last one; never stored
+        const int pos = p.positions[cu0 + q0 + tok];
+        row_hi[half] = pos;
+        row_lo[half] = p.window > 0 ? max(0, pos - p.window + 1) : 0;
     }
+    const bool warp_has_rows = warp * 16 < n_tok * g;
+    const int warp_first_pos = p.positions[cu0 + q0 + min(n_tok - 1, (warp * 16) / g)];
+    const int warp_last_pos = p.positions[cu0 + q0 + min(n_tok - 1, (warp * 16 + 15) / g)];
+    const int warp_max_lo = p.window > 0 ? max(0, warp_last_pos - p.window + 1) : 0;
 
     uint32_t qf[HD / 16][4];
     float o[HD / 8][4];
 #pragma unroll
     for (int dt = 0; dt < HD / 8; ++dt) { o[dt][0] = o[dt][1] = o[dt][2] = o[dt][3] = 0.f; }
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
-
-    for (int kt = tile_begin; kt <= tile_end; ++kt) {
-        const int buf = (kt - tile_begin) & 1;
-        if (kt + 1 <= tile_end) {
-            load_kv_tile<HD>(sK + (buf ^ 1) * kBN * HD, p, table, kvh, 0, (kt + 1) * kBN, key_lo, key_hi);
-            load_kv_tile<HD>(sV + (buf ^ 1) * kBN * HD, p, table, kvh, 1, (kt + 1) * kBN, key_lo, key_hi);
-        }
-        cp_async_commit();
-        cp_async_wait<1>();
-        __syncthreads();
-        if (kt == tile_begin) {
-#pragma unroll
-            for (int ks = 0; ks < HD / 16; ++ks)
-                ldmatrix_x4(qf[ks], sQ + swz<HD>(warp * 16 + (lane & 15), ks * 2 + (lane >> 4)));
-        }
-        // a warp whose rows all end before this tile has nothing to add (causal)
-        const int warp_hi = p.positions[cu0 + q0 + min(n_tok - 1, (warp * 16 + 15) / g)];
-        if (kt * kBN <= warp_hi && warp * 16 < n_tok * g) {
-            float s[8][4];
-            qk_product<HD, 8>(s, qf, sK + buf * kBN * HD, 0, lane);
-            softmax_step<HD, 8>(s, o, m, l, kt * kBN, row_lo, row_hi, p.scale_log2, lane);
-            pv_product<HD, 8>(o, s, sV + buf * kBN * HD, 0, lane);
-        }
-        __syncthreads();
-    }
     cp_async_wait<0>();
+    __syncthreads();
+#pragma unroll
+    for (int ks = 0; ks < HD / 16; ++ks)
+        ldmatrix_x4(qf[ks], sm.q + swz<HD>(warp * 16 + (lane & 15), ks * 2 + (lane >> 4)));
+
+    for (int it = 0; it < n_tiles; ++it) {
+        const int st = it % kPreStages;
+        if (threadIdx.x == 0 && it + kPreStages - 1 < n_tiles) {
+            const int nx = it + kPreStages - 1;
+            tma_issue_tile<HD>(sm.stages + (nx % kPreStages) * Plan::kStageElems, sm.bars + nx % kPreStages, &kv_map, p, table,
+                               kvh, (tile_begin + nx) * kBN, key_lo, key_hi);
+        }
+        mbar_wait(sm.bars + st, (it / kPreStages) & 1, p.err);
+        const int key0 = (tile_begin + it) * kBN;
+        // a warp whose rows all end before this tile has nothing to add (causal)
+        if (warp_has_rows && key0 <= warp_last_pos) {
+            const __nv_bfloat16* sK = sm.stages + st * Plan::kStageElems;
+            const __nv_bfloat16* sV = sK + kBN * HD;
+            float s[8][4];
+            qk_product<HD, 8>(s, qf, sK, 0, lane);
+            if (key0 + kBN - 1 <= warp_first_pos && key0 >= warp_max_lo)
+                softmax_step<HD, 8, false>(s, o, m, l, key0, row_lo, row_hi, p.scale_log2, lane);
+            else
+                softmax_step<HD, 8, true>(s, o, m, l, key0, row_lo, row_hi, p.scale_log2, lane);
+            pv_product<HD, 8>(o, s, sV, 0, lane);
+        }
+        __syncthreads();                                  // the stage may be refilled
+    }
 
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
@@ -309,11 +384,10 @@ constexpr int kDecStages = 3;
 
 template <int HD>
 __global__ void __launch_bounds__(kThreads)
-attn_decode_bf16_kernel(const AttnParams p) {
-    extern __shared__ __align__(128) unsigned char smem_raw[];
-    __nv_bfloat16* sQ = reinterpret_cast<__nv_bfloat16*>(smem_raw);       // [16][HD]
-    __nv_bfloat16* sK = sQ + 16 * HD;                                      // [stages][64][HD]
-    __nv_bfloat16* sV = sK + kDecStages * kBN * HD;                        // [stages][64][HD]
+attn_decode_bf16_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnParams p) {
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    using Plan = SmemPlan<HD, kDecStages, 16>;
+    Plan sm(smem_raw);
     constexpr int CPR = HD / 8;
     const int g = p.H / p.KV;
     const int seq = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
@@ -324,59 +398,63 @@ attn_decode_bf16_kernel(const AttnParams p) {
     const int key_lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
     const int key_hi = pos;
     const int* table = p.block_tables + static_cast<int64_t>(seq) * p.table_width;
-    const int first_tile = key_lo / kBN, n_tiles = key_hi / kBN - first_tile + 1;
-    const int per_split = (n_tiles + p.splits - 1) / p.splits;
+    const int first_tile = key_lo / kBN, all_tiles = key_hi / kBN - first_tile + 1;
+    const int per_split = (all_tiles + p.splits - 1) / p.splits;
     const int tile_begin = first_tile + split * per_split;
-    const int tile_end = min(first_tile + n_tiles, tile_begin + per_split) - 1;      // inclusive; may be < begin
+    const int n_tiles = max(0, min(first_tile + all_tiles, tile_begin + per_split) - tile_begin);
 
     float o[HD / 8][4];
 #pragma unroll
     for (int dt = 0; dt < HD / 8; ++dt) { o[dt][0] = o[dt][1] = o[dt][2] = o[dt][3] = 0.f; }
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
 
-    if (tile_begin <= tile_end) {
+    if (n_tiles > 0) {
+        if (threadIdx.x == 0) {
+            for (int i = 0; i < kDecStages; ++i) mbar_init(sm.bars + i, 1);
+            mbar_fence_init();
+        }
         for (int i = threadIdx.x; i < 16 * CPR; i += kThreads) {
             const int r = i / CPR, c = i % CPR;
             const bool valid = r < g;
             const __nv_bfloat16* src = valid ? p.q + ((static_cast<int64_t>(cu0) * p.H + kvh * g + r) * HD + c * 8) : p.q;
-            cp_async16(sQ + swz<HD>(r, c), src, valid);
+            cp_async16(sm.q + swz<HD>(r, c), src, valid);
         }
-#pragma unroll
-        for (int st = 0; st < kDecStages - 1; ++st) {
-            if (tile_begin + st <= tile_end) {
-                load_kv_tile<HD>(sK + st * kBN * HD, p, table, kvh, 0, (tile_begin + st) * kBN, key_lo, key_hi);
-                load_kv_tile<HD>(sV + st * kBN * HD, p, table, kvh, 1, (tile_begin + st) * kBN, key_lo, key_hi);
-            }
-            cp_async_commit();
+        cp_async_commit();
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            for (int i = 0; i < kDecStages - 1 && i < n_tiles; ++i)
+                tma_issue_tile<HD>(sm.stages + i * Plan::kStageElems, sm.bars + i, &kv_map, p, table, kvh, (tile_begin + i) * kBN, key_lo, key_hi);
         }
         const int row_lo[2] = {key_lo, key_lo};
-        const int row_hi2[2] = {(lane >> 2) < g ? key_hi : -1, ((lane >> 2) + 8) < g ? key_hi : -1};   // rows >= g carry no head
+        const int row_hi[2] = {key_hi, key_hi};             // rows >= g hold zero queries and are never stored
         uint32_t qf[HD / 16][4];
-        for (int kt = tile_begin; kt <= tile_end; ++kt) {
-            const int it = kt - tile_begin;
-            const int buf = it % kDecStages;
-            const int nxt = kt + kDecStages - 1;
-            if (nxt <= tile_end) {
-                const int nb = (it + kDecStages - 1) % kDecStages;
-                load_kv_tile<HD>(sK + nb * kBN * HD, p, table, kvh, 0, nxt * kBN, key_lo, key_hi);
-                load_kv_tile<HD>(sV + nb * kBN * HD, p, table, kvh, 1, nxt * kBN, key_lo, key_hi);
-            }
-            cp_async_commit();
-            cp_async_wait<kDecStages - 1>();
-            __syncthreads();
-            if (it == 0) {
+        cp_async_wait<0>();
+        __syncthreads();
 #pragma unroll
-                for (int ks = 0; ks < HD / 16; ++ks)
-                    ldmatrix_x4(qf[ks], sQ + swz<HD>(lane & 15, ks * 2 + (lane >> 4)));
+        for (int ks = 0; ks < HD / 16; ++ks)
+            ldmatrix_x4(qf[ks], sm.q + swz<HD>(lane & 15, ks * 2 + (lane >> 4)));
+        for (int it = 0; it < n_tiles; ++it) {
+            const int st = it % kDecStages;
+            if (threadIdx.x == 0 && it + kDecStages - 1 < n_tiles) {
+                const int nx = it + kDecStages - 1;
+                tma_issue_tile<HD>(sm.stages + (nx % kDecStages) * Plan::kStageElems, sm.bars + nx % kDecStages, &kv_map, p,
+                                   table, kvh, (tile_begin + nx) * kBN, key_lo, key_hi);
             }
-            // each warp takes 16 of the tile's 64 keys
-            float s[2][4];
-            qk_product<HD, 2>(s, qf, sK + buf * kBN * HD, warp * 16, lane);
-            softmax_step<HD, 2>(s, o, m, l, kt * kBN + warp * 16, row_lo, row_hi2, p.scale_log2, lane);
-            pv_product<HD, 2>(o, s, sV + buf * kBN * HD, warp * 16, lane);
+            mbar_wait(sm.bars + st, (it / kDecStages) & 1, p.err);
+            const __nv_bfloat16* sK = sm.stages + st * Plan::kStageElems;
+            const __nv_bfloat16* sV = sK + kBN * HD;
+            const int key0 = (tile_begin + it) * kBN + warp * 16;          // each warp takes 16 of the tile's 64 keys
+            if (key0 <= key_hi && key0 + 15 >= key_lo) {
+                float s[2][4];
+                qk_product<HD, 2>(s, qf, sK, warp * 16, lane);
+                if (key0 >= key_lo && key0 + 15 <= key_hi)
+                    softmax_step<HD, 2, false>(s, o, m, l, key0, row_lo, row_hi, p.scale_log2, lane);
+                else
+                    softmax_step<HD, 2, true>(s, o, m, l, key0, row_lo, row_hi, p.scale_log2, lane);
+                pv_product<HD, 2>(o, s, sV, warp * 16, lane);
+            }
             __syncthreads();
         }
-        cp_async_wait<0>();
     }
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
@@ -385,7 +463,7 @@ attn_decode_bf16_kernel(const AttnParams p) {
     }
     // combine the four warps through shared memory (the tiles are no longer needed)
     __syncthreads();
-    float* red_o = reinterpret_cast<float*>(smem_raw);                     // [4][16][HD]
+    float* red_o = reinterpret_cast<float*>(sm.stages);                    // [4][16][HD]
     float* red_ml = red_o + 4 * 16 * HD;                                   // [4][16][2]
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
@@ -446,11 +524,58 @@ __global__ void attn_decode_merge_kernel(const AttnParams p) {
     }
 }
 
-template <int HD> constexpr size_t prefill_smem() { return static_cast<size_t>(64 + 4 * kBN) * HD * sizeof(__nv_bfloat16); }
+// ---- host side --------------------------------------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+            qres == cudaDriverEntryPointSuccess)
+            fn = reinterpret_cast<EncodeTiledFn>(ptr);
+    });
+    return fn;
+}
+
+// A tensor map of one cache unit seen as [rows = pages * 2 * KV * page_size][head_dim] bf16, fetched in boxes of
+// [box_rows][64 columns] with the 128-byte swizzle.  Maps are kept per (address, shape).
+static int kv_tensor_map(CUtensorMap* out, const void* cache, int64_t rows, int hd, int box_rows) {
+    struct Key { const void* p; int64_t rows; int hd, box; bool operator==(const Key& o) const { return p == o.p && rows == o.rows && hd == o.hd && box == o.box; } };
+    struct Hash { size_t operator()(const Key& k) const { return std::hash<const void*>()(k.p) ^ (std::hash<int64_t>()(k.rows) * 31) ^ (k.hd * 131) ^ (k.box * 7); } };
+    static std::unordered_map<Key, CUtensorMap, Hash> maps;
+    static std::mutex mu;
+    std::lock_guard<std::mutex> lock(mu);
+    const Key key{cache, rows, hd, box_rows};
+    auto it = maps.find(key);
+    if (it == maps.end()) {
+        EncodeTiledFn fn = encode_tiled_fn();
+        if (fn == nullptr) return CVB_E_UNSUPPORTED;
+        if ((reinterpret_cast<uintptr_t>(cache) & 15) != 0) return CVB_E_ALIGN;
+        CUtensorMap m;
+        const cuuint64_t dims[2] = {static_cast<cuuint64_t>(hd), static_cast<cuuint64_t>(rows)};
+        const cuuint64_t strides[1] = {static_cast<cuuint64_t>(hd) * sizeof(__nv_bfloat16)};
+        const cuuint32_t box[2] = {64u, static_cast<cuuint32_t>(box_rows)};
+        const cuuint32_t estr[2] = {1u, 1u};
+        const CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(cache), dims, strides, box, estr,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+        if (r != CUDA_SUCCESS) return CVB_E_SHAPE;
+        it = maps.emplace(key, m).first;
+    }
+    *out = it->second;
+    return CVB_OK;
+}
+
+template <int HD> constexpr size_t prefill_smem() { return SmemPlan<HD, kPreStages, 64>::kBytes; }
 template <int HD> constexpr size_t decode_smem() {
-    const size_t tiles = static_cast<size_t>(16 + 2 * kDecStages * kBN) * HD * sizeof(__nv_bfloat16);
-    const size_t red = static_cast<size_t>(4 * 16) * (HD + 2) * sizeof(float);
-    return tiles > red ? tiles : red;
+    const size_t red = 1024 + static_cast<size_t>(4 * 16) * (HD + 2) * sizeof(float);
+    return SmemPlan<HD, kDecStages, 16>::kBytes > red ? SmemPlan<HD, kDecStages, 16>::kBytes : red;
 }
 
 static int check_common(int S, int H, int KV, int hd, int page_size, int table_width, int num_pages) {
@@ -459,6 +584,9 @@ static int check_common(int S, int H, int KV, int hd, int page_size, int table_w
     if (hd != 64 && hd != 128) return CVB_E_UNSUPPORTED;
     if (H / KV > 16) return CVB_E_UNSUPPORTED;
     if (KV > 65535) return CVB_E_SIZE;
+    // a TMA box is a whole page, or 64 rows of a larger page: pages of 16, 32, 64, 128, ... tokens
+    if (page_size < 16 || (page_size & (page_size - 1)) != 0) return CVB_E_UNSUPPORTED;
+    if (static_cast<int64_t>(num_pages) * 2 * KV * page_size > 2147483647LL) return CVB_E_SIZE;
     return CVB_OK;
 }
 
@@ -472,28 +600,39 @@ extern "C" int64_t cvb_attn_decode_scratch_floats(int S, int KV, int hd, int spl
     return static_cast<int64_t>(S) * KV * splits * 16 * (hd + 2);
 }
 
+static int fill_params(AttnParams& p, CUtensorMap& map, void* out, const void* q, const void* cache, const int* block_tables,
+                       int table_width, const int* cu_seqlens, const int* positions, int S, int H, int KV, int hd,
+                       int page_size, int window, float scale, int num_pages, int* err_flag) {
+    const int rc = check_common(S, H, KV, hd, page_size, table_width, num_pages);
+    if (rc != CVB_OK) return rc;
+    p.out = (__nv_bfloat16*)out; p.q = (const __nv_bfloat16*)q;
+    p.block_tables = block_tables; p.cu_seqlens = cu_seqlens; p.positions = positions;
+    p.table_width = table_width; p.S = S; p.H = H; p.KV = KV; p.page_size = page_size; p.window = window;
+    p.num_pages = num_pages; p.scale_log2 = scale * kLog2e; p.err = err_flag;
+    p.box_rows = page_size < kBN ? page_size : kBN;
+    return kv_tensor_map(&map, cache, static_cast<int64_t>(num_pages) * 2 * KV * page_size, hd, p.box_rows);
+}
+
 extern "C" int cvb_attn_prefill_bf16(void* out, const void* q, const void* cache, const int* block_tables,
                                      int table_width, const int* cu_seqlens, const int* positions, int S,
                                      int num_tiles, int H, int KV, int hd, int page_size, int window, float scale,
                                      int num_pages, int skip_single, int* err_flag, cudaStream_t stream) {
     if (num_tiles == 0) return CVB_OK;
-    const int rc = check_common(S, H, KV, hd, page_size, table_width, num_pages);
-    if (rc != CVB_OK) return rc;
     if (num_tiles < 0) return CVB_E_SIZE;
     AttnParams p{};
-    p.out = (__nv_bfloat16*)out; p.q = (const __nv_bfloat16*)q; p.cache = (const __nv_bfloat16*)cache;
-    p.block_tables = block_tables; p.cu_seqlens = cu_seqlens; p.positions = positions;
-    p.table_width = table_width; p.S = S; p.H = H; p.KV = KV; p.page_size = page_size; p.window = window;
-    p.num_pages = num_pages; p.scale_log2 = scale * kLog2e; p.err = err_flag;
+    CUtensorMap map;
+    const int rc = fill_params(p, map, out, q, cache, block_tables, table_width, cu_seqlens, positions, S, H, KV, hd,
+                               page_size, window, scale, num_pages, err_flag);
+    if (rc != CVB_OK) return rc;
     dim3 grid(static_cast<unsigned>(num_tiles), static_cast<unsigned>(KV));
     if (hd == 128) {
         static bool set = false;
         if (!set) { cudaFuncSetAttribute(attn_prefill_bf16_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)prefill_smem<128>()); set = true; }
-        attn_prefill_bf16_kernel<128><<<grid, kThreads, prefill_smem<128>(), stream>>>(p, skip_single);
+        attn_prefill_bf16_kernel<128><<<grid, kThreads, prefill_smem<128>(), stream>>>(map, p, skip_single);
     } else {
         static bool set = false;
         if (!set) { cudaFuncSetAttribute(attn_prefill_bf16_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)prefill_smem<64>()); set = true; }
-        attn_prefill_bf16_kernel<64><<<grid, kThreads, prefill_smem<64>(), stream>>>(p, skip_single);
+        attn_prefill_bf16_kernel<64><<<grid, kThreads, prefill_smem<64>(), stream>>>(map, p, skip_single);
     }
     return launch_status();
 }
@@ -503,16 +642,15 @@ extern "C" int cvb_attn_decode_bf16(void* out, const void* q, const void* cache,
                                     int KV, int hd, int page_size, int window, float scale, int num_pages,
                                     int splits, float* scratch, int64_t scratch_floats, int* err_flag,
                                     cudaStream_t stream) {
-    const int rc = check_common(S, H, KV, hd, page_size, table_width, num_pages);
-    if (rc != CVB_OK) return rc;
     if (splits < 1 || splits > 65535) return CVB_E_SIZE;
+    AttnParams p{};
+    CUtensorMap map;
+    const int rc = fill_params(p, map, out, q, cache, block_tables, table_width, cu_seqlens, positions, S, H, KV, hd,
+                               page_size, window, scale, num_pages, err_flag);
+    if (rc != CVB_OK) return rc;
     if (splits > 1 && (scratch == nullptr || scratch_floats < cvb_attn_decode_scratch_floats(S, KV, hd, splits)))
         return CVB_E_SCRATCH;
-    AttnParams p{};
-    p.out = (__nv_bfloat16*)out; p.q = (const __nv_bfloat16*)q; p.cache = (const __nv_bfloat16*)cache;
-    p.block_tables = block_tables; p.cu_seqlens = cu_seqlens; p.positions = positions;
-    p.table_width = table_width; p.S = S; p.H = H; p.KV = KV; p.page_size = page_size; p.window = window;
-    p.num_pages = num_pages; p.scale_log2 = scale * kLog2e; p.err = err_flag; p.splits = splits;
+    p.splits = splits;
     p.part_o = scratch;
     p.part_ml = scratch ? scratch + static_cast<int64_t>(S) * KV * splits * 16 * hd : nullptr;
     dim3 grid(static_cast<unsigned>(S), static_cast<unsigned>(KV), static_cast<unsigned>(splits));
@@ -520,12 +658,12 @@ extern "C" int cvb_attn_decode_bf16(void* out, const void* q, const void* cache,
     if (hd == 128) {
         static bool set = false;
         if (!set) { cudaFuncSetAttribute(attn_decode_bf16_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem<128>()); set = true; }
-        attn_decode_bf16_kernel<128><<<grid, kThreads, decode_smem<128>(), stream>>>(p);
+        attn_decode_bf16_kernel<128><<<grid, kThreads, decode_smem<128>(), stream>>>(map, p);
         if (splits > 1) attn_decode_merge_kernel<128><<<mgrid, 128, 0, stream>>>(p);
     } else {
         static bool set = false;
         if (!set) { cudaFuncSetAttribute(attn_decode_bf16_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem<64>()); set = true; }
-        attn_decode_bf16_kernel<64><<<grid, kThreads, decode_smem<64>(), stream>>>(p);
+        attn_decode_bf16_kernel<64><<<grid, kThreads, decode_smem<64>(), stream>>>(map, p);
         if (splits > 1) attn_decode_merge_kernel<64><<<mgrid, 64, 0, stream>>>(p);
     }
     return launch_status();

@@ -1,0 +1,128 @@
+"""Micro-benchmarks of single kernels on synthetic inputs: device time with CUDA events and the achieved fraction
+of the kernel's own roofline (bytes it must read / time, or flops / time).
+
+    python -m cppvllm_b200.kernel_bench attn_decode  --batch 8 --context 4096
+    python -m cppvllm_b200.kernel_bench attn_prefill --tokens 2048
+    python -m cppvllm_b200.kernel_bench gemv --batch 8 --rows 4096 --cols 1024
+
+Inputs are larger than the 126 MB L2 where the shape allows, or the buffers are rotated between iterations so
+that no iteration finds its operands in L2.  This is also the small case that profiler captures run on.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import sys
+
+import torch
+
+
+def _time(fn, iters: int, warmup: int = 3) -> float:
+    for _ in range(warmup):
+        fn(0)
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(iters):
+        fn(i)
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) / iters * 1e3          # microseconds
+
+
+def _paged_inputs(batch, context, q_len, H, KV, hd, page, copies, seed=0):
+    d = torch.device("cuda:0")
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    pages_per_seq = (context + page - 1) // page
+    n_pages = batch * pages_per_seq
+    caches = [torch.randn(n_pages + 1, 2, KV, page, hd, generator=g, device=d, dtype=torch.float32).to(torch.bfloat16)
+              for _ in range(copies)]
+    perm = torch.randperm(n_pages, generator=g, device=d).to(torch.int32)
+    tables = perm.view(batch, pages_per_seq).contiguous()
+    T = batch * q_len
+    q = torch.randn(T, H * hd, generator=g, device=d, dtype=torch.float32).to(torch.bfloat16)
+    cu = torch.arange(0, T + 1, q_len, dtype=torch.int32, device=d)
+    pos = (torch.arange(T, device=d, dtype=torch.int32) % q_len) + (context - q_len)
+    return caches, tables, q, cu, pos.contiguous()
+
+
+def attn_decode(a) -> dict:
+    from .csrc import ops
+    H, KV, hd, page = a.heads, a.kv_heads, a.head_dim, a.page_size
+    kv_bytes = a.batch * a.context * 2 * KV * hd * 2
+    copies = max(1, min(8, int(300e6 // kv_bytes) + 1))
+    caches, tables, q, cu, pos = _paged_inputs(a.batch, a.context, 1, H, KV, hd, page, copies)
+    out = torch.empty_like(q)
+    splits = a.splits or max(1, min(32, 296 // (a.batch * KV), (a.context + 63) // 64))
+    n = ops.attn_decode_scratch_floats(a.batch, KV, hd, splits)
+    scratch = torch.empty(max(1, n), dtype=torch.float32, device=q.device)
+    scale = 1 / math.sqrt(hd)
+
+    def run(i):
+        ops.attn_decode_bf16(out, q, caches[i % copies], tables, cu, pos, a.batch, H, KV, hd, page, scale, splits,
+                             scratch if splits > 1 else None)
+    us = _time(run, a.iters)
+    ops.check_device_errors(q.device)
+    return {"kernel": "attn_decode_bf16", "batch": a.batch, "context": a.context, "splits": splits, "us": round(us, 2),
+            "GBps": round(kv_bytes / us / 1e3, 1), "bytes": kv_bytes}
+
+
+def attn_prefill(a) -> dict:
+    from .csrc import ops
+    H, KV, hd, page = a.heads, a.kv_heads, a.head_dim, a.page_size
+    caches, tables, q, cu, pos = _paged_inputs(a.batch, a.tokens + a.cached, a.tokens, H, KV, hd, page, 1)
+    out = torch.empty_like(q)
+    tiles = ops.prefill_tiles([a.tokens] * a.batch, H, KV)
+    scale = 1 / math.sqrt(hd)
+
+    def run(i):
+        ops.attn_prefill_bf16(out, q, caches[0], tables, cu, pos, a.batch, tiles, H, KV, hd, page, scale)
+    us = _time(run, a.iters)
+    ops.check_device_errors(q.device)
+    flops = a.batch * 4 * H * hd * (a.tokens * (a.tokens + 1) // 2 + a.tokens * a.cached)
+    return {"kernel": "attn_prefill_bf16", "batch": a.batch, "tokens": a.tokens, "cached": a.cached, "us": round(us, 2),
+            "TFLOPs": round(flops / us / 1e6, 1), "flops": flops}
+
+
+def gemv(a) -> dict:
+    from .csrc import ops
+    d = torch.device("cuda:0")
+    copies = max(1, min(64, int(300e6 // (a.rows * a.cols * 2)) + 1))
+    ws = [torch.randn(a.rows, a.cols, device=d).to(torch.bfloat16) for _ in range(copies)]
+    x = torch.randn(a.batch, a.cols, device=d).to(torch.bfloat16)
+    out = torch.empty(a.batch, a.rows, device=d, dtype=torch.bfloat16)
+
+    def run(i):
+        ops.linear(x, ws[i % copies], out=out)
+    us = _time(run, a.iters)
+    nbytes = a.rows * a.cols * 2
+    return {"kernel": "linear (library)", "batch": a.batch, "rows": a.rows, "cols": a.cols, "us": round(us, 2),
+            "GBps": round(nbytes / us / 1e3, 1)}
+
+
+def main(argv=None) -> int:
+    p = argparse.ArgumentParser(prog="kernel_bench")
+    p.add_argument("kernel", choices=["attn_decode", "attn_prefill", "gemv"])
+    p.add_argument("--batch", type=int, default=8)
+    p.add_argument("--context", type=int, default=4096)
+    p.add_argument("--tokens", type=int, default=2048)
+    p.add_argument("--cached", type=int, default=0)
+    p.add_argument("--heads", type=int, default=16)
+    p.add_argument("--kv-heads", type=int, default=8)
+    p.add_argument("--head-dim", type=int, default=128)
+    p.add_argument("--page-size", type=int, default=16)
+    p.add_argument("--splits", type=int, default=0)
+    p.add_argument("--rows", type=int, default=4096)
+    p.add_argument("--cols", type=int, default=1024)
+    p.add_argument("--iters", type=int, default=20)
+    a = p.parse_args(argv)
+    if a.kernel == "attn_prefill" and a.batch == 8 and "--batch" not in (argv or sys.argv):
+        a.batch = 1
+    res = {"attn_decode": attn_decode, "attn_prefill": attn_prefill, "gemv": gemv}[a.kernel](a)
+    print(json.dumps(res))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
