@@ -21,6 +21,7 @@
 // comes by cp.async.  The matrix products are mma.sync.m16n8k16 (bf16 in, float accumulate); ldmatrix reads the
 // swizzled tiles without bank conflicts.
 #include "common.cuh"
+#include "attention_bf16.h"
 
 #include <cuda.h>
 #include <mutex>
@@ -663,6 +664,108 @@ extern "C" int cvb_attn_decode_bf16(void* out, const void* q, const void* cache,
     } else {
         static bool set = false;
         if (!set) { cudaFuncSetAttribute(attn_decode_bf16_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem<64>()); set = true; }
+        attn_decode_bf16_kernel<64><<<grid, kThreads, decode_smem<64>(), stream>>>(map, p);
+        if (splits > 1) attn_decode_merge_kernel<64><<<mgrid, 64, 0, stream>>>(p);
+    }
+    return launch_status();
+}
+
+// ---- split-KV decode attention without any allocation ---------------------------------------------------------------
+//
+// cvb_attn_decode_bf16_static is cvb_attn_decode_bf16 for callers that must not allocate device memory while they
+// run: code inside a real-time or safety-reviewed loop that may not call cudaMalloc, a plug-in that lives under
+// another program's memory budget, a host that has handed the whole device to a pool it cannot ask.  The caller
+// still passes queries, pages, tables and the output; only the scratch for the partial results of the splits, which
+// the other entry point takes as an argument, lives here in a file-scope device array of kStaticScratchFloats
+// floats (8 MiB).  Every GPU that loads this library holds that array until the process exits.
+//
+// The array's name is a host-side stand-in in host code, not a device address; the kernels need the address.  It is
+// looked up with cudaGetSymbolAddress once per device, with that device current, at the first call on that device.
+// That first call also sets kernel attributes, so make it before any stream capture starts.
+//
+// A launch whose partial results do not fit (requests * kv heads * splits * 16 * (head_dim + 2) floats) is refused
+// with CVB_E_SCRATCH; nothing is launched.  No cudaMalloc, cudaFree or allocating library routine is called, and
+// the tensor map is built on the stack at every call.  All calls share the one array and it keeps the last
+// call's contents.  Nothing in it has to start at zero: every block writes the partial results that the merge kernel
+// of the same call reads.  Calls that overlap on the GPU (two streams, or two host threads on different streams)
+// race on it; keep calls that use this entry point on one stream, or order them with events.
+namespace cvb {
+
+constexpr int64_t kStaticScratchFloats = int64_t{1} << 21;
+static __device__ __align__(256) float g_static_decode_scratch[kStaticScratchFloats];
+
+constexpr int kMaxDevices = 64;
+static float* g_static_scratch_ptr[kMaxDevices] = {};
+static std::mutex g_static_scratch_mu;
+
+// Device address of the scratch array on the current device; looked up once per device.
+static int static_scratch_for_current_device(float** out) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return static_cast<int>(e);
+    if (dev < 0 || dev >= kMaxDevices) return CVB_E_SIZE;
+    std::lock_guard<std::mutex> lock(g_static_scratch_mu);
+    if (g_static_scratch_ptr[dev] == nullptr) {
+        float* ptr = nullptr;
+        e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_static_decode_scratch);
+        if (e != cudaSuccess) return static_cast<int>(e);
+        if (ptr == nullptr) return CVB_E_SCRATCH;
+        e = cudaFuncSetAttribute(attn_decode_bf16_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem<128>());
+        if (e != cudaSuccess) return static_cast<int>(e);
+        e = cudaFuncSetAttribute(attn_decode_bf16_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem<64>());
+        if (e != cudaSuccess) return static_cast<int>(e);
+        g_static_scratch_ptr[dev] = ptr;
+    }
+    *out = g_static_scratch_ptr[dev];
+    return CVB_OK;
+}
+
+}  // namespace cvb
+
+extern "C" int64_t cvb_attn_decode_static_scratch_floats() { return cvb::kStaticScratchFloats; }
+
+extern "C" int cvb_attn_decode_bf16_static(void* out, const void* q, const void* cache, const int* block_tables,
+                                           int table_width, const int* cu_seqlens, const int* positions, int S, int H,
+                                           int KV, int hd, int page_size, int window, float scale, int num_pages,
+                                           int splits, int* err_flag, cudaStream_t stream) {
+    if (splits < 1 || splits > 65535) return CVB_E_SIZE;
+    int rc = check_common(S, H, KV, hd, page_size, table_width, num_pages);
+    if (rc != CVB_OK) return rc;
+    if (cvb_attn_decode_scratch_floats(S, KV, hd, splits) > kStaticScratchFloats) return CVB_E_SCRATCH;
+    float* scratch = nullptr;
+    rc = static_scratch_for_current_device(&scratch);
+    if (rc != CVB_OK) return rc;
+
+    AttnParams p{};
+    p.out = (__nv_bfloat16*)out; p.q = (const __nv_bfloat16*)q;
+    p.block_tables = block_tables; p.cu_seqlens = cu_seqlens; p.positions = positions;
+    p.table_width = table_width; p.S = S; p.H = H; p.KV = KV; p.page_size = page_size; p.window = window;
+    p.num_pages = num_pages; p.scale_log2 = scale * kLog2e; p.err = err_flag;
+    p.box_rows = page_size < kBN ? page_size : kBN;
+    p.splits = splits;
+    p.part_o = scratch;
+    p.part_ml = scratch + static_cast<int64_t>(S) * KV * splits * 16 * hd;
+
+    // the tensor map is encoded into a local variable: no table, no heap
+    EncodeTiledFn fn = encode_tiled_fn();
+    if (fn == nullptr) return CVB_E_UNSUPPORTED;
+    if ((reinterpret_cast<uintptr_t>(cache) & 15) != 0) return CVB_E_ALIGN;
+    CUtensorMap map;
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(hd), static_cast<cuuint64_t>(num_pages) * 2 * KV * page_size};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(hd) * sizeof(__nv_bfloat16)};
+    const cuuint32_t box[2] = {64u, static_cast<cuuint32_t>(p.box_rows)};
+    const cuuint32_t estr[2] = {1u, 1u};
+    if (fn(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(cache), dims, strides, box, estr,
+           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return CVB_E_SHAPE;
+
+    dim3 grid(static_cast<unsigned>(S), static_cast<unsigned>(KV), static_cast<unsigned>(splits));
+    dim3 mgrid(static_cast<unsigned>(S), static_cast<unsigned>(H));
+    if (hd == 128) {
+        attn_decode_bf16_kernel<128><<<grid, kThreads, decode_smem<128>(), stream>>>(map, p);
+        if (splits > 1) attn_decode_merge_kernel<128><<<mgrid, 128, 0, stream>>>(p);
+    } else {
         attn_decode_bf16_kernel<64><<<grid, kThreads, decode_smem<64>(), stream>>>(map, p);
         if (splits > 1) attn_decode_merge_kernel<64><<<mgrid, 64, 0, stream>>>(p);
     }

@@ -1,0 +1,40 @@
+// C interface of the bf16 tensor-core attention library (attention_bf16.cu, built as libcvb_attn_bf16.so).
+// All functions return 0, a negative CVB_E_* refusal (common.cuh) or a positive cudaError_t.
+#pragma once
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+// Flash attention over the paged cache for requests that bring more than one token in this step.
+int cvb_attn_prefill_bf16(void* out, const void* q, const void* cache, const int* block_tables, int table_width,
+                          const int* cu_seqlens, const int* positions, int S, int num_tiles, int H, int KV, int hd,
+                          int page_size, int window, float scale, int num_pages, int skip_single, int* err_flag,
+                          cudaStream_t stream);
+
+// Floats of scratch that cvb_attn_decode_bf16 needs for S requests, KV heads and `splits` chunks (0 for one chunk).
+int64_t cvb_attn_decode_scratch_floats(int S, int KV, int hd, int splits);
+
+// Split-KV attention for requests that bring one token; `scratch` holds the partial results of the chunks.
+int cvb_attn_decode_bf16(void* out, const void* q, const void* cache, const int* block_tables, int table_width,
+                         const int* cu_seqlens, const int* positions, int S, int H, int KV, int hd, int page_size,
+                         int window, float scale, int num_pages, int splits, float* scratch, int64_t scratch_floats,
+                         int* err_flag, cudaStream_t stream);
+
+// The same attention for callers that cannot allocate device memory (no cudaMalloc in their loop, a fixed memory
+// budget owned by someone else): its scratch is a static device array inside the library, at most
+// cvb_attn_decode_static_scratch_floats() floats (8 MiB) per launch; larger launches are refused with CVB_E_SCRATCH.
+// Its first call on a device looks the array up and should come before any stream capture.  Calls share the array:
+// do not let two of them overlap on the GPU.  This entry point has no counterpart in the reference, whose decode
+// attention takes its partial-result buffers from the framework's allocator (kernels/paged_attention.cu:395-442).
+int64_t cvb_attn_decode_static_scratch_floats(void);
+int cvb_attn_decode_bf16_static(void* out, const void* q, const void* cache, const int* block_tables, int table_width,
+                                const int* cu_seqlens, const int* positions, int S, int H, int KV, int hd,
+                                int page_size, int window, float scale, int num_pages, int splits, int* err_flag,
+                                cudaStream_t stream);
+
+#ifdef __cplusplus
+}
+#endif

@@ -36,7 +36,7 @@ LIBRARIES: Dict[str, List[str]] = {
     "attn_bf16": ["attention_bf16.cu"],
 }
 
-_HEADERS = ["common.cuh"]
+_HEADERS = ["common.cuh", "attention_bf16.h"]
 _loaded: Dict[str, ctypes.CDLL] = {}
 _lock = threading.Lock()
 
