@@ -79,6 +79,99 @@ __global__ void gather_rows_kernel(T* __restrict__ out, const T* __restrict__ in
     for (int i = threadIdx.x; i < D; i += blockDim.x) out[r * D + i] = in[static_cast<int64_t>(src) * D + i];
 }
 
+
+// ---- 16-byte vector forms (rows whose length is a multiple of the vector width and whose base is aligned) --------
+
+template <typename T> struct Vec16;
+template <> struct Vec16<float> {
+    static constexpr int N = 4;
+    float v[4];
+    __device__ __forceinline__ void load(const float* p) { const float4 t = *reinterpret_cast<const float4*>(p); v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w; }
+    __device__ __forceinline__ void store(float* p) const { *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]); }
+};
+template <> struct Vec16<__nv_bfloat16> {
+    static constexpr int N = 8;
+    float v[8];
+    __device__ __forceinline__ void load(const __nv_bfloat16* p) {
+        const uint4 t = *reinterpret_cast<const uint4*>(p);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&t);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(h[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
+    }
+    __device__ __forceinline__ void store(__nv_bfloat16* p) const {
+        uint4 t;
+        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&t);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+        *reinterpret_cast<uint4*>(p) = t;
+    }
+};
+
+constexpr int kNormThreads = 128;
+constexpr int kNormMaxChunks = 8;      // per thread: rows up to 128 * 8 * (4 or 8) elements stay in registers
+
+// Same arithmetic as rmsnorm_kernel, one global read of the row: the (summed) row is kept in registers.
+template <typename T, bool ADD>
+__global__ void __launch_bounds__(kNormThreads)
+rmsnorm_vec_kernel(T* __restrict__ out, T* resid, const T* __restrict__ x, const float* __restrict__ w, int D, float eps) {
+    __shared__ float scratch[32];
+    constexpr int N = Vec16<T>::N;
+    const int64_t row = blockIdx.x;
+    const int n_chunks = D / N;
+    Vec16<T> val[kNormMaxChunks];
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < kNormMaxChunks; ++k) {
+        const int c = threadIdx.x + k * kNormThreads;
+        if (c < n_chunks) {
+            val[k].load(x + row * D + c * N);
+            if constexpr (ADD) {
+                Vec16<T> r;
+                r.load(resid + row * D + c * N);
+#pragma unroll
+                for (int i = 0; i < N; ++i) val[k].v[i] = rnd<T>(r.v[i] + val[k].v[i]);
+                val[k].store(resid + row * D + c * N);
+            }
+#pragma unroll
+            for (int i = 0; i < N; ++i) ss += val[k].v[i] * val[k].v[i];
+        }
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = rsqrtf(ss / static_cast<float>(D) + eps);
+#pragma unroll
+    for (int k = 0; k < kNormMaxChunks; ++k) {
+        const int c = threadIdx.x + k * kNormThreads;
+        if (c < n_chunks) {
+            Vec16<T> o;
+#pragma unroll
+            for (int i = 0; i < N; ++i) o.v[i] = rnd<T>(val[k].v[i] * inv) * w[c * N + i];
+            o.store(out + row * D + c * N);
+        }
+    }
+}
+
+template <typename T>
+__global__ void swiglu_vec_kernel(T* __restrict__ out, const T* __restrict__ gu, int64_t n_chunks, int I) {
+    constexpr int N = Vec16<T>::N;
+    const int64_t k = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (k >= n_chunks) return;
+    const int per_row = I / N;
+    const int64_t r = k / per_row;
+    const int i0 = static_cast<int>(k - r * per_row) * N;
+    Vec16<T> g, u, o;
+    g.load(gu + r * 2 * I + i0);
+    u.load(gu + r * 2 * I + I + i0);
+#pragma unroll
+    for (int i = 0; i < N; ++i) o.v[i] = rnd<T>(g.v[i] / (1.f + expf(-g.v[i]))) * u.v[i];
+    o.store(out + r * I + i0);
+}
+
+template <typename T> __host__ inline bool vec_ok(const void* a, const void* b, const void* c, int width) {
+    constexpr int N = Vec16<T>::N;
+    auto al = [](const void* p) { return p == nullptr || (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+    return width % N == 0 && al(a) && al(b) && al(c);
+}
+
 }  // namespace cvb
 
 using namespace cvb;
@@ -97,7 +190,11 @@ extern "C" int cvb_rmsnorm(void* out, const void* x, const float* w, int T, int 
                            cudaStream_t stream) {
     if (T == 0) return CVB_OK;
     if (T < 0 || D <= 0) return CVB_E_SIZE;
-#define CALL(TY) rmsnorm_kernel<TY, false><<<T, 256, 0, stream>>>((TY*)out, nullptr, (const TY*)x, w, D, eps)
+#define CALL(TY)                                                                                              \
+    if (vec_ok<TY>(out, x, nullptr, D) && D <= kNormThreads * kNormMaxChunks * Vec16<TY>::N)                  \
+        rmsnorm_vec_kernel<TY, false><<<T, kNormThreads, 0, stream>>>((TY*)out, nullptr, (const TY*)x, w, D, eps); \
+    else                                                                                                      \
+        rmsnorm_kernel<TY, false><<<T, 256, 0, stream>>>((TY*)out, nullptr, (const TY*)x, w, D, eps)
     CVB_DISPATCH_DTYPE(dtype, CALL);
 #undef CALL
     return launch_status();
@@ -107,7 +204,11 @@ extern "C" int cvb_add_rmsnorm(void* out, void* resid, const void* x, const floa
                                int dtype, cudaStream_t stream) {
     if (T == 0) return CVB_OK;
     if (T < 0 || D <= 0) return CVB_E_SIZE;
-#define CALL(TY) rmsnorm_kernel<TY, true><<<T, 256, 0, stream>>>((TY*)out, (TY*)resid, (const TY*)x, w, D, eps)
+#define CALL(TY)                                                                                              \
+    if (vec_ok<TY>(out, x, resid, D) && D <= kNormThreads * kNormMaxChunks * Vec16<TY>::N)                    \
+        rmsnorm_vec_kernel<TY, true><<<T, kNormThreads, 0, stream>>>((TY*)out, (TY*)resid, (const TY*)x, w, D, eps); \
+    else                                                                                                      \
+        rmsnorm_kernel<TY, true><<<T, 256, 0, stream>>>((TY*)out, (TY*)resid, (const TY*)x, w, D, eps)
     CVB_DISPATCH_DTYPE(dtype, CALL);
 #undef CALL
     return launch_status();
@@ -128,7 +229,12 @@ extern "C" int cvb_swiglu(void* out, const void* gate_up, int T, int I, int dtyp
     if (T < 0 || I <= 0) return CVB_E_SIZE;
     const int64_t n = static_cast<int64_t>(T) * I;
     const unsigned blocks = static_cast<unsigned>((n + 255) / 256);
-#define CALL(TY) swiglu_kernel<TY><<<blocks, 256, 0, stream>>>((TY*)out, (const TY*)gate_up, n, I)
+#define CALL(TY)                                                                                              \
+    if (vec_ok<TY>(out, gate_up, nullptr, I)) {                                                               \
+        const int64_t nc = n / Vec16<TY>::N;                                                                  \
+        swiglu_vec_kernel<TY><<<static_cast<unsigned>((nc + 255) / 256), 256, 0, stream>>>((TY*)out, (const TY*)gate_up, nc, I); \
+    } else                                                                                                    \
+        swiglu_kernel<TY><<<blocks, 256, 0, stream>>>((TY*)out, (const TY*)gate_up, n, I)
     CVB_DISPATCH_DTYPE(dtype, CALL);
 #undef CALL
     return launch_status();

@@ -89,7 +89,8 @@ def core():
     if _core is None:
         lib = load_library("core")
         for name in ("cvb_embed", "cvb_rmsnorm", "cvb_add_rmsnorm", "cvb_add", "cvb_swiglu", "cvb_gather_rows",
-                     "cvb_qk_norm_rope_kv", "cvb_paged_attention_general", "cvb_sample", "cvb_feed_tokens"):
+                     "cvb_qk_norm_rope_kv", "cvb_paged_attention_general", "cvb_sample", "cvb_sample_chunked",
+                     "cvb_feed_tokens"):
             getattr(lib, name).restype = c_int
         _core = lib
     return _core
@@ -319,13 +320,22 @@ def attn_decode_bf16(out, q, cache, block_tables, cu_seqlens, positions, num_seq
 # ---- sampling ----------------------------------------------------------------------------------------------
 
 def sample(out: torch.Tensor, logits: torch.Tensor, rows: Optional[torch.Tensor], temps: torch.Tensor,
-           seeds: torch.Tensor, out_positions: torch.Tensor, num_rows: Optional[int] = None) -> torch.Tensor:
+           seeds: torch.Tensor, out_positions: torch.Tensor, num_rows: Optional[int] = None,
+           scratch: Optional[torch.Tensor] = None, chunks: int = 0) -> torch.Tensor:
+    """With `scratch` (any dtype, at least rows * chunks * 8 bytes) and `chunks` > 1 the vocabulary of every row is
+    searched by `chunks` blocks in parallel; the token is the same as with one block per row."""
     _cuda(out, logits, rows, temps, seeds, out_positions); _contig(out, logits, rows, temps, seeds, out_positions)
     R = out.numel() if num_rows is None else num_rows
     if (logits.dtype != torch.float32 or logits.dim() != 2 or out.dtype != torch.int32 or temps.dtype != torch.float32
             or seeds.dtype != torch.int64 or out_positions.dtype != torch.int32
             or (rows is not None and rows.dtype != torch.int32)):
         raise KernelError("sample: logits float32 [N, V]; out, rows, out_positions int32; temps float32; seeds int64")
+    if scratch is not None and chunks > 1:
+        _cuda(scratch); _contig(scratch)
+        _check(core().cvb_sample_chunked(_ptr(out), _ptr(logits), _ptr(rows), _ptr(temps), _ptr(seeds), _ptr(out_positions),
+                                         c_int(R), c_int(logits.shape[1]), c_int(logits.shape[0]), c_int(chunks), _ptr(scratch),
+                                         c_int64(scratch.numel() * scratch.element_size()), _stream()), "sample", kernels=2)
+        return out
     _check(core().cvb_sample(_ptr(out), _ptr(logits), _ptr(rows), _ptr(temps), _ptr(seeds), _ptr(out_positions),
                              c_int(R), c_int(logits.shape[1]), c_int(logits.shape[0]), _stream()), "sample")
     return out

@@ -96,6 +96,85 @@ sample_kernel(int* __restrict__ out, const float* __restrict__ logits, const int
     }
 }
 
+// Two-phase form for large vocabularies: phase 1 gives every row `n_chunks` blocks, each of which finds the best
+// (score, index) of its slice of the vocabulary; phase 2 picks the best of a row's partial results.  Scores, random
+// numbers and tie-breaking are those of sample_kernel, so both forms return the same token.
+__global__ void __launch_bounds__(256)
+sample_partial_kernel(float* __restrict__ part_v, int* __restrict__ part_i, const float* __restrict__ logits,
+                      const int* __restrict__ rows, const float* __restrict__ temps, const uint64_t* __restrict__ seeds,
+                      const int* __restrict__ out_positions, int V, int n_logit_rows, int n_chunks) {
+    const int r = blockIdx.x, chunk = blockIdx.y;
+    int src = rows ? rows[r] : r;
+    if (src < 0) src = 0;
+    if (src >= n_logit_rows) src = n_logit_rows - 1;
+    const float* row = logits + static_cast<int64_t>(src) * V;
+    const float temp = temps[r];
+    const bool greedy = temp <= 0.f;
+    const float inv_t = 1.0f / fmaxf(temp, 1e-5f);
+    const uint64_t seed = seeds[r];
+    const uint32_t opos = static_cast<uint32_t>(out_positions[r]);
+    const int groups = (V + 3) >> 2;                                  // groups of four vocabulary entries
+    const int per = (groups + n_chunks - 1) / n_chunks;
+    const int g_begin = chunk * per, g_end = min(groups, g_begin + per);
+
+    Best best{-INFINITY, 0x7fffffff};
+    for (int gi = g_begin + threadIdx.x; gi < g_end; gi += blockDim.x) {
+        const int base = gi << 2;
+        uint32_t rn[4] = {0, 0, 0, 0};
+        if (!greedy) {
+            const Philox4 g = philox4x32_10(Philox4{static_cast<uint32_t>(gi), opos, kSampleTag, 0u},
+                                            static_cast<uint32_t>(seed), static_cast<uint32_t>(seed >> 32));
+            rn[0] = g.x; rn[1] = g.y; rn[2] = g.z; rn[3] = g.w;
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            if (base + j >= V) break;
+            const float x = row[base + j];
+            float sc = x;
+            if (!greedy) {
+                const float e = fmaxf(-logf(uniform01(rn[j])), 1e-10f);
+                sc = x * inv_t - logf(e);
+            }
+            if (better(sc, base + j, best)) { best.v = sc; best.i = base + j; }
+        }
+    }
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) {
+        const float ov = __shfl_down_sync(0xffffffffu, best.v, d);
+        const int oi = __shfl_down_sync(0xffffffffu, best.i, d);
+        if (better(ov, oi, best)) { best.v = ov; best.i = oi; }
+    }
+    __shared__ float sv[8];
+    __shared__ int si[8];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) { sv[warp] = best.v; si[warp] = best.i; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < (blockDim.x >> 5); ++w)
+            if (better(sv[w], si[w], best)) { best.v = sv[w]; best.i = si[w]; }
+        part_v[r * n_chunks + chunk] = best.v;
+        part_i[r * n_chunks + chunk] = best.i;
+    }
+}
+
+__global__ void sample_final_kernel(int* __restrict__ out, const float* __restrict__ part_v, const int* __restrict__ part_i,
+                                    int V, int n_chunks) {
+    const int r = blockIdx.x;
+    Best best{-INFINITY, 0x7fffffff};
+    for (int c = threadIdx.x; c < n_chunks; c += 32) {
+        const float v = part_v[r * n_chunks + c];
+        const int i = part_i[r * n_chunks + c];
+        if (better(v, i, best)) { best.v = v; best.i = i; }
+    }
+#pragma unroll
+    for (int d = 16; d > 0; d >>= 1) {
+        const float ov = __shfl_down_sync(0xffffffffu, best.v, d);
+        const int oi = __shfl_down_sync(0xffffffffu, best.i, d);
+        if (better(ov, oi, best)) { best.v = ov; best.i = oi; }
+    }
+    if (threadIdx.x == 0) out[r] = best.i < V ? best.i : 0;
+}
+
 // tokens[i] = sampled[src[i]] where src[i] >= 0: hands the previous step's samples to this step's inputs on
 // the device (reference fused_ops.cu:380-397).
 __global__ void feed_tokens_kernel(int* __restrict__ tokens, const int* __restrict__ src,
@@ -116,6 +195,21 @@ extern "C" int cvb_sample(int* out, const float* logits, const int* rows, const 
     if (R == 0) return CVB_OK;
     if (R < 0 || V <= 0 || n_logit_rows <= 0) return CVB_E_SIZE;
     sample_kernel<<<R, 1024, 0, stream>>>(out, logits, rows, temps, seeds, out_positions, V, n_logit_rows);
+    return launch_status();
+}
+
+// `scratch` holds R * n_chunks floats followed by R * n_chunks ints (n_chunks <= 64).
+extern "C" int cvb_sample_chunked(int* out, const float* logits, const int* rows, const float* temps,
+                                  const uint64_t* seeds, const int* out_positions, int R, int V, int n_logit_rows,
+                                  int n_chunks, void* scratch, int64_t scratch_bytes, cudaStream_t stream) {
+    if (R == 0) return CVB_OK;
+    if (R < 0 || V <= 0 || n_logit_rows <= 0 || n_chunks < 1 || n_chunks > 64) return CVB_E_SIZE;
+    if (scratch == nullptr || scratch_bytes < static_cast<int64_t>(R) * n_chunks * 8) return CVB_E_SCRATCH;
+    float* pv = static_cast<float*>(scratch);
+    int* pi = reinterpret_cast<int*>(pv + static_cast<int64_t>(R) * n_chunks);
+    dim3 grid(static_cast<unsigned>(R), static_cast<unsigned>(n_chunks));
+    sample_partial_kernel<<<grid, 256, 0, stream>>>(pv, pi, logits, rows, temps, seeds, out_positions, V, n_logit_rows, n_chunks);
+    sample_final_kernel<<<R, 32, 0, stream>>>(out, pv, pi, V, n_chunks);
     return launch_status();
 }
 

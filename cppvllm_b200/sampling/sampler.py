@@ -38,6 +38,8 @@ class Sampler:
         self._seeds = torch.zeros(max_rows, dtype=torch.int64, device=self.device)
         self._out = torch.zeros(max_rows, dtype=torch.int32, device=self.device)
         self._out_host = torch.empty(max_rows, dtype=torch.int32, pin_memory=True)
+        self._chunks = 32
+        self._scratch = torch.empty(max_rows * self._chunks * 2, dtype=torch.float32, device=self.device)
 
     def sample(self, logits: torch.Tensor, temps: Sequence[float], seeds: Sequence[int],
                out_positions: Sequence[int]) -> List[int]:
@@ -66,7 +68,10 @@ class Sampler:
         self._temps[:R].copy_(self._host_f[:R], non_blocking=True)
         self._pos[:R].copy_(self._host_p[:R], non_blocking=True)
         self._seeds[:R].copy_(self._host_s[:R], non_blocking=True)
-        ops.sample(self._out[:R], logits, None, self._temps, self._seeds, self._pos, num_rows=R)
+        # a large vocabulary is searched by several blocks per row, unless the rows alone fill the device
+        chunks = self._chunks if logits.shape[1] >= 16384 and R <= 64 else 0
+        ops.sample(self._out[:R], logits, None, self._temps, self._seeds, self._pos, num_rows=R,
+                   scratch=self._scratch if chunks else None, chunks=chunks)
         self._out_host[:R].copy_(self._out[:R], non_blocking=True)
         self.h2d_bytes_last = R * (4 + 4 + 8)
         return self._out[:R]

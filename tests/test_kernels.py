@@ -114,7 +114,9 @@ def rope_ref(n, cos, sin, pos, rot, interleaved):
 @pytest.mark.parametrize("dt", DTYPES)
 @pytest.mark.parametrize("H,KV,hd,rot,inter,norm", [(5, 5, 16, 16, False, True), (6, 2, 48, 48, False, True),
                                                     (7, 1, 80, 32, True, True), (3, 3, 144, 144, False, False),
-                                                    (8, 4, 256, 128, False, True)])
+                                                    (8, 4, 256, 128, False, True), (16, 8, 128, 128, False, True),
+                                                    (3, 1, 64, 64, False, True), (4, 2, 32, 32, False, False),
+                                                    (2, 2, 256, 256, False, True)])
 def test_qk_norm_rope_kv_write(ops, dt, H, KV, hd, rot, inter, norm):
     T, page, pages, max_pos, eps = 23, 16, 9, 300, 2e-5
     g = torch.Generator().manual_seed(hd)
@@ -305,6 +307,24 @@ def test_sampling_matches_its_formula_and_does_not_depend_on_the_batch(ops):
             ops.sample(out, logits, None, temps, seeds, torch.full((R,), p, dtype=torch.int32, device=dev()))
             draws.add(out[5].item())
         assert len(draws) > 5
+
+
+def test_chunked_sampling_returns_the_same_tokens(ops):
+    V, R = 50021, 9
+    g = torch.Generator().manual_seed(11)
+    logits = (torch.randn(R, V, generator=g) * 3).to(dev())
+    logits[3, 40000] = logits[3, 123] = 99.0          # a tie in a greedy row, in different chunks
+    temps = torch.tensor([0.0, 0.6, 1.0, 0.0, 0.3, 2.0, 0.6, 0.6, 0.0], device=dev())
+    seeds = torch.arange(R, dtype=torch.int64, device=dev()) * 977 + 5
+    opos = torch.arange(R, dtype=torch.int32, device=dev())
+    a = torch.zeros(R, dtype=torch.int32, device=dev())
+    ops.sample(a, logits, None, temps, seeds, opos)
+    for chunks in (2, 7, 32, 64):
+        b = torch.full((R,), -1, dtype=torch.int32, device=dev())
+        scratch = torch.empty(R * chunks * 2, dtype=torch.float32, device=dev())
+        ops.sample(b, logits, None, temps, seeds, opos, scratch=scratch, chunks=chunks)
+        assert b.tolist() == a.tolist()
+    assert a[3].item() == 123
 
 
 def test_temperature_sampling_follows_the_distribution(ops):
