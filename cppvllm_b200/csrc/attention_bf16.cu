@@ -14,7 +14,8 @@
 //
 // Key and value tiles are fetched by TMA (cp.async.bulk.tensor.2d through a tensor map of the page pool seen as
 // rows of head_dim elements; one box per page and 64-column half, 128-byte swizzle, completion on an mbarrier
-// with a transaction count), issued by one thread per block into a ring of stages.  A box whose keys lie outside
+// with a transaction count), issued by a producer warp into a ring of stages: "full" barriers tell the four
+// consumer warps that a tile has landed, "empty" barriers (one arrival per consumer warp) give the stage back.  A box whose keys lie outside
 // the request's range is fetched from the nearest page inside it, so every tile brings the same number of
 // bytes and never touches a page the request does not own; such keys are excluded by the mask.  Waits on the
 // mbarrier are bounded: if one runs out, the block records error 5 and leaves without computing.  The query tile
@@ -30,7 +31,8 @@
 namespace cvb {
 
 constexpr int kBN = 64;                 // keys per tile
-constexpr int kThreads = 128;           // 4 warps
+constexpr int kConsumers = 128;         // 4 warps that compute
+constexpr int kThreads = kConsumers + 32; // plus one warp that issues the TMA copies
 constexpr float kLog2e = 1.4426950408889634f;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -74,6 +76,9 @@ __device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
 __device__ __forceinline__ void mbar_fence_init() { asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory"); }
 __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%1], %0;\n" ::"r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
 }
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     uint32_t ok;
@@ -240,10 +245,10 @@ __device__ __forceinline__ void softmax_step(float (&s)[NT][4], float (&o)[HD / 
 template <int HD, int STAGES, int QROWS>
 struct SmemPlan {
     static constexpr int kStageElems = 2 * kBN * HD;                      // K tile + V tile
-    static constexpr size_t kBytes = 1024 + static_cast<size_t>(STAGES) * kStageElems * 2 + static_cast<size_t>(QROWS) * HD * 2 + 8 * STAGES;
+    static constexpr size_t kBytes = 1024 + static_cast<size_t>(STAGES) * kStageElems * 2 + static_cast<size_t>(QROWS) * HD * 2 + 16 * STAGES;
     __nv_bfloat16* stages;
     __nv_bfloat16* q;
-    uint64_t* bars;
+    uint64_t* bars;                      // [STAGES] full, then [STAGES] empty
     __device__ explicit SmemPlan(unsigned char* raw) {
         const uint32_t addr = smem_u32(raw);
         unsigned char* base = raw + ((1024u - (addr & 1023u)) & 1023u);
@@ -290,8 +295,10 @@ attn_prefill_bf16_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnP
     const int key_hi = pos_last;
     const int tile_begin = key_lo / kBN, n_tiles = key_hi / kBN - tile_begin + 1;
 
+    uint64_t* full = sm.bars;
+    uint64_t* empty = sm.bars + kPreStages;
     if (threadIdx.x == 0) {
-        for (int i = 0; i < kPreStages; ++i) mbar_init(sm.bars + i, 1);
+        for (int i = 0; i < kPreStages; ++i) { mbar_init(full + i, 1); mbar_init(empty + i, kConsumers / 32); }
         mbar_fence_init();
     }
     // Q tile: row r = (token r / g, head kvh * g + r % g)
@@ -303,13 +310,22 @@ attn_prefill_bf16_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnP
         cp_async16(sm.q + swz<HD>(r, c), src, valid);
     }
     cp_async_commit();
-    __syncthreads();                                      // barriers are initialised
-    if (threadIdx.x == 0) {
-        for (int i = 0; i < kPreStages - 1 && i < n_tiles; ++i)
-            tma_issue_tile<HD>(sm.stages + i * Plan::kStageElems, sm.bars + i, &kv_map, p, table, kvh, (tile_begin + i) * kBN, key_lo, key_hi);
+    cp_async_wait<0>();
+    __syncthreads();                                      // barriers are initialised, the query tile is in place
+
+    if (warp == kConsumers / 32) {                        // ---- producer warp ----
+        if (lane == 0) {
+            for (int it = 0; it < n_tiles; ++it) {
+                const int st = it % kPreStages;
+                if (it >= kPreStages) mbar_wait(empty + st, ((it / kPreStages) - 1) & 1, p.err);
+                tma_issue_tile<HD>(sm.stages + st * Plan::kStageElems, full + st, &kv_map, p, table, kvh,
+                                   (tile_begin + it) * kBN, key_lo, key_hi);
+            }
+        }
+        return;
     }
 
-    // the two rows this thread owns in the warp's 16-row slab, and the warp's extremes
+    // ---- consumer warps: the two rows this thread owns in the warp's 16-row slab, and the warp's extremes ----
     int row_lo[2], row_hi[2];
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
@@ -329,22 +345,17 @@ attn_prefill_bf16_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnP
 #pragma unroll
     for (int dt = 0; dt < HD / 8; ++dt) { o[dt][0] = o[dt][1] = o[dt][2] = o[dt][3] = 0.f; }
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
-    cp_async_wait<0>();
-    __syncthreads();
 #pragma unroll
     for (int ks = 0; ks < HD / 16; ++ks)
         ldmatrix_x4(qf[ks], sm.q + swz<HD>(warp * 16 + (lane & 15), ks * 2 + (lane >> 4)));
 
     for (int it = 0; it < n_tiles; ++it) {
         const int st = it % kPreStages;
-        if (threadIdx.x == 0 && it + kPreStages - 1 < n_tiles) {
-            const int nx = it + kPreStages - 1;
-            tma_issue_tile<HD>(sm.stages + (nx % kPreStages) * Plan::kStageElems, sm.bars + nx % kPreStages, &kv_map, p, table,
-                               kvh, (tile_begin + nx) * kBN, key_lo, key_hi);
-        }
-        mbar_wait(sm.bars + st, (it / kPreStages) & 1, p.err);
         const int key0 = (tile_begin + it) * kBN;
-        // a warp whose rows all end before this tile has nothing to add (causal)
+        // Every warp waits for the tile, also one that has nothing to add to it (its rows end before the tile:
+        // causal): a warp may arrive on "empty" only once per filling of the stage, and the tile's arrival is
+        // what tells it that the previous filling was given back by all four warps.
+        mbar_wait(full + st, (it / kPreStages) & 1, p.err);
         if (warp_has_rows && key0 <= warp_last_pos) {
             const __nv_bfloat16* sK = sm.stages + st * Plan::kStageElems;
             const __nv_bfloat16* sV = sK + kBN * HD;
@@ -356,7 +367,8 @@ attn_prefill_bf16_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnP
                 softmax_step<HD, 8, true>(s, o, m, l, key0, row_lo, row_hi, p.scale_log2, lane);
             pv_product<HD, 8>(o, s, sV, 0, lane);
         }
-        __syncthreads();                                  // the stage may be refilled
+        __syncwarp();
+        if (lane == 0) mbar_arrive(empty + st);
     }
 
 #pragma unroll
@@ -410,8 +422,10 @@ attn_decode_bf16_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnPa
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
 
     if (n_tiles > 0) {
+        uint64_t* full = sm.bars;
+        uint64_t* empty = sm.bars + kDecStages;
         if (threadIdx.x == 0) {
-            for (int i = 0; i < kDecStages; ++i) mbar_init(sm.bars + i, 1);
+            for (int i = 0; i < kDecStages; ++i) { mbar_init(full + i, 1); mbar_init(empty + i, kConsumers / 32); }
             mbar_fence_init();
         }
         for (int i = threadIdx.x; i < 16 * CPR; i += kThreads) {
@@ -421,40 +435,42 @@ attn_decode_bf16_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnPa
             cp_async16(sm.q + swz<HD>(r, c), src, valid);
         }
         cp_async_commit();
-        __syncthreads();
-        if (threadIdx.x == 0) {
-            for (int i = 0; i < kDecStages - 1 && i < n_tiles; ++i)
-                tma_issue_tile<HD>(sm.stages + i * Plan::kStageElems, sm.bars + i, &kv_map, p, table, kvh, (tile_begin + i) * kBN, key_lo, key_hi);
-        }
-        const int row_lo[2] = {key_lo, key_lo};
-        const int row_hi[2] = {key_hi, key_hi};             // rows >= g hold zero queries and are never stored
-        uint32_t qf[HD / 16][4];
         cp_async_wait<0>();
         __syncthreads();
+        if (warp == kConsumers / 32) {                                     // ---- producer warp ----
+            if (lane == 0) {
+                for (int it = 0; it < n_tiles; ++it) {
+                    const int st = it % kDecStages;
+                    if (it >= kDecStages) mbar_wait(empty + st, ((it / kDecStages) - 1) & 1, p.err);
+                    tma_issue_tile<HD>(sm.stages + st * Plan::kStageElems, full + st, &kv_map, p, table, kvh,
+                                       (tile_begin + it) * kBN, key_lo, key_hi);
+                }
+            }
+        } else {                                                           // ---- consumer warps ----
+            const int row_lo[2] = {key_lo, key_lo};
+            const int row_hi[2] = {key_hi, key_hi};         // rows >= g hold zero queries and are never stored
+            uint32_t qf[HD / 16][4];
 #pragma unroll
-        for (int ks = 0; ks < HD / 16; ++ks)
-            ldmatrix_x4(qf[ks], sm.q + swz<HD>(lane & 15, ks * 2 + (lane >> 4)));
-        for (int it = 0; it < n_tiles; ++it) {
-            const int st = it % kDecStages;
-            if (threadIdx.x == 0 && it + kDecStages - 1 < n_tiles) {
-                const int nx = it + kDecStages - 1;
-                tma_issue_tile<HD>(sm.stages + (nx % kDecStages) * Plan::kStageElems, sm.bars + nx % kDecStages, &kv_map, p,
-                                   table, kvh, (tile_begin + nx) * kBN, key_lo, key_hi);
+            for (int ks = 0; ks < HD / 16; ++ks)
+                ldmatrix_x4(qf[ks], sm.q + swz<HD>(lane & 15, ks * 2 + (lane >> 4)));
+            for (int it = 0; it < n_tiles; ++it) {
+                const int st = it % kDecStages;
+                const int key0 = (tile_begin + it) * kBN + warp * 16;      // each warp takes 16 of the tile's 64 keys
+                mbar_wait(full + st, (it / kDecStages) & 1, p.err);       // also when this warp's keys are all outside
+                if (key0 <= key_hi && key0 + 15 >= key_lo) {
+                    const __nv_bfloat16* sK = sm.stages + st * Plan::kStageElems;
+                    const __nv_bfloat16* sV = sK + kBN * HD;
+                    float s[2][4];
+                    qk_product<HD, 2>(s, qf, sK, warp * 16, lane);
+                    if (key0 >= key_lo && key0 + 15 <= key_hi)
+                        softmax_step<HD, 2, false>(s, o, m, l, key0, row_lo, row_hi, p.scale_log2, lane);
+                    else
+                        softmax_step<HD, 2, true>(s, o, m, l, key0, row_lo, row_hi, p.scale_log2, lane);
+                    pv_product<HD, 2>(o, s, sV, warp * 16, lane);
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(empty + st);
             }
-            mbar_wait(sm.bars + st, (it / kDecStages) & 1, p.err);
-            const __nv_bfloat16* sK = sm.stages + st * Plan::kStageElems;
-            const __nv_bfloat16* sV = sK + kBN * HD;
-            const int key0 = (tile_begin + it) * kBN + warp * 16;          // each warp takes 16 of the tile's 64 keys
-            if (key0 <= key_hi && key0 + 15 >= key_lo) {
-                float s[2][4];
-                qk_product<HD, 2>(s, qf, sK, warp * 16, lane);
-                if (key0 >= key_lo && key0 + 15 <= key_hi)
-                    softmax_step<HD, 2, false>(s, o, m, l, key0, row_lo, row_hi, p.scale_log2, lane);
-                else
-                    softmax_step<HD, 2, true>(s, o, m, l, key0, row_lo, row_hi, p.scale_log2, lane);
-                pv_product<HD, 2>(o, s, sV, warp * 16, lane);
-            }
-            __syncthreads();
         }
     }
 #pragma unroll
@@ -468,6 +484,7 @@ attn_decode_bf16_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnPa
     float* red_ml = red_o + 4 * 16 * HD;                                   // [4][16][2]
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
+        if (warp >= kConsumers / 32) break;                                // the producer warp holds no results
         const int r = (lane >> 2) + half * 8;
 #pragma unroll
         for (int dt = 0; dt < HD / 8; ++dt) {
