@@ -1,0 +1,240 @@
+// Matrix products for a handful of tokens (decode steps of up to 8 rows), bf16 weights and activations:
+//   y[m, n] = sum_k x[m, k] * W[n, k]
+// With so few rows the product is a stream of the weight matrix through the SMs; a library GEMM leaves most of the
+// HBM bandwidth unused at these shapes and cannot take the neighbouring elementwise work along.
+//
+// The weights are the A operand of mma.sync.m16n8k16 (16 or 8 rows of W per tile), the activations the B operand
+// (8 columns = rows of x, zero-padded).  The sum over k does not care in which order k is walked, so every lane feeds
+// the tensor core straight from 16-byte loads: lane (r = lane / 4, q = lane % 4) reads W[r][32j + 8q .. +7] and
+// W[r + 8][same] from global memory and x[r][same] from shared memory, and the two k16 steps of a 32-wide slab use
+// elements (0..3) and (4..7) of those vectors on both operands alike.  No conversion, no shuffle, no staging of W.
+// A block holds a few tiles; the warps of a tile split K and add their partial sums through shared memory.
+//
+// Fused around the product (formulas of the reference's kernels/fused_ops.cu):
+//   NORM      the activations are produced in the block itself: v = rnd(resid + delta) (written out once, by block 0,
+//             as the new residual stream), x = rnd( rnd(v * rsqrt(mean(v^2) + eps)) * w )       (:61-88, add_rms_norm)
+//   SWIGLU    W holds gate rows [0, I) and up rows [I, 2I); a tile is 8 gate rows over the 8 matching up rows and
+//             the block stores T( rnd(silu(T(g))) * T(u) )                                      (:210-220)
+// The result is rounded to bf16 once, as a library product with bf16 output is.
+#include "common.cuh"
+
+namespace cvb {
+
+constexpr int kXPad = 32;              // elements of padding per activation row: rows land in different banks
+constexpr int kBatch = 8;              // columns of the B operand
+constexpr int kJBatch = 8;             // 32-wide slabs fetched ahead per warp
+
+__device__ __forceinline__ void unpack8(const uint4& t, float (&v)[8]) {
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&t);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(h[i]); v[2 * i] = f.x; v[2 * i + 1] = f.y; }
+}
+
+__device__ __forceinline__ void mma_16816(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+                 : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+struct GemvParams {
+    __nv_bfloat16* out;            // [M, N] (SWIGLU: [M, N / 2])
+    const __nv_bfloat16* x;        // [M, K] activations (NORM: the residual stream)
+    const __nv_bfloat16* delta;    // NORM: added to the residual first, or nullptr
+    __nv_bfloat16* resid_out;      // NORM with delta: receives rnd(x + delta)
+    const float* norm_w;           // NORM: [K]
+    const __nv_bfloat16* W;        // [N, K]
+    int M, N, K;
+    int warps_k;                   // warps that share one tile's K range
+    int tiles_per_block;
+    float eps;
+};
+
+// TILE_ROWS: rows of W per tile (16, or 8 with the lower half of the A operand left zero).
+template <int TILE_ROWS, bool NORM, bool SWIGLU>
+__global__ void __launch_bounds__(512)
+gemv_mma_kernel(const GemvParams p) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int K = p.K, chunks = K >> 3;
+    const int xstride = K + kXPad;
+    __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(smem_raw);                    // [8][K + pad]
+    float* red = reinterpret_cast<float*>(xs + kBatch * xstride);                      // [warps][16][8]
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+
+    // ---- activations into shared memory ----
+    if constexpr (NORM) {
+        // one warp per row: add, round, sum of squares, scale; the row passes through shared memory in between
+        for (int m = warp; m < kBatch; m += n_warps) {
+            if (m >= p.M) {
+                for (int c = lane; c < chunks; c += 32) *reinterpret_cast<uint4*>(xs + m * xstride + c * 8) = make_uint4(0, 0, 0, 0);
+                continue;
+            }
+            float ss = 0.f;
+            for (int c = lane; c < chunks; c += 32) {
+                float v[8];
+                unpack8(*reinterpret_cast<const uint4*>(p.x + static_cast<int64_t>(m) * K + c * 8), v);
+                if (p.delta != nullptr) {
+                    float d[8];
+                    unpack8(*reinterpret_cast<const uint4*>(p.delta + static_cast<int64_t>(m) * K + c * 8), d);
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) v[i] = rnd<__nv_bfloat16>(v[i] + d[i]);
+                }
+                uint4 packed;
+                __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+                for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+                *reinterpret_cast<uint4*>(xs + m * xstride + c * 8) = packed;
+                if (p.delta != nullptr && blockIdx.x == 0)
+                    *reinterpret_cast<uint4*>(p.resid_out + static_cast<int64_t>(m) * K + c * 8) = packed;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) ss += v[i] * v[i];
+            }
+            ss = warp_sum(ss);
+            const float inv = rsqrtf(ss / static_cast<float>(K) + p.eps);
+            for (int c = lane; c < chunks; c += 32) {          // each lane re-reads the chunks it wrote itself
+                float v[8];
+                unpack8(*reinterpret_cast<const uint4*>(xs + m * xstride + c * 8), v);
+                const float4 w0 = *reinterpret_cast<const float4*>(p.norm_w + c * 8);
+                const float4 w1 = *reinterpret_cast<const float4*>(p.norm_w + c * 8 + 4);
+                const float w[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
+                uint4 packed;
+                __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                    h[i] = __floats2bfloat162_rn(rnd<__nv_bfloat16>(v[2 * i] * inv) * w[2 * i],
+                                                 rnd<__nv_bfloat16>(v[2 * i + 1] * inv) * w[2 * i + 1]);
+                *reinterpret_cast<uint4*>(xs + m * xstride + c * 8) = packed;
+            }
+        }
+    } else {
+        for (int i = threadIdx.x; i < kBatch * chunks; i += blockDim.x) {
+            const int m = i / chunks, c = i - m * chunks;
+            *reinterpret_cast<uint4*>(xs + m * xstride + c * 8) =
+                m < p.M ? *reinterpret_cast<const uint4*>(p.x + static_cast<int64_t>(m) * K + c * 8) : make_uint4(0, 0, 0, 0);
+        }
+    }
+    __syncthreads();
+
+    // ---- the product: this warp's tile and K range ----
+    constexpr int OUT_PER_TILE = SWIGLU ? 8 : TILE_ROWS;               // output columns a tile produces
+    const int n_out = SWIGLU ? p.N / 2 : p.N;
+    const int tile_in_block = warp / p.warps_k, wk = warp % p.warps_k;
+    const int tile = blockIdx.x * p.tiles_per_block + tile_in_block;
+    const int n0 = tile * OUT_PER_TILE;
+    const int r = lane >> 2, q = lane & 3;
+    // rows of W behind the upper (a0, a2) and lower (a1, a3) halves of the A operand
+    int row_hi = n0 + r, row_lo = SWIGLU ? n_out + n0 + r : n0 + r + 8;
+    row_hi = min(row_hi, p.N - 1);                                       // a ragged last tile repeats a row; dropped below
+    row_lo = min(row_lo, p.N - 1);
+    const uint4* w_hi = reinterpret_cast<const uint4*>(p.W + static_cast<int64_t>(row_hi) * K);
+    const uint4* w_lo = reinterpret_cast<const uint4*>(p.W + static_cast<int64_t>(row_lo) * K);
+    const uint4* x_row = reinterpret_cast<const uint4*>(xs + r * xstride);
+    constexpr bool LOWER = SWIGLU || TILE_ROWS == 16;
+
+    // K range of this warp, in 32-wide slabs
+    const int slabs = (K + 31) >> 5;
+    const int per_warp = (slabs + p.warps_k - 1) / p.warps_k;
+    const int j_begin = wk * per_warp, j_end = min(slabs, j_begin + per_warp);
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    const uint4 zero = make_uint4(0, 0, 0, 0);
+    if (n0 < n_out) {
+        for (int jb = j_begin; jb < j_end; jb += kJBatch) {
+            uint4 wh[kJBatch], wl[kJBatch];
+#pragma unroll
+            for (int u = 0; u < kJBatch; ++u) {
+                const int c = (jb + u) * 4 + q;                          // 16-byte chunk index along K
+                const bool ok = jb + u < j_end && c < chunks;
+                wh[u] = ok ? __ldg(w_hi + c) : zero;
+                if constexpr (LOWER) wl[u] = ok ? __ldg(w_lo + c) : zero; else wl[u] = zero;
+            }
+#pragma unroll
+            for (int u = 0; u < kJBatch; ++u) {
+                const int c = (jb + u) * 4 + q;
+                if (jb + u >= j_end) break;
+                const uint4 xv = c < chunks ? x_row[c] : zero;
+                mma_16816(acc, wh[u].x, wl[u].x, wh[u].y, wl[u].y, xv.x, xv.y);
+                mma_16816(acc, wh[u].z, wl[u].z, wh[u].w, wl[u].w, xv.z, xv.w);
+            }
+        }
+    }
+    // acc[0], acc[1]: (row r, batch 2q, 2q+1); acc[2], acc[3]: (row r + 8, same)
+    float* mine = red + warp * 128;
+    mine[r * 8 + 2 * q] = acc[0];
+    mine[r * 8 + 2 * q + 1] = acc[1];
+    mine[(r + 8) * 8 + 2 * q] = acc[2];
+    mine[(r + 8) * 8 + 2 * q + 1] = acc[3];
+    __syncthreads();
+
+    // ---- add the K parts of every tile and store ----
+    for (int i = threadIdx.x; i < p.tiles_per_block * OUT_PER_TILE * kBatch; i += blockDim.x) {
+        const int t = i / (OUT_PER_TILE * kBatch), rem = i % (OUT_PER_TILE * kBatch);
+        const int row = rem / kBatch, m = rem % kBatch;
+        const int n = (blockIdx.x * p.tiles_per_block + t) * OUT_PER_TILE + row;
+        if (n >= n_out || m >= p.M) continue;
+        float s0 = 0.f, s1 = 0.f;
+        for (int w = 0; w < p.warps_k; ++w) {
+            const float* part = red + (t * p.warps_k + w) * 128;
+            s0 += part[row * 8 + m];
+            if constexpr (SWIGLU) s1 += part[(row + 8) * 8 + m];
+        }
+        float y = s0;
+        if constexpr (SWIGLU) {
+            const float g = rnd<__nv_bfloat16>(s0), u = rnd<__nv_bfloat16>(s1);
+            y = rnd<__nv_bfloat16>(g / (1.f + expf(-g))) * u;
+        }
+        p.out[static_cast<int64_t>(m) * n_out + n] = __float2bfloat16_rn(y);
+    }
+}
+
+template <int TILE_ROWS, bool NORM, bool SWIGLU>
+static int launch_gemv(GemvParams p, cudaStream_t stream) {
+    constexpr int OUT_PER_TILE = SWIGLU ? 8 : TILE_ROWS;
+    const int n_out = SWIGLU ? p.N / 2 : p.N;
+    const int tiles = (n_out + OUT_PER_TILE - 1) / OUT_PER_TILE;
+    const int slabs = (p.K + 31) / 32;
+    p.warps_k = max(1, min(8, (slabs + kJBatch - 1) / kJBatch));          // about one batch of loads per warp
+    p.tiles_per_block = max(1, 8 / p.warps_k);
+    while (p.tiles_per_block > 1 && (tiles + p.tiles_per_block - 1) / p.tiles_per_block < 120) p.tiles_per_block >>= 1;
+    const int warps = p.warps_k * p.tiles_per_block;
+    const int blocks = (tiles + p.tiles_per_block - 1) / p.tiles_per_block;
+    const size_t smem = static_cast<size_t>(kBatch) * (p.K + kXPad) * sizeof(__nv_bfloat16) + static_cast<size_t>(warps) * 128 * sizeof(float);
+    if (smem > 200 * 1024) return CVB_E_SIZE;
+    if (smem > 48 * 1024) {
+        cudaError_t e = cudaFuncSetAttribute(gemv_mma_kernel<TILE_ROWS, NORM, SWIGLU>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
+        if (e != cudaSuccess) return static_cast<int>(e);
+    }
+    gemv_mma_kernel<TILE_ROWS, NORM, SWIGLU><<<blocks, warps * 32, smem, stream>>>(p);
+    return launch_status();
+}
+
+template <bool NORM>
+static int dispatch_gemv(const GemvParams& p, cudaStream_t stream) {
+    // tiles of 16 rows while they still give about one block per SM, else tiles of 8
+    if (p.N / 16 >= 120) return launch_gemv<16, NORM, false>(p, stream);
+    return launch_gemv<8, NORM, false>(p, stream);
+}
+
+}  // namespace cvb
+
+using namespace cvb;
+
+// mode: 0 = plain product, 1 = norm(+add) prologue, 2 = norm(+add) prologue and SwiGLU epilogue.
+extern "C" int cvb_gemv_bf16(void* out, const void* x, const void* delta, void* resid_out, const float* norm_w,
+                             const void* W, int M, int N, int K, float eps, int mode, cudaStream_t stream) {
+    if (M == 0) return CVB_OK;
+    if (M < 0 || M > kBatch || N <= 0 || K <= 0) return CVB_E_SIZE;
+    if (K % 8) return CVB_E_ALIGN;
+    auto al = [](const void* q) { return q == nullptr || (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+    if (!al(out) || !al(x) || !al(delta) || !al(resid_out) || !al(W) || !al(norm_w)) return CVB_E_ALIGN;
+    if (mode != 0 && norm_w == nullptr) return CVB_E_SHAPE;
+    if (delta != nullptr && (resid_out == nullptr || resid_out == x)) return CVB_E_SHAPE;   // blocks read x while block 0 writes
+    if (mode == 2 && (N % 2)) return CVB_E_SHAPE;
+    GemvParams p{};
+    p.out = (__nv_bfloat16*)out; p.x = (const __nv_bfloat16*)x; p.delta = (const __nv_bfloat16*)delta;
+    p.resid_out = (__nv_bfloat16*)resid_out; p.norm_w = norm_w; p.W = (const __nv_bfloat16*)W;
+    p.M = M; p.N = N; p.K = K; p.eps = eps;
+    if (mode == 0) return dispatch_gemv<false>(p, stream);
+    if (mode == 1) return dispatch_gemv<true>(p, stream);
+    if (mode == 2) return launch_gemv<16, true, true>(p, stream);
+    return CVB_E_SHAPE;
+}

@@ -317,6 +317,48 @@ def attn_decode_bf16(out, q, cache, block_tables, cu_seqlens, positions, num_seq
     return out
 
 
+_gemv = None
+
+GEMV_MAX_ROWS = 8
+
+
+def gemv_supported(x_dtype: torch.dtype, weight: torch.Tensor, rows: int) -> bool:
+    """The weight-streaming product covers bf16 operands, up to 8 rows and inner sizes that are multiples of 8."""
+    return (x_dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and 0 < rows <= GEMV_MAX_ROWS
+            and weight.shape[1] % 8 == 0 and weight.shape[1] * 8 * 2 <= 200 * 1024)
+
+
+def gemv_bf16(out: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, rows: int, norm_weight: Optional[torch.Tensor] = None,
+              eps: float = 0.0, delta: Optional[torch.Tensor] = None, resid_out: Optional[torch.Tensor] = None,
+              swiglu: bool = False) -> torch.Tensor:
+    """out[:rows] = x[:rows] @ weight^T for a few rows.  With `norm_weight`, x is the residual stream: `delta` (if given)
+    is added first and the sum written to `resid_out`, then the RMSNorm with `norm_weight` is applied before the
+    product.  With `swiglu`, weight holds gate rows over up rows and out receives silu(gate) * up."""
+    global _gemv
+    if _gemv is None:
+        lib = load_library("gemv_bf16")
+        lib.cvb_gemv_bf16.restype = c_int
+        _gemv = lib
+    _cuda(out, x, weight, norm_weight, delta, resid_out)
+    _contig(out, x, weight, norm_weight, delta, resid_out)
+    N, K = weight.shape
+    if x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or x.shape[1] != K:
+        raise KernelError("gemv_bf16: x [M, K], weight [N, K] and out must be bf16")
+    if out.shape[1] != (N // 2 if swiglu else N) or out.shape[0] < rows or x.shape[0] < rows:
+        raise KernelError("gemv_bf16: out must be [M, N] (or [M, N / 2] with swiglu)")
+    if swiglu and norm_weight is None:
+        raise KernelError("gemv_bf16: the SwiGLU form comes with the norm prologue")
+    if norm_weight is not None and (norm_weight.dtype != torch.float32 or norm_weight.numel() != K):
+        raise KernelError("gemv_bf16: norm_weight must be float32 [K]")
+    if delta is not None and (norm_weight is None or resid_out is None or delta.dtype != torch.bfloat16
+                              or resid_out.dtype != torch.bfloat16 or resid_out.data_ptr() == x.data_ptr()):
+        raise KernelError("gemv_bf16: delta needs the norm prologue and a resid_out buffer other than x")
+    mode = 0 if norm_weight is None else (2 if swiglu else 1)
+    _check(_gemv.cvb_gemv_bf16(_ptr(out), _ptr(x), _ptr(delta), _ptr(resid_out), _ptr(norm_weight), _ptr(weight), c_int(rows),
+                               c_int(N), c_int(K), c_float(eps), c_int(mode), _stream()), "gemv_bf16")
+    return out
+
+
 # ---- sampling ----------------------------------------------------------------------------------------------
 
 def sample(out: torch.Tensor, logits: torch.Tensor, rows: Optional[torch.Tensor], temps: torch.Tensor,

@@ -115,9 +115,35 @@ def gemv(a) -> dict:
             "GBps": round(nbytes / us / 1e3, 1)}
 
 
+def gemv_fused(a) -> dict:
+    """The package's own weight-streaming product: plain, with the norm prologue, or with norm and SwiGLU."""
+    from .csrc import ops
+    d = torch.device("cuda:0")
+    copies = max(1, min(64, int(300e6 // (a.rows * a.cols * 2)) + 1))
+    ws = [torch.randn(a.rows, a.cols, device=d).to(torch.bfloat16) for _ in range(copies)]
+    x = torch.randn(a.batch, a.cols, device=d).to(torch.bfloat16)
+    delta = torch.randn(a.batch, a.cols, device=d).to(torch.bfloat16)
+    h2 = torch.empty_like(x)
+    nw = torch.ones(a.cols, device=d)
+    n_out = a.rows // 2 if a.form == "swiglu" else a.rows
+    out = torch.empty(a.batch, n_out, device=d, dtype=torch.bfloat16)
+
+    def run(i):
+        if a.form == "plain":
+            ops.gemv_bf16(out, x, ws[i % copies], a.batch)
+        else:
+            ops.gemv_bf16(out, x, ws[i % copies], a.batch, norm_weight=nw, eps=1e-6, delta=delta, resid_out=h2,
+                          swiglu=a.form == "swiglu")
+    us = _time(run, a.iters)
+    nbytes = a.rows * a.cols * 2
+    return {"kernel": f"gemv_bf16 ({a.form})", "batch": a.batch, "rows": a.rows, "cols": a.cols, "us": round(us, 2),
+            "GBps": round(nbytes / us / 1e3, 1)}
+
+
 def main(argv=None) -> int:
     p = argparse.ArgumentParser(prog="kernel_bench")
-    p.add_argument("kernel", choices=["attn_decode", "attn_prefill", "gemv"])
+    p.add_argument("kernel", choices=["attn_decode", "attn_prefill", "gemv", "gemv_fused"])
+    p.add_argument("--form", default="plain", choices=["plain", "norm", "swiglu"])
     p.add_argument("--batch", type=int, default=8)
     p.add_argument("--context", type=int, default=4096)
     p.add_argument("--tokens", type=int, default=2048)
@@ -133,7 +159,7 @@ def main(argv=None) -> int:
     a = p.parse_args(argv)
     if a.kernel == "attn_prefill" and a.batch == 8 and "--batch" not in (argv or sys.argv):
         a.batch = 1
-    res = {"attn_decode": attn_decode, "attn_prefill": attn_prefill, "gemv": gemv}[a.kernel](a)
+    res = {"attn_decode": attn_decode, "attn_prefill": attn_prefill, "gemv": gemv, "gemv_fused": gemv_fused}[a.kernel](a)
     print(json.dumps(res))
     return 0
 

@@ -78,9 +78,35 @@ class PagedAttention(Mixer):
     def forward(self, x, ctx, cache, state):
         T = x.shape[0]
         H, KV, hd = self.num_heads, self.num_kv_heads, self.head_dim
+        qkv = ops.linear(x, self.w_qkv, out=self.rt.workspace.rows("attn_qkv", T, (H + 2 * KV) * hd, x.dtype))
+        return self._after_projection(qkv, ctx, cache)
+
+    def can_fuse_norm(self, norm, ctx) -> bool:
+        """A step of a few tokens can take the preceding RMSNorm (and the residual add before it) into the
+        projection's weight-streaming kernel."""
+        return (getattr(norm, "weight", None) is not None and hasattr(norm, "eps")
+                and ops.gemv_supported(self.rt.dtype, self.w_qkv, ctx.num_tokens)
+                and ops.gemv_supported(self.rt.dtype, self.w_o, ctx.num_tokens))
+
+    def forward_fused(self, h, pending, norm, ctx, cache, state):
+        """h: residual stream, pending: delta not yet added (or None).  Returns (output, residual stream)."""
+        T = ctx.num_tokens
+        H, KV, hd = self.num_heads, self.num_kv_heads, self.head_dim
+        ws = self.rt.workspace
+        h_new = h
+        if pending is not None:
+            h_new = ws.rows("residual_alt" if h.data_ptr() == ws.rows("residual", T, h.shape[1], h.dtype).data_ptr()
+                            else "residual", T, h.shape[1], h.dtype)
+        qkv = ops.gemv_bf16(ws.rows("attn_qkv", T, (H + 2 * KV) * hd, h.dtype), h, self.w_qkv, T, norm_weight=norm.weight,
+                            eps=norm.eps, delta=pending, resid_out=h_new if pending is not None else None)
+        return self._after_projection(qkv, ctx, cache), h_new
+
+    def _after_projection(self, qkv, ctx, cache):
+        T = qkv.shape[0]
+        x = qkv
+        H, KV, hd = self.num_heads, self.num_kv_heads, self.head_dim
         ws = self.rt.workspace
         g = ctx.groups[cache.group]
-        qkv = ops.linear(x, self.w_qkv, out=ws.rows("attn_qkv", T, (H + 2 * KV) * hd, x.dtype))
         q = ws.rows("attn_q", T, H * hd, x.dtype)
         pos = self.position
         ops.qk_norm_rope_kv(
@@ -92,7 +118,10 @@ class PagedAttention(Mixer):
             interleaved=pos.interleaved if pos is not None else False)
         att = ws.rows("attn_out", T, H * hd, x.dtype)
         self.attend(att, q, ctx, cache, g)
-        return ops.linear(att, self.w_o, out=ws.rows("attn_proj", T, self.hidden_size, x.dtype))
+        out = ws.rows("attn_proj", T, self.hidden_size, x.dtype)
+        if ops.gemv_supported(att.dtype, self.w_o, T):
+            return ops.gemv_bf16(out, att, self.w_o, T)
+        return ops.linear(att, self.w_o, out=out)
 
     # target number of blocks for the split-KV decode kernel: two per SM of a B200
     DECODE_TARGET_BLOCKS = 296

@@ -21,8 +21,18 @@ class PreNormBlock(Block):
         return (self.mixer_norm, self.mixer, self.ffn_norm, self.ffn)
 
     def forward(self, h, pending, ctx, cache, state):
-        x = self.mixer_norm.forward(h) if pending is None else self.mixer_norm.add_forward(h, pending)
-        a = self.mixer.forward(x, ctx, cache, state)
-        x = self.ffn_norm.add_forward(h, a)
-        m = self.ffn.forward(x, ctx)
+        # A part may offer to take the norm in front of it (and the residual add in front of that) into its own
+        # first kernel; it says so with can_fuse_norm(norm, ctx) and then runs forward_fused.
+        fuse = getattr(self.mixer, "can_fuse_norm", None)
+        if fuse is not None and fuse(self.mixer_norm, ctx):
+            a, h = self.mixer.forward_fused(h, pending, self.mixer_norm, ctx, cache, state)
+        else:
+            x = self.mixer_norm.forward(h) if pending is None else self.mixer_norm.add_forward(h, pending)
+            a = self.mixer.forward(x, ctx, cache, state)
+        fuse = getattr(self.ffn, "can_fuse_norm", None)
+        if fuse is not None and fuse(self.ffn_norm, ctx):
+            m, h = self.ffn.forward_fused(h, a, self.ffn_norm, ctx)
+        else:
+            x = self.ffn_norm.add_forward(h, a)
+            m = self.ffn.forward(x, ctx)
         return h, m

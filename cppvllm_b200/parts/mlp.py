@@ -41,4 +41,29 @@ class SwiGLUMLP(FeedForward):
         ws = self.rt.workspace
         gu = ops.linear(x, self.w_gate_up, out=ws.rows("ffn_gate_up", T, 2 * self.intermediate_size, x.dtype))
         act = ops.swiglu(ws.rows("ffn_act", T, self.intermediate_size, x.dtype), gu)
-        return ops.linear(act, self.w_down, out=ws.rows("ffn_out", T, self.hidden_size, x.dtype))
+        return self._down(act, T)
+
+    def _down(self, act, T):
+        out = self.rt.workspace.rows("ffn_out", T, self.hidden_size, act.dtype)
+        if ops.gemv_supported(act.dtype, self.w_down, T):
+            return ops.gemv_bf16(out, act, self.w_down, T)
+        return ops.linear(act, self.w_down, out=out)
+
+    def can_fuse_norm(self, norm, ctx) -> bool:
+        return (getattr(norm, "weight", None) is not None and hasattr(norm, "eps")
+                and ops.gemv_supported(self.rt.dtype, self.w_gate_up, ctx.num_tokens)
+                and ops.gemv_supported(self.rt.dtype, self.w_down, ctx.num_tokens))
+
+    def forward_fused(self, h, pending, norm, ctx):
+        """Residual add, RMSNorm, gate/up product and SwiGLU in one kernel, then the down product.
+        Returns (output, residual stream)."""
+        T = ctx.num_tokens
+        ws = self.rt.workspace
+        h_new = h
+        if pending is not None:
+            h_new = ws.rows("residual_alt" if h.data_ptr() == ws.rows("residual", T, h.shape[1], h.dtype).data_ptr()
+                            else "residual", T, h.shape[1], h.dtype)
+        act = ops.gemv_bf16(ws.rows("ffn_act", T, self.intermediate_size, h.dtype), h, self.w_gate_up, T,
+                            norm_weight=norm.weight, eps=norm.eps, delta=pending,
+                            resid_out=h_new if pending is not None else None, swiglu=True)
+        return self._down(act, T), h_new

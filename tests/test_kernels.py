@@ -432,3 +432,41 @@ def test_tensor_core_attention_refuses_what_it_does_not_cover(ops):
     z = torch.zeros(1, 2 * 64, dtype=torch.bfloat16, device=d)
     with pytest.raises(ops.KernelError, match="scratch"):
         ops.attn_decode_bf16(z, z, torch.zeros(2, 2, 1, 16, 64, dtype=torch.bfloat16, device=d), i.view(1, 2), i, i, 1, 2, 1, 64, 16, 0.1, 4, None)
+
+
+# ---- weight-streaming products for a few rows -----------------------------------------------------------------
+
+@pytest.mark.parametrize("M", [1, 3, 8])
+@pytest.mark.parametrize("N,K", [(1024, 2048), (4096, 1024), (40, 72), (1000, 3064)])
+def test_gemv_plain_norm_and_swiglu_forms(ops, M, N, K):
+    dt = torch.bfloat16
+    g = torch.Generator().manual_seed(M * 31 + N + K)
+    d = dev()
+    W = (torch.randn(N, K, generator=g) * 0.05).to(dt).to(d)
+    x = torch.randn(M, K, generator=g).to(dt).to(d)
+    assert ops.gemv_supported(dt, W, M) and not ops.gemv_supported(dt, W, 9) and not ops.gemv_supported(torch.float32, W, 1)
+    # plain
+    out = torch.full((M, N), float("nan"), dtype=dt, device=d)
+    ops.gemv_bf16(out, x, W, M)
+    ref = (x.float() @ W.float().t())
+    torch.testing.assert_close(out.float(), rnd(ref, dt), atol=2e-2, rtol=2e-2)
+    # norm prologue with residual add
+    delta = (torch.randn(M, K, generator=g) * 0.3).to(dt).to(d)
+    nw = (1 + 0.2 * torch.randn(K, generator=g)).to(d)
+    eps = 1e-5
+    h2 = torch.zeros_like(x)
+    ops.gemv_bf16(out, x, W, M, norm_weight=nw, eps=eps, delta=delta, resid_out=h2)
+    s_ = rnd(x.float() + delta.float(), dt)
+    assert torch.equal(h2.float(), s_)
+    xn = rnd(rnd(s_ * torch.rsqrt((s_ * s_).mean(-1, keepdim=True) + eps), dt) * nw, dt)
+    torch.testing.assert_close(out.float(), rnd(xn @ W.float().t(), dt), atol=3e-2, rtol=3e-2)
+    # norm prologue without add leaves the residual alone; SwiGLU epilogue
+    out2 = torch.full((M, N // 2), float("nan"), dtype=dt, device=d)
+    ops.gemv_bf16(out2, x, W, M, norm_weight=nw, eps=eps, swiglu=True)
+    xf = x.float()
+    xn = rnd(rnd(xf * torch.rsqrt((xf * xf).mean(-1, keepdim=True) + eps), dt) * nw, dt)
+    gu = rnd(xn @ W.float().t(), dt)
+    gate, up = gu[:, :N // 2], gu[:, N // 2:]
+    torch.testing.assert_close(out2.float(), rnd(rnd(gate / (1 + torch.exp(-gate)), dt) * up, dt), atol=3e-2, rtol=3e-2)
+    with pytest.raises(ops.KernelError, match="resid_out"):
+        ops.gemv_bf16(out, x, W, M, norm_weight=nw, eps=eps, delta=delta, resid_out=x)
