@@ -265,6 +265,8 @@ constexpr int kPreStages = 2;
 template <int HD>
 __global__ void __launch_bounds__(kThreads)
 attn_prefill_bf16_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnParams p, const int skip_single) {
+    pdl_trigger();
+    pdl_wait();
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     using Plan = SmemPlan<HD, kPreStages, 64>;
     Plan sm(smem_raw);
@@ -398,6 +400,8 @@ constexpr int kDecStages = 3;
 template <int HD>
 __global__ void __launch_bounds__(kThreads)
 attn_decode_bf16_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnParams p) {
+    pdl_trigger();
+    pdl_wait();
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     using Plan = SmemPlan<HD, kDecStages, 16>;
     Plan sm(smem_raw);
@@ -523,6 +527,8 @@ attn_decode_bf16_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnPa
 
 template <int HD>
 __global__ void attn_decode_merge_kernel(const AttnParams p) {
+    pdl_trigger();
+    pdl_wait();
     const int seq = blockIdx.x, h = blockIdx.y;
     const int cu0 = p.cu_seqlens[seq];
     if (p.cu_seqlens[seq + 1] - cu0 != 1) return;
@@ -646,11 +652,11 @@ extern "C" int cvb_attn_prefill_bf16(void* out, const void* q, const void* cache
     if (hd == 128) {
         static bool set = false;
         if (!set) { cudaFuncSetAttribute(attn_prefill_bf16_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)prefill_smem<128>()); set = true; }
-        attn_prefill_bf16_kernel<128><<<grid, kThreads, prefill_smem<128>(), stream>>>(map, p, skip_single);
+        launch_kernel(attn_prefill_bf16_kernel<128>, dim3(grid), dim3(kThreads), prefill_smem<128>(), stream, map, p, skip_single);
     } else {
         static bool set = false;
         if (!set) { cudaFuncSetAttribute(attn_prefill_bf16_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)prefill_smem<64>()); set = true; }
-        attn_prefill_bf16_kernel<64><<<grid, kThreads, prefill_smem<64>(), stream>>>(map, p, skip_single);
+        launch_kernel(attn_prefill_bf16_kernel<64>, dim3(grid), dim3(kThreads), prefill_smem<64>(), stream, map, p, skip_single);
     }
     return launch_status();
 }
@@ -676,13 +682,13 @@ extern "C" int cvb_attn_decode_bf16(void* out, const void* q, const void* cache,
     if (hd == 128) {
         static bool set = false;
         if (!set) { cudaFuncSetAttribute(attn_decode_bf16_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem<128>()); set = true; }
-        attn_decode_bf16_kernel<128><<<grid, kThreads, decode_smem<128>(), stream>>>(map, p);
-        if (splits > 1) attn_decode_merge_kernel<128><<<mgrid, 128, 0, stream>>>(p);
+        launch_kernel(attn_decode_bf16_kernel<128>, dim3(grid), dim3(kThreads), decode_smem<128>(), stream, map, p);
+        if (splits > 1) launch_kernel(attn_decode_merge_kernel<128>, dim3(mgrid), dim3(128), 0, stream, p);
     } else {
         static bool set = false;
         if (!set) { cudaFuncSetAttribute(attn_decode_bf16_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem<64>()); set = true; }
-        attn_decode_bf16_kernel<64><<<grid, kThreads, decode_smem<64>(), stream>>>(map, p);
-        if (splits > 1) attn_decode_merge_kernel<64><<<mgrid, 64, 0, stream>>>(p);
+        launch_kernel(attn_decode_bf16_kernel<64>, dim3(grid), dim3(kThreads), decode_smem<64>(), stream, map, p);
+        if (splits > 1) launch_kernel(attn_decode_merge_kernel<64>, dim3(mgrid), dim3(64), 0, stream, p);
     }
     return launch_status();
 }
@@ -780,11 +786,11 @@ extern "C" int cvb_attn_decode_bf16_static(void* out, const void* q, const void*
     dim3 grid(static_cast<unsigned>(S), static_cast<unsigned>(KV), static_cast<unsigned>(splits));
     dim3 mgrid(static_cast<unsigned>(S), static_cast<unsigned>(H));
     if (hd == 128) {
-        attn_decode_bf16_kernel<128><<<grid, kThreads, decode_smem<128>(), stream>>>(map, p);
-        if (splits > 1) attn_decode_merge_kernel<128><<<mgrid, 128, 0, stream>>>(p);
+        launch_kernel(attn_decode_bf16_kernel<128>, dim3(grid), dim3(kThreads), decode_smem<128>(), stream, map, p);
+        if (splits > 1) launch_kernel(attn_decode_merge_kernel<128>, dim3(mgrid), dim3(128), 0, stream, p);
     } else {
-        attn_decode_bf16_kernel<64><<<grid, kThreads, decode_smem<64>(), stream>>>(map, p);
-        if (splits > 1) attn_decode_merge_kernel<64><<<mgrid, 64, 0, stream>>>(p);
+        launch_kernel(attn_decode_bf16_kernel<64>, dim3(grid), dim3(kThreads), decode_smem<64>(), stream, map, p);
+        if (splits > 1) launch_kernel(attn_decode_merge_kernel<64>, dim3(mgrid), dim3(64), 0, stream, p);
     }
     return launch_status();
 }

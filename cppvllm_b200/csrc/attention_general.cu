@@ -24,6 +24,8 @@ paged_attention_general_kernel(T* __restrict__ out, const T* __restrict__ q, con
                                const int* __restrict__ seq_of_token, const int* __restrict__ positions,
                                int H, int KV, int hd, int page_size, int window, float scale, int num_pages,
                                int* __restrict__ err) {
+    pdl_trigger();
+    pdl_wait();
     extern __shared__ int64_t smem64[];
     int64_t* v_off = smem64;                            // [kAttnThreads]
     float* probs = reinterpret_cast<float*>(v_off + kAttnThreads);   // [kAttnThreads]
@@ -114,7 +116,7 @@ extern "C" int cvb_paged_attention_general(void* out, const void* q, const void*
     dim3 grid(static_cast<unsigned>(T), static_cast<unsigned>(H));
     const size_t smem = kAttnThreads * sizeof(int64_t) + (static_cast<size_t>(hd) + kAttnThreads + 32) * sizeof(float);
 #define CALL(TY)                                                                                         \
-    paged_attention_general_kernel<TY><<<grid, kAttnThreads, smem, stream>>>(                            \
+    launch_kernel(paged_attention_general_kernel<TY>, dim3(grid), dim3(kAttnThreads), smem, stream,                             \
         (TY*)out, (const TY*)q, (const TY*)cache, block_tables, table_width, seq_of_token, positions, H, \
         KV, hd, page_size, window, scale, num_pages, err_flag)
     CVB_DISPATCH_DTYPE(dtype, CALL);

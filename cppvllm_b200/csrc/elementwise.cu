@@ -13,6 +13,8 @@ namespace cvb {
 template <typename T>
 __global__ void embed_kernel(T* __restrict__ out, const T* __restrict__ table, const int* __restrict__ tokens,
                              int D, int V, int* __restrict__ err) {
+    pdl_trigger();
+    pdl_wait();
     const int64_t t = blockIdx.x;
     int tok = tokens[t];
     if (tok < 0 || tok >= V) {           // never read outside the table: record and clamp
@@ -27,6 +29,8 @@ __global__ void embed_kernel(T* __restrict__ out, const T* __restrict__ table, c
 template <typename T, bool ADD>
 __global__ void rmsnorm_kernel(T* __restrict__ out, T* resid, const T* __restrict__ x, const float* __restrict__ w,
                                int D, float eps) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ float scratch[32];
     const int64_t row = blockIdx.x;
     const T* xin = x + row * D;
@@ -53,12 +57,16 @@ __global__ void rmsnorm_kernel(T* __restrict__ out, T* resid, const T* __restric
 
 template <typename T>
 __global__ void add_kernel(T* __restrict__ resid, const T* __restrict__ x, int64_t n) {
+    pdl_trigger();
+    pdl_wait();
     const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (i < n) resid[i] = from_float<T>(to_float(resid[i]) + to_float(x[i]));
 }
 
 template <typename T>
 __global__ void swiglu_kernel(T* __restrict__ out, const T* __restrict__ gu, int64_t n, int I) {
+    pdl_trigger();
+    pdl_wait();
     const int64_t k = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (k >= n) return;
     const int64_t r = k / I;
@@ -72,6 +80,8 @@ __global__ void swiglu_kernel(T* __restrict__ out, const T* __restrict__ gu, int
 template <typename T>
 __global__ void gather_rows_kernel(T* __restrict__ out, const T* __restrict__ in, const int* __restrict__ rows,
                                    int D, int n_in) {
+    pdl_trigger();
+    pdl_wait();
     const int64_t r = blockIdx.x;
     int src = rows[r];
     if (src < 0) src = 0;
@@ -114,6 +124,8 @@ constexpr int kNormMaxChunks = 8;      // per thread: rows up to 128 * 8 * (4 or
 template <typename T, bool ADD>
 __global__ void __launch_bounds__(kNormThreads)
 rmsnorm_vec_kernel(T* __restrict__ out, T* resid, const T* __restrict__ x, const float* __restrict__ w, int D, float eps) {
+    pdl_trigger();
+    pdl_wait();
     __shared__ float scratch[32];
     constexpr int N = Vec16<T>::N;
     const int64_t row = blockIdx.x;
@@ -152,6 +164,8 @@ rmsnorm_vec_kernel(T* __restrict__ out, T* resid, const T* __restrict__ x, const
 
 template <typename T>
 __global__ void swiglu_vec_kernel(T* __restrict__ out, const T* __restrict__ gu, int64_t n_chunks, int I) {
+    pdl_trigger();
+    pdl_wait();
     constexpr int N = Vec16<T>::N;
     const int64_t k = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (k >= n_chunks) return;
@@ -180,7 +194,7 @@ extern "C" int cvb_embed(void* out, const void* table, const int* tokens, int T,
                          int* err_flag, cudaStream_t stream) {
     if (T == 0) return CVB_OK;
     if (T < 0 || D <= 0 || V <= 0) return CVB_E_SIZE;
-#define CALL(TY) embed_kernel<TY><<<T, 128, 0, stream>>>((TY*)out, (const TY*)table, tokens, D, V, err_flag)
+#define CALL(TY) launch_kernel(embed_kernel<TY>, dim3(T), dim3(128), 0, stream, (TY*)out, (const TY*)table, tokens, D, V, err_flag)
     CVB_DISPATCH_DTYPE(dtype, CALL);
 #undef CALL
     return launch_status();
@@ -192,9 +206,9 @@ extern "C" int cvb_rmsnorm(void* out, const void* x, const float* w, int T, int 
     if (T < 0 || D <= 0) return CVB_E_SIZE;
 #define CALL(TY)                                                                                              \
     if (vec_ok<TY>(out, x, nullptr, D) && D <= kNormThreads * kNormMaxChunks * Vec16<TY>::N)                  \
-        rmsnorm_vec_kernel<TY, false><<<T, kNormThreads, 0, stream>>>((TY*)out, nullptr, (const TY*)x, w, D, eps); \
+        launch_kernel(rmsnorm_vec_kernel<TY, false>, dim3(T), dim3(kNormThreads), 0, stream, (TY*)out, nullptr, (const TY*)x, w, D, eps); \
     else                                                                                                      \
-        rmsnorm_kernel<TY, false><<<T, 256, 0, stream>>>((TY*)out, nullptr, (const TY*)x, w, D, eps)
+        launch_kernel(rmsnorm_kernel<TY, false>, dim3(T), dim3(256), 0, stream, (TY*)out, nullptr, (const TY*)x, w, D, eps)
     CVB_DISPATCH_DTYPE(dtype, CALL);
 #undef CALL
     return launch_status();
@@ -206,9 +220,9 @@ extern "C" int cvb_add_rmsnorm(void* out, void* resid, const void* x, const floa
     if (T < 0 || D <= 0) return CVB_E_SIZE;
 #define CALL(TY)                                                                                              \
     if (vec_ok<TY>(out, x, resid, D) && D <= kNormThreads * kNormMaxChunks * Vec16<TY>::N)                    \
-        rmsnorm_vec_kernel<TY, true><<<T, kNormThreads, 0, stream>>>((TY*)out, (TY*)resid, (const TY*)x, w, D, eps); \
+        launch_kernel(rmsnorm_vec_kernel<TY, true>, dim3(T), dim3(kNormThreads), 0, stream, (TY*)out, (TY*)resid, (const TY*)x, w, D, eps); \
     else                                                                                                      \
-        rmsnorm_kernel<TY, true><<<T, 256, 0, stream>>>((TY*)out, (TY*)resid, (const TY*)x, w, D, eps)
+        launch_kernel(rmsnorm_kernel<TY, true>, dim3(T), dim3(256), 0, stream, (TY*)out, (TY*)resid, (const TY*)x, w, D, eps)
     CVB_DISPATCH_DTYPE(dtype, CALL);
 #undef CALL
     return launch_status();
@@ -218,7 +232,7 @@ extern "C" int cvb_add(void* resid, const void* x, int64_t n, int dtype, cudaStr
     if (n == 0) return CVB_OK;
     if (n < 0) return CVB_E_SIZE;
     const unsigned blocks = static_cast<unsigned>((n + 255) / 256);
-#define CALL(TY) add_kernel<TY><<<blocks, 256, 0, stream>>>((TY*)resid, (const TY*)x, n)
+#define CALL(TY) launch_kernel(add_kernel<TY>, dim3(blocks), dim3(256), 0, stream, (TY*)resid, (const TY*)x, n)
     CVB_DISPATCH_DTYPE(dtype, CALL);
 #undef CALL
     return launch_status();
@@ -232,9 +246,9 @@ extern "C" int cvb_swiglu(void* out, const void* gate_up, int T, int I, int dtyp
 #define CALL(TY)                                                                                              \
     if (vec_ok<TY>(out, gate_up, nullptr, I)) {                                                               \
         const int64_t nc = n / Vec16<TY>::N;                                                                  \
-        swiglu_vec_kernel<TY><<<static_cast<unsigned>((nc + 255) / 256), 256, 0, stream>>>((TY*)out, (const TY*)gate_up, nc, I); \
+        launch_kernel(swiglu_vec_kernel<TY>, dim3(static_cast<unsigned>((nc + 255) / 256)), dim3(256), 0, stream, (TY*)out, (const TY*)gate_up, nc, I); \
     } else                                                                                                    \
-        swiglu_kernel<TY><<<blocks, 256, 0, stream>>>((TY*)out, (const TY*)gate_up, n, I)
+        launch_kernel(swiglu_kernel<TY>, dim3(blocks), dim3(256), 0, stream, (TY*)out, (const TY*)gate_up, n, I)
     CVB_DISPATCH_DTYPE(dtype, CALL);
 #undef CALL
     return launch_status();
@@ -244,7 +258,7 @@ extern "C" int cvb_gather_rows(void* out, const void* in, const int* rows, int R
                                cudaStream_t stream) {
     if (R == 0) return CVB_OK;
     if (R < 0 || D <= 0 || n_in <= 0) return CVB_E_SIZE;
-#define CALL(TY) gather_rows_kernel<TY><<<R, 128, 0, stream>>>((TY*)out, (const TY*)in, rows, D, n_in)
+#define CALL(TY) launch_kernel(gather_rows_kernel<TY>, dim3(R), dim3(128), 0, stream, (TY*)out, (const TY*)in, rows, D, n_in)
     CVB_DISPATCH_DTYPE(dtype, CALL);
 #undef CALL
     return launch_status();

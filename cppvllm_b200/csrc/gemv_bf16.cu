@@ -59,6 +59,39 @@ gemv_mma_kernel(const GemvParams p) {
     __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(smem_raw);                    // [8][K + pad]
     float* red = reinterpret_cast<float*>(xs + kBatch * xstride);                      // [warps][16][8]
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
+    pdl_trigger();
+
+    // ---- this warp's tile and K range; its first batch of weights is fetched before anything else: weights do not
+    // depend on the kernels before this one, so the fetch overlaps their tail and this kernel's own prologue ----
+    constexpr int OUT_PER_TILE = SWIGLU ? 8 : TILE_ROWS;               // output columns a tile produces
+    const int n_out = SWIGLU ? p.N / 2 : p.N;
+    const int tile_in_block = warp / p.warps_k, wk = warp % p.warps_k;
+    const int tile = blockIdx.x * p.tiles_per_block + tile_in_block;
+    const int n0 = tile * OUT_PER_TILE;
+    const int r = lane >> 2, q = lane & 3;
+    // rows of W behind the upper (a0, a2) and lower (a1, a3) halves of the A operand
+    int row_hi = n0 + r, row_lo = SWIGLU ? n_out + n0 + r : n0 + r + 8;
+    row_hi = min(row_hi, p.N - 1);                                       // a ragged last tile repeats a row; dropped below
+    row_lo = min(row_lo, p.N - 1);
+    const uint4* w_hi = reinterpret_cast<const uint4*>(p.W + static_cast<int64_t>(row_hi) * K);
+    const uint4* w_lo = reinterpret_cast<const uint4*>(p.W + static_cast<int64_t>(row_lo) * K);
+    constexpr bool LOWER = SWIGLU || TILE_ROWS == 16;
+    const int slabs = (K + 31) >> 5;
+    const int per_warp = (slabs + p.warps_k - 1) / p.warps_k;
+    const int j_begin = wk * per_warp, j_end = min(slabs, j_begin + per_warp);
+    const uint4 zero = make_uint4(0, 0, 0, 0);
+    uint4 wh[kJBatch], wl[kJBatch];
+    auto fetch = [&](int jb) {
+#pragma unroll
+        for (int u = 0; u < kJBatch; ++u) {
+            const int c = (jb + u) * 4 + q;                              // 16-byte chunk index along K
+            const bool ok = n0 < n_out && jb + u < j_end && c < chunks;
+            wh[u] = ok ? __ldg(w_hi + c) : zero;
+            if constexpr (LOWER) wl[u] = ok ? __ldg(w_lo + c) : zero; else wl[u] = zero;
+        }
+    };
+    fetch(j_begin);
+    pdl_wait();
 
     // ---- activations into shared memory ----
     if constexpr (NORM) {
@@ -114,46 +147,18 @@ gemv_mma_kernel(const GemvParams p) {
     }
     __syncthreads();
 
-    // ---- the product: this warp's tile and K range ----
-    constexpr int OUT_PER_TILE = SWIGLU ? 8 : TILE_ROWS;               // output columns a tile produces
-    const int n_out = SWIGLU ? p.N / 2 : p.N;
-    const int tile_in_block = warp / p.warps_k, wk = warp % p.warps_k;
-    const int tile = blockIdx.x * p.tiles_per_block + tile_in_block;
-    const int n0 = tile * OUT_PER_TILE;
-    const int r = lane >> 2, q = lane & 3;
-    // rows of W behind the upper (a0, a2) and lower (a1, a3) halves of the A operand
-    int row_hi = n0 + r, row_lo = SWIGLU ? n_out + n0 + r : n0 + r + 8;
-    row_hi = min(row_hi, p.N - 1);                                       // a ragged last tile repeats a row; dropped below
-    row_lo = min(row_lo, p.N - 1);
-    const uint4* w_hi = reinterpret_cast<const uint4*>(p.W + static_cast<int64_t>(row_hi) * K);
-    const uint4* w_lo = reinterpret_cast<const uint4*>(p.W + static_cast<int64_t>(row_lo) * K);
+    // ---- the product ----
     const uint4* x_row = reinterpret_cast<const uint4*>(xs + r * xstride);
-    constexpr bool LOWER = SWIGLU || TILE_ROWS == 16;
-
-    // K range of this warp, in 32-wide slabs
-    const int slabs = (K + 31) >> 5;
-    const int per_warp = (slabs + p.warps_k - 1) / p.warps_k;
-    const int j_begin = wk * per_warp, j_end = min(slabs, j_begin + per_warp);
     float acc[4] = {0.f, 0.f, 0.f, 0.f};
-    const uint4 zero = make_uint4(0, 0, 0, 0);
-    if (n0 < n_out) {
-        for (int jb = j_begin; jb < j_end; jb += kJBatch) {
-            uint4 wh[kJBatch], wl[kJBatch];
+    for (int jb = j_begin; jb < j_end; jb += kJBatch) {
+        if (jb != j_begin) fetch(jb);
 #pragma unroll
-            for (int u = 0; u < kJBatch; ++u) {
-                const int c = (jb + u) * 4 + q;                          // 16-byte chunk index along K
-                const bool ok = jb + u < j_end && c < chunks;
-                wh[u] = ok ? __ldg(w_hi + c) : zero;
-                if constexpr (LOWER) wl[u] = ok ? __ldg(w_lo + c) : zero; else wl[u] = zero;
-            }
-#pragma unroll
-            for (int u = 0; u < kJBatch; ++u) {
-                const int c = (jb + u) * 4 + q;
-                if (jb + u >= j_end) break;
-                const uint4 xv = c < chunks ? x_row[c] : zero;
-                mma_16816(acc, wh[u].x, wl[u].x, wh[u].y, wl[u].y, xv.x, xv.y);
-                mma_16816(acc, wh[u].z, wl[u].z, wh[u].w, wl[u].w, xv.z, xv.w);
-            }
+        for (int u = 0; u < kJBatch; ++u) {
+            const int c = (jb + u) * 4 + q;
+            if (jb + u >= j_end) break;
+            const uint4 xv = c < chunks ? x_row[c] : zero;
+            mma_16816(acc, wh[u].x, wl[u].x, wh[u].y, wl[u].y, xv.x, xv.y);
+            mma_16816(acc, wh[u].z, wl[u].z, wh[u].w, wl[u].w, xv.z, xv.w);
         }
     }
     // acc[0], acc[1]: (row r, batch 2q, 2q+1); acc[2], acc[3]: (row r + 8, same)
@@ -203,7 +208,7 @@ static int launch_gemv(GemvParams p, cudaStream_t stream) {
                                              cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
         if (e != cudaSuccess) return static_cast<int>(e);
     }
-    gemv_mma_kernel<TILE_ROWS, NORM, SWIGLU><<<blocks, warps * 32, smem, stream>>>(p);
+    launch_kernel(gemv_mma_kernel<TILE_ROWS, NORM, SWIGLU>, dim3(blocks), dim3(warps * 32), smem, stream, p);
     return launch_status();
 }
 

@@ -24,6 +24,8 @@ __global__ void qk_norm_rope_kv_kernel(T* __restrict__ q_out, const T* __restric
                                        T* __restrict__ cache, int H, int KV, int hd, int rot, int interleaved,
                                        int page_size, int max_pos, float eps, int64_t cache_elems,
                                        int* __restrict__ err) {
+    pdl_trigger();
+    pdl_wait();
     extern __shared__ float smem[];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int task = blockIdx.y * kWarpsPerBlock + warp;
@@ -128,6 +130,8 @@ qk_norm_rope_kv_vec_kernel(T* __restrict__ q_out, const T* __restrict__ qkv, con
                            const int* __restrict__ positions, const int* __restrict__ slots, T* __restrict__ cache,
                            int H, int KV, int hd, int CH, int page_size, int max_pos, float eps, int64_t cache_elems,
                            int* __restrict__ err) {
+    pdl_trigger();
+    pdl_wait();
     constexpr int N = Chunk<T>::N;
     const int tasks_per_block = kVecThreads / CH;
     const int task = blockIdx.y * tasks_per_block + threadIdx.x / CH;
@@ -222,7 +226,7 @@ extern "C" int cvb_qk_norm_rope_kv(void* q_out, const void* qkv, const float* q_
             const int tasks_per_block = kVecThreads / CH;
             dim3 vgrid(static_cast<unsigned>(T), static_cast<unsigned>((n_tasks + tasks_per_block - 1) / tasks_per_block));
 #define VCALL(TY)                                                                                             \
-    qk_norm_rope_kv_vec_kernel<TY><<<vgrid, kVecThreads, 0, stream>>>(                                        \
+    launch_kernel(qk_norm_rope_kv_vec_kernel<TY>, dim3(vgrid), dim3(kVecThreads), 0, stream,                                         \
         (TY*)q_out, (const TY*)qkv, q_w, k_w, cos_t, sin_t, positions, slots, (TY*)cache, H, KV, hd, CH,       \
         page_size, max_pos, eps, cache_elems, err_flag)
             CVB_DISPATCH_DTYPE(dtype, VCALL);
@@ -233,7 +237,7 @@ extern "C" int cvb_qk_norm_rope_kv(void* q_out, const void* qkv, const float* q_
     dim3 grid(static_cast<unsigned>(T), static_cast<unsigned>((n_tasks + kWarpsPerBlock - 1) / kWarpsPerBlock));
     const size_t smem = static_cast<size_t>(kWarpsPerBlock) * hd * sizeof(float);
 #define CALL(TY)                                                                                              \
-    qk_norm_rope_kv_kernel<TY><<<grid, kWarpsPerBlock * 32, smem, stream>>>(                                  \
+    launch_kernel(qk_norm_rope_kv_kernel<TY>, dim3(grid), dim3(kWarpsPerBlock * 32), smem, stream,                                   \
         (TY*)q_out, (const TY*)qkv, q_w, k_w, cos_t, sin_t, positions, slots, (TY*)cache, H, KV, hd, rot,      \
         interleaved, page_size, max_pos, eps, cache_elems, err_flag)
     CVB_DISPATCH_DTYPE(dtype, CALL);

@@ -41,6 +41,8 @@ __global__ void __launch_bounds__(1024)
 sample_kernel(int* __restrict__ out, const float* __restrict__ logits, const int* __restrict__ rows,
               const float* __restrict__ temps, const uint64_t* __restrict__ seeds,
               const int* __restrict__ out_positions, int V, int n_logit_rows) {
+    pdl_trigger();
+    pdl_wait();
     const int r = blockIdx.x;
     int src = rows ? rows[r] : r;
     if (src < 0) src = 0;
@@ -103,6 +105,8 @@ __global__ void __launch_bounds__(256)
 sample_partial_kernel(float* __restrict__ part_v, int* __restrict__ part_i, const float* __restrict__ logits,
                       const int* __restrict__ rows, const float* __restrict__ temps, const uint64_t* __restrict__ seeds,
                       const int* __restrict__ out_positions, int V, int n_logit_rows, int n_chunks) {
+    pdl_trigger();
+    pdl_wait();
     const int r = blockIdx.x, chunk = blockIdx.y;
     int src = rows ? rows[r] : r;
     if (src < 0) src = 0;
@@ -159,6 +163,8 @@ sample_partial_kernel(float* __restrict__ part_v, int* __restrict__ part_i, cons
 
 __global__ void sample_final_kernel(int* __restrict__ out, const float* __restrict__ part_v, const int* __restrict__ part_i,
                                     int V, int n_chunks) {
+    pdl_trigger();
+    pdl_wait();
     const int r = blockIdx.x;
     Best best{-INFINITY, 0x7fffffff};
     for (int c = threadIdx.x; c < n_chunks; c += 32) {
@@ -179,6 +185,8 @@ __global__ void sample_final_kernel(int* __restrict__ out, const float* __restri
 // the device (reference fused_ops.cu:380-397).
 __global__ void feed_tokens_kernel(int* __restrict__ tokens, const int* __restrict__ src,
                                    const int* __restrict__ sampled, int n, int n_sampled) {
+    pdl_trigger();
+    pdl_wait();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     const int s = src[i];
@@ -194,7 +202,7 @@ extern "C" int cvb_sample(int* out, const float* logits, const int* rows, const 
                           cudaStream_t stream) {
     if (R == 0) return CVB_OK;
     if (R < 0 || V <= 0 || n_logit_rows <= 0) return CVB_E_SIZE;
-    sample_kernel<<<R, 1024, 0, stream>>>(out, logits, rows, temps, seeds, out_positions, V, n_logit_rows);
+    launch_kernel(sample_kernel, dim3(R), dim3(1024), 0, stream, out, logits, rows, temps, seeds, out_positions, V, n_logit_rows);
     return launch_status();
 }
 
@@ -208,8 +216,8 @@ extern "C" int cvb_sample_chunked(int* out, const float* logits, const int* rows
     float* pv = static_cast<float*>(scratch);
     int* pi = reinterpret_cast<int*>(pv + static_cast<int64_t>(R) * n_chunks);
     dim3 grid(static_cast<unsigned>(R), static_cast<unsigned>(n_chunks));
-    sample_partial_kernel<<<grid, 256, 0, stream>>>(pv, pi, logits, rows, temps, seeds, out_positions, V, n_logit_rows, n_chunks);
-    sample_final_kernel<<<R, 32, 0, stream>>>(out, pv, pi, V, n_chunks);
+    launch_kernel(sample_partial_kernel, dim3(grid), dim3(256), 0, stream, pv, pi, logits, rows, temps, seeds, out_positions, V, n_logit_rows, n_chunks);
+    launch_kernel(sample_final_kernel, dim3(R), dim3(32), 0, stream, out, pv, pi, V, n_chunks);
     return launch_status();
 }
 
@@ -217,6 +225,6 @@ extern "C" int cvb_feed_tokens(int* tokens, const int* src, const int* sampled, 
                                cudaStream_t stream) {
     if (n == 0) return CVB_OK;
     if (n < 0) return CVB_E_SIZE;
-    feed_tokens_kernel<<<(n + 255) / 256, 256, 0, stream>>>(tokens, src, sampled, n, n_sampled);
+    launch_kernel(feed_tokens_kernel, dim3((n + 255) / 256), dim3(256), 0, stream, tokens, src, sampled, n, n_sampled);
     return launch_status();
 }
