@@ -24,7 +24,7 @@ def _engine_flags(p: argparse.ArgumentParser, util: float) -> None:
     p.add_argument("--max-model-len", type=int, default=4096)
     p.add_argument("--gpu-memory-utilization", type=float, default=util)
     p.add_argument("--num-kv-blocks", type=int, default=-1)
-    p.add_argument("--block-size", type=int, default=16)
+    p.add_argument("--block-size", type=int, default=32)
     p.add_argument("--enforce-eager", action="store_true")
     p.add_argument("--seed", type=int, default=0)
 

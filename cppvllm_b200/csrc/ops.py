@@ -262,10 +262,12 @@ def attn_bf16():
     return _attn
 
 
-def fast_attention_supported(dtype: torch.dtype, num_heads: int, num_kv_heads: int, head_dim: int) -> bool:
-    """The tensor-core kernels cover bf16, head sizes 64 and 128 and up to 16 query heads per kv head."""
+def fast_attention_supported(dtype: torch.dtype, num_heads: int, num_kv_heads: int, head_dim: int,
+                             page_size: int = 16) -> bool:
+    """The tensor-core kernels cover bf16, head sizes 64 and 128, up to 16 query heads per kv head and pages of
+    16, 32, 64, ... tokens (a power of two)."""
     return (dtype == torch.bfloat16 and head_dim in (64, 128) and num_heads % num_kv_heads == 0
-            and num_heads // num_kv_heads <= 16)
+            and num_heads // num_kv_heads <= 16 and page_size >= 16 and page_size & (page_size - 1) == 0)
 
 
 def prefill_tiles(q_lens, num_heads: int, num_kv_heads: int, skip_single: bool = True) -> int:

@@ -52,7 +52,7 @@ GRAPH_BUCKETS = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256)
 
 
 class ModelRunner:
-    def __init__(self, model_dir: str, dtype=torch.bfloat16, device="cuda:0", page_size: int = 16,
+    def __init__(self, model_dir: str, dtype=torch.bfloat16, device="cuda:0", page_size: int = 32,
                  num_pages: Optional[int] = None, max_step_tokens: int = 4096, max_seqs: int = 256,
                  max_model_len: int = 4096, gpu_memory_utilization: float = 0.90, enforce_eager: bool = False,
                  num_state_slots: Optional[int] = None):

@@ -33,7 +33,7 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--out", required=True, help="folder that receives <step>.f32")
     p.add_argument("--max-tokens", type=int, required=True,
                    help="tokens the cache pool holds (each live request's count rounded up to a multiple of 64)")
-    p.add_argument("--block-size", type=int, default=16, help="tokens per cache page (must divide 64)")
+    p.add_argument("--block-size", type=int, default=32, help="tokens per cache page (must divide 64)")
     p.add_argument("--max-num-seqs", type=int, default=16, help="most requests in one step")
     p.add_argument("--enforce-eager", action="store_true", help="never replay CUDA graphs for decode-only steps")
     return p

@@ -151,7 +151,7 @@ def main(argv=None) -> int:
     p.add_argument("--heads", type=int, default=16)
     p.add_argument("--kv-heads", type=int, default=8)
     p.add_argument("--head-dim", type=int, default=128)
-    p.add_argument("--page-size", type=int, default=16)
+    p.add_argument("--page-size", type=int, default=32)
     p.add_argument("--splits", type=int, default=0)
     p.add_argument("--rows", type=int, default=4096)
     p.add_argument("--cols", type=int, default=1024)

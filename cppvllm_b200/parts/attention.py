@@ -134,7 +134,7 @@ class PagedAttention(Mixer):
 
     def attend(self, att, q, ctx, cache, g):
         H, KV, hd = self.num_heads, self.num_kv_heads, self.head_dim
-        if not self.force_general and ops.fast_attention_supported(q.dtype, H, KV, hd):
+        if not self.force_general and ops.fast_attention_supported(q.dtype, H, KV, hd, g.page_size):
             S = ctx.num_seqs
             q_lens = ctx.q_lens if ctx.q_lens is not None else [1] * S
             tiles = ops.prefill_tiles(q_lens, H, KV)
