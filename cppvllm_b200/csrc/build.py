@@ -35,6 +35,7 @@ LIBRARIES: Dict[str, List[str]] = {
     "core": ["elementwise.cu", "qk_rope_kv.cu", "attention_general.cu", "sampling.cu"],
     "attn_bf16": ["attention_bf16.cu"],
     "gemv_bf16": ["gemv_bf16.cu"],
+    "gemm_bf16": ["gemm_tcgen05.cu"],
 }
 
 _HEADERS = ["common.cuh", "attention_bf16.h"]

@@ -361,6 +361,41 @@ def gemv_bf16(out: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, rows: in
     return out
 
 
+_gemm = None
+
+
+def gemm_tcgen05_supported(x_dtype: torch.dtype, weight: torch.Tensor, swiglu: bool = False) -> bool:
+    """The tcgen05 product covers bf16 operands with inner sizes that are multiples of 8 and output widths that are
+    multiples of 8."""
+    n_out = weight.shape[0] // 2 if swiglu else weight.shape[0]
+    return (x_dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and weight.shape[1] % 8 == 0 and n_out % 8 == 0
+            and (not swiglu or weight.shape[0] % 2 == 0))
+
+
+def gemm_bf16_tcgen05(out: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, swiglu: bool = False, tile_n: int = 0) -> torch.Tensor:
+    """out = x @ weight^T on the tcgen05 tensor cores; with `swiglu`, weight holds gate rows over up rows and
+    out = silu(x @ gate^T) * (x @ up^T).  `tile_n` (128 or 256) picks the tile width; 0 chooses by the grid it gives."""
+    global _gemm
+    if _gemm is None:
+        lib = load_library("gemm_bf16")
+        lib.cvb_gemm_bf16_tcgen05.restype = c_int
+        _gemm = lib
+    _cuda(out, x, weight); _contig(out, x, weight)
+    M, K = x.shape
+    N = weight.shape[0]
+    n_out = N // 2 if swiglu else N
+    if x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or weight.shape[1] != K \
+            or out.shape != (M, n_out):
+        raise KernelError("gemm_bf16_tcgen05: x [M, K], weight [N, K], out [M, N] (or [M, N / 2] with swiglu), all bf16")
+    if tile_n == 0:
+        # tiles of 256 columns halve the traffic of A; take them when they still fill the SMs
+        tiles_256 = ((M + 127) // 128) * ((N + 255) // 256)
+        tile_n = 256 if tiles_256 >= 120 else 128
+    _check(_gemm.cvb_gemm_bf16_tcgen05(_ptr(out), _ptr(x), _ptr(weight), c_int(M), c_int(N), c_int(K), c_int(1 if swiglu else 0),
+                                       c_int(tile_n), _ptr(error_flag(x.device)), _stream()), "gemm_bf16_tcgen05")
+    return out
+
+
 # ---- sampling ----------------------------------------------------------------------------------------------
 
 def sample(out: torch.Tensor, logits: torch.Tensor, rows: Optional[torch.Tensor], temps: torch.Tensor,

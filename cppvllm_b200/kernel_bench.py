@@ -140,9 +140,36 @@ def gemv_fused(a) -> dict:
             "GBps": round(nbytes / us / 1e3, 1)}
 
 
+def gemm(a) -> dict:
+    """Prefill-sized product: the package's tcgen05 kernel (plain or with the SwiGLU epilogue) and the library's."""
+    from .csrc import ops
+    d = torch.device("cuda:0")
+    M, N, K = a.tokens, a.rows, a.cols
+    w = (torch.randn(N, K, device=d) * 0.05).to(torch.bfloat16)
+    x = torch.randn(M, K, device=d).to(torch.bfloat16)
+    swiglu = a.form == "swiglu"
+    out = torch.empty(M, N // 2 if swiglu else N, device=d, dtype=torch.bfloat16)
+    lib_out = torch.empty(M, N, device=d, dtype=torch.bfloat16)
+    act = torch.empty(M, N // 2, device=d, dtype=torch.bfloat16)
+
+    def ours(i):
+        ops.gemm_bf16_tcgen05(out, x, w, swiglu=swiglu, tile_n=a.tile_n)
+
+    def library(i):
+        ops.linear(x, w, out=lib_out)
+        if swiglu:
+            ops.swiglu(act, lib_out)
+    us, us_lib = _time(ours, a.iters), _time(library, a.iters)
+    ops.check_device_errors(d)
+    flops = 2.0 * M * N * K
+    return {"kernel": f"gemm_bf16_tcgen05 ({a.form})", "M": M, "N": N, "K": K, "us": round(us, 2), "TFLOPs": round(flops / us / 1e6, 1),
+            "library_us": round(us_lib, 2), "library_TFLOPs": round(flops / us_lib / 1e6, 1)}
+
+
 def main(argv=None) -> int:
     p = argparse.ArgumentParser(prog="kernel_bench")
-    p.add_argument("kernel", choices=["attn_decode", "attn_prefill", "gemv", "gemv_fused"])
+    p.add_argument("kernel", choices=["attn_decode", "attn_prefill", "gemv", "gemv_fused", "gemm"])
+    p.add_argument("--tile-n", type=int, default=0)
     p.add_argument("--form", default="plain", choices=["plain", "norm", "swiglu"])
     p.add_argument("--batch", type=int, default=8)
     p.add_argument("--context", type=int, default=4096)
@@ -159,7 +186,7 @@ def main(argv=None) -> int:
     a = p.parse_args(argv)
     if a.kernel == "attn_prefill" and a.batch == 8 and "--batch" not in (argv or sys.argv):
         a.batch = 1
-    res = {"attn_decode": attn_decode, "attn_prefill": attn_prefill, "gemv": gemv, "gemv_fused": gemv_fused}[a.kernel](a)
+    res = {"attn_decode": attn_decode, "attn_prefill": attn_prefill, "gemv": gemv, "gemv_fused": gemv_fused, "gemm": gemm}[a.kernel](a)
     print(json.dumps(res))
     return 0
 

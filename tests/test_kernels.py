@@ -470,3 +470,34 @@ def test_gemv_plain_norm_and_swiglu_forms(ops, M, N, K):
     torch.testing.assert_close(out2.float(), rnd(rnd(gate / (1 + torch.exp(-gate)), dt) * up, dt), atol=3e-2, rtol=3e-2)
     with pytest.raises(ops.KernelError, match="resid_out"):
         ops.gemv_bf16(out, x, W, M, norm_weight=nw, eps=eps, delta=delta, resid_out=x)
+
+
+# ---- tcgen05 matrix product -----------------------------------------------------------------------------------
+
+@pytest.mark.parametrize("M,N,K,tile_n", [(128, 128, 64, 128), (2048, 1024, 2048, 128), (300, 520, 200, 128), (1, 8, 8, 128),
+                                          (257, 4096, 1024, 256), (129, 264, 3072, 256)])
+def test_tcgen05_gemm_against_float32(ops, M, N, K, tile_n):
+    g = torch.Generator().manual_seed(M + N + K)
+    d = dev()
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16).to(d)
+    w = (torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16).to(d)
+    out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=d)
+    ops.gemm_bf16_tcgen05(out, x, w, tile_n=tile_n)
+    ops.check_device_errors(d)
+    ref = x.float() @ w.float().t()
+    torch.testing.assert_close(out.float(), rnd(ref, torch.bfloat16), atol=2e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("M,I,K", [(128, 128, 64), (2048, 3072, 1024), (77, 200, 136)])
+def test_tcgen05_gemm_with_swiglu_epilogue(ops, M, I, K):
+    dt = torch.bfloat16
+    g = torch.Generator().manual_seed(M + I + K)
+    d = dev()
+    x = torch.randn(M, K, generator=g).to(dt).to(d)
+    w = (torch.randn(2 * I, K, generator=g) * 0.08).to(dt).to(d)
+    out = torch.full((M, I), float("nan"), dtype=dt, device=d)
+    ops.gemm_bf16_tcgen05(out, x, w, swiglu=True)
+    ops.check_device_errors(d)
+    gu = rnd(x.float() @ w.float().t(), dt)
+    gate, up = gu[:, :I], gu[:, I:]
+    torch.testing.assert_close(out.float(), rnd(rnd(gate / (1 + torch.exp(-gate)), dt) * up, dt), atol=3e-2, rtol=3e-2)
