@@ -87,15 +87,21 @@ def attn_prefill(a) -> dict:
     H, KV, hd, page = a.heads, a.kv_heads, a.head_dim, a.page_size
     caches, tables, q, cu, pos = _paged_inputs(a.batch, a.tokens + a.cached, a.tokens, H, KV, hd, page, 1)
     out = torch.empty_like(q)
-    tiles = ops.prefill_tiles([a.tokens] * a.batch, H, KV)
     scale = 1 / math.sqrt(hd)
+    if a.impl == "tcgen05":
+        tiles = ops.prefill_tiles_tcgen05([a.tokens] * a.batch, H, KV)
 
-    def run(i):
-        ops.attn_prefill_bf16(out, q, caches[0], tables, cu, pos, a.batch, tiles, H, KV, hd, page, scale)
+        def run(i):
+            ops.attn_prefill_tcgen05(out, q, caches[0], tables, cu, pos, a.batch, tiles, H, KV, hd, page, scale)
+    else:
+        tiles = ops.prefill_tiles([a.tokens] * a.batch, H, KV)
+
+        def run(i):
+            ops.attn_prefill_bf16(out, q, caches[0], tables, cu, pos, a.batch, tiles, H, KV, hd, page, scale)
     us = _time(run, a.iters)
     ops.check_device_errors(q.device)
     flops = a.batch * 4 * H * hd * (a.tokens * (a.tokens + 1) // 2 + a.tokens * a.cached)
-    return {"kernel": "attn_prefill_bf16", "batch": a.batch, "tokens": a.tokens, "cached": a.cached, "us": round(us, 2),
+    return {"kernel": f"attn_prefill ({a.impl})", "batch": a.batch, "tokens": a.tokens, "cached": a.cached, "us": round(us, 2),
             "TFLOPs": round(flops / us / 1e6, 1), "flops": flops}
 
 
@@ -170,6 +176,7 @@ def main(argv=None) -> int:
     p = argparse.ArgumentParser(prog="kernel_bench")
     p.add_argument("kernel", choices=["attn_decode", "attn_prefill", "gemv", "gemv_fused", "gemm"])
     p.add_argument("--tile-n", type=int, default=0)
+    p.add_argument("--impl", default="tcgen05", choices=["tcgen05", "mma"])
     p.add_argument("--form", default="plain", choices=["plain", "norm", "swiglu"])
     p.add_argument("--batch", type=int, default=8)
     p.add_argument("--context", type=int, default=4096)

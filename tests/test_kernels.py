@@ -348,9 +348,10 @@ def test_feed_tokens(ops):
 
 # ---- tensor-core attention (bf16, head sizes 64 and 128) against the plain restatement -----------------------
 
+@pytest.mark.parametrize("prefill", ["tcgen05", "mma"])
 @pytest.mark.parametrize("H,KV,hd,page,window", [(4, 2, 128, 16, 0), (6, 2, 64, 16, 0), (8, 1, 128, 32, 0), (5, 5, 64, 64, 0),
                                                  (16, 8, 128, 16, 0), (14, 2, 128, 16, 150), (3, 1, 64, 16, 70), (32, 2, 64, 16, 0)])
-def test_tensor_core_attention_mixed_portions_and_single_tokens(ops, H, KV, hd, page, window):
+def test_tensor_core_attention_mixed_portions_and_single_tokens(ops, H, KV, hd, page, window, prefill):
     dt = torch.bfloat16
     g = torch.Generator().manual_seed(H * 7 + hd + page)
     # (tokens already in the cache, tokens in this step): portions at the start, in the middle, crossing tile and page
@@ -373,9 +374,12 @@ def test_tensor_core_attention_mixed_portions_and_single_tokens(ops, H, KV, hd, 
     q_lens = [n for _, n in reqs]
     cu_t = torch.tensor(cu, dtype=torch.int32, device=d)
     pos_t = torch.tensor(positions, dtype=torch.int32, device=d)
-    tiles = ops.prefill_tiles(q_lens, H, KV)
-    ops.attn_prefill_bf16(out, q.view(T, -1).to(d), cache.to(d), tables.to(d), cu_t, pos_t, len(reqs), tiles, H, KV, hd, page,
-                          scale, window=window)
+    if prefill == "tcgen05":
+        ops.attn_prefill_tcgen05(out, q.view(T, -1).to(d), cache.to(d), tables.to(d), cu_t, pos_t, len(reqs),
+                                 ops.prefill_tiles_tcgen05(q_lens, H, KV), H, KV, hd, page, scale, window=window)
+    else:
+        ops.attn_prefill_bf16(out, q.view(T, -1).to(d), cache.to(d), tables.to(d), cu_t, pos_t, len(reqs),
+                              ops.prefill_tiles(q_lens, H, KV), H, KV, hd, page, scale, window=window)
     results = {}
     for splits in (1, 3, 7):
         o2 = out.clone()
@@ -411,8 +415,8 @@ def test_tensor_core_attention_finds_one_far_key(ops):
     qq = torch.cat([q[:1], q[1:2], q[:1]]).to(dt)     # request 1 brings two tokens at positions n-2, n-1; its last equals token 0
     pos = torch.tensor([n - 1, n - 2, n - 1], dtype=torch.int32, device=d)
     out = torch.zeros(3, H * hd, dtype=dt, device=d)
-    ops.attn_prefill_bf16(out, qq.view(3, -1).to(d), cache.to(d), tables.to(d), cu, pos, 2, ops.prefill_tiles([1, 2], H, KV), H, KV,
-                          hd, page, 1 / math.sqrt(hd))
+    ops.attn_prefill_tcgen05(out, qq.view(3, -1).to(d), cache.to(d), tables.to(d), cu, pos, 2, ops.prefill_tiles_tcgen05([1, 2], H, KV),
+                             H, KV, hd, page, 1 / math.sqrt(hd))
     scratch = torch.zeros(ops.attn_decode_scratch_floats(2, KV, hd, 5), device=d)
     ops.attn_decode_bf16(out, qq.view(3, -1).to(d), cache.to(d), tables.to(d), cu, pos, 2, H, KV, hd, page, 1 / math.sqrt(hd), 5, scratch)
     o = out.float().cpu().view(3, H, hd)
