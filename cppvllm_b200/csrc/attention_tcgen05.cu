@@ -11,12 +11,13 @@
 //                  S_j  = Q K_j^T   (M 128, N 128, K = head size; both operands K-major)       -> S buffer j % 2
 //                  PV_j = P_j V_j   (M 128, N = head size, K 128; P K-major, V MN-major)      -> PV buffer j % 2
 //              in the order S_0, S_1, PV_0, S_2, PV_1, ... so that the softmax of tile j + 1 runs beside PV_j;
-//   warps 2-5  softmax: one thread per query row reads its row of S_j with tcgen05.ld (two passes: maximum, then
-//              probabilities), keeps running maximum and sum, writes P_j as bf16 into shared memory in the layout
-//              the tensor core reads, then adds PV_{j-1} from tensor memory into its float accumulator of the output
-//              row (rescaled by the change of the maximum).  No value crosses threads.
+//   warps 2-9  softmax: two threads per query row, one for keys 0..63 of the tile and one for keys 64..127 (and the same
+//              halves of the output row).  A thread reads its half row of S_j with tcgen05.ld once, takes the
+//              maximum, swaps it with its partner through shared memory (one named barrier per tile), writes its half
+//              of P_j as bf16 into shared memory in the layout the tensor core reads, and then adds its half of
+//              PV_{j-1} from tensor memory into its float accumulator (rescaled by the change of the maximum).
 // Buffers are handed over with mbarriers: TMA transaction counts, tcgen05.commit arrivals from the tensor core, and
-// plain arrivals from the 128 softmax threads.  Every wait is bounded by a cycle count; a wait that runs out records
+// plain arrivals from the 256 softmax threads.  Every wait is bounded by a cycle count; a wait that runs out records
 // error 5 and the block runs on to its end (tensor memory is always given back).
 #include "common.cuh"
 
@@ -30,7 +31,8 @@ constexpr int kTM = 128;                      // query rows per block
 constexpr int kTN = 128;                      // keys per tile
 constexpr int kKStages = 3;
 constexpr int kVStages = 2;
-constexpr int kTcThreads = 192;
+constexpr int kSoftmaxThreads = 256;           // two threads per query row: each owns half of the columns
+constexpr int kTcThreads = 64 + kSoftmaxThreads;
 constexpr float kLog2eF = 1.4426950408889634f;
 
 __device__ __forceinline__ uint32_t saddr(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -127,7 +129,8 @@ struct TcSmem {
     static constexpr int kTile = 128 * HD * 2;                       // bytes of a [128][HD] bf16 tile
     static constexpr int kP = 128 * kTN * 2;                         // bytes of P [128][128]
     static constexpr int kNumBars = 2 * kKStages + 2 * kVStages + 2 + 2 + 1 + 1 + 2 + 2;
-    static constexpr size_t kBytes = 1024 + static_cast<size_t>(kTile) * (1 + kKStages + kVStages) + kP + kNumBars * 8 + 16;
+    // no slack for alignment: with 128-wide heads the tiles leave 3 KB of the 227 KB; the kernel checks the base instead
+    static constexpr size_t kBytes = static_cast<size_t>(kTile) * (1 + kKStages + kVStages) + kP + kNumBars * 8 + 16 + 2 * 2 * 128 * 4;
 };
 
 // One thread: fetch keys [key0, key0 + 128) of one kv head (`which` 0 = K, 1 = V) into a tile.
@@ -154,9 +157,11 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, const Tc
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     using L = TcSmem<HD>;
     pdl_trigger();
-    const uint32_t raw = saddr(smem_raw);
-    unsigned char* base = smem_raw + ((1024u - (raw & 1023u)) & 1023u);
-    unsigned char* sQ = base;
+    if ((saddr(smem_raw) & 1023u) != 0) {            // the swizzled tiles need a 1024-byte aligned base
+        if (threadIdx.x == 0) atomicExch(p.err, 6);
+        return;
+    }
+    unsigned char* sQ = smem_raw;
     unsigned char* sK = sQ + L::kTile;
     unsigned char* sV = sK + kKStages * L::kTile;
     unsigned char* sP = sV + kVStages * L::kTile;
@@ -172,6 +177,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, const Tc
     uint64_t* pv_full = p_empty + 1;               // [2]  tensor core
     uint64_t* pv_empty = pv_full + 2;              // [2]  128 softmax threads
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_empty + 2);
+    float* xch = reinterpret_cast<float*>(tmem_slot + 4);           // [2 tiles in flight][2 halves][128 rows]
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g = p.H / p.KV;
@@ -204,8 +210,11 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, const Tc
     if (threadIdx.x == 0) {
         for (int i = 0; i < kKStages; ++i) { mb_init(k_full + i, 1); mb_init(k_empty + i, 1); }
         for (int i = 0; i < kVStages; ++i) { mb_init(v_full + i, 1); mb_init(v_empty + i, 1); }
-        for (int i = 0; i < 2; ++i) { mb_init(s_full + i, 1); mb_init(s_empty + i, 128); mb_init(pv_full + i, 1); mb_init(pv_empty + i, 128); }
-        mb_init(p_full, 128);
+        for (int i = 0; i < 2; ++i) {
+            mb_init(s_full + i, 1); mb_init(s_empty + i, kSoftmaxThreads);
+            mb_init(pv_full + i, 1); mb_init(pv_empty + i, kSoftmaxThreads);
+        }
+        mb_init(p_full, kSoftmaxThreads);
         mb_init(p_empty, 1);
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
@@ -279,30 +288,38 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, const Tc
                 commit_to(v_empty + vs);
             }
         }
-    } else {                                         // ---- softmax: one thread per query row ----
+    } else {                                         // ---- softmax: two threads per query row ----
+        constexpr int HC = HD / 2;                   // output columns per thread
         const int quarter = warp & 3;
+        const int half = (warp - 2) >> 2;            // 0: keys / columns of the first half, 1: of the second
         const int r = quarter * 32 + lane;
         const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
         const int tok = min(r / g, n_tok - 1);
         const int row_pos = p.positions[cu0 + q0 + tok];
         const int row_lo = p.window > 0 ? max(0, row_pos - p.window + 1) : 0;
-        float o[HD];
+        float o[HC];
 #pragma unroll
-        for (int i = 0; i < HD; ++i) o[i] = 0.f;
+        for (int i = 0; i < HC; ++i) o[i] = 0.f;
         float m = -INFINITY, l = 0.f, corr_prev = 0.f;
         __nv_bfloat16* prow = reinterpret_cast<__nv_bfloat16*>(sP);
 
-        auto add_pv = [&](int j, float corr) {      // o = o * corr + PV_j
+        auto add_pv = [&](int j, float corr) {      // o = o * corr + (this thread's half of) PV_j
             const int b = j & 1;
             mb_wait(pv_full + b, (j >> 1) & 1, p.err);
             tc_after();
+            const float2 corr2 = make_float2(corr, corr);
 #pragma unroll
-            for (int c0 = 0; c0 < HD; c0 += 32) {
+            for (int c0 = 0; c0 < HC; c0 += 32) {
                 uint32_t v[32];
-                tm_load32(tPV[b] + lane_base + c0, v);
+                tm_load32(tPV[b] + lane_base + half * HC + c0, v);
                 tm_wait_ld();
 #pragma unroll
-                for (int i = 0; i < 32; ++i) o[c0 + i] = fmaf(o[c0 + i], corr, __uint_as_float(v[i]));
+                for (int i = 0; i < 32; i += 2) {                    // two columns per packed multiply-add
+                    const float2 acc = __ffma2_rn(make_float2(o[c0 + i], o[c0 + i + 1]), corr2,
+                                                  make_float2(__uint_as_float(v[i]), __uint_as_float(v[i + 1])));
+                    o[c0 + i] = acc.x;
+                    o[c0 + i + 1] = acc.y;
+                }
             }
             tc_before();
             mb_arrive(pv_empty + b);
@@ -310,59 +327,58 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, const Tc
 
         for (int j = 0; j < n_tiles; ++j) {
             const int b = j & 1;
-            const int key0 = (tile_begin + j) * kTN;
-            const bool need_mask = key0 + kTN - 1 > row_pos || key0 < row_lo;
+            const int key0 = (tile_begin + j) * kTN + half * 64;     // first key of this thread's 64
+            const bool need_mask = key0 + 63 > row_pos || key0 < row_lo;
             mb_wait(s_full + b, (j >> 1) & 1, p.err);
             tc_after();
-            // pass 1: the row's maximum over this tile
-            float tile_max = -INFINITY;
+            uint32_t v[64];
+            tm_load32(tS[b] + lane_base + half * 64, *reinterpret_cast<uint32_t(*)[32]>(&v[0]));
+            tm_load32(tS[b] + lane_base + half * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&v[32]));
+            tm_wait_ld();
+            tc_before();
+            mb_arrive(s_empty + b);                                  // S_j is in registers: its buffer may be refilled
+            if (need_mask) {
 #pragma unroll
-            for (int c0 = 0; c0 < kTN; c0 += 32) {
-                uint32_t v[32];
-                tm_load32(tS[b] + lane_base + c0, v);
-                tm_wait_ld();
-#pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    float s = __uint_as_float(v[i]);
-                    if (need_mask) { const int key = key0 + c0 + i; if (key > row_pos || key < row_lo) s = -INFINITY; }
-                    tile_max = fmaxf(tile_max, s);
+                for (int i = 0; i < 64; ++i) {
+                    const int key = key0 + i;
+                    if (key > row_pos || key < row_lo) v[i] = 0xff800000u;     // -inf
                 }
             }
+            float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};       // four chains instead of one long one
+#pragma unroll
+            for (int i = 0; i < 64; i += 4) {
+#pragma unroll
+                for (int k = 0; k < 4; ++k) mx[k] = fmaxf(mx[k], __uint_as_float(v[i + k]));
+            }
+            float tile_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+            // the row's maximum is the larger of the two halves'
+            xch[(b * 2 + half) * 128 + r] = tile_max;
+            asm volatile("bar.sync 1, %0;\n" ::"n"(kSoftmaxThreads) : "memory");
+            tile_max = fmaxf(tile_max, xch[(b * 2 + (half ^ 1)) * 128 + r]);
             const float m_new = fmaxf(m, tile_max * p.scale_log2);
             const float m_use = m_new == -INFINITY ? 0.f : m_new;
             const float corr = ex2(m - m_use);                       // 2^(-inf) = 0 at the first tile
             m = m_new;
-            // pass 2: probabilities, rounded to bf16, into the P tile; it must be free (PV_{j-1} has read it)
+            // probabilities, rounded to bf16, into this thread's half row of the P tile (free once PV_{j-1} has read it)
             if (j > 0) mb_wait(p_empty, (j - 1) & 1, p.err);
-            float tile_sum = 0.f;
+            const float2 scale2 = make_float2(p.scale_log2, p.scale_log2), neg_m2 = make_float2(-m_use, -m_use);
+            float2 sum2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
 #pragma unroll
-            for (int c0 = 0; c0 < kTN; c0 += 32) {
-                uint32_t v[32];
-                tm_load32(tS[b] + lane_base + c0, v);
-                tm_wait_ld();
-                uint32_t packed[16];
+            for (int c = 0; c < 8; ++c) {
+                uint32_t packed[4];
 #pragma unroll
-                for (int i = 0; i < 32; i += 2) {
-                    float s0 = __uint_as_float(v[i]), s1 = __uint_as_float(v[i + 1]);
-                    if (need_mask) {
-                        const int key = key0 + c0 + i;
-                        if (key > row_pos || key < row_lo) s0 = -INFINITY;
-                        if (key + 1 > row_pos || key + 1 < row_lo) s1 = -INFINITY;
-                    }
-                    const float p0 = ex2(fmaf(s0, p.scale_log2, -m_use)), p1 = ex2(fmaf(s1, p.scale_log2, -m_use));
-                    __nv_bfloat162 h = __floats2bfloat162_rn(p0, p1);
-                    // the sum is taken over the rounded values, as the product with V sees them
-                    tile_sum += __bfloat162float(h.x) + __bfloat162float(h.y);
-                    packed[i >> 1] = *reinterpret_cast<uint32_t*>(&h);
+                for (int i = 0; i < 4; ++i) {
+                    const float2 arg = __ffma2_rn(make_float2(__uint_as_float(v[c * 8 + 2 * i]), __uint_as_float(v[c * 8 + 2 * i + 1])),
+                                                  scale2, neg_m2);
+                    const float2 pr = make_float2(ex2(arg.x), ex2(arg.y));
+                    sum2[i & 1] = __fadd2_rn(sum2[i & 1], pr);
+                    __nv_bfloat162 h = __floats2bfloat162_rn(pr.x, pr.y);
+                    packed[i] = *reinterpret_cast<uint32_t*>(&h);
                 }
-#pragma unroll
-                for (int cc = 0; cc < 4; ++cc)
-                    *reinterpret_cast<uint4*>(prow + tile_off(r, (c0 >> 3) + cc)) =
-                        make_uint4(packed[cc * 4], packed[cc * 4 + 1], packed[cc * 4 + 2], packed[cc * 4 + 3]);
+                *reinterpret_cast<uint4*>(prow + tile_off(r, half * 8 + c)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
             }
+            const float tile_sum = (sum2[0].x + sum2[0].y) + (sum2[1].x + sum2[1].y);
             l = l * corr + tile_sum;
-            tc_before();
-            mb_arrive(s_empty + b);                                  // S_j has been read
             fence_async_smem();                                      // P_j is visible to the tensor core
             mb_arrive(p_full);
             if (j > 0) add_pv(j - 1, corr_prev);
@@ -370,11 +386,16 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, const Tc
         }
         add_pv(n_tiles - 1, corr_prev);
 
+        // the row's sum is the sum of the two halves'
+        asm volatile("bar.sync 1, %0;\n" ::"n"(kSoftmaxThreads) : "memory");      // everyone has read the last maxima
+        xch[half * 128 + r] = l;
+        asm volatile("bar.sync 1, %0;\n" ::"n"(kSoftmaxThreads) : "memory");
+        l += xch[(half ^ 1) * 128 + r];
         if (r / g < n_tok) {
             const float inv = l > 0.f ? 1.f / l : 0.f;
-            __nv_bfloat16* dst = p.out + (static_cast<int64_t>(cu0 + q0 + r / g) * p.H + kvh * g + r % g) * HD;
+            __nv_bfloat16* dst = p.out + (static_cast<int64_t>(cu0 + q0 + r / g) * p.H + kvh * g + r % g) * HD + half * HC;
 #pragma unroll
-            for (int c = 0; c < HD; c += 8) {
+            for (int c = 0; c < HC; c += 8) {
                 uint4 t;
                 __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&t);
 #pragma unroll

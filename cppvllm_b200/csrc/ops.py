@@ -29,6 +29,7 @@ DEVICE_ERRORS = {
     3: "a position lies outside the rotary tables (beyond max_position_embeddings)",
     4: "attention needed a key whose page is missing from the block table",
     5: "a bounded wait in a kernel ran out",
+    6: "a kernel found its shared memory misaligned for swizzled tiles",
 }
 
 

@@ -25,7 +25,8 @@ from .base import CacheSpec, Mixer, WeightSpec, register_part
 class PagedAttention(Mixer):
     def __init__(self, runtime, prefix="", names=None, *, hidden_size: int, num_heads: int, num_kv_heads: int,
                  head_dim: int, qk_norm: bool = True, qk_norm_eps: float = 1e-6, window: int = 0,
-                 scale: Optional[float] = None, position=None, force_general: bool = False):
+                 scale: Optional[float] = None, position=None, force_general: bool = False,
+                 prefill_kernel: str = "tcgen05"):
         super().__init__(runtime, prefix, names)
         if num_heads % num_kv_heads:
             raise ValueError(f"{num_heads} query heads are not a multiple of {num_kv_heads} key/value heads")
@@ -33,6 +34,9 @@ class PagedAttention(Mixer):
         self.qk_norm, self.qk_norm_eps, self.window = bool(qk_norm), float(qk_norm_eps), int(window)
         self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(self.head_dim)
         self.force_general = bool(force_general)     # always use the general kernel (tests compare the two)
+        if prefill_kernel not in ("tcgen05", "mma"):
+            raise ValueError("prefill_kernel must be 'tcgen05' or 'mma'")
+        self.prefill_kernel = prefill_kernel         # which tensor-core kernel runs prompt portions
         self.position = position            # a RotaryEmbedding part or None
         if self.position is not None and self.position.rotary_dim > self.head_dim:
             raise ValueError("rotary_dim exceeds head_dim")
@@ -137,10 +141,16 @@ class PagedAttention(Mixer):
         if not self.force_general and ops.fast_attention_supported(q.dtype, H, KV, hd, g.page_size):
             S = ctx.num_seqs
             q_lens = ctx.q_lens if ctx.q_lens is not None else [1] * S
-            tiles = ops.prefill_tiles(q_lens, H, KV)
-            if tiles:
-                ops.attn_prefill_bf16(att, q, cache.pages, g.block_tables, ctx.cu_seqlens, ctx.positions, S, tiles,
-                                      H, KV, hd, g.page_size, self.scale, window=self.window, skip_single=True)
+            if self.prefill_kernel == "tcgen05":
+                tiles = ops.prefill_tiles_tcgen05(q_lens, H, KV)
+                if tiles:
+                    ops.attn_prefill_tcgen05(att, q, cache.pages, g.block_tables, ctx.cu_seqlens, ctx.positions, S, tiles,
+                                             H, KV, hd, g.page_size, self.scale, window=self.window, skip_single=True)
+            else:
+                tiles = ops.prefill_tiles(q_lens, H, KV)
+                if tiles:
+                    ops.attn_prefill_bf16(att, q, cache.pages, g.block_tables, ctx.cu_seqlens, ctx.positions, S, tiles,
+                                          H, KV, hd, g.page_size, self.scale, window=self.window, skip_single=True)
             if any(n == 1 for n in q_lens):
                 splits = self.decode_splits(S, ctx.max_kv_len)
                 scratch = None
