@@ -4,7 +4,9 @@ cap), ``max_model_len`` (4096), ``gpu_memory_utilization`` (0.90), ``num_kv_bloc
 memory), ``enforce_eager`` (false = decode steps replay CUDA graphs), ``dtype`` and ``seed``.
 ``tensor_parallel_size`` exists only so that a value other than 1 is refused: this engine runs on one GPU.
 Added here: ``block_size`` (tokens per cache page; the reference fixes 16 in sequence.h:28; the default here is 32,
-because a TMA box is one page of one head and boxes of 32 rows reach the full HBM rate where boxes of 16 reach 3/4).
+because a TMA box is one page of one head and boxes of 32 rows reach the full HBM rate where boxes of 16 reach 3/4)
+and ``pipeline_depth`` (steps in flight: 2 as the reference's ``kDepth``, engine/llm_engine.h:51, or 1 to wait for
+every step's samples before the next step is scheduled).
 """
 from __future__ import annotations
 
@@ -43,6 +45,7 @@ class EngineConfig:
     dtype: object = "bfloat16"
     seed: int = 0
     block_size: int = 32
+    pipeline_depth: int = 2
     device: str = "cuda:0"
 
     def __post_init__(self):
@@ -53,5 +56,7 @@ class EngineConfig:
             raise ValueError(f"block_size must be a positive multiple of 16, got {self.block_size}")
         if self.max_num_batched_tokens <= 0 or self.max_num_seqs <= 0 or self.max_model_len <= 0:
             raise ValueError("max_num_batched_tokens, max_num_seqs and max_model_len must be positive")
+        if self.pipeline_depth not in (1, 2):
+            raise ValueError("pipeline_depth must be 1 or 2")
         if self.max_chunk_tokens < 0:
             raise ValueError("max_chunk_tokens must be >= 0 (0 = no cap)")

@@ -19,7 +19,7 @@ from ..config.engine_config import EngineConfig
 from ..sampling.params import SamplingParams
 from ..sampling.sampler import Sampler, mix_seed
 from .runner import ModelRunner, StepEntry
-from .scheduler import FINISHED, ScheduledBatch, Scheduler, SchedulerConfig, Sequence
+from .scheduler import FINISHED, PENDING, ScheduledBatch, Scheduler, SchedulerConfig, Sequence
 
 
 @dataclass
@@ -76,6 +76,8 @@ class LLMEngine:
         self._next_id = 0
         self._stats = EngineStats()
         self._empty_steps = 0
+        self._inflight: List[dict] = []
+        self._slot = 0
 
     # ---- requests ------------------------------------------------------------------------------------
     def add_request(self, prompt: Seq[int], params: Optional[SamplingParams] = None) -> int:
@@ -93,7 +95,7 @@ class LLMEngine:
         return rid
 
     def is_finished(self) -> bool:
-        return self.scheduler.is_finished()
+        return not self._inflight and self.scheduler.is_finished()
 
     @property
     def num_kv_blocks(self) -> int:
@@ -104,38 +106,79 @@ class LLMEngine:
 
     # ---- one step -------------------------------------------------------------------------------------
     def step(self) -> StepInfo:
+        """Schedule and launch one step; with ``pipeline_depth`` 2 the previous step's samples are read back only
+        after this one has been handed to the device (reference engine/llm_engine.cpp:70-113).  A token that is not
+        known on the host yet travels from the previous step's samples to this step's inputs on the device."""
         info = StepInfo()
-        if self.scheduler.is_finished():
-            return info
         t0 = time.perf_counter()
-        batch = self.scheduler.schedule()
+        if self.scheduler.is_finished():
+            self.sync(info)
+            return info
+        batch = self.scheduler.schedule(allow_preempt=not self._inflight)
         self._stats.preemptions = self.scheduler.num_preemptions
         if not batch.seqs:
+            if self._inflight:                                 # everything runnable waits for tokens in flight
+                self.sync(info)
+                self._account(info, t0)
+                return info
             self._empty_steps += 1
             if self._empty_steps > 2:
                 raise RuntimeError("the scheduler produced no work although requests are pending")
             return info
         self._empty_steps = 0
-        entries = []
+
+        prev = self._inflight[-1] if self._inflight else None
+        entries, feed_src, need_feed = [], [], False
         for seq in batch.seqs:
             c, n = seq.num_cached_tokens, seq.num_scheduled_tokens
-            entries.append(StepEntry(seq.seq_id, seq.token_ids[c:c + n], c, (n - 1,) if seq.samples_this_step() else ()))
-        logits = self.runner.step(entries)
-        flags = self.scheduler.on_launched(batch)
-        samplers = [s for s, f in zip(batch.seqs, flags) if f]
-        tokens = self.sampler.sample(
+            toks = seq.token_ids[c:c + n]
+            src = [-1] * n
+            if toks[-1] == PENDING:                            # sampled by the step in flight: fed on the device
+                toks = toks[:-1] + [0]
+                src[-1] = prev["index"][seq.seq_id]
+                need_feed = True
+            entries.append(StepEntry(seq.seq_id, toks, c, (n - 1,) if seq.samples_this_step() else ()))
+            feed_src.extend(src)
+        feed = (prev["sampled"], feed_src) if need_feed else None
+        logits = self.runner.step(entries, feed=feed)
+        samplers = [s for s in batch.seqs if s.samples_this_step()]
+        slot = self._slot
+        self._slot ^= 1
+        sampled_dev = self.sampler.sample_async(
             logits, [s.params.temperature for s in samplers], [s.row_seed for s in samplers],
-            [s.num_completion_tokens for s in samplers]) if samplers else []
-        finished = self.scheduler.postprocess(batch, flags, tokens)
-        for seq in finished:
-            self._harvest(seq)
+            [s.num_completion_tokens for s in samplers], slot=slot) if samplers else None
+        flags = self.scheduler.on_launched(batch)
+        self._inflight.append({"batch": batch, "flags": flags, "slot": slot, "n": len(samplers), "sampled": sampled_dev,
+                               "index": {s.seq_id: i for i, s in enumerate(samplers)}})
         info.num_seqs, info.num_tokens = len(batch.seqs), batch.total_tokens
-        info.num_sampled, info.num_finished = len(tokens), len(finished)
         self._stats.steps += 1
         self._stats.tokens_processed += batch.total_tokens
-        self._stats.tokens_generated += len(tokens)
-        self._stats.seconds += time.perf_counter() - t0
+        if batch.blocked:
+            self.sync(info)                                    # drain, so that the next schedule may preempt
+        else:
+            while len(self._inflight) >= self.config.pipeline_depth:
+                self._retire_oldest(info)
+        self._account(info, t0)
         return info
+
+    def _account(self, info: StepInfo, t0: float) -> None:
+        self._stats.tokens_generated += info.num_sampled
+        self._stats.seconds += time.perf_counter() - t0
+
+    def _retire_oldest(self, info: StepInfo) -> None:
+        rec = self._inflight.pop(0)
+        tokens = self.sampler.collect(rec["n"], slot=rec["slot"]) if rec["n"] else []
+        finished = self.scheduler.postprocess(rec["batch"], rec["flags"], tokens)
+        for seq in finished:
+            self._harvest(seq)
+        info.num_sampled += len(tokens)
+        info.num_finished += len(finished)
+
+    def sync(self, info: Optional[StepInfo] = None) -> None:
+        """Read back every step that is still in flight."""
+        info = info if info is not None else StepInfo()
+        while self._inflight:
+            self._retire_oldest(info)
 
     def _harvest(self, seq: Sequence) -> None:
         out = GenerationOutput(seq.seq_id, seq.token_ids[:seq.num_prompt_tokens], seq.token_ids[seq.num_prompt_tokens:],
@@ -161,6 +204,7 @@ class LLMEngine:
         ids = [self.add_request(p, sp) for p, sp in zip(prompts, plist)]
         while not self.is_finished():
             self.step()
+        self.sync()
         self.runner.check_errors()
         outs = []
         for rid in ids:

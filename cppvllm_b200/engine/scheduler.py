@@ -19,7 +19,12 @@ Policy after the reference's ``Scheduler`` (engine/scheduler.cpp):
 * a request whose prompt plus ``max_tokens`` can never fit the pool, or exceeds ``max_model_len``, is refused at
   ``add_request`` (:18-26);
 * a request finishes on an end-of-sequence token (unless ``ignore_eos``) or at ``max_tokens`` new tokens, and
-  its pages are freed at once (:123-155).
+  its pages are freed at once (:123-155);
+* with a step still in flight (the engine overlaps the host's work on step n + 1 with the device's work on step n,
+  engine/llm_engine.cpp:70-113) a request's newest token is a placeholder whose value is handed over on the device;
+  nothing is preempted while a step is in flight: a request that cannot grow is left out, the batch is marked
+  ``blocked`` and the engine drains its pipeline before it schedules again (:74-85, llm_engine.cpp:106-107); a request
+  that already has ``max_tokens`` tokens counting the placeholder is not scheduled again (:62-66).
 """
 from __future__ import annotations
 
@@ -31,12 +36,14 @@ from ..cache.manager import CacheManager
 from ..sampling.params import SamplingParams
 
 WAITING, RUNNING, FINISHED = "waiting", "running", "finished"
+PENDING = -1        # placeholder for a token that was sampled on the device but has not been read back yet
+                    # (reference engine/sequence.h:16, kPendingToken)
 
 
 class Sequence:
     """One request: its tokens (prompt, then generated), how many are in the cache, and its options."""
     __slots__ = ("seq_id", "token_ids", "num_prompt_tokens", "num_cached_tokens", "num_scheduled_tokens",
-                 "params", "status", "stopped_on_eos", "row_seed", "num_preemptions")
+                 "params", "status", "stopped_on_eos", "row_seed", "num_preemptions", "num_inflight")
 
     def __init__(self, seq_id: int, prompt: Seq[int], params: Optional[SamplingParams] = None):
         if len(prompt) == 0:
@@ -51,6 +58,7 @@ class Sequence:
         self.stopped_on_eos = False
         self.row_seed = 0
         self.num_preemptions = 0
+        self.num_inflight = 0
 
     def __len__(self) -> int:
         return len(self.token_ids)
@@ -81,6 +89,8 @@ class ScheduledBatch:
     seqs: List[Sequence] = field(default_factory=list)
     total_tokens: int = 0
     preempted: List[Sequence] = field(default_factory=list)
+    blocked: bool = False                      # a request could not grow and nothing may be preempted right now
+    sample_pos: List[int] = field(default_factory=list)   # per sequence: index in token_ids of its placeholder, or -1
 
     @property
     def all_single_token(self) -> bool:
@@ -121,7 +131,7 @@ class Scheduler:
         self.num_preemptions += 1
 
     # ---- one step's decisions --------------------------------------------------------------------------
-    def schedule(self) -> ScheduledBatch:
+    def schedule(self, allow_preempt: bool = True) -> ScheduledBatch:
         out = ScheduledBatch()
         budget = self.cfg.max_num_batched_tokens
         cap = self.cfg.max_chunk_tokens if self.cfg.max_chunk_tokens > 0 else 1 << 62
@@ -136,14 +146,21 @@ class Scheduler:
             out.total_tokens += n
             budget -= n
 
+        blocked = False
         while pending:
             seq = pending.popleft()
+            if seq.num_completion_tokens > 0 and seq.num_completion_tokens >= seq.params.max_tokens:
+                kept.append(seq)                       # its last token is still in flight
+                continue
             want = min(seq.num_uncached_tokens, budget, cap)
             if want <= 0 or len(out.seqs) >= self.cfg.max_num_seqs:
                 kept.append(seq)
                 continue
-            yielded = False
+            yielded = stuck = False
             while not self.cache.can_reserve(seq.seq_id, len(seq)):
+                if not allow_preempt:
+                    stuck = True
+                    break
                 if pending:
                     victim = pending.pop()
                 else:
@@ -153,6 +170,10 @@ class Scheduler:
                 preempted_now = True
                 if yielded:
                     break
+            if stuck:
+                blocked = True
+                kept.append(seq)
+                continue
             if yielded:
                 continue
             self.cache.reserve(seq.seq_id, len(seq))
@@ -160,7 +181,8 @@ class Scheduler:
             kept.append(seq)
         self.running = kept
 
-        while (not preempted_now and self.waiting and budget > 0 and len(self.running) < self.cfg.max_num_seqs
+        out.blocked = blocked
+        while (not preempted_now and not blocked and self.waiting and budget > 0 and len(self.running) < self.cfg.max_num_seqs
                and len(out.seqs) < self.cfg.max_num_seqs):
             seq = self.waiting[0]
             if self.cache.slots.num_free == 0 or not self.cache.can_reserve(seq.seq_id, len(seq)):
@@ -175,27 +197,42 @@ class Scheduler:
 
     # ---- after the step ----------------------------------------------------------------------------------
     def on_launched(self, batch: ScheduledBatch) -> List[bool]:
-        """The step ran: its tokens are in the cache.  Returns, per sequence, whether it sampled this step."""
+        """The step was handed to the device: its tokens count as cached, and every sequence that samples in it gets a
+        placeholder for the token that is not known on the host yet.  Returns, per sequence, whether it samples."""
         sampled = []
+        batch.sample_pos = []
         for seq in batch.seqs:
-            sampled.append(seq.samples_this_step())
+            samples = seq.samples_this_step()
+            sampled.append(samples)
             seq.num_cached_tokens += seq.num_scheduled_tokens
             seq.num_scheduled_tokens = 0
+            seq.num_inflight += 1
+            if samples:
+                batch.sample_pos.append(len(seq.token_ids))
+                seq.token_ids.append(PENDING)
+            else:
+                batch.sample_pos.append(-1)
         return sampled
 
     def postprocess(self, batch: ScheduledBatch, sampled_flags: List[bool], tokens: List[int]) -> List[Sequence]:
-        """Append the sampled tokens (`tokens` holds one per sampling sequence, in batch order); finish and free.
-        Returns the sequences that finished."""
+        """The step's samples arrived (`tokens`: one per sampling sequence, in batch order): they replace the
+        placeholders; requests finish and give back what they hold.  Results for a request that finished in an earlier
+        step while this one was in flight are dropped.  Returns the sequences that finished."""
         finished = []
         it = iter(tokens)
-        for seq, did in zip(batch.seqs, sampled_flags):
+        for seq, did, pos in zip(batch.seqs, sampled_flags, batch.sample_pos):
+            seq.num_inflight -= 1
             if not did:
                 continue
             tok = int(next(it))
-            seq.token_ids.append(tok)
+            if seq.status == FINISHED:
+                continue
+            seq.token_ids[pos] = tok
             hit_eos = (not seq.params.ignore_eos) and tok in self.cfg.eos_token_ids
-            hit_len = seq.num_completion_tokens >= seq.params.max_tokens
+            hit_len = pos + 1 - seq.num_prompt_tokens >= seq.params.max_tokens
             if hit_eos or hit_len:
+                del seq.token_ids[pos + 1:]               # a placeholder of a later step that is still in flight
+                seq.num_cached_tokens = min(seq.num_cached_tokens, len(seq.token_ids))
                 seq.stopped_on_eos = hit_eos
                 seq.status = FINISHED
                 self.cache.release(seq.seq_id)

@@ -26,20 +26,27 @@ def mix_seed(engine_seed: int, request_key: int) -> int:
 
 
 class Sampler:
+    """Two sets of buffers (`slot` 0 and 1) so that the samples of one step can still be on their way to the host
+    while the next step is being sampled."""
+
+    SLOTS = 2
+
     def __init__(self, device, max_rows: int):
         self.device = torch.device(device)
         self.max_rows = max_rows
-        # one pinned block: temps (float32 bits), out positions, seeds lo/hi interleaved as int64
-        self._host_f = torch.empty(max_rows, dtype=torch.float32, pin_memory=True)
-        self._host_p = torch.empty(max_rows, dtype=torch.int32, pin_memory=True)
-        self._host_s = torch.empty(max_rows, dtype=torch.int64, pin_memory=True)
-        self._temps = torch.zeros(max_rows, dtype=torch.float32, device=self.device)
-        self._pos = torch.zeros(max_rows, dtype=torch.int32, device=self.device)
-        self._seeds = torch.zeros(max_rows, dtype=torch.int64, device=self.device)
-        self._out = torch.zeros(max_rows, dtype=torch.int32, device=self.device)
-        self._out_host = torch.empty(max_rows, dtype=torch.int32, pin_memory=True)
+        n = self.SLOTS
+        self._host_f = [torch.empty(max_rows, dtype=torch.float32, pin_memory=True) for _ in range(n)]
+        self._host_p = [torch.empty(max_rows, dtype=torch.int32, pin_memory=True) for _ in range(n)]
+        self._host_s = [torch.empty(max_rows, dtype=torch.int64, pin_memory=True) for _ in range(n)]
+        self._temps = [torch.zeros(max_rows, dtype=torch.float32, device=self.device) for _ in range(n)]
+        self._pos = [torch.zeros(max_rows, dtype=torch.int32, device=self.device) for _ in range(n)]
+        self._seeds = [torch.zeros(max_rows, dtype=torch.int64, device=self.device) for _ in range(n)]
+        self._out = [torch.zeros(max_rows, dtype=torch.int32, device=self.device) for _ in range(n)]
+        self._out_host = [torch.empty(max_rows, dtype=torch.int32, pin_memory=True) for _ in range(n)]
+        self._done = [None] * n
         self._chunks = 32
         self._scratch = torch.empty(max_rows * self._chunks * 2, dtype=torch.float32, device=self.device)
+        self.h2d_bytes_last = 0
 
     def sample(self, logits: torch.Tensor, temps: Sequence[float], seeds: Sequence[int],
                out_positions: Sequence[int]) -> List[int]:
@@ -47,31 +54,38 @@ class Sampler:
         R = logits.shape[0]
         if R == 0:
             return []
-        self.sample_async(logits, temps, seeds, out_positions)
-        return self.collect(R)
+        self.sample_async(logits, temps, seeds, out_positions, slot=0)
+        return self.collect(R, slot=0)
 
-    def collect(self, R: int) -> List[int]:
-        """Wait for the last sample_async and return its R tokens."""
-        torch.cuda.current_stream().synchronize()
-        return self._out_host[:R].tolist()
+    def collect(self, R: int, slot: int = 0) -> List[int]:
+        """Wait for the sample_async that last used `slot` and return its R tokens."""
+        ev = self._done[slot]
+        if ev is not None:
+            ev.synchronize()
+        else:
+            torch.cuda.current_stream().synchronize()
+        return self._out_host[slot][:R].tolist()
 
     def sample_async(self, logits: torch.Tensor, temps: Sequence[float], seeds: Sequence[int],
-                     out_positions: Sequence[int]) -> torch.Tensor:
+                     out_positions: Sequence[int], slot: int = 0) -> torch.Tensor:
         """Enqueue the sampling of R rows and the copy of the tokens to pinned host memory; returns the device
         tensor of tokens (int32 [R]) without waiting for it."""
         R = logits.shape[0]
         if R > self.max_rows or len(temps) != R or len(seeds) != R or len(out_positions) != R:
             raise ValueError("sampler: row count does not match its arguments or exceeds its capacity")
-        self._host_f.numpy()[:R] = temps
-        self._host_p.numpy()[:R] = out_positions
-        self._host_s.numpy()[:R] = np.asarray([s if s < (1 << 63) else s - (1 << 64) for s in seeds], dtype=np.int64)
-        self._temps[:R].copy_(self._host_f[:R], non_blocking=True)
-        self._pos[:R].copy_(self._host_p[:R], non_blocking=True)
-        self._seeds[:R].copy_(self._host_s[:R], non_blocking=True)
+        self._host_f[slot].numpy()[:R] = temps
+        self._host_p[slot].numpy()[:R] = out_positions
+        self._host_s[slot].numpy()[:R] = np.asarray([x if x < (1 << 63) else x - (1 << 64) for x in seeds], dtype=np.int64)
+        self._temps[slot][:R].copy_(self._host_f[slot][:R], non_blocking=True)
+        self._pos[slot][:R].copy_(self._host_p[slot][:R], non_blocking=True)
+        self._seeds[slot][:R].copy_(self._host_s[slot][:R], non_blocking=True)
         # a large vocabulary is searched by several blocks per row, unless the rows alone fill the device
         chunks = self._chunks if logits.shape[1] >= 16384 and R <= 64 else 0
-        ops.sample(self._out[:R], logits, None, self._temps, self._seeds, self._pos, num_rows=R,
+        ops.sample(self._out[slot][:R], logits, None, self._temps[slot], self._seeds[slot], self._pos[slot], num_rows=R,
                    scratch=self._scratch if chunks else None, chunks=chunks)
-        self._out_host[:R].copy_(self._out[:R], non_blocking=True)
+        self._out_host[slot][:R].copy_(self._out[slot][:R], non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self._done[slot] = ev
         self.h2d_bytes_last = R * (4 + 4 + 8)
-        return self._out[:R]
+        return self._out[slot][:R]

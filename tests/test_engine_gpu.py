@@ -89,6 +89,27 @@ def test_pages_run_out_requests_are_preempted_recomputed_and_still_right(model_d
         llm.add_request([1, 2, 999], sp)
 
 
+def test_overlapped_and_step_by_step_engines_generate_the_same_tokens(model_dirs):
+    """pipeline_depth 2 schedules step n + 1 before the samples of step n are read back (the tokens travel on the
+    device); depth 1 waits for every step.  Same tokens, greedy and sampled, also when pages run out."""
+    from cppvllm_b200 import SamplingParams
+    d = model_dirs["tiny_b"]
+    prompts = [tiny_models.random_tokens(320, n, 70 + n) for n in (1, 31, 32, 65, 100, 7)]
+    for kw, sp in ((dict(), SamplingParams(temperature=0.0, max_tokens=12, ignore_eos=True)),
+                   (dict(), SamplingParams(temperature=0.8, max_tokens=9, ignore_eos=True, seed=3)),
+                   (dict(num_kv_blocks=7), SamplingParams(temperature=0.0, max_tokens=20, ignore_eos=True))):
+        outs = {}
+        for depth in (1, 2):
+            llm = engine(d, "tiny_b", pipeline_depth=depth, **kw)
+            outs[depth] = [o.token_ids for o in llm.generate(prompts, sp)]
+            llm.runner.cache.check_invariants()
+            assert llm.runner.cache.num_free_pages() == llm.num_kv_blocks
+            if kw:
+                assert llm.stats().preemptions > 0
+        assert outs[1] == outs[2]
+        assert all(len(t) == sp.max_tokens for t in outs[2])
+
+
 def test_end_of_sequence_stops_a_request(model_dirs, tmp_path):
     from cppvllm_b200 import SamplingParams
     d = model_dirs["tiny_a"]

@@ -128,3 +128,54 @@ def test_a_request_alone_preempts_itself_only_if_it_cannot_fit():
     a = Sequence(0, list(range(40)), SamplingParams(max_tokens=8, ignore_eos=True))       # 48 tokens = 3 pages: fits
     run(sched, cache, [a])
     assert sched.num_preemptions == 0 and a.num_completion_tokens == 8
+
+
+def test_with_a_step_in_flight_nothing_is_preempted_and_the_batch_is_blocked():
+    sched, cache = make(4, 64, 0, 4)
+    a = Sequence(0, list(range(31)), SamplingParams(max_tokens=8, ignore_eos=True))
+    b = Sequence(1, list(range(100, 131)), SamplingParams(max_tokens=8, ignore_eos=True))
+    sched.add_request(a)
+    sched.add_request(b)
+    inflight = []
+    for _ in range(2):                                        # two steps without reading anything back
+        batch = sched.schedule(allow_preempt=not inflight)
+        for s in batch.seqs:
+            cache.advance(s.seq_id, s.num_cached_tokens + s.num_scheduled_tokens)
+        inflight.append((batch, sched.on_launched(batch)))
+    assert a.token_ids[-1] == -1 and len(a) == 33             # a placeholder stands for the token in flight
+    blocked = sched.schedule(allow_preempt=False)             # both need a third page, none is free
+    assert blocked.blocked and blocked.seqs == [] and sched.num_preemptions == 0
+    for batch, flags in inflight:                             # the engine drains ...
+        sched.postprocess(batch, flags, [7] * sum(flags))
+    assert a.token_ids[-2:] == [7, 7] and -1 not in a.token_ids
+    nxt = sched.schedule(allow_preempt=True)                  # ... and now the last running request gives way
+    assert [s.seq_id for s in nxt.seqs] == [0] and sched.num_preemptions == 1 and not nxt.blocked
+
+
+def test_a_request_that_finished_while_a_later_step_was_in_flight_drops_the_later_result():
+    sched, cache = make(8, 64, 0, 4, eos=(99,))
+    a = Sequence(0, [1, 2, 3], SamplingParams(max_tokens=10))
+    sched.add_request(a)
+    recs = []
+    for _ in range(2):
+        batch = sched.schedule(allow_preempt=not recs)
+        for s in batch.seqs:
+            cache.advance(s.seq_id, s.num_cached_tokens + s.num_scheduled_tokens)
+        recs.append((batch, sched.on_launched(batch)))
+    assert a.token_ids == [1, 2, 3, -1, -1]
+    assert sched.postprocess(recs[0][0], recs[0][1], [99]) == [a]      # the first sample ends the request
+    assert a.token_ids == [1, 2, 3, 99] and a.stopped_on_eos and cache.num_free_pages() == 8
+    assert sched.postprocess(recs[1][0], recs[1][1], [5]) == []         # the second step's sample is dropped
+    assert a.token_ids == [1, 2, 3, 99] and sched.is_finished()
+    cache.check_invariants()
+
+
+def test_max_tokens_counts_the_token_in_flight():
+    sched, cache = make(8, 64, 0, 4)
+    a = Sequence(0, [1, 2, 3], SamplingParams(max_tokens=1, ignore_eos=True))
+    sched.add_request(a)
+    batch = sched.schedule()
+    rec = (batch, sched.on_launched(batch))
+    assert sched.schedule(allow_preempt=False).seqs == []               # its only token is in flight already
+    sched.postprocess(rec[0], rec[1], [4])
+    assert a.token_ids == [1, 2, 3, 4] and sched.is_finished()
