@@ -36,6 +36,9 @@ MODEL = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", hidden_size
              num_attention_heads=16, num_key_value_heads=8, head_dim=128, intermediate_size=3072, vocab_size=151936,
              rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=True, max_position_embeddings=40960)
 FULL_LAYERS = 28
+# the next larger shape of the same architecture (Qwen3-8B sizes); --shape 8b with --layers N checks the kernels there
+MODEL_8B = dict(MODEL, hidden_size=4096, num_hidden_layers=36, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
+                intermediate_size=12288, tie_word_embeddings=False)
 CONTEXT = 4096
 PREFILL_TOKENS = 2048
 
@@ -137,6 +140,7 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--context", type=int, default=CONTEXT)
     ap.add_argument("--no-points", action="store_true", help="skip the batch 1 and 64 points")
+    ap.add_argument("--shape", default="0.6b", choices=["0.6b", "8b"], help="layer sizes: Qwen3-0.6B (default) or Qwen3-8B")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm()
@@ -153,7 +157,11 @@ def main():
     from cppvllm_b200.weights.random_init import write_random_model
 
     pk = peaks()
-    cfg = dict(MODEL, num_hidden_layers=args.layers)
+    base = MODEL if args.shape == "0.6b" else MODEL_8B
+    full_layers = base["num_hidden_layers"]
+    if args.shape != "0.6b" and args.layers == FULL_LAYERS:
+        args.layers = full_layers
+    cfg = dict(base, num_hidden_layers=args.layers)
     tmp = tempfile.mkdtemp(prefix="cppvllm_b200_bench_")
     t_build = time.time()
     model_dir = write_random_model(os.path.join(tmp, "qwen3_0p6b_random"), cfg, seed=0, std=0.02, norm_spread=0.0)
@@ -276,12 +284,14 @@ def main():
     clocks.stop()
 
     line = {
-        "metric": "decode tok/s at batch 8, context 4096 (Qwen3-0.6B shape, random weights)",
+        "metric": f"decode tok/s at batch {B}, context {CTX} (Qwen3-{args.shape.upper()} shape, random weights)",
         "value": round(value, 1), "unit": "tok/s", "n_gpus": 1, "steps": K, "warmup": W,
         "ms_per_step": round(ms8, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic: random weights N(0, 0.02), uniform random token ids",
-        "config": {"model": "Qwen3-0.6B shape", "layers": args.layers, "layers_full": FULL_LAYERS, "hidden": 1024, "q_heads": 16,
-                   "kv_heads": 8, "head_dim": 128, "intermediate": 3072, "vocab": 151936, "tied": True,
+        "config": {"model": f"Qwen3-{args.shape.upper()} shape", "layers": args.layers, "layers_full": full_layers,
+                   "hidden": cfg["hidden_size"], "q_heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
+                   "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
+                   "tied": cfg["tie_word_embeddings"],
                    "global_batch": B, "seq_len": CTX, "page_size": page, "parallelism": "single GPU",
                    "l2": "each step reads > L2 (weights + cache)", "peaks": pk["source"],
                    "hbm_peak_gbs": pk["hbm_gbs"], "bf16_peak_tflops": pk["bf16_tflops"]},
