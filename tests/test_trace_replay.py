@@ -37,7 +37,7 @@ def check_rows(rows, refs, dtype, refs32=None, noise=None):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["tiny_a", "tiny_b", "tiny_c"])
+@pytest.mark.parametrize("name", ["tiny_a", "tiny_b", "tiny_c", "tiny_d"])
 def test_one_request_in_three_cuttings(model_dirs, tmp_path, name, dtype):
     d = model_dirs[name]
     vocab = tiny_models.config(name)["vocab_size"]

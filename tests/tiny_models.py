@@ -24,11 +24,18 @@ TINY_C = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", hidden_siz
               num_attention_heads=6, num_key_value_heads=2, head_dim=64, intermediate_size=144, vocab_size=200,
               rope_theta=50000.0, rms_norm_eps=1e-6, tie_word_embeddings=False, max_position_embeddings=512)
 
+# sizes that fit no vector width: hidden 100 and intermediate 172 (rows of bf16 that are no multiple of 16 bytes),
+# an odd vocabulary, head size 48 with a group of 3
+TINY_D = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", hidden_size=100, num_hidden_layers=2,
+              num_attention_heads=3, num_key_value_heads=1, head_dim=48, intermediate_size=172, vocab_size=257,
+              rope_theta=20000.0, rms_norm_eps=1e-6, tie_word_embeddings=True, max_position_embeddings=300)
+
 # name -> (config, seed, std, norm spread, page size)
 SETUPS = {
     "tiny_a": (TINY_A, 0, 0.02, 0.1, 16),
     "tiny_b": (TINY_B, 1, 0.03, 0.2, 32),
     "tiny_c": (TINY_C, 2, 0.03, 0.1, 16),
+    "tiny_d": (TINY_D, 3, 0.03, 0.1, 64),
 }
 
 
