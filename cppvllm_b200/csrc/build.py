@@ -36,6 +36,7 @@ LIBRARIES: Dict[str, List[str]] = {
     "attn_bf16": ["attention_bf16.cu"],
     "gemv_bf16": ["gemv_bf16.cu"],
     "gemm_bf16": ["gemm_tcgen05.cu"],
+    "decode_fused": ["decode_fused.cu"],
     "attn_tcgen05": ["attention_tcgen05.cu"],
 }
 

@@ -425,6 +425,65 @@ def gemm_bf16_tcgen05(out: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, 
     return out
 
 
+_fused = None
+
+
+def _fused_lib():
+    global _fused
+    if _fused is None:
+        lib = load_library("decode_fused")
+        lib.cvb_decode_block_tail.restype = c_int
+        lib.cvb_decode_block_head.restype = c_int
+        _fused = lib
+    return _fused
+
+
+def decode_fusion_supported(dtype: torch.dtype, rows: int, widths, head_dim: int) -> bool:
+    """The persistent decode kernels cover bf16 steps of up to 8 tokens, widths that are multiples of 8 and fit into
+    shared memory eight rows at a time, and head sizes of 16, 32, 64, 128 or 256."""
+    ch = head_dim // 8
+    return (dtype == torch.bfloat16 and 0 < rows <= GEMV_MAX_ROWS and all(w % 8 == 0 for w in widths)
+            and 8 * (max(widths) + 32) * 2 + 8 * 128 * 4 <= 200 * 1024
+            and head_dim % 8 == 0 and 2 <= ch <= 32 and ch & (ch - 1) == 0)
+
+
+def decode_block_head(h_in, delta, h_out, norm_weight, eps, w_qkv, qkv, q_out, q_weight, k_weight, qk_eps, cos, sin, positions,
+                      slots, cache, rows: int, num_heads: int, num_kv_heads: int, head_dim: int, page_size: int, barrier):
+    """Residual add, RMSNorm, QKV product, per-head norm, rotary and cache write of a decode step in one persistent kernel."""
+    _cuda(h_in, delta, h_out, norm_weight, w_qkv, qkv, q_out, q_weight, k_weight, cos, sin, positions, slots, cache, barrier)
+    _contig(h_in, delta, h_out, norm_weight, w_qkv, qkv, q_out, q_weight, k_weight, cos, sin, positions, slots, cache, barrier)
+    D = h_in.shape[1]
+    if any(t.dtype != torch.bfloat16 for t in (h_in, w_qkv, qkv, q_out, cache)) or norm_weight.dtype != torch.float32:
+        raise KernelError("decode_block_head: activations, weights and pages must be bf16, norm weights float32")
+    if w_qkv.shape != ((num_heads + 2 * num_kv_heads) * head_dim, D) or barrier.dtype != torch.int32 or barrier.numel() < 2:
+        raise KernelError("decode_block_head: w_qkv must be [(H + 2 KV) hd, D]; barrier two int32")
+    if positions.dtype != torch.int32 or slots.dtype != torch.int32:
+        raise KernelError("decode_block_head: positions and slots must be int32")
+    _check(_fused_lib().cvb_decode_block_head(
+        _ptr(h_in), _ptr(delta), _ptr(h_out), _ptr(norm_weight), _ptr(w_qkv), _ptr(qkv), _ptr(q_out), _ptr(q_weight), _ptr(k_weight),
+        _ptr(cos), _ptr(sin), _ptr(positions), _ptr(slots), _ptr(cache), c_int(rows), c_int(D), c_int(num_heads),
+        c_int(num_kv_heads), c_int(head_dim), c_int(page_size), c_int(cos.shape[0] if cos is not None else 0),
+        c_int64(cache.numel()), c_float(eps), c_float(qk_eps), _ptr(barrier), _ptr(error_flag(h_in.device)), _stream()),
+        "decode_block_head")
+
+
+def decode_block_tail(att, w_o, y1, h_in, h_out, norm_weight, eps, w_gate_up, act, w_down, y2, rows: int, barrier):
+    """O product, residual add, RMSNorm, gate/up product with SwiGLU and down product of a decode step in one kernel."""
+    _cuda(att, w_o, y1, h_in, h_out, norm_weight, w_gate_up, act, w_down, y2, barrier)
+    _contig(att, w_o, y1, h_in, h_out, norm_weight, w_gate_up, act, w_down, y2, barrier)
+    D, Kq = w_o.shape
+    I = w_down.shape[1]
+    if any(t.dtype != torch.bfloat16 for t in (att, w_o, y1, h_in, h_out, w_gate_up, act, w_down, y2)) \
+            or norm_weight.dtype != torch.float32:
+        raise KernelError("decode_block_tail: activations and weights must be bf16, norm weights float32")
+    if w_gate_up.shape != (2 * I, D) or w_down.shape[0] != D or att.shape[1] != Kq or h_in.shape[1] != D:
+        raise KernelError("decode_block_tail: shapes of the weights do not fit one another")
+    _check(_fused_lib().cvb_decode_block_tail(
+        _ptr(att), _ptr(w_o), _ptr(y1), _ptr(h_in), _ptr(h_out), _ptr(norm_weight), _ptr(w_gate_up), _ptr(act), _ptr(w_down),
+        _ptr(y2), c_int(rows), c_int(D), c_int(Kq), c_int(I), c_float(eps), _ptr(barrier), _ptr(error_flag(att.device)),
+        _stream()), "decode_block_tail")
+
+
 # ---- sampling ----------------------------------------------------------------------------------------------
 
 def sample(out: torch.Tensor, logits: torch.Tensor, rows: Optional[torch.Tensor], temps: torch.Tensor,

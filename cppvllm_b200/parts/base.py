@@ -105,12 +105,12 @@ class Workspace:
             raise ValueError(f"a step of {n_rows} tokens exceeds the workspace of {self.max_tokens}")
         return buf[:n_rows]
 
-    def flat(self, name: str, numel: int, dtype: torch.dtype) -> torch.Tensor:
-        """A named scratch buffer of a fixed number of elements (allocated once, at its first use)."""
+    def flat(self, name: str, numel: int, dtype: torch.dtype, zero: bool = False) -> torch.Tensor:
+        """A named scratch buffer of a fixed number of elements (allocated once, at its first use; `zero`: zero-filled)."""
         key = f"{name}|flat|{dtype}"
         buf = self._buffers.get(key)
         if buf is None:
-            buf = torch.empty(numel, dtype=dtype, device=self.device)
+            buf = (torch.zeros if zero else torch.empty)(numel, dtype=dtype, device=self.device)
             self._buffers[key] = buf
         elif buf.numel() < numel:           # never reallocated: captured graphs hold the address
             raise ValueError(f"scratch buffer '{name}' was sized for {buf.numel()} elements, {numel} are asked for")

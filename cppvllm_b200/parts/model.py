@@ -38,7 +38,8 @@ class CausalLM:
             mixer_norm = build_part("norm", ls.mixer_norm, runtime)
             ffn_norm = build_part("norm", ls.ffn_norm, runtime)
             block_cls = part_class("block", ls.block)
-            self.blocks.append(block_cls(runtime, mixer=mixer, ffn=ffn, mixer_norm=mixer_norm, ffn_norm=ffn_norm))
+            self.blocks.append(block_cls(runtime, mixer=mixer, ffn=ffn, mixer_norm=mixer_norm, ffn_norm=ffn_norm,
+                                         **ls.block_params))
         self.final_norm = build_part("norm", spec.final_norm, runtime)
         self.head = build_part("head", spec.lm_head, runtime)
         self.run_order: List[RunEntry] = spec.resolved_run_order()

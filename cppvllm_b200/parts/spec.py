@@ -37,6 +37,7 @@ class LayerSpec:
     mixer_norm: PartSpec
     ffn_norm: PartSpec
     block: str = "prenorm"
+    block_params: Dict[str, Any] = field(default_factory=dict)
 
 
 @dataclass

@@ -148,6 +148,66 @@ def test_layers_differ_and_the_run_list_is_data(model_dirs):
         unregister_architecture("ToyWindowedForCausalLM")
 
 
+@pytest.mark.parametrize("name", ["tiny_b", "tiny_c"])
+def test_blocks_with_the_persistent_decode_kernels_give_the_same_logits(model_dirs, name, monkeypatch):
+    """A block's options are data (LayerSpec.block_params).  With fuse_decode, steps of up to eight tokens run
+    through the two persistent kernels; the logits agree with the blocks made of separate kernels to rounding, over
+    a prompt cut into small portions, decoded tokens and a second request beside them."""
+    from cppvllm_b200.config.model_config import Qwen3Config
+    from cppvllm_b200.config.registry import register_architecture, unregister_architecture
+    from cppvllm_b200.csrc import ops
+    from cppvllm_b200.engine.runner import StepEntry
+    from cppvllm_b200.models.qwen3 import build_qwen3_spec
+
+    def build(cfg):
+        spec = build_qwen3_spec(cfg)
+        for layer in spec.layers:
+            layer.block_params["fuse_decode"] = True
+        return spec
+
+    calls = {"head": 0, "tail": 0}
+    head, tail = ops.decode_block_head, ops.decode_block_tail
+    monkeypatch.setattr(ops, "decode_block_head", lambda *a, **k: (calls.__setitem__("head", calls["head"] + 1), head(*a, **k))[1])
+    monkeypatch.setattr(ops, "decode_block_tail", lambda *a, **k: (calls.__setitem__("tail", calls["tail"] + 1), tail(*a, **k))[1])
+    register_architecture("ToyFusedForCausalLM", Qwen3Config.from_dict, build)
+    try:
+        d = model_dirs[name] + "_toy_fused"
+        os.makedirs(d, exist_ok=True)
+        cfg = dict(tiny_models.config(name), architectures=["ToyFusedForCausalLM"])
+        json.dump(cfg, open(os.path.join(d, "config.json"), "w"))
+        if not os.path.exists(os.path.join(d, "model.safetensors")):
+            os.symlink(os.path.join(model_dirs[name], "model.safetensors"), os.path.join(d, "model.safetensors"))
+        vocab = cfg["vocab_size"]
+        a, b = tiny_models.random_tokens(vocab, 60, 5), tiny_models.random_tokens(vocab, 23, 6)
+        # (request, tokens) per step: whole portions, portions of 2 to 8 tokens, single tokens, two requests in a step
+        plan = [[("a", 40)], [("a", 5)], [("a", 2), ("b", 6)], [("a", 1), ("b", 1)], [("b", 16)], [("a", 8)], [("a", 1)],
+                [("a", 3)]]
+        results = []
+        for folder in (model_dirs[name], d):
+            r = make_runner(folder, torch.bfloat16, tiny_models.page_size(name), enforce_eager=(folder == d))
+            pos = {"a": 0, "b": 0}
+            seqs = {"a": a, "b": b}
+            for rid in pos:
+                r.cache.admit(rid)
+            got = []
+            for step in plan:
+                entries = []
+                for rid, n in step:
+                    r.cache.reserve(rid, pos[rid] + n)
+                    entries.append(StepEntry(rid, seqs[rid][pos[rid]:pos[rid] + n], pos[rid], list(range(n))))
+                    pos[rid] += n
+                got.append(r.step(entries).float().cpu().clone())
+            r.check_errors()
+            results.append(torch.cat(got))
+        layers = cfg["num_hidden_layers"]
+        small_steps = sum(1 for step in plan if sum(n for _, n in step) <= 8)
+        assert calls["head"] == calls["tail"] == small_steps * layers
+        ref, fused = results
+        assert (fused - ref).abs().max() <= 2e-2 * max(1.0, float(ref.abs().max()))
+    finally:
+        unregister_architecture("ToyFusedForCausalLM")
+
+
 def _toy_reference(d, toks):
     """Plain float32 forward of the toy arrangement above."""
     c, w = plain.read_config(d), plain.read_weights(d)
