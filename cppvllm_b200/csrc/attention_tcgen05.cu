@@ -412,6 +412,322 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, const Tc
     }
 }
 
+// ---- two query tiles per block -------------------------------------------------------------------------------------
+// One block owns 256 query rows of one kv head as two tiles X = A, B of 128 rows, and the tensor core alternates between
+// them: while the softmax of one tile runs, the products of the other do.
+//   warp 0     producer (TMA), K ring of three stages, V ring of two; a K/V tile serves both query tiles;
+//   warp 1     one thread issues, per key tile j and query tile X:  PV_j(X) = P_j(X) V_j  accumulated into O(X) in tensor
+//              memory, then S_{j+1}(X) = Q(X) K_{j+1}^T.  P_j(X) is read from tensor memory, where the softmax threads put
+//              it over the first half of S_j(X);
+//   warps 4-7  softmax of tile A, warps 8-11 of tile B: one thread per query row (registers move from the first warpgroup
+//              to these two with setmaxnreg).  A thread reads its row of S (128 floats),
+//              exponentiates against a reference maximum, writes the row of P as bf16 back into tensor memory.  The output
+//              accumulator stays in tensor memory; it is rescaled (read, multiplied, written back by the row's thread) only
+//              when the running maximum of some row of the warp has grown by more than 2^8 since the reference was set,
+//              which happens in the first tiles and then hardly ever.  The result is exact: the same reference scales
+//              P and the row sum.
+// Tensor memory columns: S(A) 0..127, S(B) 128..255, O(A) 256.., O(B) 256 + HD...
+constexpr int kPPThreads = 128 + 256;         // one warpgroup of helpers (two warps idle), one warpgroup per query tile
+
+template <int HD>
+struct PPSmem {
+    static constexpr int kTile = 128 * HD * 2;
+    static constexpr int kNumBars = 2 * kKStages + 2 * kVStages + 2 + 2 + 2;
+    static constexpr size_t kBytes = static_cast<size_t>(kTile) * (2 + kKStages + kVStages) + kNumBars * 8 + 16;
+};
+
+__device__ __forceinline__ void umma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n"
+                 ::"r"(tmem_d), "r"(tmem_a), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tm_store32(uint32_t taddr, const uint32_t (&v)[32]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+                 "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};\n"
+                 ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]),
+                   "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]),
+                   "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]),
+                   "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
+                 : "memory");
+}
+__device__ __forceinline__ void tm_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
+
+constexpr float kRescaleStep = 8.f;            // log2 of the growth of a row's maximum that forces a rescale
+
+template <int HD>
+__global__ void __launch_bounds__(kPPThreads, 1)
+attn_prefill_tcgen05_2q_kernel(const __grid_constant__ CUtensorMap kv_map, const TcAttnParams p, const int skip_single) {
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    using L = PPSmem<HD>;
+    pdl_trigger();
+    if ((saddr(smem_raw) & 1023u) != 0) {
+        if (threadIdx.x == 0) atomicExch(p.err, 6);
+        return;
+    }
+    unsigned char* sQ = smem_raw;                                   // two tiles
+    unsigned char* sK = sQ + 2 * L::kTile;
+    unsigned char* sV = sK + kKStages * L::kTile;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sV + kVStages * L::kTile);
+    uint64_t* k_full = bars;                       // [3]  TMA
+    uint64_t* k_empty = k_full + kKStages;         // [3]  tensor core
+    uint64_t* v_full = k_empty + kKStages;         // [2]  TMA
+    uint64_t* v_empty = v_full + kVStages;         // [2]  tensor core
+    uint64_t* s_ready = v_empty + kVStages;        // [2 tiles]  tensor core: S_j(X) and everything issued before it is done
+    uint64_t* p_ready = s_ready + 2;               // [2 tiles]  128 softmax threads: P_j(X) is in tensor memory
+    uint64_t* o_done = p_ready + 2;                // [2 tiles]  tensor core: the last PV(X) is done
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_done + 2);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = p.H / p.KV;
+    const int tok_per_tile = kTM / g;
+    const int tok_per_block = 2 * tok_per_tile;
+    const int kvh = blockIdx.y;
+    constexpr int CPR = HD / 8;
+
+    int seq = -1, q0 = 0, q_len = 0, cu0 = 0;
+    {
+        int tile = gridDim.x - 1 - blockIdx.x;                      // long blocks (late in the request) come first
+        for (int s = 0; s < p.S; ++s) {
+            const int a = p.cu_seqlens[s], n = p.cu_seqlens[s + 1] - a;
+            if (skip_single && n == 1) continue;
+            const int tiles = (n + tok_per_block - 1) / tok_per_block;
+            if (tile < tiles) { seq = s; q0 = tile * tok_per_block; q_len = n; cu0 = a; break; }
+            tile -= tiles;
+        }
+    }
+    if (seq < 0) return;
+    pdl_wait();
+    const int* table = p.block_tables + static_cast<int64_t>(seq) * p.table_width;
+    // per query tile: its tokens, and the range of key tiles it needs
+    int n_tok[2], t_lo[2], t_hi[2];                                 // key tiles t_lo <= j < t_hi (none if t_lo >= t_hi)
+#pragma unroll
+    for (int x = 0; x < 2; ++x) {
+        n_tok[x] = max(0, min(tok_per_tile, q_len - q0 - x * tok_per_tile));
+        if (n_tok[x] > 0) {
+            const int first = p.positions[cu0 + q0 + x * tok_per_tile];
+            const int last = p.positions[cu0 + q0 + x * tok_per_tile + n_tok[x] - 1];
+            t_lo[x] = (p.window > 0 ? max(0, first - p.window + 1) : 0) / kTN;
+            t_hi[x] = last / kTN + 1;
+        } else {
+            t_lo[x] = 0x3fffffff;
+            t_hi[x] = 0;
+        }
+    }
+    const int j_lo = min(t_lo[0], t_lo[1]), j_hi = max(t_hi[0], t_hi[1]);
+    const int key_lo = j_lo * kTN;                                  // keys that exist for the clamp of the loads
+    const int key_hi = p.positions[cu0 + q0 + n_tok[0] + n_tok[1] - 1];
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < kKStages; ++i) { mb_init(k_full + i, 1); mb_init(k_empty + i, 1); }
+        for (int i = 0; i < kVStages; ++i) { mb_init(v_full + i, 1); mb_init(v_empty + i, 1); }
+        for (int i = 0; i < 2; ++i) { mb_init(s_ready + i, 1); mb_init(p_ready + i, 128); mb_init(o_done + i, 1); }
+        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(saddr(tmem_slot)), "r"(512));
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
+    }
+    // query rows: row r of tile x = (token x * tok_per_tile + r / g, head kvh * g + r % g); rows past the portion are zero
+    for (int i = threadIdx.x; i < 2 * kTM * CPR; i += kPPThreads) {
+        const int row = i / CPR, c = i % CPR;
+        const int x = row >> 7, r = row & 127;
+        const int tok = x * tok_per_tile + r / g;
+        const bool valid = r / g < n_tok[x];
+        const __nv_bfloat16* src = valid ? p.q + ((static_cast<int64_t>(cu0 + q0 + tok) * p.H + kvh * g + r % g) * HD + c * 8) : p.q;
+        cpa16(reinterpret_cast<__nv_bfloat16*>(sQ + x * L::kTile) + tile_off(r, c), src, valid);
+    }
+    asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;\n" ::: "memory");
+    fence_async_smem();
+    tc_before();
+    __syncthreads();
+    tc_after();
+    const uint32_t tmem = *tmem_slot;
+    const uint32_t tS[2] = {tmem, tmem + 128};
+    const uint32_t tO[2] = {tmem + 256, tmem + 256 + HD};
+
+    if (warp < 4) {
+    asm volatile("setmaxnreg.dec.sync.aligned.u32 56;\n" ::);
+    if (warp == 0) {
+        if (lane == 0) {                             // ---- producer ----
+            for (int j = j_lo; j < j_hi; ++j) {
+                const int i = j - j_lo, ks = i % kKStages, vs = i % kVStages;
+                if (i >= kKStages) mb_wait(k_empty + ks, ((i / kKStages) - 1) & 1, p.err);
+                issue_tile<HD>(sK + ks * L::kTile, k_full + ks, &kv_map, p, table, kvh, 0, j * kTN, key_lo, key_hi);
+                if (i >= kVStages) mb_wait(v_empty + vs, ((i / kVStages) - 1) & 1, p.err);
+                issue_tile<HD>(sV + vs * L::kTile, v_full + vs, &kv_map, p, table, kvh, 1, j * kTN, key_lo, key_hi);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {                             // ---- tensor-core issue ----
+            constexpr uint32_t idesc_s = idesc_bf16(kTM, kTN, false);
+            constexpr uint32_t idesc_pv = idesc_bf16(kTM, HD, true);
+            auto active = [&](int x, int j) { return j >= t_lo[x] && j < t_hi[x]; };
+            auto issue_s = [&](int x, int j) {       // S_j(X); the K tile has been waited for
+                const int ks = (j - j_lo) % kKStages;
+                const uint32_t q_addr = saddr(sQ + x * L::kTile), k_addr = saddr(sK + ks * L::kTile);
+#pragma unroll
+                for (int k = 0; k < HD / 16; ++k) {
+                    const uint32_t off = (k >> 2) * 16384 + (k & 3) * 32;
+                    umma(tS[x], desc_sw128(q_addr + off, 16, 1024), desc_sw128(k_addr + off, 16, 1024), idesc_s, k > 0 ? 1u : 0u);
+                }
+                commit_to(s_ready + x);
+            };
+            auto wait_k = [&](int j) {
+                const int i = j - j_lo;
+                mb_wait(k_full + i % kKStages, (i / kKStages) & 1, p.err);
+                tc_after();
+            };
+            {
+                wait_k(j_lo);
+#pragma unroll
+                for (int x = 0; x < 2; ++x)
+                    if (active(x, j_lo)) issue_s(x, j_lo);
+                commit_to(k_empty + 0);
+            }
+            for (int j = j_lo; j < j_hi; ++j) {
+                const int i = j - j_lo, vs = i % kVStages;
+                bool have_v = false, have_k = false;
+#pragma unroll
+                for (int x = 0; x < 2; ++x) {
+                    if (!active(x, j)) {
+                        // a tile that starts later (window): its first S belongs to the round before its first PV
+                        if (j + 1 < j_hi && active(x, j + 1)) {
+                            if (!have_k) { wait_k(j + 1); have_k = true; }
+                            issue_s(x, j + 1);
+                        }
+                        continue;
+                    }
+                    mb_wait(p_ready + x, (j - t_lo[x]) & 1, p.err);
+                    if (!have_v) { mb_wait(v_full + vs, (i / kVStages) & 1, p.err); have_v = true; }
+                    tc_after();
+                    const uint32_t v_addr = saddr(sV + vs * L::kTile);
+#pragma unroll
+                    for (int k = 0; k < kTN / 16; ++k)   // P: 16 keys = 8 columns of packed pairs; V: 16 keys further down
+                        umma_ts(tO[x], tS[x] + k * 8, desc_sw128(v_addr + k * 16 * 128, 16384, 1024), idesc_pv,
+                                (j > t_lo[x] || k > 0) ? 1u : 0u);
+                    if (active(x, j + 1)) {
+                        if (!have_k) { wait_k(j + 1); have_k = true; }
+                        issue_s(x, j + 1);
+                    } else {
+                        commit_to(o_done + x);
+                    }
+                }
+                if (!have_v) mb_wait(v_full + vs, (i / kVStages) & 1, p.err);    // nobody needed it: hand it back in order
+                commit_to(v_empty + vs);
+                if (j + 1 < j_hi) {
+                    if (!have_k) wait_k(j + 1);          // nobody needs it: still hand the stage back in order
+                    commit_to(k_empty + (i + 1) % kKStages);
+                }
+            }
+        }
+    }
+    } else {                                         // ---- softmax: one thread per query row ----
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 224;\n" ::);
+        const int x = (warp - 4) >> 2;               // query tile
+        const int quarter = warp & 3;                // the 32 lanes of tensor memory this warp may touch
+        const int r = quarter * 32 + lane;           // row within the tile
+        const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
+        if (t_lo[x] < t_hi[x]) {
+            const int tok_in_tile = min(r / g, n_tok[x] - 1);
+            const int tok = x * tok_per_tile + tok_in_tile;
+            const int row_pos = p.positions[cu0 + q0 + tok];
+            const int row_lo = p.window > 0 ? max(0, row_pos - p.window + 1) : 0;
+            float m_ref = -INFINITY, l = 0.f;
+            for (int j = t_lo[x]; j < t_hi[x]; ++j) {
+                const int i = j - t_lo[x];
+                const int key0 = j * kTN;
+                mb_wait(s_ready + x, i & 1, p.err);
+                tc_after();
+                uint32_t v[128];
+#pragma unroll
+                for (int c = 0; c < 4; ++c) tm_load32(tS[x] + lane_base + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&v[c * 32]));
+                tm_wait_ld();
+                if (key0 + 127 > row_pos || key0 < row_lo) {
+#pragma unroll
+                    for (int c = 0; c < 128; ++c) {
+                        const int key = key0 + c;
+                        if (key > row_pos || key < row_lo) v[c] = 0xff800000u;     // -inf
+                    }
+                }
+                float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+                for (int c = 0; c < 128; c += 4) {
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) mx[k] = fmaxf(mx[k], __uint_as_float(v[c + k]));
+                }
+                const float m_new = fmaxf(m_ref, fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * p.scale_log2);
+                // the reference maximum follows only when some row of the warp has outgrown it
+                const bool grow = m_new > m_ref + kRescaleStep;
+                if (__any_sync(0xffffffffu, grow)) {
+                    const float m_use = m_new == -INFINITY ? 0.f : m_new;
+                    const float factor = ex2(m_ref - m_use);             // 2^(-inf) = 0 before the first key
+                    m_ref = m_new;
+                    l *= factor;
+                    if (i > 0) {                                          // O(X) holds PV_0 .. PV_{j-1}, all done
+#pragma unroll
+                        for (int c = 0; c < HD; c += 32) {
+                            uint32_t o[32];
+                            tm_load32(tO[x] + lane_base + c, o);
+                            tm_wait_ld();
+#pragma unroll
+                            for (int k = 0; k < 32; ++k) o[k] = __float_as_uint(__uint_as_float(o[k]) * factor);
+                            tm_store32(tO[x] + lane_base + c, o);
+                        }
+                    }
+                }
+                const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
+                const float2 scale2 = make_float2(p.scale_log2, p.scale_log2), neg_m2 = make_float2(-m_use, -m_use);
+                float2 sum2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+#pragma unroll
+                for (int h = 0; h < 2; ++h) {
+                    uint32_t packed[32];
+#pragma unroll
+                    for (int k = 0; k < 32; ++k) {
+                        const int c = h * 64 + 2 * k;
+                        const float2 arg = __ffma2_rn(make_float2(__uint_as_float(v[c]), __uint_as_float(v[c + 1])), scale2, neg_m2);
+                        const float2 pr = make_float2(ex2(arg.x), ex2(arg.y));
+                        sum2[k & 1] = __fadd2_rn(sum2[k & 1], pr);
+                        __nv_bfloat162 hh = __floats2bfloat162_rn(pr.x, pr.y);
+                        packed[k] = *reinterpret_cast<uint32_t*>(&hh);
+                    }
+                    tm_store32(tS[x] + lane_base + h * 32, packed);     // P over the first 64 columns of S
+                }
+                l += (sum2[0].x + sum2[0].y) + (sum2[1].x + sum2[1].y);
+                tm_wait_st();
+                tc_before();
+                mb_arrive(p_ready + x);
+            }
+            mb_wait(o_done + x, 0, p.err);
+            tc_after();
+            const bool valid = r / g < n_tok[x];
+            const float inv = l > 0.f ? 1.f / l : 0.f;
+            __nv_bfloat16* dst = p.out + (static_cast<int64_t>(cu0 + q0 + tok) * p.H + kvh * g + r % g) * HD;
+#pragma unroll
+            for (int c = 0; c < HD; c += 32) {
+                uint32_t o[32];
+                tm_load32(tO[x] + lane_base + c, o);
+                tm_wait_ld();
+                if (valid) {
+#pragma unroll
+                    for (int k = 0; k < 32; k += 8) {
+                        uint4 t;
+                        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&t);
+#pragma unroll
+                        for (int e = 0; e < 4; ++e)
+                            h[e] = __floats2bfloat162_rn(__uint_as_float(o[k + 2 * e]) * inv, __uint_as_float(o[k + 2 * e + 1]) * inv);
+                        *reinterpret_cast<uint4*>(dst + c + k) = t;
+                    }
+                }
+            }
+        }
+    }
+    tc_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(512));
+    }
+}
+
 // ---- host side ------------------------------------------------------------------------------------------------
 
 typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
@@ -492,6 +808,41 @@ extern "C" int cvb_attn_prefill_tcgen05(void* out, const void* q, const void* ca
         static bool set = false;
         if (!set) { cudaFuncSetAttribute(attn_prefill_tcgen05_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TcSmem<64>::kBytes); set = true; }
         launch_kernel(attn_prefill_tcgen05_kernel<64>, grid, dim3(kTcThreads), TcSmem<64>::kBytes, stream, map, p, skip_single);
+    }
+    return launch_status();
+}
+
+// Blocks the grid needs: per request with more than one token, ceil(tokens / (256 / group)).
+extern "C" int cvb_attn_prefill_tcgen05_2q(void* out, const void* q, const void* cache, const int* block_tables,
+                                           int table_width, const int* cu_seqlens, const int* positions, int S,
+                                           int num_tiles, int H, int KV, int hd, int page_size, int window, float scale,
+                                           int num_pages, int skip_single, int* err_flag, cudaStream_t stream) {
+    if (num_tiles == 0) return CVB_OK;
+    if (num_tiles < 0 || S <= 0 || H <= 0 || KV <= 0 || page_size <= 0 || table_width <= 0 || num_pages <= 0) return CVB_E_SIZE;
+    if (H % KV) return CVB_E_SHAPE;
+    if (hd != 64 && hd != 128) return CVB_E_UNSUPPORTED;
+    const int g = H / KV;
+    if (g > 16 || KV > 65535) return CVB_E_UNSUPPORTED;
+    if (page_size < 16 || (page_size & (page_size - 1)) != 0) return CVB_E_UNSUPPORTED;
+    if (static_cast<int64_t>(num_pages) * 2 * KV * page_size > 2147483647LL) return CVB_E_SIZE;
+    TcAttnParams p{};
+    p.out = (__nv_bfloat16*)out; p.q = (const __nv_bfloat16*)q;
+    p.block_tables = block_tables; p.cu_seqlens = cu_seqlens; p.positions = positions;
+    p.table_width = table_width; p.S = S; p.H = H; p.KV = KV; p.page_size = page_size; p.window = window;
+    p.num_pages = num_pages; p.scale_log2 = scale * kLog2eF; p.err = err_flag;
+    p.box_rows = page_size < 64 ? page_size : 64;
+    CUtensorMap map;
+    const int rc = kv_map_for(&map, cache, static_cast<int64_t>(num_pages) * 2 * KV * page_size, hd, p.box_rows);
+    if (rc != CVB_OK) return rc;
+    dim3 grid(static_cast<unsigned>(num_tiles), static_cast<unsigned>(KV));
+    if (hd == 128) {
+        static bool set = false;
+        if (!set) { cudaFuncSetAttribute(attn_prefill_tcgen05_2q_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PPSmem<128>::kBytes); set = true; }
+        launch_kernel(attn_prefill_tcgen05_2q_kernel<128>, grid, dim3(kPPThreads), PPSmem<128>::kBytes, stream, map, p, skip_single);
+    } else {
+        static bool set = false;
+        if (!set) { cudaFuncSetAttribute(attn_prefill_tcgen05_2q_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PPSmem<64>::kBytes); set = true; }
+        launch_kernel(attn_prefill_tcgen05_2q_kernel<64>, grid, dim3(kPPThreads), PPSmem<64>::kBytes, stream, map, p, skip_single);
     }
     return launch_status();
 }
