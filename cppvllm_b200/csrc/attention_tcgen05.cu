@@ -2,22 +2,27 @@
 // over the paged cache with a causal offset (and an optional window).  Same arithmetic as attention_bf16.cu (reference
 // kernels/paged_attention.cu:89-359: scale * q.k over keys lo..p, online softmax in float, o = sum p v / l).
 //
-// One block owns 128 query rows of one kv head: the query heads that share the kv head are packed next to each other
-// (row r = token r / g, head kvh * g + r % g), so a key/value tile is fetched once for the whole group.  Keys are
-// walked in tiles of 128.  Roles, by warp:
-//   warp 0     producer: one thread issues TMA copies (one box per page and 64-column half, 128-byte swizzle) of K tiles
-//              into a ring of three stages and of V tiles into a ring of two;
-//   warp 1     allocates 512 columns of tensor memory; one thread issues the products
-//                  S_j  = Q K_j^T   (M 128, N 128, K = head size; both operands K-major)       -> S buffer j % 2
-//                  PV_j = P_j V_j   (M 128, N = head size, K 128; P K-major, V MN-major)      -> PV buffer j % 2
-//              in the order S_0, S_1, PV_0, S_2, PV_1, ... so that the softmax of tile j + 1 runs beside PV_j;
-//   warps 2-9  softmax: two threads per query row, one for keys 0..63 of the tile and one for keys 64..127 (and the same
-//              halves of the output row).  A thread reads its half row of S_j with tcgen05.ld once, takes the
-//              maximum, swaps it with its partner through shared memory (one named barrier per tile), writes its half
-//              of P_j as bf16 into shared memory in the layout the tensor core reads, and then adds its half of
-//              PV_{j-1} from tensor memory into its float accumulator (rescaled by the change of the maximum).
+// One block owns 256 query rows of one kv head as two tiles X = A, B of 128 rows: the query heads that share the kv head
+// are packed next to each other (row r of a tile = token r / g, head kvh * g + r % g), so a key/value tile is fetched
+// once for the whole group and for both query tiles.  Keys are walked in tiles of 128.  The tensor core alternates
+// between the two query tiles: while the softmax of one runs, the products of the other do.  Roles, by warp:
+//   warp 0     producer: one lane per TMA box (a page or 64 keys, times 64-column half, times K and V; 128-byte swizzle),
+//              K ring of three stages, V ring of two; the block-table reads of a tile are in flight together;
+//   warp 1     allocates 512 columns of tensor memory; one thread issues, per key tile j and query tile X,
+//                  PV_j(X)    = P_j(X) V_j        (M 128, N = head size, K 128; P from tensor memory, V MN-major)
+//                  S_{j+1}(X) = Q(X) K_{j+1}^T    (M 128, N 128, K = head size; both operands K-major)
+//              PV_j(X) accumulates into O(X) in tensor memory; P_j(X) lies over the first half of S_j(X), where the
+//              softmax threads put it, so S_{j+1}(X) follows PV_j(X) in the tensor core's queue;
+//   warps 2-3  idle (they fill the first warpgroup, which hands its registers to the other two with setmaxnreg);
+//   warps 4-7  softmax of tile A, warps 8-11 of tile B: one thread per query row.  A thread reads its row of S (128
+//              floats) with tcgen05.ld, exponentiates against a reference maximum and writes the row of P as bf16 back
+//              into tensor memory with tcgen05.st.  The output accumulator stays in tensor memory; it is rescaled (read,
+//              multiplied, written back by the row's thread) only when the running maximum of some row of the warp has
+//              grown by more than 2^8 since the reference was set, which happens in the first tiles and then hardly
+//              ever.  The result is exact: the same reference scales P and the row sum.
+// Tensor memory columns: S(A) 0..127, S(B) 128..255, O(A) 256.., O(B) 256 + head size...
 // Buffers are handed over with mbarriers: TMA transaction counts, tcgen05.commit arrivals from the tensor core, and
-// plain arrivals from the 256 softmax threads.  Every wait is bounded by a cycle count; a wait that runs out records
+// plain arrivals from the softmax threads.  Every wait is bounded by a cycle count; a wait that runs out records
 // error 5 and the block runs on to its end (tensor memory is always given back).
 #include "common.cuh"
 
@@ -31,8 +36,6 @@ constexpr int kTM = 128;                      // query rows per block
 constexpr int kTN = 128;                      // keys per tile
 constexpr int kKStages = 3;
 constexpr int kVStages = 2;
-constexpr int kSoftmaxThreads = 256;           // two threads per query row: each owns half of the columns
-constexpr int kTcThreads = 64 + kSoftmaxThreads;
 constexpr float kLog2eF = 1.4426950408889634f;
 
 __device__ __forceinline__ uint32_t saddr(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
@@ -104,6 +107,11 @@ __device__ __forceinline__ void tm_wait_ld() { asm volatile("tcgen05.wait::ld.sy
 __device__ __forceinline__ void tc_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
 __device__ __forceinline__ void tc_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
 __device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
 __device__ __forceinline__ float ex2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -124,313 +132,10 @@ struct TcAttnParams {
     int* err;
 };
 
+constexpr int kTcThreads = 128 + 256;         // one warpgroup of helpers (two warps idle), one warpgroup per query tile
+
 template <int HD>
 struct TcSmem {
-    static constexpr int kTile = 128 * HD * 2;                       // bytes of a [128][HD] bf16 tile
-    static constexpr int kP = 128 * kTN * 2;                         // bytes of P [128][128]
-    static constexpr int kNumBars = 2 * kKStages + 2 * kVStages + 2 + 2 + 1 + 1 + 2 + 2;
-    // no slack for alignment: with 128-wide heads the tiles leave 3 KB of the 227 KB; the kernel checks the base instead
-    static constexpr size_t kBytes = static_cast<size_t>(kTile) * (1 + kKStages + kVStages) + kP + kNumBars * 8 + 16 + 2 * 2 * 128 * 4;
-};
-
-// One thread: fetch keys [key0, key0 + 128) of one kv head (`which` 0 = K, 1 = V) into a tile.
-template <int HD>
-__device__ __forceinline__ void issue_tile(unsigned char* tile, uint64_t* bar, const CUtensorMap* map, const TcAttnParams& p,
-                                           const int* table, int kvh, int which, int key0, int key_lo, int key_hi) {
-    mb_expect_tx(bar, TcSmem<HD>::kTile);
-    for (int b0 = 0; b0 < kTN; b0 += p.box_rows) {
-        int key = min(max(key0 + b0, key_lo), key_hi);              // outside the range: the nearest key inside it
-        key -= key % p.box_rows;
-        const int slot = key / p.page_size;
-        int page = slot < p.table_width ? table[slot] : -1;
-        if (page < 0 || page >= p.num_pages) { atomicExch(p.err, 4); page = 0; }
-        const int row = ((page * 2 + which) * p.KV + kvh) * p.page_size + key % p.page_size;
-#pragma unroll
-        for (int half = 0; half < HD / 64; ++half)
-            tma_2d(tile + half * 16384 + b0 * 128, map, bar, half * 64, row);
-    }
-}
-
-template <int HD>
-__global__ void __launch_bounds__(kTcThreads)
-attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, const TcAttnParams p, const int skip_single) {
-    extern __shared__ __align__(1024) unsigned char smem_raw[];
-    using L = TcSmem<HD>;
-    pdl_trigger();
-    if ((saddr(smem_raw) & 1023u) != 0) {            // the swizzled tiles need a 1024-byte aligned base
-        if (threadIdx.x == 0) atomicExch(p.err, 6);
-        return;
-    }
-    unsigned char* sQ = smem_raw;
-    unsigned char* sK = sQ + L::kTile;
-    unsigned char* sV = sK + kKStages * L::kTile;
-    unsigned char* sP = sV + kVStages * L::kTile;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sP + L::kP);
-    uint64_t* k_full = bars;                       // [3]  TMA
-    uint64_t* k_empty = k_full + kKStages;         // [3]  tensor core
-    uint64_t* v_full = k_empty + kKStages;         // [2]  TMA
-    uint64_t* v_empty = v_full + kVStages;         // [2]  tensor core
-    uint64_t* s_full = v_empty + kVStages;         // [2]  tensor core
-    uint64_t* s_empty = s_full + 2;                // [2]  128 softmax threads
-    uint64_t* p_full = s_empty + 2;                // [1]  128 softmax threads
-    uint64_t* p_empty = p_full + 1;                // [1]  tensor core
-    uint64_t* pv_full = p_empty + 1;               // [2]  tensor core
-    uint64_t* pv_empty = pv_full + 2;              // [2]  128 softmax threads
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_empty + 2);
-    float* xch = reinterpret_cast<float*>(tmem_slot + 4);           // [2 tiles in flight][2 halves][128 rows]
-
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int g = p.H / p.KV;
-    const int tok_per_tile = kTM / g;
-    const int kvh = blockIdx.y;
-    constexpr int CPR = HD / 8;
-
-    // which request and which tile of it; long tiles (late in the request) come first in the grid
-    int seq = -1, q0 = 0, q_len = 0, cu0 = 0;
-    {
-        int tile = gridDim.x - 1 - blockIdx.x;
-        for (int s = 0; s < p.S; ++s) {
-            const int a = p.cu_seqlens[s], n = p.cu_seqlens[s + 1] - a;
-            if (skip_single && n == 1) continue;
-            const int tiles = (n + tok_per_tile - 1) / tok_per_tile;
-            if (tile < tiles) { seq = s; q0 = tile * tok_per_tile; q_len = n; cu0 = a; break; }
-            tile -= tiles;
-        }
-    }
-    if (seq < 0) return;
-    pdl_wait();
-    const int n_tok = min(tok_per_tile, q_len - q0);
-    const int* table = p.block_tables + static_cast<int64_t>(seq) * p.table_width;
-    const int pos_first = p.positions[cu0 + q0];
-    const int pos_last = p.positions[cu0 + q0 + n_tok - 1];
-    const int key_lo = p.window > 0 ? max(0, pos_first - p.window + 1) : 0;
-    const int key_hi = pos_last;
-    const int tile_begin = key_lo / kTN, n_tiles = key_hi / kTN - tile_begin + 1;
-
-    if (threadIdx.x == 0) {
-        for (int i = 0; i < kKStages; ++i) { mb_init(k_full + i, 1); mb_init(k_empty + i, 1); }
-        for (int i = 0; i < kVStages; ++i) { mb_init(v_full + i, 1); mb_init(v_empty + i, 1); }
-        for (int i = 0; i < 2; ++i) {
-            mb_init(s_full + i, 1); mb_init(s_empty + i, kSoftmaxThreads);
-            mb_init(pv_full + i, 1); mb_init(pv_empty + i, kSoftmaxThreads);
-        }
-        mb_init(p_full, kSoftmaxThreads);
-        mb_init(p_empty, 1);
-        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
-    }
-    if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(saddr(tmem_slot)), "r"(512));
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
-    }
-    // the query tile: row r = (token r / g, head kvh * g + r % g); rows past the portion are zero
-    for (int i = threadIdx.x; i < kTM * CPR; i += kTcThreads) {
-        const int r = i / CPR, c = i % CPR;
-        const int tok = r / g;
-        const bool valid = tok < n_tok;
-        const __nv_bfloat16* src = valid ? p.q + ((static_cast<int64_t>(cu0 + q0 + tok) * p.H + kvh * g + r % g) * HD + c * 8) : p.q;
-        cpa16(reinterpret_cast<__nv_bfloat16*>(sQ) + tile_off(r, c), src, valid);
-    }
-    asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;\n" ::: "memory");
-    fence_async_smem();                              // the tensor core reads what these threads wrote
-    tc_before();
-    __syncthreads();
-    tc_after();
-    const uint32_t tmem = *tmem_slot;
-    const uint32_t tS[2] = {tmem, tmem + 128};
-    const uint32_t tPV[2] = {tmem + 256, tmem + 256 + HD};
-
-    if (warp == 0) {
-        if (lane == 0) {                             // ---- producer ----
-            for (int j = 0; j < n_tiles; ++j) {
-                const int ks = j % kKStages, vs = j % kVStages;
-                if (j >= kKStages) mb_wait(k_empty + ks, ((j / kKStages) - 1) & 1, p.err);
-                issue_tile<HD>(sK + ks * L::kTile, k_full + ks, &kv_map, p, table, kvh, 0, (tile_begin + j) * kTN, key_lo, key_hi);
-                if (j >= kVStages) mb_wait(v_empty + vs, ((j / kVStages) - 1) & 1, p.err);
-                issue_tile<HD>(sV + vs * L::kTile, v_full + vs, &kv_map, p, table, kvh, 1, (tile_begin + j) * kTN, key_lo, key_hi);
-            }
-        }
-    } else if (warp == 1) {
-        if (lane == 0) {                             // ---- tensor-core issue ----
-            constexpr uint32_t idesc_s = idesc_bf16(kTM, kTN, false);
-            constexpr uint32_t idesc_pv = idesc_bf16(kTM, HD, true);
-            const uint32_t q_addr = saddr(sQ), p_addr = saddr(sP);
-            auto issue_s = [&](int j) {
-                const int ks = j % kKStages, b = j & 1;
-                mb_wait(k_full + ks, (j / kKStages) & 1, p.err);
-                if (j >= 2) mb_wait(s_empty + b, ((j >> 1) - 1) & 1, p.err);
-                tc_after();
-                const uint32_t k_addr = saddr(sK + ks * L::kTile);
-#pragma unroll
-                for (int k = 0; k < HD / 16; ++k) {
-                    const uint32_t off = (k >> 2) * 16384 + (k & 3) * 32;         // half, then 32 bytes per k-step
-                    umma(tS[b], desc_sw128(q_addr + off, 16, 1024), desc_sw128(k_addr + off, 16, 1024), idesc_s, k > 0 ? 1u : 0u);
-                }
-                commit_to(s_full + b);
-                commit_to(k_empty + ks);
-            };
-            issue_s(0);
-            for (int j = 0; j < n_tiles; ++j) {
-                if (j + 1 < n_tiles) issue_s(j + 1);
-                const int vs = j % kVStages, b = j & 1;
-                mb_wait(v_full + vs, (j / kVStages) & 1, p.err);
-                mb_wait(p_full, j & 1, p.err);
-                if (j >= 2) mb_wait(pv_empty + b, ((j >> 1) - 1) & 1, p.err);
-                tc_after();
-                const uint32_t v_addr = saddr(sV + vs * L::kTile);
-#pragma unroll
-                for (int k = 0; k < kTN / 16; ++k) {
-                    const uint32_t a_off = (k >> 2) * 16384 + (k & 3) * 32;       // P: K-major, keys along K
-                    const uint32_t b_off = k * 16 * 128;                          // V: 16 keys further down
-                    umma(tPV[b], desc_sw128(p_addr + a_off, 16, 1024), desc_sw128(v_addr + b_off, 16384, 1024), idesc_pv, k > 0 ? 1u : 0u);
-                }
-                commit_to(pv_full + b);
-                commit_to(p_empty);
-                commit_to(v_empty + vs);
-            }
-        }
-    } else {                                         // ---- softmax: two threads per query row ----
-        constexpr int HC = HD / 2;                   // output columns per thread
-        const int quarter = warp & 3;
-        const int half = (warp - 2) >> 2;            // 0: keys / columns of the first half, 1: of the second
-        const int r = quarter * 32 + lane;
-        const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
-        const int tok = min(r / g, n_tok - 1);
-        const int row_pos = p.positions[cu0 + q0 + tok];
-        const int row_lo = p.window > 0 ? max(0, row_pos - p.window + 1) : 0;
-        float o[HC];
-#pragma unroll
-        for (int i = 0; i < HC; ++i) o[i] = 0.f;
-        float m = -INFINITY, l = 0.f, corr_prev = 0.f;
-        __nv_bfloat16* prow = reinterpret_cast<__nv_bfloat16*>(sP);
-
-        auto add_pv = [&](int j, float corr) {      // o = o * corr + (this thread's half of) PV_j
-            const int b = j & 1;
-            mb_wait(pv_full + b, (j >> 1) & 1, p.err);
-            tc_after();
-            const float2 corr2 = make_float2(corr, corr);
-#pragma unroll
-            for (int c0 = 0; c0 < HC; c0 += 32) {
-                uint32_t v[32];
-                tm_load32(tPV[b] + lane_base + half * HC + c0, v);
-                tm_wait_ld();
-#pragma unroll
-                for (int i = 0; i < 32; i += 2) {                    // two columns per packed multiply-add
-                    const float2 acc = __ffma2_rn(make_float2(o[c0 + i], o[c0 + i + 1]), corr2,
-                                                  make_float2(__uint_as_float(v[i]), __uint_as_float(v[i + 1])));
-                    o[c0 + i] = acc.x;
-                    o[c0 + i + 1] = acc.y;
-                }
-            }
-            tc_before();
-            mb_arrive(pv_empty + b);
-        };
-
-        for (int j = 0; j < n_tiles; ++j) {
-            const int b = j & 1;
-            const int key0 = (tile_begin + j) * kTN + half * 64;     // first key of this thread's 64
-            const bool need_mask = key0 + 63 > row_pos || key0 < row_lo;
-            mb_wait(s_full + b, (j >> 1) & 1, p.err);
-            tc_after();
-            uint32_t v[64];
-            tm_load32(tS[b] + lane_base + half * 64, *reinterpret_cast<uint32_t(*)[32]>(&v[0]));
-            tm_load32(tS[b] + lane_base + half * 64 + 32, *reinterpret_cast<uint32_t(*)[32]>(&v[32]));
-            tm_wait_ld();
-            tc_before();
-            mb_arrive(s_empty + b);                                  // S_j is in registers: its buffer may be refilled
-            if (need_mask) {
-#pragma unroll
-                for (int i = 0; i < 64; ++i) {
-                    const int key = key0 + i;
-                    if (key > row_pos || key < row_lo) v[i] = 0xff800000u;     // -inf
-                }
-            }
-            float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};       // four chains instead of one long one
-#pragma unroll
-            for (int i = 0; i < 64; i += 4) {
-#pragma unroll
-                for (int k = 0; k < 4; ++k) mx[k] = fmaxf(mx[k], __uint_as_float(v[i + k]));
-            }
-            float tile_max = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
-            // the row's maximum is the larger of the two halves'
-            xch[(b * 2 + half) * 128 + r] = tile_max;
-            asm volatile("bar.sync 1, %0;\n" ::"n"(kSoftmaxThreads) : "memory");
-            tile_max = fmaxf(tile_max, xch[(b * 2 + (half ^ 1)) * 128 + r]);
-            const float m_new = fmaxf(m, tile_max * p.scale_log2);
-            const float m_use = m_new == -INFINITY ? 0.f : m_new;
-            const float corr = ex2(m - m_use);                       // 2^(-inf) = 0 at the first tile
-            m = m_new;
-            // probabilities, rounded to bf16, into this thread's half row of the P tile (free once PV_{j-1} has read it)
-            if (j > 0) mb_wait(p_empty, (j - 1) & 1, p.err);
-            const float2 scale2 = make_float2(p.scale_log2, p.scale_log2), neg_m2 = make_float2(-m_use, -m_use);
-            float2 sum2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
-#pragma unroll
-            for (int c = 0; c < 8; ++c) {
-                uint32_t packed[4];
-#pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const float2 arg = __ffma2_rn(make_float2(__uint_as_float(v[c * 8 + 2 * i]), __uint_as_float(v[c * 8 + 2 * i + 1])),
-                                                  scale2, neg_m2);
-                    const float2 pr = make_float2(ex2(arg.x), ex2(arg.y));
-                    sum2[i & 1] = __fadd2_rn(sum2[i & 1], pr);
-                    __nv_bfloat162 h = __floats2bfloat162_rn(pr.x, pr.y);
-                    packed[i] = *reinterpret_cast<uint32_t*>(&h);
-                }
-                *reinterpret_cast<uint4*>(prow + tile_off(r, half * 8 + c)) = make_uint4(packed[0], packed[1], packed[2], packed[3]);
-            }
-            const float tile_sum = (sum2[0].x + sum2[0].y) + (sum2[1].x + sum2[1].y);
-            l = l * corr + tile_sum;
-            fence_async_smem();                                      // P_j is visible to the tensor core
-            mb_arrive(p_full);
-            if (j > 0) add_pv(j - 1, corr_prev);
-            corr_prev = corr;
-        }
-        add_pv(n_tiles - 1, corr_prev);
-
-        // the row's sum is the sum of the two halves'
-        asm volatile("bar.sync 1, %0;\n" ::"n"(kSoftmaxThreads) : "memory");      // everyone has read the last maxima
-        xch[half * 128 + r] = l;
-        asm volatile("bar.sync 1, %0;\n" ::"n"(kSoftmaxThreads) : "memory");
-        l += xch[(half ^ 1) * 128 + r];
-        if (r / g < n_tok) {
-            const float inv = l > 0.f ? 1.f / l : 0.f;
-            __nv_bfloat16* dst = p.out + (static_cast<int64_t>(cu0 + q0 + r / g) * p.H + kvh * g + r % g) * HD + half * HC;
-#pragma unroll
-            for (int c = 0; c < HC; c += 8) {
-                uint4 t;
-                __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&t);
-#pragma unroll
-                for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(o[c + 2 * i] * inv, o[c + 2 * i + 1] * inv);
-                *reinterpret_cast<uint4*>(dst + c) = t;
-            }
-        }
-    }
-    tc_before();
-    __syncthreads();
-    if (warp == 1) {
-        tc_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem), "r"(512));
-    }
-}
-
-// ---- two query tiles per block -------------------------------------------------------------------------------------
-// One block owns 256 query rows of one kv head as two tiles X = A, B of 128 rows, and the tensor core alternates between
-// them: while the softmax of one tile runs, the products of the other do.
-//   warp 0     producer (TMA), K ring of three stages, V ring of two; a K/V tile serves both query tiles;
-//   warp 1     one thread issues, per key tile j and query tile X:  PV_j(X) = P_j(X) V_j  accumulated into O(X) in tensor
-//              memory, then S_{j+1}(X) = Q(X) K_{j+1}^T.  P_j(X) is read from tensor memory, where the softmax threads put
-//              it over the first half of S_j(X);
-//   warps 4-7  softmax of tile A, warps 8-11 of tile B: one thread per query row (registers move from the first warpgroup
-//              to these two with setmaxnreg).  A thread reads its row of S (128 floats),
-//              exponentiates against a reference maximum, writes the row of P as bf16 back into tensor memory.  The output
-//              accumulator stays in tensor memory; it is rescaled (read, multiplied, written back by the row's thread) only
-//              when the running maximum of some row of the warp has grown by more than 2^8 since the reference was set,
-//              which happens in the first tiles and then hardly ever.  The result is exact: the same reference scales
-//              P and the row sum.
-// Tensor memory columns: S(A) 0..127, S(B) 128..255, O(A) 256.., O(B) 256 + HD...
-constexpr int kPPThreads = 128 + 256;         // one warpgroup of helpers (two warps idle), one warpgroup per query tile
-
-template <int HD>
-struct PPSmem {
     static constexpr int kTile = 128 * HD * 2;
     static constexpr int kNumBars = 2 * kKStages + 2 * kVStages + 2 + 2 + 2;
     static constexpr size_t kBytes = static_cast<size_t>(kTile) * (2 + kKStages + kVStages) + kNumBars * 8 + 16;
@@ -454,10 +159,10 @@ __device__ __forceinline__ void tm_wait_st() { asm volatile("tcgen05.wait::st.sy
 constexpr float kRescaleStep = 8.f;            // log2 of the growth of a row's maximum that forces a rescale
 
 template <int HD>
-__global__ void __launch_bounds__(kPPThreads, 1)
-attn_prefill_tcgen05_2q_kernel(const __grid_constant__ CUtensorMap kv_map, const TcAttnParams p, const int skip_single) {
+__global__ void __launch_bounds__(kTcThreads, 1)
+attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, const TcAttnParams p, const int skip_single) {
     extern __shared__ __align__(1024) unsigned char smem_raw[];
-    using L = PPSmem<HD>;
+    using L = TcSmem<HD>;
     pdl_trigger();
     if ((saddr(smem_raw) & 1023u) != 0) {
         if (threadIdx.x == 0) atomicExch(p.err, 6);
@@ -497,16 +202,32 @@ attn_prefill_tcgen05_2q_kernel(const __grid_constant__ CUtensorMap kv_map, const
     if (seq < 0) return;
     pdl_wait();
     const int* table = p.block_tables + static_cast<int64_t>(seq) * p.table_width;
-    // per query tile: its tokens, and the range of key tiles it needs
-    int n_tok[2], t_lo[2], t_hi[2];                                 // key tiles t_lo <= j < t_hi (none if t_lo >= t_hi)
+    int n_tok[2];
+#pragma unroll
+    for (int x = 0; x < 2; ++x) n_tok[x] = max(0, min(tok_per_tile, q_len - q0 - x * tok_per_tile));
+    // query rows: row r of tile x = (token x * tok_per_tile + r / g, head kvh * g + r % g); rows past the portion are zero.
+    // Warp 0 takes no part: it starts fetching keys as soon as the barriers exist.
+    if (warp > 0) {
+        for (int i = threadIdx.x - 32; i < 2 * kTM * CPR; i += kTcThreads - 32) {
+            const int row = i / CPR, c = i % CPR;
+            const int x = row >> 7, r = row & 127;
+            const int tok = x * tok_per_tile + r / g;
+            const bool valid = r / g < n_tok[x];
+            const __nv_bfloat16* src = valid ? p.q + ((static_cast<int64_t>(cu0 + q0 + tok) * p.H + kvh * g + r % g) * HD + c * 8) : p.q;
+            cpa16(reinterpret_cast<__nv_bfloat16*>(sQ + x * L::kTile) + tile_off(r, c), src, valid);
+        }
+        asm volatile("cp.async.commit_group;\n" ::: "memory");
+    }
+    // per query tile: the range of key tiles it needs, t_lo <= j < t_hi (none if t_lo >= t_hi)
+    int t_lo[2], t_hi[2], key_hi = 0;
 #pragma unroll
     for (int x = 0; x < 2; ++x) {
-        n_tok[x] = max(0, min(tok_per_tile, q_len - q0 - x * tok_per_tile));
         if (n_tok[x] > 0) {
             const int first = p.positions[cu0 + q0 + x * tok_per_tile];
             const int last = p.positions[cu0 + q0 + x * tok_per_tile + n_tok[x] - 1];
             t_lo[x] = (p.window > 0 ? max(0, first - p.window + 1) : 0) / kTN;
             t_hi[x] = last / kTN + 1;
+            key_hi = last;                                          // the block's last token
         } else {
             t_lo[x] = 0x3fffffff;
             t_hi[x] = 0;
@@ -514,47 +235,62 @@ attn_prefill_tcgen05_2q_kernel(const __grid_constant__ CUtensorMap kv_map, const
     }
     const int j_lo = min(t_lo[0], t_lo[1]), j_hi = max(t_hi[0], t_hi[1]);
     const int key_lo = j_lo * kTN;                                  // keys that exist for the clamp of the loads
-    const int key_hi = p.positions[cu0 + q0 + n_tok[0] + n_tok[1] - 1];
 
-    if (threadIdx.x == 0) {
-        for (int i = 0; i < kKStages; ++i) { mb_init(k_full + i, 1); mb_init(k_empty + i, 1); }
-        for (int i = 0; i < kVStages; ++i) { mb_init(v_full + i, 1); mb_init(v_empty + i, 1); }
-        for (int i = 0; i < 2; ++i) { mb_init(s_ready + i, 1); mb_init(p_ready + i, 128); mb_init(o_done + i, 1); }
-        asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int i = 0; i < kKStages; ++i) { mb_init(k_full + i, 1); mb_init(k_empty + i, 1); }
+            for (int i = 0; i < kVStages; ++i) { mb_init(v_full + i, 1); mb_init(v_empty + i, 1); }
+            for (int i = 0; i < 2; ++i) { mb_init(s_ready + i, 1); mb_init(p_ready + i, 128); mb_init(o_done + i, 1); }
+            asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+        }
+        __syncwarp();
+        asm volatile("bar.arrive 1, %0;\n" ::"n"(kTcThreads) : "memory");       // the others wait for this below
+    } else {
+        if (warp == 1) {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(saddr(tmem_slot)), "r"(512));
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
+        }
+        asm volatile("cp.async.wait_group 0;\n" ::: "memory");
+        fence_async_smem();                                         // the tensor core reads what these threads wrote
+        tc_before();
+        asm volatile("bar.sync 1, %0;\n" ::"n"(kTcThreads) : "memory");
+        tc_after();
     }
-    if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(saddr(tmem_slot)), "r"(512));
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
-    }
-    // query rows: row r of tile x = (token x * tok_per_tile + r / g, head kvh * g + r % g); rows past the portion are zero
-    for (int i = threadIdx.x; i < 2 * kTM * CPR; i += kPPThreads) {
-        const int row = i / CPR, c = i % CPR;
-        const int x = row >> 7, r = row & 127;
-        const int tok = x * tok_per_tile + r / g;
-        const bool valid = r / g < n_tok[x];
-        const __nv_bfloat16* src = valid ? p.q + ((static_cast<int64_t>(cu0 + q0 + tok) * p.H + kvh * g + r % g) * HD + c * 8) : p.q;
-        cpa16(reinterpret_cast<__nv_bfloat16*>(sQ + x * L::kTile) + tile_off(r, c), src, valid);
-    }
-    asm volatile("cp.async.commit_group;\ncp.async.wait_group 0;\n" ::: "memory");
-    fence_async_smem();
-    tc_before();
-    __syncthreads();
-    tc_after();
-    const uint32_t tmem = *tmem_slot;
+    const uint32_t tmem = warp == 0 ? 0u : *tmem_slot;
     const uint32_t tS[2] = {tmem, tmem + 128};
     const uint32_t tO[2] = {tmem + 256, tmem + 256 + HD};
 
     if (warp < 4) {
     asm volatile("setmaxnreg.dec.sync.aligned.u32 56;\n" ::);
     if (warp == 0) {
-        if (lane == 0) {                             // ---- producer ----
-            for (int j = j_lo; j < j_hi; ++j) {
-                const int i = j - j_lo, ks = i % kKStages, vs = i % kVStages;
-                if (i >= kKStages) mb_wait(k_empty + ks, ((i / kKStages) - 1) & 1, p.err);
-                issue_tile<HD>(sK + ks * L::kTile, k_full + ks, &kv_map, p, table, kvh, 0, j * kTN, key_lo, key_hi);
-                if (i >= kVStages) mb_wait(v_empty + vs, ((i / kVStages) - 1) & 1, p.err);
-                issue_tile<HD>(sV + vs * L::kTile, v_full + vs, &kv_map, p, table, kvh, 1, j * kTN, key_lo, key_hi);
+        // ---- producer: one lane per TMA box (page or 64 keys, times 64-column half, times K and V), so that the
+        // block-table reads of a tile are in flight together instead of one after the other ----
+        const int boxes = kTN / p.box_rows, per_tile = boxes * (HD / 64);
+        const int which = lane / per_tile;           // 0: K, 1: V, above: idle lanes
+        const int box = (lane % per_tile) / (HD / 64), half = lane % (HD / 64);
+        for (int j = j_lo; j < j_hi; ++j) {
+            const int i = j - j_lo, ks = i % kKStages, vs = i % kVStages;
+            int row = 0;
+            if (which < 2) {
+                int key = min(max(j * kTN + box * p.box_rows, key_lo), key_hi);      // outside the range: the nearest key inside it
+                key -= key % p.box_rows;
+                const int slot = key / p.page_size;
+                int page = slot < p.table_width ? table[slot] : -1;
+                if (page < 0 || page >= p.num_pages) { atomicExch(p.err, 4); page = 0; }
+                row = ((page * 2 + which) * p.KV + kvh) * p.page_size + key % p.page_size;
             }
+            if (lane == 0) {
+                if (i >= kKStages) mb_wait(k_empty + ks, ((i / kKStages) - 1) & 1, p.err);
+                mb_expect_tx(k_full + ks, L::kTile);
+            }
+            __syncwarp();
+            if (which == 0) tma_2d(sK + ks * L::kTile + half * 16384 + box * p.box_rows * 128, &kv_map, k_full + ks, half * 64, row);
+            if (lane == 0) {
+                if (i >= kVStages) mb_wait(v_empty + vs, ((i / kVStages) - 1) & 1, p.err);
+                mb_expect_tx(v_full + vs, L::kTile);
+            }
+            __syncwarp();
+            if (which == 1) tma_2d(sV + vs * L::kTile + half * 16384 + box * p.box_rows * 128, &kv_map, v_full + vs, half * 64, row);
         }
     } else if (warp == 1) {
         if (lane == 0) {                             // ---- tensor-core issue ----
@@ -648,11 +384,11 @@ attn_prefill_tcgen05_2q_kernel(const __grid_constant__ CUtensorMap kv_map, const
                         if (key > row_pos || key < row_lo) v[c] = 0xff800000u;     // -inf
                     }
                 }
-                float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+                float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};       // four chains of three-input maxima
 #pragma unroll
-                for (int c = 0; c < 128; c += 4) {
+                for (int c = 0; c < 128; c += 8) {
 #pragma unroll
-                    for (int k = 0; k < 4; ++k) mx[k] = fmaxf(mx[k], __uint_as_float(v[c + k]));
+                    for (int k = 0; k < 4; ++k) mx[k] = max3(mx[k], __uint_as_float(v[c + 2 * k]), __uint_as_float(v[c + 2 * k + 1]));
                 }
                 const float m_new = fmaxf(m_ref, fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3])) * p.scale_log2);
                 // the reference maximum follows only when some row of the warp has outgrown it
@@ -778,42 +514,8 @@ static int kv_map_for(CUtensorMap* out, const void* cache, int64_t rows, int hd,
 
 using namespace cvb;
 
-// Tiles the grid needs: per request with more than one token, ceil(tokens / (128 / group)).
-extern "C" int cvb_attn_prefill_tcgen05(void* out, const void* q, const void* cache, const int* block_tables,
-                                        int table_width, const int* cu_seqlens, const int* positions, int S,
-                                        int num_tiles, int H, int KV, int hd, int page_size, int window, float scale,
-                                        int num_pages, int skip_single, int* err_flag, cudaStream_t stream) {
-    if (num_tiles == 0) return CVB_OK;
-    if (num_tiles < 0 || S <= 0 || H <= 0 || KV <= 0 || page_size <= 0 || table_width <= 0 || num_pages <= 0) return CVB_E_SIZE;
-    if (H % KV) return CVB_E_SHAPE;
-    if (hd != 64 && hd != 128) return CVB_E_UNSUPPORTED;
-    if (H / KV > 16 || KV > 65535) return CVB_E_UNSUPPORTED;
-    if (page_size < 16 || (page_size & (page_size - 1)) != 0) return CVB_E_UNSUPPORTED;
-    if (static_cast<int64_t>(num_pages) * 2 * KV * page_size > 2147483647LL) return CVB_E_SIZE;
-    TcAttnParams p{};
-    p.out = (__nv_bfloat16*)out; p.q = (const __nv_bfloat16*)q;
-    p.block_tables = block_tables; p.cu_seqlens = cu_seqlens; p.positions = positions;
-    p.table_width = table_width; p.S = S; p.H = H; p.KV = KV; p.page_size = page_size; p.window = window;
-    p.num_pages = num_pages; p.scale_log2 = scale * kLog2eF; p.err = err_flag;
-    p.box_rows = page_size < 64 ? page_size : 64;
-    CUtensorMap map;
-    const int rc = kv_map_for(&map, cache, static_cast<int64_t>(num_pages) * 2 * KV * page_size, hd, p.box_rows);
-    if (rc != CVB_OK) return rc;
-    dim3 grid(static_cast<unsigned>(num_tiles), static_cast<unsigned>(KV));
-    if (hd == 128) {
-        static bool set = false;
-        if (!set) { cudaFuncSetAttribute(attn_prefill_tcgen05_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TcSmem<128>::kBytes); set = true; }
-        launch_kernel(attn_prefill_tcgen05_kernel<128>, grid, dim3(kTcThreads), TcSmem<128>::kBytes, stream, map, p, skip_single);
-    } else {
-        static bool set = false;
-        if (!set) { cudaFuncSetAttribute(attn_prefill_tcgen05_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TcSmem<64>::kBytes); set = true; }
-        launch_kernel(attn_prefill_tcgen05_kernel<64>, grid, dim3(kTcThreads), TcSmem<64>::kBytes, stream, map, p, skip_single);
-    }
-    return launch_status();
-}
-
 // Blocks the grid needs: per request with more than one token, ceil(tokens / (256 / group)).
-extern "C" int cvb_attn_prefill_tcgen05_2q(void* out, const void* q, const void* cache, const int* block_tables,
+extern "C" int cvb_attn_prefill_tcgen05(void* out, const void* q, const void* cache, const int* block_tables,
                                            int table_width, const int* cu_seqlens, const int* positions, int S,
                                            int num_tiles, int H, int KV, int hd, int page_size, int window, float scale,
                                            int num_pages, int skip_single, int* err_flag, cudaStream_t stream) {
@@ -837,12 +539,12 @@ extern "C" int cvb_attn_prefill_tcgen05_2q(void* out, const void* q, const void*
     dim3 grid(static_cast<unsigned>(num_tiles), static_cast<unsigned>(KV));
     if (hd == 128) {
         static bool set = false;
-        if (!set) { cudaFuncSetAttribute(attn_prefill_tcgen05_2q_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PPSmem<128>::kBytes); set = true; }
-        launch_kernel(attn_prefill_tcgen05_2q_kernel<128>, grid, dim3(kPPThreads), PPSmem<128>::kBytes, stream, map, p, skip_single);
+        if (!set) { cudaFuncSetAttribute(attn_prefill_tcgen05_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TcSmem<128>::kBytes); set = true; }
+        launch_kernel(attn_prefill_tcgen05_kernel<128>, grid, dim3(kTcThreads), TcSmem<128>::kBytes, stream, map, p, skip_single);
     } else {
         static bool set = false;
-        if (!set) { cudaFuncSetAttribute(attn_prefill_tcgen05_2q_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)PPSmem<64>::kBytes); set = true; }
-        launch_kernel(attn_prefill_tcgen05_2q_kernel<64>, grid, dim3(kPPThreads), PPSmem<64>::kBytes, stream, map, p, skip_single);
+        if (!set) { cudaFuncSetAttribute(attn_prefill_tcgen05_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TcSmem<64>::kBytes); set = true; }
+        launch_kernel(attn_prefill_tcgen05_kernel<64>, grid, dim3(kTcThreads), TcSmem<64>::kBytes, stream, map, p, skip_single);
     }
     return launch_status();
 }

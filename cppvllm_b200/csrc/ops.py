@@ -303,29 +303,24 @@ def attn_prefill_bf16(out, q, cache, block_tables, cu_seqlens, positions, num_se
 _attn_tc = None
 
 
-def prefill_tiles_tcgen05(q_lens, num_heads: int, num_kv_heads: int, skip_single: bool = True, two_tiles: bool = True) -> int:
-    """Blocks the tcgen05 prefill kernel's grid needs: per request ceil(tokens / (128 / group)), or half as many for the
-    kernel whose blocks own two query tiles."""
-    tpt = (128 // (num_heads // num_kv_heads)) * (2 if two_tiles else 1)
+def prefill_tiles_tcgen05(q_lens, num_heads: int, num_kv_heads: int, skip_single: bool = True) -> int:
+    """Blocks the tcgen05 prefill kernel's grid needs: per request ceil(tokens / (2 * (128 // group)))."""
+    tpt = (128 // (num_heads // num_kv_heads)) * 2
     return sum((n + tpt - 1) // tpt for n in q_lens if not (skip_single and n == 1))
 
 
 def attn_prefill_tcgen05(out, q, cache, block_tables, cu_seqlens, positions, num_seqs: int, num_tiles: int,
                          num_heads: int, num_kv_heads: int, head_dim: int, page_size: int, scale: float,
-                         window: int = 0, skip_single: bool = True, two_tiles: bool = True):
-    """Flash attention of prompt portions on the tcgen05 tensor cores (same contract as attn_prefill_bf16).  `two_tiles`
-    chooses the kernel whose blocks own two query tiles and keep the output in tensor memory; `num_tiles` must have been
-    counted for the same choice."""
+                         window: int = 0, skip_single: bool = True):
+    """Flash attention of prompt portions on the tcgen05 tensor cores (same contract as attn_prefill_bf16)."""
     global _attn_tc
     if _attn_tc is None:
         lib = load_library("attn_tcgen05")
         lib.cvb_attn_prefill_tcgen05.restype = c_int
-        lib.cvb_attn_prefill_tcgen05_2q.restype = c_int
         _attn_tc = lib
     _attn_common_checks(out, q, cache, block_tables, cu_seqlens, positions)
     num_pages = cache.numel() // (2 * num_kv_heads * page_size * head_dim)
-    fn = _attn_tc.cvb_attn_prefill_tcgen05_2q if two_tiles else _attn_tc.cvb_attn_prefill_tcgen05
-    _check(fn(
+    _check(_attn_tc.cvb_attn_prefill_tcgen05(
         _ptr(out), _ptr(q), _ptr(cache), _ptr(block_tables), c_int(block_tables.shape[1]), _ptr(cu_seqlens),
         _ptr(positions), c_int(num_seqs), c_int(num_tiles), c_int(num_heads), c_int(num_kv_heads), c_int(head_dim),
         c_int(page_size), c_int(window), c_float(scale), c_int(num_pages), c_int(1 if skip_single else 0),

@@ -88,12 +88,11 @@ def attn_prefill(a) -> dict:
     caches, tables, q, cu, pos = _paged_inputs(a.batch, a.tokens + a.cached, a.tokens, H, KV, hd, page, 1)
     out = torch.empty_like(q)
     scale = 1 / math.sqrt(hd)
-    if a.impl in ("tcgen05", "tcgen05_1q"):
-        two = a.impl == "tcgen05"
-        tiles = ops.prefill_tiles_tcgen05([a.tokens] * a.batch, H, KV, two_tiles=two)
+    if a.impl == "tcgen05":
+        tiles = ops.prefill_tiles_tcgen05([a.tokens] * a.batch, H, KV)
 
         def run(i):
-            ops.attn_prefill_tcgen05(out, q, caches[0], tables, cu, pos, a.batch, tiles, H, KV, hd, page, scale, two_tiles=two)
+            ops.attn_prefill_tcgen05(out, q, caches[0], tables, cu, pos, a.batch, tiles, H, KV, hd, page, scale)
     else:
         tiles = ops.prefill_tiles([a.tokens] * a.batch, H, KV)
 
@@ -222,7 +221,7 @@ def main(argv=None) -> int:
     p = argparse.ArgumentParser(prog="kernel_bench")
     p.add_argument("kernel", choices=["attn_decode", "attn_prefill", "gemv", "gemv_fused", "gemm", "decode_block"])
     p.add_argument("--tile-n", type=int, default=0)
-    p.add_argument("--impl", default="tcgen05", choices=["tcgen05", "tcgen05_1q", "mma"])
+    p.add_argument("--impl", default="tcgen05", choices=["tcgen05", "mma"])
     p.add_argument("--form", default="plain", choices=["plain", "norm", "swiglu"])
     p.add_argument("--batch", type=int, default=8)
     p.add_argument("--context", type=int, default=4096)

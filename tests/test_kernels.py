@@ -348,7 +348,7 @@ def test_feed_tokens(ops):
 
 # ---- tensor-core attention (bf16, head sizes 64 and 128) against the plain restatement -----------------------
 
-@pytest.mark.parametrize("prefill", ["tcgen05", "tcgen05_1q", "mma"])
+@pytest.mark.parametrize("prefill", ["tcgen05", "mma"])
 @pytest.mark.parametrize("H,KV,hd,page,window", [(4, 2, 128, 16, 0), (6, 2, 64, 16, 0), (8, 1, 128, 32, 0), (5, 5, 64, 64, 0),
                                                  (16, 8, 128, 16, 0), (14, 2, 128, 16, 150), (3, 1, 64, 16, 70), (32, 2, 64, 16, 0)])
 def test_tensor_core_attention_mixed_portions_and_single_tokens(ops, H, KV, hd, page, window, prefill):
@@ -374,11 +374,9 @@ def test_tensor_core_attention_mixed_portions_and_single_tokens(ops, H, KV, hd, 
     q_lens = [n for _, n in reqs]
     cu_t = torch.tensor(cu, dtype=torch.int32, device=d)
     pos_t = torch.tensor(positions, dtype=torch.int32, device=d)
-    if prefill.startswith("tcgen05"):
-        two = prefill == "tcgen05"
+    if prefill == "tcgen05":
         ops.attn_prefill_tcgen05(out, q.view(T, -1).to(d), cache.to(d), tables.to(d), cu_t, pos_t, len(reqs),
-                                 ops.prefill_tiles_tcgen05(q_lens, H, KV, two_tiles=two), H, KV, hd, page, scale, window=window,
-                                 two_tiles=two)
+                                 ops.prefill_tiles_tcgen05(q_lens, H, KV), H, KV, hd, page, scale, window=window)
     else:
         ops.attn_prefill_bf16(out, q.view(T, -1).to(d), cache.to(d), tables.to(d), cu_t, pos_t, len(reqs),
                               ops.prefill_tiles(q_lens, H, KV), H, KV, hd, page, scale, window=window)
