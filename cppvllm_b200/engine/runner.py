@@ -11,11 +11,16 @@ the block tables; the reference stages the same arrays, model_runner.cpp:290-320
 device, model_architecture.cpp:137-141) and copies it with one asynchronous transfer.  Steps that consist only
 of single decoded tokens replay a CUDA graph captured per batch-size bucket (reference model_runner.cpp:371-428);
 rows that pad a bucket read and write a scratch page that no request owns (model_runner.cpp:69,329,346).
+Other steps (prompt portions, mixed batches) are launched kernel by kernel the first time their shape (the tuple of
+portion lengths and the number of wanted rows) occurs; the second time the shape is captured into a graph of its
+own and replayed from then on: the launches of a long prompt cut into equal portions, or of a stream of equal
+prompts, then cost the host one call instead of some hundred.
 """
 from __future__ import annotations
 
 import os
 import sys
+from collections import OrderedDict
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence
 
@@ -49,6 +54,8 @@ def _align(n: int, a: int = 4) -> int:
 
 
 GRAPH_BUCKETS = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256)
+SHAPE_GRAPHS = 16             # graphs kept for steps that are not decode-only, least recently used first out
+SHAPE_GRAPH_MIN_TOKENS = 64   # shorter steps are cheap to launch and come in too many shapes
 
 
 class ModelRunner:
@@ -130,6 +137,8 @@ class ModelRunner:
         self._logits = torch.empty((self.max_seqs, self.vocab_size), dtype=torch.float32, device=self.device)
         self._graphs: Dict[int, tuple] = {}
         self._graph_launches: Dict[int, int] = {}
+        self._shape_graphs: "OrderedDict[tuple, tuple]" = OrderedDict()
+        self._shape_seen: Dict[tuple, int] = {}
         self._feed = None
         self.h2d_bytes_last_step = 0
         self.stats = {"steps": 0, "graph_steps": 0, "tokens": 0}
@@ -329,6 +338,9 @@ class ModelRunner:
         if (not self.enforce_eager and self.model.capturable and T == S and self._bucket(S)
                 and all(len(e.want) == 1 for e in entries)):
             logits = self._step_graph(entries, S, max_kv)
+        if (logits is None and not self.enforce_eager and self.model.capturable and T >= SHAPE_GRAPH_MIN_TOKENS
+                and R <= self._logits.shape[0]):
+            logits = self._step_shape_graph(entries, q_lens, T, S, R)
         if logits is None:
             W = max(1, max(len(self.cache.lease(e.request_id).tables[g]) for e in entries
                            for g in range(len(self.group_specs))) if self.group_specs else 1)
@@ -393,6 +405,59 @@ class ModelRunner:
         ops.LAUNCHES += self._graph_launches[B]
         self.stats["graph_steps"] += 1
         return self._logits[:S]
+
+    # ---- CUDA graphs for other steps, by shape ---------------------------------------------------------
+    def _step_shape_graph(self, entries, q_lens, T: int, S: int, R: int):
+        """Replay the graph of this step's shape if there is one; capture one if the shape has occurred before;
+        None (the caller launches the step kernel by kernel) otherwise.  Everything that differs between two steps
+        of one shape (tokens, positions, slots, block tables, wanted rows) lies in the staging block on the device;
+        block tables are staged at their full width and the split of decode attention is chosen for the longest
+        context, so that the captured launches hold for every step of the shape."""
+        key = (tuple(q_lens), R)
+        hit = self._shape_graphs.get(key)
+        if hit is None:
+            seen = self._shape_seen.get(key, 0) + 1
+            if len(self._shape_seen) > 4096:
+                self._shape_seen.clear()
+            self._shape_seen[key] = seen
+            if seen < 2:
+                return None
+        W = self.table_width
+        lay, _, _, _ = self._fill(entries, T, S, R, W)
+        if hit is None:
+            ctx = self._context(lay, T, S, R, W, q_lens, self.max_model_len)
+            ctx.extras["captured"] = True
+            graph = torch.cuda.CUDAGraph()
+            before = ops.launches()
+            try:
+                # the first step of this shape ran eagerly: lazy initialisation is done.  Capture runs nothing.
+                with torch.cuda.graph(graph):
+                    if R > 0:
+                        self.model.forward(ctx, self.cache_views, self.states, self._logits)
+                    else:
+                        self.model.forward_hidden(ctx, self.cache_views, self.states)
+            except Exception as ex:
+                torch.cuda.synchronize(self.device)
+                ops.LAUNCHES = before
+                self._shape_seen[key] = -(1 << 30)            # never try this shape again
+                print(f"[cppvllm_b200] a step of shape {key if len(str(key)) < 80 else str(key)[:80] + '...'} cannot be "
+                      f"captured ({type(ex).__name__}: {str(ex).splitlines()[0][:120]}); running it eagerly",
+                      file=sys.stderr, flush=True)
+                ctx = self._context(lay, T, S, R, W, q_lens, max(e.start + len(e.tokens) for e in entries))
+                if R > 0:
+                    return self.model.forward(ctx, self.cache_views, self.states, self._logits)[:R]
+                return self._forward_no_logits(ctx)
+            hit = (graph, ctx, ops.launches() - before)
+            ops.LAUNCHES = before
+            self._shape_graphs[key] = hit
+            while len(self._shape_graphs) > SHAPE_GRAPHS:
+                self._shape_graphs.popitem(last=False)
+        else:
+            self._shape_graphs.move_to_end(key)
+        hit[0].replay()
+        ops.LAUNCHES += hit[2]
+        self.stats["graph_steps"] += 1
+        return self._logits[:R]
 
     # ---- bookkeeping helpers ----------------------------------------------------------------------------
     def check_errors(self) -> None:

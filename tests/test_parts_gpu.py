@@ -208,6 +208,51 @@ def test_blocks_with_the_persistent_decode_kernels_give_the_same_logits(model_di
         unregister_architecture("ToyFusedForCausalLM")
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_steps_of_a_repeated_shape_replay_a_graph_and_stay_right(model_dirs, dtype):
+    """The second step of a shape (portion lengths, wanted rows) is captured, later ones replay the capture: a prompt
+    cut into equal portions beside a second request, other tokens, positions, pages and wanted rows every time.  Every
+    logit row is compared with the plain implementation, and a runner that never captures gives the same rows."""
+    name = "tiny_c"
+    d = model_dirs[name]
+    act = "float32" if dtype == torch.float32 else "bfloat16"
+    from cppvllm_b200.engine.runner import StepEntry
+    vocab = tiny_models.config(name)["vocab_size"]
+    a, b = tiny_models.random_tokens(vocab, 400, 31), tiny_models.random_tokens(vocab, 120, 32)
+    ref = {"a": plain.forward(d, a, act), "b": plain.forward(d, b, act)}
+    # shapes: (80,), (80,), (80,) [graph from the 2nd on], (64, 16) x 3 mixed, (80,) again, then (70,) once (eager)
+    plan = [[("a", 80, [0, 79])], [("a", 80, [5, 79])], [("a", 80, [40, 41])], [("a", 64, [63, 1]), ("b", 16, [15])],
+            [("b", 64, [0, 63]), ("a", 16, [3])], [("a", 64, [10, 20]), ("b", 16, [0])], [("b", 24, [23])]]
+    got = {}
+    for eager in (False, True):
+        r = make_runner(d, dtype, tiny_models.page_size(name), num_pages=40, max_model_len=512, enforce_eager=eager)
+        pos, seqs, rows = {"a": 0, "b": 0}, {"a": a, "b": b}, []
+        for rid in pos:
+            r.cache.admit(rid)
+        for step in plan:
+            entries = []
+            for rid, n, want in step:
+                r.cache.reserve(rid, pos[rid] + n)
+                entries.append(StepEntry(rid, seqs[rid][pos[rid]:pos[rid] + n], pos[rid], want))
+            out = r.step(entries).float().cpu().clone()
+            k = 0
+            for rid, n, want in step:
+                for w in want:
+                    rows.append((rid, pos[rid] + w, out[k]))
+                    k += 1
+                pos[rid] += n
+        r.check_errors()
+        got[eager] = rows
+        if not eager:
+            assert r.stats["graph_steps"] == 4           # the 2nd and 3rd (80,), the 2nd and 3rd (64, 16)
+    tol = 1e-5 if dtype == torch.float32 else 2e-2
+    for (rid, p_, row), (_, _, row_e) in zip(got[False], got[True]):
+        want = ref[rid][p_]
+        scale = max(1.0, float(want.abs().max()))
+        assert (row - want).abs().max() <= tol * scale
+        assert (row - row_e).abs().max() <= tol * scale
+
+
 def _toy_reference(d, toks):
     """Plain float32 forward of the toy arrangement above."""
     c, w = plain.read_config(d), plain.read_weights(d)
