@@ -162,6 +162,92 @@ rmsnorm_vec_kernel(T* __restrict__ out, T* resid, const T* __restrict__ x, const
     }
 }
 
+// One warp per row, for rows of up to 32 * kWarpNormChunks chunks: several 16-byte loads in flight per lane, the sum
+// over the row by shuffles alone.  Same arithmetic as above.
+constexpr int kWarpNormChunks = 16;
+constexpr int kWarpNormWarps = 4;
+
+template <typename T, bool ADD, int CHUNKS>
+__global__ void __launch_bounds__(kWarpNormWarps * 32)
+rmsnorm_warp_kernel(T* __restrict__ out, T* resid, const T* __restrict__ x, const float* __restrict__ w, int T_rows, int D, float eps) {
+    pdl_trigger();
+    pdl_wait();
+    constexpr int N = Vec16<T>::N;
+    const int lane = threadIdx.x & 31;
+    const int64_t row = static_cast<int64_t>(blockIdx.x) * kWarpNormWarps + (threadIdx.x >> 5);
+    if (row >= T_rows) return;
+    const int n_chunks = D / N;
+    Vec16<T> val[CHUNKS];
+#pragma unroll
+    for (int k = 0; k < CHUNKS; ++k) {
+        const int c = lane + k * 32;
+        if (c < n_chunks) val[k].load(x + row * D + c * N);
+    }
+    if constexpr (ADD) {
+        Vec16<T> r[CHUNKS];
+#pragma unroll
+        for (int k = 0; k < CHUNKS; ++k) {
+            const int c = lane + k * 32;
+            if (c < n_chunks) r[k].load(resid + row * D + c * N);
+        }
+#pragma unroll
+        for (int k = 0; k < CHUNKS; ++k) {
+            const int c = lane + k * 32;
+            if (c < n_chunks) {
+#pragma unroll
+                for (int i = 0; i < N; ++i) val[k].v[i] = rnd<T>(r[k].v[i] + val[k].v[i]);
+                val[k].store(resid + row * D + c * N);
+            }
+        }
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int k = 0; k < CHUNKS; ++k) {
+        const int c = lane + k * 32;
+        if (c < n_chunks) {
+#pragma unroll
+            for (int i = 0; i < N; ++i) ss += val[k].v[i] * val[k].v[i];
+        }
+    }
+    ss = warp_sum(ss);
+    const float inv = rsqrtf(ss / static_cast<float>(D) + eps);
+#pragma unroll
+    for (int k = 0; k < CHUNKS; ++k) {
+        const int c = lane + k * 32;
+        if (c < n_chunks) {
+            Vec16<T> o;
+#pragma unroll
+            for (int i = 0; i < N; i += 4) {
+                const float4 ww = *reinterpret_cast<const float4*>(w + c * N + i);
+                o.v[i] = rnd<T>(val[k].v[i] * inv) * ww.x;
+                o.v[i + 1] = rnd<T>(val[k].v[i + 1] * inv) * ww.y;
+                o.v[i + 2] = rnd<T>(val[k].v[i + 2] * inv) * ww.z;
+                o.v[i + 3] = rnd<T>(val[k].v[i + 3] * inv) * ww.w;
+            }
+            o.store(out + row * D + c * N);
+        }
+    }
+}
+
+// launches the warp form with the smallest chunk count that holds the row; false if the row is too long for it
+template <typename T, bool ADD>
+__host__ bool launch_warp_norm(T* out, T* resid, const T* x, const float* w, int T_rows, int D, float eps, cudaStream_t stream) {
+    const int per_lane = (D / Vec16<T>::N + 31) / 32;
+    if (per_lane > kWarpNormChunks || (reinterpret_cast<uintptr_t>(w) & 15) != 0) return false;
+    const dim3 grid((T_rows + kWarpNormWarps - 1) / kWarpNormWarps), block(kWarpNormWarps * 32);
+    if (per_lane <= 1) launch_kernel(rmsnorm_warp_kernel<T, ADD, 1>, grid, block, 0, stream, out, resid, x, w, T_rows, D, eps);
+    else if (per_lane <= 2) launch_kernel(rmsnorm_warp_kernel<T, ADD, 2>, grid, block, 0, stream, out, resid, x, w, T_rows, D, eps);
+    else if (per_lane <= 4) launch_kernel(rmsnorm_warp_kernel<T, ADD, 4>, grid, block, 0, stream, out, resid, x, w, T_rows, D, eps);
+    else if (per_lane <= 8) launch_kernel(rmsnorm_warp_kernel<T, ADD, 8>, grid, block, 0, stream, out, resid, x, w, T_rows, D, eps);
+    else launch_kernel(rmsnorm_warp_kernel<T, ADD, 16>, grid, block, 0, stream, out, resid, x, w, T_rows, D, eps);
+    return true;
+}
+
+// g / (1 + exp(-g)).  In bfloat16 the quotient is rounded to 8 bits of mantissa right away, so the fast exponential and
+// division (errors of a few units in the last place of a float) serve; in float32 the exact ones are used.
+template <typename T> __device__ __forceinline__ float silu_of(float g) { return g / (1.f + expf(-g)); }
+template <> __device__ __forceinline__ float silu_of<__nv_bfloat16>(float g) { return __fdividef(g, 1.f + __expf(-g)); }
+
 template <typename T>
 __global__ void swiglu_vec_kernel(T* __restrict__ out, const T* __restrict__ gu, int64_t n_chunks, int I) {
     pdl_trigger();
@@ -176,7 +262,7 @@ __global__ void swiglu_vec_kernel(T* __restrict__ out, const T* __restrict__ gu,
     g.load(gu + r * 2 * I + i0);
     u.load(gu + r * 2 * I + I + i0);
 #pragma unroll
-    for (int i = 0; i < N; ++i) o.v[i] = rnd<T>(g.v[i] / (1.f + expf(-g.v[i]))) * u.v[i];
+    for (int i = 0; i < N; ++i) o.v[i] = rnd<T>(silu_of<T>(g.v[i])) * u.v[i];
     o.store(out + r * I + i0);
 }
 
@@ -205,7 +291,8 @@ extern "C" int cvb_rmsnorm(void* out, const void* x, const float* w, int T, int 
     if (T == 0) return CVB_OK;
     if (T < 0 || D <= 0) return CVB_E_SIZE;
 #define CALL(TY)                                                                                              \
-    if (vec_ok<TY>(out, x, nullptr, D) && D <= kNormThreads * kNormMaxChunks * Vec16<TY>::N)                  \
+    if (vec_ok<TY>(out, x, nullptr, D) && launch_warp_norm<TY, false>((TY*)out, nullptr, (const TY*)x, w, T, D, eps, stream)) {} \
+    else if (vec_ok<TY>(out, x, nullptr, D) && D <= kNormThreads * kNormMaxChunks * Vec16<TY>::N)             \
         launch_kernel(rmsnorm_vec_kernel<TY, false>, dim3(T), dim3(kNormThreads), 0, stream, (TY*)out, nullptr, (const TY*)x, w, D, eps); \
     else                                                                                                      \
         launch_kernel(rmsnorm_kernel<TY, false>, dim3(T), dim3(256), 0, stream, (TY*)out, nullptr, (const TY*)x, w, D, eps)
@@ -219,7 +306,8 @@ extern "C" int cvb_add_rmsnorm(void* out, void* resid, const void* x, const floa
     if (T == 0) return CVB_OK;
     if (T < 0 || D <= 0) return CVB_E_SIZE;
 #define CALL(TY)                                                                                              \
-    if (vec_ok<TY>(out, x, resid, D) && D <= kNormThreads * kNormMaxChunks * Vec16<TY>::N)                    \
+    if (vec_ok<TY>(out, x, resid, D) && launch_warp_norm<TY, true>((TY*)out, (TY*)resid, (const TY*)x, w, T, D, eps, stream)) {} \
+    else if (vec_ok<TY>(out, x, resid, D) && D <= kNormThreads * kNormMaxChunks * Vec16<TY>::N)               \
         launch_kernel(rmsnorm_vec_kernel<TY, true>, dim3(T), dim3(kNormThreads), 0, stream, (TY*)out, (TY*)resid, (const TY*)x, w, D, eps); \
     else                                                                                                      \
         launch_kernel(rmsnorm_kernel<TY, true>, dim3(T), dim3(256), 0, stream, (TY*)out, (TY*)resid, (const TY*)x, w, D, eps)

@@ -217,9 +217,41 @@ def decode_block(a) -> dict:
             "separate_us": round(us_s, 2), "weights_MB": round(nbytes / 1e6, 1), "fused_GBps": round(nbytes / us_f / 1e3, 1)}
 
 
+def elementwise(a) -> dict:
+    """The memory-bound kernels of a prompt portion of --tokens tokens at the model's widths (--cols hidden, --rows
+    intermediate): residual add + RMSNorm, SwiGLU, per-head norm + rotary + cache write.  Inputs stay in L2 between
+    calls, as they do in the model, where the product before each of these kernels has just written them."""
+    from .csrc import ops
+    d = torch.device("cuda:0")
+    T, D, I, H, KV, hd, page = a.tokens, a.cols, a.rows, a.heads, a.kv_heads, a.head_dim, a.page_size
+    bf = torch.bfloat16
+    x, resid, out = (torch.randn(T, D, device=d).to(bf) for _ in range(3))
+    w = torch.ones(D, device=d)
+    gu, act = torch.randn(T, 2 * I, device=d).to(bf), torch.empty(T, I, device=d, dtype=bf)
+    qkv, q = torch.randn(T, (H + 2 * KV) * hd, device=d).to(bf), torch.empty(T, H * hd, device=d, dtype=bf)
+    qw = torch.ones(hd, device=d)
+    inv = 1.0 / (1e6 ** (torch.arange(0, hd, 2, dtype=torch.float64) / hd))
+    ang = torch.arange(T + 8, dtype=torch.float64)[:, None] * inv[None, :]
+    cos, sin = ang.cos().float().to(d), ang.sin().float().to(d)
+    pos = torch.arange(T, dtype=torch.int32, device=d)
+    n_pages = (T + page - 1) // page
+    cache = torch.zeros(n_pages, 2, KV, page, hd, device=d, dtype=bf)
+    slots = torch.randperm(n_pages * page, device=d)[:T].to(torch.int32)
+    res = {"kernel": "elementwise", "tokens": T}
+    for name, fn, nbytes in (
+            ("add_rmsnorm", lambda i: ops.add_rmsnorm(out, resid, x, w, 1e-6), 4 * T * D * 2),
+            ("swiglu", lambda i: ops.swiglu(act, gu), 3 * T * I * 2),
+            ("qk_norm_rope_kv", lambda i: ops.qk_norm_rope_kv(q, qkv, qw, qw, cos, sin, pos, slots, cache, H, KV, hd, page, 1e-6),
+             2 * T * (H + 2 * KV) * hd * 2)):
+        us = _time(fn, a.iters)
+        res[name] = {"us": round(us, 2), "GBps": round(nbytes / us / 1e3, 1)}
+    ops.check_device_errors(d)
+    return res
+
+
 def main(argv=None) -> int:
     p = argparse.ArgumentParser(prog="kernel_bench")
-    p.add_argument("kernel", choices=["attn_decode", "attn_prefill", "gemv", "gemv_fused", "gemm", "decode_block"])
+    p.add_argument("kernel", choices=["attn_decode", "attn_prefill", "gemv", "gemv_fused", "gemm", "decode_block", "elementwise"])
     p.add_argument("--tile-n", type=int, default=0)
     p.add_argument("--impl", default="tcgen05", choices=["tcgen05", "mma"])
     p.add_argument("--form", default="plain", choices=["plain", "norm", "swiglu"])
@@ -238,7 +270,8 @@ def main(argv=None) -> int:
     a = p.parse_args(argv)
     if a.kernel == "attn_prefill" and a.batch == 8 and "--batch" not in (argv or sys.argv):
         a.batch = 1
-    res = {"attn_decode": attn_decode, "attn_prefill": attn_prefill, "gemv": gemv, "gemv_fused": gemv_fused, "gemm": gemm, "decode_block": decode_block}[a.kernel](a)
+    res = {"attn_decode": attn_decode, "attn_prefill": attn_prefill, "gemv": gemv, "gemv_fused": gemv_fused, "gemm": gemm, "decode_block": decode_block,
+           "elementwise": elementwise}[a.kernel](a)
     print(json.dumps(res))
     return 0
 
