@@ -45,7 +45,8 @@ struct GemvParams {
     const __nv_bfloat16* W;        // [N, K]
     int M, N, K;
     int warps_k;                   // warps that share one tile's K range
-    int tiles_per_block;
+    int tiles_per_block;           // tiles side by side in a block
+    int n_tiles;
     float eps;
 };
 
@@ -61,25 +62,32 @@ gemv_mma_kernel(const GemvParams p) {
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
     pdl_trigger();
 
-    // ---- this warp's tile and K range; its first batch of weights is fetched before anything else: weights do not
-    // depend on the kernels before this one, so the fetch overlaps their tail and this kernel's own prologue ----
+    // ---- this warp's tiles and K range.  A block walks the tiles blockIdx.x, blockIdx.x + gridDim.x, ... (each
+    // `tiles_per_block` wide), so that the activations are staged once per block however many rows W has.  The first
+    // batch of weights is fetched before anything else: weights do not depend on the kernels before this one, so the
+    // fetch overlaps their tail and this kernel's own prologue ----
     constexpr int OUT_PER_TILE = SWIGLU ? 8 : TILE_ROWS;               // output columns a tile produces
     const int n_out = SWIGLU ? p.N / 2 : p.N;
     const int tile_in_block = warp / p.warps_k, wk = warp % p.warps_k;
-    const int tile = blockIdx.x * p.tiles_per_block + tile_in_block;
-    const int n0 = tile * OUT_PER_TILE;
     const int r = lane >> 2, q = lane & 3;
-    // rows of W behind the upper (a0, a2) and lower (a1, a3) halves of the A operand
-    int row_hi = n0 + r, row_lo = SWIGLU ? n_out + n0 + r : n0 + r + 8;
-    row_hi = min(row_hi, p.N - 1);                                       // a ragged last tile repeats a row; dropped below
-    row_lo = min(row_lo, p.N - 1);
-    const uint4* w_hi = reinterpret_cast<const uint4*>(p.W + static_cast<int64_t>(row_hi) * K);
-    const uint4* w_lo = reinterpret_cast<const uint4*>(p.W + static_cast<int64_t>(row_lo) * K);
     constexpr bool LOWER = SWIGLU || TILE_ROWS == 16;
     const int slabs = (K + 31) >> 5;
     const int per_warp = (slabs + p.warps_k - 1) / p.warps_k;
     const int j_begin = wk * per_warp, j_end = min(slabs, j_begin + per_warp);
     const uint4 zero = make_uint4(0, 0, 0, 0);
+    const int n_rounds = (p.n_tiles + gridDim.x * p.tiles_per_block - 1) / (gridDim.x * p.tiles_per_block);
+    int n0 = 0;
+    const uint4 *w_hi = nullptr, *w_lo = nullptr;
+    auto set_tile = [&](int round) {
+        const int tile = (round * gridDim.x + blockIdx.x) * p.tiles_per_block + tile_in_block;
+        n0 = tile * OUT_PER_TILE;
+        // rows of W behind the upper (a0, a2) and lower (a1, a3) halves of the A operand
+        int row_hi = n0 + r, row_lo = SWIGLU ? n_out + n0 + r : n0 + r + 8;
+        row_hi = min(row_hi, p.N - 1);                                   // a ragged last tile repeats a row; dropped below
+        row_lo = min(row_lo, p.N - 1);
+        w_hi = reinterpret_cast<const uint4*>(p.W + static_cast<int64_t>(row_hi) * K);
+        w_lo = reinterpret_cast<const uint4*>(p.W + static_cast<int64_t>(row_lo) * K);
+    };
     uint4 wh[kJBatch], wl[kJBatch];
     auto fetch = [&](int jb) {
 #pragma unroll
@@ -90,6 +98,7 @@ gemv_mma_kernel(const GemvParams p) {
             if constexpr (LOWER) wl[u] = ok ? __ldg(w_lo + c) : zero; else wl[u] = zero;
         }
     };
+    set_tile(0);
     fetch(j_begin);
     pdl_wait();
 
@@ -147,46 +156,54 @@ gemv_mma_kernel(const GemvParams p) {
     }
     __syncthreads();
 
-    // ---- the product ----
+    // ---- the product, tile after tile ----
     const uint4* x_row = reinterpret_cast<const uint4*>(xs + r * xstride);
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};
-    for (int jb = j_begin; jb < j_end; jb += kJBatch) {
-        if (jb != j_begin) fetch(jb);
+    for (int round = 0; round < n_rounds; ++round) {
+        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+        for (int jb = j_begin; jb < j_end; jb += kJBatch) {
+            if (jb != j_begin) fetch(jb);
 #pragma unroll
-        for (int u = 0; u < kJBatch; ++u) {
-            const int c = (jb + u) * 4 + q;
-            if (jb + u >= j_end) break;
-            const uint4 xv = c < chunks ? x_row[c] : zero;
-            mma_16816(acc, wh[u].x, wl[u].x, wh[u].y, wl[u].y, xv.x, xv.y);
-            mma_16816(acc, wh[u].z, wl[u].z, wh[u].w, wl[u].w, xv.z, xv.w);
+            for (int u = 0; u < kJBatch; ++u) {
+                const int c = (jb + u) * 4 + q;
+                if (jb + u >= j_end) break;
+                const uint4 xv = c < chunks ? x_row[c] : zero;
+                mma_16816(acc, wh[u].x, wl[u].x, wh[u].y, wl[u].y, xv.x, xv.y);
+                mma_16816(acc, wh[u].z, wl[u].z, wh[u].w, wl[u].w, xv.z, xv.w);
+            }
         }
-    }
-    // acc[0], acc[1]: (row r, batch 2q, 2q+1); acc[2], acc[3]: (row r + 8, same)
-    float* mine = red + warp * 128;
-    mine[r * 8 + 2 * q] = acc[0];
-    mine[r * 8 + 2 * q + 1] = acc[1];
-    mine[(r + 8) * 8 + 2 * q] = acc[2];
-    mine[(r + 8) * 8 + 2 * q + 1] = acc[3];
-    __syncthreads();
+        const int tile_base = (round * gridDim.x + blockIdx.x) * p.tiles_per_block;
+        if (round + 1 < n_rounds) {                                      // the next tile's weights are on their way
+            set_tile(round + 1);                                         // while this one's parts are added up
+            fetch(j_begin);
+        }
+        // acc[0], acc[1]: (row r, batch 2q, 2q+1); acc[2], acc[3]: (row r + 8, same)
+        float* mine = red + warp * 128;
+        mine[r * 8 + 2 * q] = acc[0];
+        mine[r * 8 + 2 * q + 1] = acc[1];
+        mine[(r + 8) * 8 + 2 * q] = acc[2];
+        mine[(r + 8) * 8 + 2 * q + 1] = acc[3];
+        __syncthreads();
 
-    // ---- add the K parts of every tile and store ----
-    for (int i = threadIdx.x; i < p.tiles_per_block * OUT_PER_TILE * kBatch; i += blockDim.x) {
-        const int t = i / (OUT_PER_TILE * kBatch), rem = i % (OUT_PER_TILE * kBatch);
-        const int row = rem / kBatch, m = rem % kBatch;
-        const int n = (blockIdx.x * p.tiles_per_block + t) * OUT_PER_TILE + row;
-        if (n >= n_out || m >= p.M) continue;
-        float s0 = 0.f, s1 = 0.f;
-        for (int w = 0; w < p.warps_k; ++w) {
-            const float* part = red + (t * p.warps_k + w) * 128;
-            s0 += part[row * 8 + m];
-            if constexpr (SWIGLU) s1 += part[(row + 8) * 8 + m];
+        // ---- add the K parts of every tile and store ----
+        for (int i = threadIdx.x; i < p.tiles_per_block * OUT_PER_TILE * kBatch; i += blockDim.x) {
+            const int t = i / (OUT_PER_TILE * kBatch), rem = i % (OUT_PER_TILE * kBatch);
+            const int row = rem / kBatch, m = rem % kBatch;
+            const int n = (tile_base + t) * OUT_PER_TILE + row;
+            if (n >= n_out || m >= p.M) continue;
+            float s0 = 0.f, s1 = 0.f;
+            for (int w = 0; w < p.warps_k; ++w) {
+                const float* part = red + (t * p.warps_k + w) * 128;
+                s0 += part[row * 8 + m];
+                if constexpr (SWIGLU) s1 += part[(row + 8) * 8 + m];
+            }
+            float y = s0;
+            if constexpr (SWIGLU) {
+                const float g = rnd<__nv_bfloat16>(s0), u = rnd<__nv_bfloat16>(s1);
+                y = rnd<__nv_bfloat16>(g / (1.f + expf(-g))) * u;
+            }
+            p.out[static_cast<int64_t>(m) * n_out + n] = __float2bfloat16_rn(y);
         }
-        float y = s0;
-        if constexpr (SWIGLU) {
-            const float g = rnd<__nv_bfloat16>(s0), u = rnd<__nv_bfloat16>(s1);
-            y = rnd<__nv_bfloat16>(g / (1.f + expf(-g))) * u;
-        }
-        p.out[static_cast<int64_t>(m) * n_out + n] = __float2bfloat16_rn(y);
+        if (round + 1 < n_rounds) __syncthreads();                       // `red` is free again
     }
 }
 
@@ -199,15 +216,40 @@ static int launch_gemv(GemvParams p, cudaStream_t stream) {
     p.warps_k = max(1, min(8, (slabs + kJBatch - 1) / kJBatch));          // about one batch of loads per warp
     p.tiles_per_block = max(1, 8 / p.warps_k);
     while (p.tiles_per_block > 1 && (tiles + p.tiles_per_block - 1) / p.tiles_per_block < 120) p.tiles_per_block >>= 1;
-    const int warps = p.warps_k * p.tiles_per_block;
-    const int blocks = (tiles + p.tiles_per_block - 1) / p.tiles_per_block;
-    const size_t smem = static_cast<size_t>(kBatch) * (p.K + kXPad) * sizeof(__nv_bfloat16) + static_cast<size_t>(warps) * 128 * sizeof(float);
-    if (smem > 200 * 1024) return CVB_E_SIZE;
-    if (smem > 48 * 1024) {
-        cudaError_t e = cudaFuncSetAttribute(gemv_mma_kernel<TILE_ROWS, NORM, SWIGLU>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(smem));
-        if (e != cudaSuccess) return static_cast<int>(e);
+    p.n_tiles = tiles;
+    auto smem_for = [&](int tpb) {
+        return static_cast<size_t>(kBatch) * (p.K + kXPad) * sizeof(__nv_bfloat16) + static_cast<size_t>(p.warps_k * tpb) * 128 * sizeof(float);
+    };
+    // Blocks stage all of the activations: with long rows few of them fit on an SM, and each then takes more warps
+    // (up to 16) to keep as many loads in flight.  The grid is what the device holds at once; blocks walk the tiles.
+    static int sms = 0;
+    if (sms == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
     }
+    if (smem_for(p.tiles_per_block) > 200 * 1024) return CVB_E_SIZE;
+    auto resident = [&](int tpb) {                                   // blocks of this shape that an SM holds
+        const size_t smem = smem_for(tpb);
+        if (smem > 48 * 1024 &&
+            cudaFuncSetAttribute(gemv_mma_kernel<TILE_ROWS, NORM, SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 static_cast<int>(smem)) != cudaSuccess)
+            return 0;
+        int n = 0;
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, gemv_mma_kernel<TILE_ROWS, NORM, SWIGLU>, p.warps_k * tpb * 32, smem) != cudaSuccess)
+            return 0;
+        return n;
+    };
+    int per_sm = resident(p.tiles_per_block);
+    while (per_sm * p.warps_k * p.tiles_per_block < 16 && p.warps_k * p.tiles_per_block * 2 <= 16 &&
+           smem_for(p.tiles_per_block * 2) <= 200 * 1024 && (tiles + p.tiles_per_block * 2 - 1) / (p.tiles_per_block * 2) >= sms) {
+        p.tiles_per_block *= 2;
+        per_sm = resident(p.tiles_per_block);
+    }
+    if (per_sm < 1) return CVB_E_SIZE;
+    const int warps = p.warps_k * p.tiles_per_block;
+    const int blocks = min((tiles + p.tiles_per_block - 1) / p.tiles_per_block, sms * per_sm);
+    const size_t smem = smem_for(p.tiles_per_block);
     launch_kernel(gemv_mma_kernel<TILE_ROWS, NORM, SWIGLU>, dim3(blocks), dim3(warps * 32), smem, stream, p);
     return launch_status();
 }
@@ -217,6 +259,108 @@ static int dispatch_gemv(const GemvParams& p, cudaStream_t stream) {
     // tiles of 16 rows while they still give about one block per SM, else tiles of 8
     if (p.N / 16 >= 120) return launch_gemv<16, NORM, false>(p, stream);
     return launch_gemv<8, NORM, false>(p, stream);
+}
+
+// ---- large weights: the inner dimension is split over blocks as well -----------------------------------------------
+// The kernel above stages all of the activations in every block, which is right while W has a few thousand columns and a
+// few MB.  For larger W a block takes kSkTiles tiles of 16 rows (one per warp) times one chunk of kSkChunk columns: 128 KB
+// of weights behind 8 KB of staged activations, two batches of loads per warp, and enough blocks for every size.  The
+// partial sums of the chunks go to a float scratch [chunk][batch row][N]; the block that finishes last among the chunks of
+// its rows adds them up in chunk order (so the result does not depend on which block that was) and writes the output.
+// `counters` holds one int per group of kSkTiles * 16 rows, zero before the first launch and zero again after each.
+constexpr int kSkTiles = 8;
+constexpr int kSkChunk = 512;
+constexpr int kSkThreads = kSkTiles * 32;
+
+struct SplitKParams {
+    __nv_bfloat16* out;            // [M, N]
+    const __nv_bfloat16* x;        // [M, K]
+    const __nv_bfloat16* W;        // [N, K]
+    float* part;                   // [splits, 8, N]
+    int* counters;                 // [ceil(N / 128)]
+    int M, N, K, splits;
+};
+
+__global__ void __launch_bounds__(kSkThreads, 2)
+gemv_splitk_kernel(const SplitKParams p) {
+    __shared__ __align__(16) __nv_bfloat16 xs[kBatch * (kSkChunk + kXPad)];
+    __shared__ int is_last;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int r = lane >> 2, q = lane & 3;
+    const int K = p.K, chunks = K >> 3;
+    const int k0 = blockIdx.y * kSkChunk;                                // first column of this block's chunk
+    const int c0 = k0 >> 3, c_end = min(chunks, c0 + (kSkChunk >> 3));   // 16-byte chunks [c0, c_end)
+    const int n0 = (blockIdx.x * kSkTiles + warp) * 16;
+    pdl_trigger();
+    const uint4* w_hi = reinterpret_cast<const uint4*>(p.W + static_cast<int64_t>(min(n0 + r, p.N - 1)) * K);
+    const uint4* w_lo = reinterpret_cast<const uint4*>(p.W + static_cast<int64_t>(min(n0 + r + 8, p.N - 1)) * K);
+    const uint4 zero = make_uint4(0, 0, 0, 0);
+    uint4 wh[kJBatch], wl[kJBatch];
+    auto fetch = [&](int jb) {                                           // slabs jb .. jb + kJBatch - 1 of this chunk
+#pragma unroll
+        for (int u = 0; u < kJBatch; ++u) {
+            const int c = c0 + (jb + u) * 4 + q;
+            const bool ok = n0 < p.N && c < c_end;
+            wh[u] = ok ? __ldg(w_hi + c) : zero;
+            wl[u] = ok ? __ldg(w_lo + c) : zero;
+        }
+    };
+    fetch(0);
+    pdl_wait();
+    constexpr int xstride = kSkChunk + kXPad;
+    for (int i = threadIdx.x; i < kBatch * (kSkChunk >> 3); i += kSkThreads) {
+        const int m = i / (kSkChunk >> 3), c = i % (kSkChunk >> 3);
+        *reinterpret_cast<uint4*>(xs + m * xstride + c * 8) =
+            (m < p.M && c0 + c < c_end) ? *reinterpret_cast<const uint4*>(p.x + static_cast<int64_t>(m) * K + (c0 + c) * 8) : zero;
+    }
+    __syncthreads();
+    const uint4* x_row = reinterpret_cast<const uint4*>(xs + r * xstride);
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    constexpr int kSlabs = kSkChunk / 32;
+#pragma unroll
+    for (int jb = 0; jb < kSlabs; jb += kJBatch) {
+        if (jb != 0) fetch(jb);
+#pragma unroll
+        for (int u = 0; u < kJBatch; ++u) {
+            const uint4 xv = x_row[(jb + u) * 4 + q];
+            mma_16816(acc, wh[u].x, wl[u].x, wh[u].y, wl[u].y, xv.x, xv.y);
+            mma_16816(acc, wh[u].z, wl[u].z, wh[u].w, wl[u].w, xv.z, xv.w);
+        }
+    }
+    // acc[0], acc[1]: (row r, batch 2q, 2q+1); acc[2], acc[3]: (row r + 8, same)
+    float* part = p.part + static_cast<int64_t>(blockIdx.y) * kBatch * p.N;
+    if (n0 + r < p.N) {
+        part[static_cast<int64_t>(2 * q) * p.N + n0 + r] = acc[0];
+        part[static_cast<int64_t>(2 * q + 1) * p.N + n0 + r] = acc[1];
+    }
+    if (n0 + r + 8 < p.N) {
+        part[static_cast<int64_t>(2 * q) * p.N + n0 + r + 8] = acc[2];
+        part[static_cast<int64_t>(2 * q + 1) * p.N + n0 + r + 8] = acc[3];
+    }
+    __threadfence();
+    __syncthreads();
+    if (threadIdx.x == 0) is_last = atomicAdd(p.counters + blockIdx.x, 1) == p.splits - 1;
+    __syncthreads();
+    if (!is_last) return;
+    __threadfence();
+    const int row0 = blockIdx.x * kSkTiles * 16;
+    for (int i = threadIdx.x; i < p.M * kSkTiles * 16; i += kSkThreads) {
+        const int m = i / (kSkTiles * 16), n = row0 + i % (kSkTiles * 16);
+        if (n >= p.N) continue;
+        const float* src = p.part + static_cast<int64_t>(m) * p.N + n;
+        float sum = 0.f;
+        int s = 0;
+        for (; s + 4 <= p.splits; s += 4) {                              // four loads in flight, added in chunk order
+            const float a = __ldcg(src + static_cast<int64_t>(s) * kBatch * p.N);
+            const float b = __ldcg(src + static_cast<int64_t>(s + 1) * kBatch * p.N);
+            const float c = __ldcg(src + static_cast<int64_t>(s + 2) * kBatch * p.N);
+            const float d = __ldcg(src + static_cast<int64_t>(s + 3) * kBatch * p.N);
+            sum = (((sum + a) + b) + c) + d;
+        }
+        for (; s < p.splits; ++s) sum += __ldcg(src + static_cast<int64_t>(s) * kBatch * p.N);
+        p.out[static_cast<int64_t>(m) * p.N + n] = __float2bfloat16_rn(sum);
+    }
+    if (threadIdx.x == 0) p.counters[blockIdx.x] = 0;
 }
 
 }  // namespace cvb
@@ -242,4 +386,29 @@ extern "C" int cvb_gemv_bf16(void* out, const void* x, const void* delta, void* 
     if (mode == 1) return dispatch_gemv<true>(p, stream);
     if (mode == 2) return launch_gemv<16, true, true>(p, stream);
     return CVB_E_SHAPE;
+}
+
+// Floats of scratch and ints of counters that cvb_gemv_splitk_bf16 needs for a weight of N rows and K columns.
+extern "C" int64_t cvb_gemv_splitk_scratch_floats(int N, int K) {
+    return static_cast<int64_t>((K + kSkChunk - 1) / kSkChunk) * kBatch * N;
+}
+extern "C" int cvb_gemv_splitk_counters(int N) { return (N + kSkTiles * 16 - 1) / (kSkTiles * 16); }
+
+// out[:M] = x[:M] W^T for up to 8 rows, the inner dimension split over blocks (for large W).
+extern "C" int cvb_gemv_splitk_bf16(void* out, const void* x, const void* W, int M, int N, int K, float* scratch,
+                                    int64_t scratch_floats, int* counters, cudaStream_t stream) {
+    if (M == 0) return CVB_OK;
+    if (M < 0 || M > kBatch || N <= 0 || K <= 0) return CVB_E_SIZE;
+    if (K % 8) return CVB_E_ALIGN;
+    auto al = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+    if (!al(out) || !al(x) || !al(W)) return CVB_E_ALIGN;
+    if (scratch == nullptr || counters == nullptr || scratch_floats < cvb_gemv_splitk_scratch_floats(N, K)) return CVB_E_SCRATCH;
+    SplitKParams p{};
+    p.out = (__nv_bfloat16*)out; p.x = (const __nv_bfloat16*)x; p.W = (const __nv_bfloat16*)W;
+    p.part = scratch; p.counters = counters; p.M = M; p.N = N; p.K = K;
+    p.splits = (K + kSkChunk - 1) / kSkChunk;
+    if (p.splits > 65535) return CVB_E_SIZE;
+    dim3 grid(static_cast<unsigned>(cvb_gemv_splitk_counters(N)), static_cast<unsigned>(p.splits));
+    launch_kernel(gemv_splitk_kernel, grid, dim3(kSkThreads), 0, stream, p);
+    return launch_status();
 }

@@ -369,6 +369,9 @@ def gemv_bf16(out: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, rows: in
     if _gemv is None:
         lib = load_library("gemv_bf16")
         lib.cvb_gemv_bf16.restype = c_int
+        lib.cvb_gemv_splitk_bf16.restype = c_int
+        lib.cvb_gemv_splitk_scratch_floats.restype = c_int64
+        lib.cvb_gemv_splitk_counters.restype = c_int
         _gemv = lib
     _cuda(out, x, weight, norm_weight, delta, resid_out)
     _contig(out, x, weight, norm_weight, delta, resid_out)
@@ -388,6 +391,60 @@ def gemv_bf16(out: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, rows: in
     _check(_gemv.cvb_gemv_bf16(_ptr(out), _ptr(x), _ptr(delta), _ptr(resid_out), _ptr(norm_weight), _ptr(weight), c_int(rows),
                                c_int(N), c_int(K), c_float(eps), c_int(mode), _stream()), "gemv_bf16")
     return out
+
+
+SPLITK_MIN_BYTES = 16 << 20
+_splitk_buffers: Dict[int, list] = {}
+
+
+def gemv_splitk_preferred(x_dtype: torch.dtype, weight: torch.Tensor, rows: int) -> bool:
+    """Weights of 16 MB and more go through the kernel that splits the inner dimension over blocks as well."""
+    return (x_dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and 0 < rows <= GEMV_MAX_ROWS
+            and weight.dim() == 2 and weight.shape[1] % 8 == 0 and weight.numel() * 2 >= SPLITK_MIN_BYTES)
+
+
+def gemv_splitk_bf16(out: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, rows: int) -> torch.Tensor:
+    """out[:rows] = x[:rows] @ weight^T for up to 8 rows and a large weight.  The scratch for the partial sums and the
+    counters belong to the device and grow with the largest weight seen; they are made at the first call with a weight
+    (a warm-up before any graph capture, as the runner does, sizes them)."""
+    global _gemv
+    if _gemv is None:
+        lib = load_library("gemv_bf16")
+        lib.cvb_gemv_bf16.restype = c_int
+        lib.cvb_gemv_splitk_bf16.restype = c_int
+        lib.cvb_gemv_splitk_scratch_floats.restype = c_int64
+        lib.cvb_gemv_splitk_counters.restype = c_int
+        _gemv = lib
+    _cuda(out, x, weight)
+    _contig(out, x, weight)
+    N, K = weight.shape
+    if x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or x.shape[1] != K:
+        raise KernelError("gemv_splitk_bf16: x [M, K], weight [N, K] and out must be bf16")
+    if out.shape[1] != N or out.shape[0] < rows or x.shape[0] < rows:
+        raise KernelError("gemv_splitk_bf16: out must be [M, N]")
+    need_f = int(_gemv.cvb_gemv_splitk_scratch_floats(c_int(N), c_int(K)))
+    need_c = int(_gemv.cvb_gemv_splitk_counters(c_int(N)))
+    idx = x.device.index if x.device.index is not None else torch.cuda.current_device()
+    buf = _splitk_buffers.get(idx)
+    if buf is None or buf[0].numel() < need_f or buf[1].numel() < need_c:
+        if torch.cuda.is_current_stream_capturing():
+            raise KernelError("gemv_splitk_bf16: its scratch has to grow; run the shape once before capturing it")
+        buf = [torch.empty(max(need_f, buf[0].numel() if buf else 0), dtype=torch.float32, device=x.device),
+               torch.zeros(max(need_c, buf[1].numel() if buf else 0, 1024), dtype=torch.int32, device=x.device)]
+        _splitk_buffers[idx] = buf
+    _check(_gemv.cvb_gemv_splitk_bf16(_ptr(out), _ptr(x), _ptr(weight), c_int(rows), c_int(N), c_int(K), _ptr(buf[0]),
+                                      c_int64(buf[0].numel()), _ptr(buf[1]), _stream()), "gemv_splitk_bf16")
+    return out
+
+
+def project_rows(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, rows: int) -> torch.Tensor:
+    """out = x @ weight^T by the kernel that suits the step: the weight-streaming kernels for a few bf16 rows (split over
+    the inner dimension when the weight is large), the library product otherwise."""
+    if gemv_splitk_preferred(x.dtype, weight, rows):
+        return gemv_splitk_bf16(out, x, weight, rows)
+    if gemv_supported(x.dtype, weight, rows):
+        return gemv_bf16(out, x, weight, rows)
+    return linear(x, weight, out=out)
 
 
 _gemm = None

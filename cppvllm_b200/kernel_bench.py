@@ -135,7 +135,9 @@ def gemv_fused(a) -> dict:
     out = torch.empty(a.batch, n_out, device=d, dtype=torch.bfloat16)
 
     def run(i):
-        if a.form == "plain":
+        if a.form == "splitk":
+            ops.gemv_splitk_bf16(out, x, ws[i % copies], a.batch)
+        elif a.form == "plain":
             ops.gemv_bf16(out, x, ws[i % copies], a.batch)
         else:
             ops.gemv_bf16(out, x, ws[i % copies], a.batch, norm_weight=nw, eps=1e-6, delta=delta, resid_out=h2,
@@ -254,7 +256,7 @@ def main(argv=None) -> int:
     p.add_argument("kernel", choices=["attn_decode", "attn_prefill", "gemv", "gemv_fused", "gemm", "decode_block", "elementwise"])
     p.add_argument("--tile-n", type=int, default=0)
     p.add_argument("--impl", default="tcgen05", choices=["tcgen05", "mma"])
-    p.add_argument("--form", default="plain", choices=["plain", "norm", "swiglu"])
+    p.add_argument("--form", default="plain", choices=["plain", "norm", "swiglu", "splitk"])
     p.add_argument("--batch", type=int, default=8)
     p.add_argument("--context", type=int, default=4096)
     p.add_argument("--tokens", type=int, default=2048)

@@ -82,7 +82,7 @@ class PagedAttention(Mixer):
     def forward(self, x, ctx, cache, state):
         T = x.shape[0]
         H, KV, hd = self.num_heads, self.num_kv_heads, self.head_dim
-        qkv = ops.linear(x, self.w_qkv, out=self.rt.workspace.rows("attn_qkv", T, (H + 2 * KV) * hd, x.dtype))
+        qkv = ops.project_rows(x, self.w_qkv, self.rt.workspace.rows("attn_qkv", T, (H + 2 * KV) * hd, x.dtype), T)
         return self._after_projection(qkv, ctx, cache)
 
     def can_fuse_norm(self, norm, ctx) -> bool:
@@ -90,6 +90,7 @@ class PagedAttention(Mixer):
         projection's weight-streaming kernel."""
         return (getattr(norm, "weight", None) is not None and hasattr(norm, "eps")
                 and ops.gemv_supported(self.rt.dtype, self.w_qkv, ctx.num_tokens)
+                and not ops.gemv_splitk_preferred(self.rt.dtype, self.w_qkv, ctx.num_tokens)
                 and ops.gemv_supported(self.rt.dtype, self.w_o, ctx.num_tokens))
 
     def forward_fused(self, h, pending, norm, ctx, cache, state):
@@ -151,10 +152,7 @@ class PagedAttention(Mixer):
             interleaved=pos.interleaved if pos is not None else False)
         att = ws.rows("attn_out", T, H * hd, x.dtype)
         self.attend(att, q, ctx, cache, g)
-        out = ws.rows("attn_proj", T, self.hidden_size, x.dtype)
-        if ops.gemv_supported(att.dtype, self.w_o, T):
-            return ops.gemv_bf16(out, att, self.w_o, T)
-        return ops.linear(att, self.w_o, out=out)
+        return ops.project_rows(att, self.w_o, ws.rows("attn_proj", T, self.hidden_size, x.dtype), T)
 
     # target number of blocks for the split-KV decode kernel: two per SM of a B200
     DECODE_TARGET_BLOCKS = 296

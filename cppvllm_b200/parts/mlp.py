@@ -39,19 +39,17 @@ class SwiGLUMLP(FeedForward):
     def forward(self, x, ctx):
         T = x.shape[0]
         ws = self.rt.workspace
-        gu = ops.linear(x, self.w_gate_up, out=ws.rows("ffn_gate_up", T, 2 * self.intermediate_size, x.dtype))
+        gu = ops.project_rows(x, self.w_gate_up, ws.rows("ffn_gate_up", T, 2 * self.intermediate_size, x.dtype), T)
         act = ops.swiglu(ws.rows("ffn_act", T, self.intermediate_size, x.dtype), gu)
         return self._down(act, T)
 
     def _down(self, act, T):
-        out = self.rt.workspace.rows("ffn_out", T, self.hidden_size, act.dtype)
-        if ops.gemv_supported(act.dtype, self.w_down, T):
-            return ops.gemv_bf16(out, act, self.w_down, T)
-        return ops.linear(act, self.w_down, out=out)
+        return ops.project_rows(act, self.w_down, self.rt.workspace.rows("ffn_out", T, self.hidden_size, act.dtype), T)
 
     def can_fuse_norm(self, norm, ctx) -> bool:
         return (getattr(norm, "weight", None) is not None and hasattr(norm, "eps")
                 and ops.gemv_supported(self.rt.dtype, self.w_gate_up, ctx.num_tokens)
+                and not ops.gemv_splitk_preferred(self.rt.dtype, self.w_gate_up, ctx.num_tokens)
                 and ops.gemv_supported(self.rt.dtype, self.w_down, ctx.num_tokens))
 
     def forward_fused(self, h, pending, norm, ctx):

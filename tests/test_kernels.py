@@ -476,6 +476,21 @@ def test_gemv_plain_norm_and_swiglu_forms(ops, M, N, K):
         ops.gemv_bf16(out, x, W, M, norm_weight=nw, eps=eps, delta=delta, resid_out=x)
 
 
+@pytest.mark.parametrize("M,N,K", [(1, 200, 1000), (5, 128, 512), (8, 1031, 2056), (3, 4096, 4096)])
+def test_split_k_weight_streaming_product(ops, M, N, K):
+    """The product for large weights (inner dimension split over blocks, last block adds the parts) at sizes that are no
+    multiples of its tiles, twice in a row (the counters must be back at zero), against float32."""
+    g = torch.Generator().manual_seed(M * 1000 + N + K)
+    W = (torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16)
+    for rep in range(2):
+        x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+        out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=dev())
+        ops.gemv_splitk_bf16(out, x.to(dev()), W.to(dev()), M)
+        ref = x.float() @ W.float().t()
+        torch.testing.assert_close(out.float().cpu(), rnd(ref, torch.bfloat16), atol=2e-2, rtol=2e-2)
+    ops.check_device_errors(dev())
+
+
 # ---- tcgen05 matrix product -----------------------------------------------------------------------------------
 
 @pytest.mark.parametrize("M,N,K,tile_n", [(128, 128, 64, 128), (2048, 1024, 2048, 128), (300, 520, 200, 128), (1, 8, 8, 128),
