@@ -15,7 +15,9 @@ sizes, batch 8, context 4096 (the last timed step runs at 4096 tokens per reques
                (flops of the matrix products and of causal attention / time / peak).
     roofline   for the decode step: bytes it has to read (every weight once, the cache of the live requests)
                / time, against the measured copy bandwidth.
-    points     decode tokens per second at batch 1 and 64, same context.
+    points     decode tokens per second at batch 1 and 64, same context; and the reference's own benchmark (256
+               requests with random lengths through the engine, output tokens a second; the reference's README gives
+               5156 tok/s for it on an A10G).
 Peaks come from MEASURED_PEAKS.json next to this file when the driver wrote it, else from the fallback
 (6650 GB/s, 1590 TFLOP/s).  Every timed step reads several GB, far more than the 126 MB L2.
 """
@@ -165,12 +167,13 @@ def main():
     tmp = tempfile.mkdtemp(prefix="cppvllm_b200_bench_")
     t_build = time.time()
     model_dir = write_random_model(os.path.join(tmp, "qwen3_0p6b_random"), cfg, seed=0, std=0.02, norm_spread=0.0)
-    max_b = B if args.no_points else max(B, 64)
+    max_b = B if args.no_points else max(B, 256)                # 256: the reference's throughput workload (bench.cpp)
     max_len = CTX + 64
     page = 32
     llm = LLMEngine(EngineConfig(model_path=model_dir, dtype="bfloat16", max_num_batched_tokens=8192, max_num_seqs=max_b,
                                  max_chunk_tokens=4096, max_model_len=max_len, block_size=page,
-                                 num_kv_blocks=max_b * ((max_len + page - 1) // page) + 8, seed=0))
+                                 num_kv_blocks=max(max(B, 64) * ((max_len + page - 1) // page),
+                                                   0 if args.no_points else 256 * (2048 // page)) + 8, seed=0))
     r, sampler = llm.runner, llm.sampler
     vocab = r.vocab_size
     gen = torch.Generator().manual_seed(0)
@@ -281,6 +284,27 @@ def main():
     h2d = r.h2d_bytes_last_step + sampler.h2d_bytes_last
     while not llm.is_finished():
         llm.step()
+    llm.take_finished()
+
+    # ---- the reference's own benchmark (bench.cpp:10-63): 256 requests, prompt and output lengths uniform in
+    # [100, 1024], token ids uniform in [0, 10000], temperature 0.6, ignore_eos; output tokens a second -----------
+    if not args.no_points:
+        import random
+        rng = random.Random(0)
+        reqs = [([rng.randint(0, min(10000, vocab - 1)) for _ in range(rng.randint(100, 1024))],
+                 SamplingParams(temperature=0.6, ignore_eos=True, max_tokens=rng.randint(100, 1024))) for _ in range(256)]
+        llm.generate([[1, 2, 3, 4, 5, 6, 7, 8]], SamplingParams(max_tokens=16))
+        torch.cuda.synchronize()
+        t0 = time.time()
+        c0 = time.perf_counter()
+        for pr, sp_i in reqs:
+            llm.add_request(pr, sp_i)
+        while not llm.is_finished():
+            llm.step()
+        torch.cuda.synchronize()
+        points["throughput_256_requests"] = round(sum(sp_i.max_tokens for _, sp_i in reqs) / (time.perf_counter() - c0), 1)
+        windows.append((t0, time.time()))
+        llm.take_finished()
     clocks.stop()
 
     line = {

@@ -51,6 +51,7 @@ def resolve_architecture(config_dict: Mapping[str, Any]) -> Architecture:
 
     A config.json with neither key is accepted only while exactly one architecture is registered (the
     reference never reads either key, so such files exist)."""
+    from .. import models as _models  # noqa: F401  (the package's own architectures register themselves on import)
     archs = config_dict.get("architectures")
     if isinstance(archs, (list, tuple)) and archs:
         name = str(archs[0])
