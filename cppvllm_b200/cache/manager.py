@@ -12,7 +12,16 @@ keys holds its pages until the request ends.
 Policy, after the reference's BlockManager (engine/block_manager.cpp): pages are handed out least-recently-freed
 first (:35-69); a request's pages are released last-logical-page first (:145-153); ``reserve`` tops a table up to
 cover a given length like ``allocate``/``may_append`` (:80-126) and is all-or-nothing, so a failed reservation
-changes nothing.  Not carried over: the prefix cache (hash chain over full blocks, :10-24,71-143).
+changes nothing.
+
+Prefix cache (optional, ``prefix_caching=True``; reference :10-24,71-143).  Full pages are registered under a chain
+key (the key of the page before, and the page's tokens) once their keys are in the cache (``commit``); a page that is
+given back keeps its key until it is handed out again for other contents.  ``admit`` with the request's tokens takes
+the longest chain of registered pages that match its prefix, at most ``(len - 1) // page_size`` pages so that at
+least one token is computed, and counts them as computed; pages are then shared (reference counts) and read-only for
+the requests that share them, since a request only ever writes positions beyond its computed length.  The cache of a
+windowed group or of per-request state cannot be shared this way: the manager refuses the option unless there is
+exactly one group and it keeps all keys.
 
 State slots.  A request also receives one slot number for per-request state of fixed size (what a recurrent or
 convolutional mixer would keep).  The attention-only architecture here keeps no such state, but the slot
@@ -20,7 +29,7 @@ travels with every step, and the runner zeroes a slot's tensors when it is hande
 """
 from __future__ import annotations
 
-from collections import deque
+from collections import OrderedDict, deque
 from dataclasses import dataclass, field
 from typing import Deque, Dict, List, Optional, Sequence
 
@@ -41,31 +50,76 @@ class GroupConfig:
 
 
 class PagePool:
-    """Free list of one group, least-recently-freed first, with ownership tracking against double frees."""
+    """Pages of one group: a free list, least-recently-freed first, reference counts against double frees, and for the
+    prefix cache the chain key and tokens of a page's contents."""
 
     def __init__(self, num_pages: int):
         if num_pages <= 0:
             raise ValueError("a page pool needs at least one page")
         self.num_pages = num_pages
-        self._free: Deque[int] = deque(range(num_pages))
-        self._held = [False] * num_pages
+        self._free: "OrderedDict[int, None]" = OrderedDict((p, None) for p in range(num_pages))
+        self._refs = [0] * num_pages
+        self._key: List[Optional[int]] = [None] * num_pages       # chain key of the page's contents, if registered
+        self._tokens: List[Optional[tuple]] = [None] * num_pages
+        self._by_key: Dict[int, int] = {}
 
     @property
     def num_free(self) -> int:
         return len(self._free)
 
+    def refs(self, page: int) -> int:
+        return self._refs[page]
+
     def take(self) -> int:
+        """A page for new contents: the least recently freed one; what it was registered as is forgotten."""
         if not self._free:
             raise OutOfPages("no free page")
-        p = self._free.popleft()
-        self._held[p] = True
+        p, _ = self._free.popitem(last=False)
+        k = self._key[p]
+        if k is not None:
+            if self._by_key.get(k) == p:
+                del self._by_key[k]
+            self._key[p] = self._tokens[p] = None
+        self._refs[p] = 1
         return p
 
     def give_back(self, page: int) -> None:
-        if not (0 <= page < self.num_pages) or not self._held[page]:
+        if not (0 <= page < self.num_pages) or self._refs[page] <= 0:
             raise CacheError(f"page {page} is given back but is not held")
-        self._held[page] = False
-        self._free.append(page)
+        self._refs[page] -= 1
+        if self._refs[page] == 0:
+            self._free[page] = None                               # to the tail; it keeps its key until taken again
+
+    # ---- prefix cache ----
+    @staticmethod
+    def chain_key(prefix_key: Optional[int], tokens: tuple) -> int:
+        return hash((prefix_key, tokens))
+
+    def find(self, prefix_key: Optional[int], tokens: tuple):
+        """(page, key) registered for these tokens after that prefix, or (None, key)."""
+        k = self.chain_key(prefix_key, tokens)
+        p = self._by_key.get(k)
+        if p is None or self._tokens[p] != tokens:
+            return None, k
+        return p, k
+
+    def share(self, page: int) -> None:
+        """One more holder of a registered page (taken off the free list if nobody held it)."""
+        if self._refs[page] == 0:
+            del self._free[page]
+        self._refs[page] += 1
+
+    def register(self, page: int, prefix_key: Optional[int], tokens: tuple) -> int:
+        """Record what a held page contains; returns its chain key.  The first page registered under a key keeps it."""
+        if self._key[page] is None:
+            k = self.chain_key(prefix_key, tokens)
+            self._key[page] = k
+            self._tokens[page] = tokens
+            self._by_key.setdefault(k, page)
+        return self._key[page]
+
+    def key_of(self, page: int) -> Optional[int]:
+        return self._key[page]
 
 
 class SlotPool:
@@ -103,27 +157,84 @@ class Lease:
     tables: List[List[int]]              # per group: logical page -> physical page or -1
     computed: int = 0                    # tokens whose keys are in the cache
     first_held: List[int] = field(default_factory=list)   # per group: first logical page still held
+    registered: int = 0                  # prefix cache: leading pages whose contents are registered
 
 
 class CacheManager:
-    def __init__(self, groups: Sequence[GroupConfig], page_size: int, num_state_slots: int):
+    def __init__(self, groups: Sequence[GroupConfig], page_size: int, num_state_slots: int, prefix_caching: bool = False):
         if page_size <= 0:
             raise ValueError("page_size must be positive")
         self.page_size = page_size
         self.groups = list(groups)
+        if prefix_caching and not (len(self.groups) == 1 and self.groups[0].window <= 0):
+            raise ValueError("the prefix cache needs exactly one group of cache units, and one that keeps all keys")
+        self.prefix_caching = bool(prefix_caching)
+        self.prefix_hits = 0                                      # pages taken from the prefix cache so far
         self.pools = [PagePool(g.num_pages) for g in self.groups]
         self.slots = SlotPool(num_state_slots)
         self.leases: Dict[object, Lease] = {}
         self._fresh_slots: List[int] = []
 
     # ---- requests ------------------------------------------------------------------------------------
-    def admit(self, request_id) -> Lease:
+    def _prefix_pages(self, tokens: Sequence[int]):
+        """[(page, key)] of the longest registered chain that matches the prefix of `tokens`."""
+        out = []
+        if not self.prefix_caching or tokens is None:
+            return out
+        ps, pool = self.page_size, self.pools[0]
+        key = None
+        for i in range((len(tokens) - 1) // ps):                  # at least one token is always computed
+            chunk = tuple(tokens[i * ps:(i + 1) * ps])
+            if min(chunk) < 0:
+                break
+            page, key = pool.find(key, chunk)
+            if page is None:
+                break
+            out.append((page, key))
+        return out
+
+    def can_admit(self, tokens: Sequence[int], upto_len: int) -> bool:
+        """Whether a request with these tokens could be admitted and covered up to `upto_len` now.  Registered pages
+        that somebody holds cost nothing; registered pages on the free list are counted as taken from it."""
+        if self.slots.num_free == 0:
+            return False
+        shared = sum(1 for page, _ in self._prefix_pages(tokens) if self.pools[0].refs(page) > 0)
+        need = self.num_pages_for(upto_len)
+        return all((need - shared if g == 0 else need) <= p.num_free for g, p in enumerate(self.pools))
+
+    def admit(self, request_id, tokens: Optional[Sequence[int]] = None) -> Lease:
+        """A new request.  With the prefix cache and the request's tokens, the pages of its longest registered prefix
+        are shared with it and count as computed (``lease.computed``)."""
         if request_id in self.leases:
             raise CacheError(f"request {request_id!r} is already admitted")
         lease = Lease(request_id, self.slots.take(), [[] for _ in self.groups], 0, [0] * len(self.groups))
+        for page, _ in self._prefix_pages(tokens):
+            self.pools[0].share(page)
+            lease.tables[0].append(page)
+        lease.registered = len(lease.tables[0]) if self.prefix_caching else 0
+        lease.computed = lease.registered * self.page_size
+        self.prefix_hits += lease.registered
         self.leases[request_id] = lease
         self._fresh_slots.append(lease.state_slot)
         return lease
+
+    def commit(self, request_id, tokens: Sequence[int]) -> None:
+        """Register the request's full pages whose keys are in the cache (and whose tokens are all known), so that
+        later requests with the same prefix can share them.  Does nothing without the prefix cache."""
+        if not self.prefix_caching:
+            return
+        lease = self.lease(request_id)
+        ps, pool, table = self.page_size, self.pools[0], lease.tables[0]
+        full = min(lease.computed, len(tokens)) // ps
+        i = lease.registered
+        while i < full:
+            chunk = tuple(tokens[i * ps:(i + 1) * ps])
+            if min(chunk) < 0:
+                break                                             # a token that is not known on the host yet
+            prefix = pool.key_of(table[i - 1]) if i > 0 else None
+            pool.register(table[i], prefix, chunk)
+            i += 1
+        lease.registered = i
 
     def lease(self, request_id) -> Lease:
         try:
@@ -226,23 +337,30 @@ class CacheManager:
 
     # ---- self-check (used by tests) -------------------------------------------------------------------------
     def check_invariants(self) -> None:
-        """Every page is either free exactly once or held by exactly one request exactly once."""
+        """Every page is either free exactly once, or held: by exactly one request, or (prefix cache) by as many
+        requests as its reference count says, each at most once."""
         for g, pool in enumerate(self.pools):
-            seen = {}
-            for p in pool._free:
-                if p in seen:
-                    raise AssertionError(f"group {g}: page {p} is in the free list twice")
-                seen[p] = "free"
+            free = list(pool._free)
+            if len(set(free)) != len(free):
+                raise AssertionError(f"group {g}: a page is in the free list twice")
+            holders: Dict[int, int] = {}
             for rid, lease in self.leases.items():
-                for p in lease.tables[g]:
-                    if p < 0:
-                        continue
-                    if p in seen:
-                        raise AssertionError(f"group {g}: page {p} held by {rid!r} is also {seen[p]}")
-                    seen[p] = f"held by {rid!r}"
-            if len(seen) != pool.num_pages:
-                lost = sorted(set(range(pool.num_pages)) - set(seen))
-                raise AssertionError(f"group {g}: pages {lost} are neither free nor held")
+                mine = [p for p in lease.tables[g] if p >= 0]
+                if len(set(mine)) != len(mine):
+                    raise AssertionError(f"group {g}: request {rid!r} holds a page twice")
+                for p in mine:
+                    holders[p] = holders.get(p, 0) + 1
+            for p in range(pool.num_pages):
+                n = holders.get(p, 0)
+                if n != pool.refs(p):
+                    raise AssertionError(f"group {g}: page {p} is held by {n} requests but counts {pool.refs(p)}")
+                if (n == 0) != (p in pool._free):
+                    raise AssertionError(f"group {g}: page {p} is {'neither' if n == 0 else 'both'} free {'nor' if n == 0 else 'and'} held")
+                if n > 1 and not self.prefix_caching:
+                    raise AssertionError(f"group {g}: page {p} is held by {n} requests")
+            for k, p in pool._by_key.items():
+                if pool.key_of(p) != k:
+                    raise AssertionError(f"group {g}: key of page {p} and the key table disagree")
         held_slots = [l.state_slot for l in self.leases.values()]
         if len(set(held_slots)) != len(held_slots):
             raise AssertionError("a state slot is held by two requests")

@@ -44,6 +44,7 @@ class EngineStats:
     tokens_processed: int = 0
     tokens_generated: int = 0
     preemptions: int = 0
+    prefix_hit_pages: int = 0            # cache pages that admissions took from the prefix cache
     seconds: float = 0.0
 
     def generated_per_second(self) -> float:
@@ -64,7 +65,7 @@ class LLMEngine:
             num_pages=config.num_kv_blocks if config.num_kv_blocks > 0 else None,
             max_step_tokens=config.max_num_batched_tokens, max_seqs=config.max_num_seqs,
             max_model_len=config.max_model_len, gpu_memory_utilization=config.gpu_memory_utilization,
-            enforce_eager=config.enforce_eager)
+            enforce_eager=config.enforce_eager, enable_prefix_caching=config.enable_prefix_caching)
         eos = tuple(getattr(self.runner.config, "eos_token_ids", ()) or ())
         self.scheduler = Scheduler(SchedulerConfig(
             max_num_batched_tokens=config.max_num_batched_tokens, max_num_seqs=config.max_num_seqs,
@@ -116,6 +117,7 @@ class LLMEngine:
             return info
         batch = self.scheduler.schedule(allow_preempt=not self._inflight)
         self._stats.preemptions = self.scheduler.num_preemptions
+        self._stats.prefix_hit_pages = self.runner.cache.prefix_hits
         if not batch.seqs:
             if self._inflight:                                 # everything runnable waits for tokens in flight
                 self.sync(info)

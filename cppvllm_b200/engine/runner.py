@@ -62,7 +62,7 @@ class ModelRunner:
     def __init__(self, model_dir: str, dtype=torch.bfloat16, device="cuda:0", page_size: int = 32,
                  num_pages: Optional[int] = None, max_step_tokens: int = 4096, max_seqs: int = 256,
                  max_model_len: int = 4096, gpu_memory_utilization: float = 0.90, enforce_eager: bool = False,
-                 num_state_slots: Optional[int] = None):
+                 num_state_slots: Optional[int] = None, enable_prefix_caching: bool = False):
         if not torch.cuda.is_available():
             raise RuntimeError("cppvllm_b200 runs on a CUDA device only; torch.cuda.is_available() is False")
         self.device = torch.device(device)
@@ -110,10 +110,15 @@ class ModelRunner:
                                     dtype=dtype, device=self.device) for cs, m in self.group_specs]
         self.scratch_page = self.num_pages                    # the extra page: padding rows of captured graphs
         n_slots = int(num_state_slots if num_state_slots is not None else max_seqs)
-        self.cache = CacheManager([GroupConfig(self.num_pages, cs.window, tuple(m)) for cs, m in self.group_specs],
-                                  page_size, n_slots)
-        self.scratch_slot = n_slots
         self.state_specs = self.model.state_specs()
+        if enable_prefix_caching and (len(self.group_specs) != 1 or self.group_specs[0][0].window > 0
+                                      or any(ss is not None for ss in self.state_specs)):
+            print("[cppvllm_b200] the prefix cache is off: it needs one group of cache units that keeps all keys and "
+                  "no per-request state", file=sys.stderr, flush=True)
+            enable_prefix_caching = False
+        self.cache = CacheManager([GroupConfig(self.num_pages, cs.window, tuple(m)) for cs, m in self.group_specs],
+                                  page_size, n_slots, prefix_caching=enable_prefix_caching)
+        self.scratch_slot = n_slots
         self.states = {i: torch.zeros((n_slots + 1,) + tuple(ss.shape), dtype=ss.dtype, device=self.device)
                        for i, ss in enumerate(self.state_specs) if ss is not None}
         self.cache_views: Dict[int, CacheUnitView] = {}

@@ -20,6 +20,9 @@ Policy after the reference's ``Scheduler`` (engine/scheduler.cpp):
   ``add_request`` (:18-26);
 * a request finishes on an end-of-sequence token (unless ``ignore_eos``) or at ``max_tokens`` new tokens, and
   its pages are freed at once (:123-155);
+* with the cache manager's prefix cache on, admission shares the pages of the longest registered prefix and the
+  request starts behind them; after every step the full pages of its requests are registered (:94-96,133-150;
+  engine/block_manager.cpp:71-143);
 * with a step still in flight (the engine overlaps the host's work on step n + 1 with the device's work on step n,
   engine/llm_engine.cpp:70-113) a request's newest token is a placeholder whose value is handed over on the device;
   nothing is preempted while a step is in flight: a request that cannot grow is left out, the batch is marked
@@ -185,10 +188,11 @@ class Scheduler:
         while (not preempted_now and not blocked and self.waiting and budget > 0 and len(self.running) < self.cfg.max_num_seqs
                and len(out.seqs) < self.cfg.max_num_seqs):
             seq = self.waiting[0]
-            if self.cache.slots.num_free == 0 or not self.cache.can_reserve(seq.seq_id, len(seq)):
+            if not self.cache.can_admit(seq.token_ids, len(seq)):
                 break
             self.waiting.popleft()
-            self.cache.admit(seq.seq_id)
+            lease = self.cache.admit(seq.seq_id, seq.token_ids)      # with the prefix cache: shared pages count as computed
+            seq.num_cached_tokens = lease.computed
             self.cache.reserve(seq.seq_id, len(seq))
             seq.status = RUNNING
             self.running.append(seq)
@@ -223,6 +227,8 @@ class Scheduler:
         for seq, did, pos in zip(batch.seqs, sampled_flags, batch.sample_pos):
             seq.num_inflight -= 1
             if not did:
+                if seq.status != FINISHED:
+                    self.cache.commit(seq.seq_id, seq.token_ids)  # full pages of a prompt portion become shareable
                 continue
             tok = int(next(it))
             if seq.status == FINISHED:
@@ -235,8 +241,11 @@ class Scheduler:
                 seq.num_cached_tokens = min(seq.num_cached_tokens, len(seq.token_ids))
                 seq.stopped_on_eos = hit_eos
                 seq.status = FINISHED
+                self.cache.commit(seq.seq_id, seq.token_ids)
                 self.cache.release(seq.seq_id)
                 finished.append(seq)
+            else:
+                self.cache.commit(seq.seq_id, seq.token_ids)
         if finished:
             self.running = [s for s in self.running if s.status != FINISHED]
         return finished

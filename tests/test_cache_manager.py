@@ -124,3 +124,77 @@ def test_random_orders_keep_every_page_accounted_for(seed):
         m.release(rid)
     m.check_invariants()
     assert all(p.num_free == p.num_pages for p in m.pools) and m.slots.num_free == 5
+
+
+def test_prefix_cache_shares_registered_pages_and_forgets_reused_ones():
+    m = CacheManager([GroupConfig(6)], 4, 4, prefix_caching=True)
+    toks = list(range(100, 111))                               # 11 tokens: two full pages and a partial one
+    a = m.admit("a", toks)
+    assert a.computed == 0
+    m.reserve("a", len(toks))
+    m.advance("a", 11)
+    m.commit("a", toks)
+    assert a.registered == 2
+    b = m.admit("b", toks[:8] + [1, 2])                         # same first two pages
+    assert b.computed == 8 and b.tables[0] == a.tables[0][:2]
+    assert [m.pools[0].refs(p) for p in a.tables[0]] == [2, 2, 1]
+    m.reserve("b", 10)
+    m.check_invariants()
+    m.release("a")
+    assert [m.pools[0].refs(p) for p in b.tables[0]] == [1, 1, 1]
+    m.check_invariants()
+    m.release("b")
+    assert m.num_free_pages() == 6
+    # the pages keep their keys while they are free: a third request finds them again, taking them off the free list
+    assert m.can_admit(toks, 11)
+    c = m.admit("c", toks)
+    assert c.computed == 8 and m.num_free_pages() == 4
+    m.release("c")
+    # fresh contents for all six pages: the keys are forgotten
+    m.admit("d")
+    m.reserve("d", 24)
+    assert m.admit("e", toks).computed == 0
+    m.release("d")
+    m.release("e")
+    m.check_invariants()
+    # tokens that are not known yet (negative placeholders) are never registered or looked up
+    f = m.admit("f", [5, 6, 7, 8, -1])
+    m.reserve("f", 5)
+    m.advance("f", 5)
+    m.commit("f", [5, 6, 7, 8, -1])
+    assert f.registered == 1
+    g = m.admit("g", [5, 6, 7, -1, 9])
+    assert g.computed == 0
+    with pytest.raises(ValueError):
+        CacheManager([GroupConfig(4), GroupConfig(4, window=8)], 4, 2, prefix_caching=True)
+
+
+def test_prefix_cache_under_random_orders():
+    """Random admissions with shared prefixes, growth, commits and releases: reference counts and the free list stay
+    consistent, and a request never gets a page whose registered tokens differ from its own."""
+    rng = random.Random(7)
+    m = CacheManager([GroupConfig(40)], 4, 16, prefix_caching=True)
+    stems = [[rng.randrange(50) for _ in range(24)] for _ in range(3)]
+    live = {}
+    for step in range(600):
+        if live and rng.random() < 0.35:
+            rid = rng.choice(list(live))
+            m.release(rid)
+            del live[rid]
+        elif len(live) < 10:
+            stem = rng.choice(stems)
+            toks = stem[:rng.randrange(1, 25)] + [rng.randrange(50, 60) for _ in range(rng.randrange(0, 6))]
+            if m.can_admit(toks, len(toks)):
+                lease = m.admit(step, toks)
+                assert lease.computed % 4 == 0 and lease.computed < len(toks)
+                for i, p in enumerate(lease.tables[0]):
+                    assert m.pools[0]._tokens[p] == tuple(toks[4 * i:4 * i + 4])
+                m.reserve(step, len(toks))
+                m.advance(step, len(toks))
+                m.commit(step, toks)
+                live[step] = toks
+        m.check_invariants()
+    for rid in list(live):
+        m.release(rid)
+    m.check_invariants()
+    assert m.num_free_pages() == 40 and m.prefix_hits > 0

@@ -89,6 +89,39 @@ def test_pages_run_out_requests_are_preempted_recomputed_and_still_right(model_d
         llm.add_request([1, 2, 999], sp)
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_requests_that_share_a_prefix_read_the_same_pages_and_generate_the_same_tokens(model_dirs, dtype):
+    """With the prefix cache, later requests start behind the registered pages of a common prefix (here also behind
+    their own pages after a preemption).  Tokens are those of an engine without it, and in float32 those of the plain
+    implementation."""
+    from cppvllm_b200 import SamplingParams
+    name = "tiny_c"
+    d = model_dirs[name]
+    vocab = tiny_models.config(name)["vocab_size"]
+    stem = tiny_models.random_tokens(vocab, 70, 5)
+    prompts = [stem + tiny_models.random_tokens(vocab, n, 60 + n) for n in (3, 9, 1)] + [stem[:49], stem[:48]]
+    sp = SamplingParams(temperature=0.0, max_tokens=10, ignore_eos=True)
+    outs = {}
+    for on in (False, True):
+        llm = engine(d, name, dtype, enable_prefix_caching=on, max_num_seqs=2)      # two at a time: later ones find pages
+        outs[on] = [o.token_ids for o in llm.generate(prompts, sp)]
+        llm.runner.check_errors()
+        llm.runner.cache.check_invariants()
+        assert llm.runner.cache.num_free_pages() == 64
+        # pages of 16: the third request finds the stem's four full pages, the 49-token one three, the 48-token one two
+        assert llm.stats().prefix_hit_pages == (9 if on else 0)
+    if dtype == "float32":
+        assert outs[True] == outs[False]
+        for p, o in zip(prompts, outs[True]):
+            assert o == plain.greedy_generate(d, p, 10)
+    else:
+        for p, o in zip(prompts, outs[True]):
+            ref = plain.forward(d, (p + o)[:-1], "bfloat16")
+            for i, tok in enumerate(o):
+                row = ref[len(p) - 1 + i]
+                assert row[tok] >= row.max() - 0.02 * max(1.0, float(row.abs().max()))
+
+
 def test_overlapped_and_step_by_step_engines_generate_the_same_tokens(model_dirs):
     """pipeline_depth 2 schedules step n + 1 before the samples of step n are read back (the tokens travel on the
     device); depth 1 waits for every step.  Same tokens, greedy and sampled, also when pages run out."""

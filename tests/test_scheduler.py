@@ -14,8 +14,8 @@ from cppvllm_b200.sampling.params import SamplingParams
 GOLDEN = os.path.join(os.path.dirname(__file__), "golden", "scheduler_golden.json")
 
 
-def make(blocks, budget, chunk, max_seqs, page=16, max_model_len=4096, eos=()):
-    cache = CacheManager([GroupConfig(blocks)], page, max(8, max_seqs))
+def make(blocks, budget, chunk, max_seqs, page=16, max_model_len=4096, eos=(), prefix_caching=False):
+    cache = CacheManager([GroupConfig(blocks)], page, max(8, max_seqs), prefix_caching=prefix_caching)
     return Scheduler(SchedulerConfig(budget, max_seqs, chunk, max_model_len, tuple(eos)), cache), cache
 
 
@@ -40,6 +40,46 @@ def run(sched, cache, seqs, token=lambda step, seq: 7, max_steps=2000):
 
 
 @pytest.mark.parametrize("case", json.load(open(GOLDEN)), ids=lambda c: f"blocks{c['blocks']}")
+def test_same_batches_as_the_reference_scheduler_with_the_prefix_cache(case):
+    """With the prefix cache on (as in the reference, where it cannot be switched off) and the driver's tokens (every
+    prompt token and every sampled token distinct, counted up from 1000 in the driver's order), every step of every
+    case is the reference's, the re-admission of preempted requests behind their own surviving pages included."""
+    sched, cache = make(case["blocks"], case["budget"], case["chunk"], case["max_seqs"], prefix_caching=True)
+    nxt = [1000]
+
+    def fresh(n):
+        out = list(range(nxt[0], nxt[0] + n))
+        nxt[0] += n
+        return out
+
+    seqs = [Sequence(i, fresh(n), SamplingParams(max_tokens=case["max_tokens"], ignore_eos=True))
+            for i, n in enumerate(case["prompts"])]
+    for s in seqs:
+        sched.add_request(s)
+    steps = []
+    while not sched.is_finished():
+        assert len(steps) < 2000
+        b = sched.schedule()
+        cache.check_invariants()
+        steps.append([[s.seq_id, s.num_scheduled_tokens, int(s.samples_this_step())] for s in b.seqs])
+        for s in b.seqs:
+            cache.slots_for(s.seq_id, 0, s.num_cached_tokens, s.num_scheduled_tokens)
+            cache.advance(s.seq_id, s.num_cached_tokens + s.num_scheduled_tokens)
+        flags = sched.on_launched(b)
+        toks = []
+        for f in flags:                                   # the driver draws a token for every scheduled request
+            if f:
+                toks.append(nxt[0])
+            nxt[0] += 1
+        sched.postprocess(b, flags, toks)
+    cache.check_invariants()
+    assert steps == case["steps"]
+    assert sched.num_preemptions == case["preemptions"]
+    assert (cache.prefix_hits > 0) == (case["preemptions"] > 0)
+    assert cache.num_free_pages() == case["blocks"]
+
+
+@pytest.mark.parametrize("case", json.load(open(GOLDEN)), ids=lambda c: f"blocks{c['blocks']}")
 def test_same_batches_as_the_reference_scheduler(case):
     sched, cache = make(case["blocks"], case["budget"], case["chunk"], case["max_seqs"])
     seqs = [Sequence(i, list(range(n)), SamplingParams(max_tokens=case["max_tokens"], ignore_eos=True))
@@ -48,9 +88,9 @@ def test_same_batches_as_the_reference_scheduler(case):
     if case["preemptions"] == 0:
         assert steps == case["steps"]
     else:
-        # The reference re-admits a preempted request with its first full blocks still found by its prefix cache
-        # (engine/block_manager.cpp:80-116), so it recomputes fewer tokens; this engine recomputes all of them.
-        # Up to the first re-admission, victims included, the decisions are the same.
+        # Without the prefix cache a preempted request recomputes all of its tokens, where the reference finds its
+        # first full blocks again (engine/block_manager.cpp:80-116) and recomputes fewer.  Up to the first
+        # re-admission, victims included, the decisions are the same.
         gone = set()
         for n, (mine, ref) in enumerate(zip(steps, case["steps"])):
             back = [x[0] for x in ref if x[0] in gone]
@@ -65,6 +105,27 @@ def test_same_batches_as_the_reference_scheduler(case):
     assert sched.num_preemptions == case["preemptions"]
     assert all(s.status == FINISHED and s.num_completion_tokens == case["max_tokens"] for s in seqs)
     assert cache.num_free_pages() == case["blocks"]
+
+
+def test_requests_with_a_common_prefix_share_pages():
+    """Three requests whose prompts begin with the same 40 tokens: the first computes everything; the later ones,
+    admitted after the first one's pages were registered, start behind two shared pages of 16."""
+    sched, cache = make(32, budget=64, chunk=0, max_seqs=4, prefix_caching=True)
+    common = list(range(500, 540))
+    a = Sequence(0, common + [1, 2, 3], SamplingParams(max_tokens=3, ignore_eos=True))
+    steps = run(sched, cache, [a], token=lambda step, seq: 900 + step)
+    assert steps[0] == [(0, 43, 1)]
+    b = Sequence(1, common + [7, 8], SamplingParams(max_tokens=2, ignore_eos=True))
+    c = Sequence(2, common[:33], SamplingParams(max_tokens=2, ignore_eos=True))
+    steps = run(sched, cache, [b, c], token=lambda step, seq: 800 + step)
+    assert steps[0] == [(1, 42 - 32, 1), (2, 33 - 32, 1)]   # both start at token 32: two full pages are shared
+    assert cache.prefix_hits == 4
+    cache.check_invariants()
+    assert cache.num_free_pages() == 32
+    # a prompt that IS two full pages still computes its last token (at least one token always runs)
+    d = Sequence(3, common[:32], SamplingParams(max_tokens=1, ignore_eos=True))
+    steps = run(sched, cache, [d], token=lambda step, seq: 700)
+    assert steps[0] == [(3, 16, 1)]
 
 
 def test_budget_and_chunk_cap_cut_prompts_into_portions():
