@@ -115,6 +115,7 @@ struct AttnParams {
     float* part_o;                      // [S, KV, splits, 16, HD]
     float* part_ml;                     // [S, KV, splits, 16, 2]
     int splits;
+    int cluster;                        // 1: the splits of a (request, kv head) are one thread-block cluster
 };
 
 // Issued by ONE thread: fetch keys [key0, key0 + 64) of one kv head, K then V, into a stage.  `stage` points at
@@ -397,6 +398,19 @@ attn_prefill_bf16_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnP
 
 constexpr int kDecStages = 3;
 
+// barrier over all threads of the cluster; what they wrote to shared memory before it is visible after it
+__device__ __forceinline__ void cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;\n" ::: "memory");
+}
+// the float at the same shared-memory address in block `rank` of the cluster
+__device__ __forceinline__ float ld_cluster(const float* local, int rank) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(remote) : "r"(smem_u32(local)), "r"(rank));
+    float v;
+    asm volatile("ld.shared::cluster.f32 %0, [%1];\n" : "=f"(v) : "r"(remote) : "memory");
+    return v;
+}
+
 template <int HD>
 __global__ void __launch_bounds__(kThreads)
 attn_decode_bf16_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnParams p) {
@@ -486,6 +500,8 @@ attn_decode_bf16_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnPa
     __syncthreads();
     float* red_o = reinterpret_cast<float*>(sm.stages);                    // [4][16][HD]
     float* red_ml = red_o + 4 * 16 * HD;                                   // [4][16][2]
+    float* comb_o = red_ml + 4 * 16 * 2;                                   // [16][HD]  this block's part, for its cluster
+    float* comb_ml = comb_o + 16 * HD;                                     // [16][2]
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
         if (warp >= kConsumers / 32) break;                                // the producer warp holds no results
@@ -517,12 +533,35 @@ attn_decode_bf16_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnPa
         }
         if (p.splits == 1) {
             p.out[(static_cast<int64_t>(cu0) * p.H + kvh * g + r) * HD + d] = __float2bfloat16_rn(ll > 0.f ? acc / ll : 0.f);
+        } else if (p.cluster) {
+            comb_o[r * HD + d] = acc;
+            if (d == 0) { comb_ml[r * 2] = mm; comb_ml[r * 2 + 1] = ll; }
         } else {
             const int64_t base = ((static_cast<int64_t>(seq) * p.KV + kvh) * p.splits + split) * 16 + r;
             p.part_o[base * HD + d] = acc;
             if (d == 0) { p.part_ml[base * 2] = mm; p.part_ml[base * 2 + 1] = ll; }
         }
     }
+    if (p.splits == 1 || !p.cluster) return;
+    // The splits of this (request, kv head) are the blocks of one cluster: each has left its part in its own shared
+    // memory, and after the cluster's barrier each merges a share of the output elements, reading the others' parts
+    // through distributed shared memory.  The second barrier keeps every block's shared memory alive until all have read.
+    cluster_sync();
+    const int items = g * HD, share = (items + p.splits - 1) / p.splits;
+    for (int i = split * share + threadIdx.x; i < min(items, (split + 1) * share); i += kThreads) {
+        const int r = i / HD, d = i % HD;
+        float mm = -INFINITY;
+        for (int c = 0; c < p.splits; ++c) mm = fmaxf(mm, ld_cluster(comb_ml + r * 2, c));
+        float acc = 0.f, ll = 0.f;
+        for (int c = 0; c < p.splits; ++c) {
+            const float mc = ld_cluster(comb_ml + r * 2, c);
+            const float f = mc == -INFINITY ? 0.f : exp2f(mc - mm);
+            acc += ld_cluster(comb_o + r * HD + d, c) * f;
+            ll += ld_cluster(comb_ml + r * 2 + 1, c) * f;
+        }
+        p.out[(static_cast<int64_t>(cu0) * p.H + kvh * g + r) * HD + d] = __float2bfloat16_rn(ll > 0.f ? acc / ll : 0.f);
+    }
+    cluster_sync();
 }
 
 template <int HD>
@@ -598,8 +637,61 @@ static int kv_tensor_map(CUtensorMap* out, const void* cache, int64_t rows, int 
 
 template <int HD> constexpr size_t prefill_smem() { return SmemPlan<HD, kPreStages, 64>::kBytes; }
 template <int HD> constexpr size_t decode_smem() {
-    const size_t red = 1024 + static_cast<size_t>(4 * 16) * (HD + 2) * sizeof(float);
+    const size_t red = 1024 + static_cast<size_t>(5 * 16) * (HD + 2) * sizeof(float);
     return SmemPlan<HD, kDecStages, 16>::kBytes > red ? SmemPlan<HD, kDecStages, 16>::kBytes : red;
+}
+
+constexpr int kMaxClusterSplits = 16;       // 8 is the portable cluster size; up to 16 blocks with the opt-in attribute
+
+// The decode kernel, then the merge kernel; or, with `cluster_merge` and 2 to 16 splits, the decode kernel alone with
+// the splits of each (request, kv head) launched as one thread-block cluster that merges in shared memory.
+template <int HD>
+static int launch_decode(const CUtensorMap& map, AttnParams p, dim3 grid, dim3 mgrid, bool cluster_merge, cudaStream_t stream) {
+    static bool set = false, wide_ok = false;
+    if (!set) {
+        cudaFuncSetAttribute(attn_decode_bf16_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem<HD>());
+        wide_ok = cudaFuncSetAttribute(attn_decode_bf16_kernel<HD>, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess;
+        cudaGetLastError();
+        set = true;
+    }
+    if (cluster_merge && p.splits > 1 && p.splits <= kMaxClusterSplits && (p.splits <= 8 || wide_ok)) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = grid;
+        cfg.blockDim = dim3(kThreads);
+        cfg.dynamicSmemBytes = decode_smem<HD>();
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[2];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 1;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = static_cast<unsigned>(p.splits);
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        // can the device hold a cluster of this size at all?  Asked once per size.
+        static int fits[kMaxClusterSplits + 1] = {};              // 0: not asked yet, 1: yes, -1: no
+        if (fits[p.splits] == 0) {
+            int n = 0;
+            const cudaError_t e = cudaOccupancyMaxActiveClusters(&n, attn_decode_bf16_kernel<HD>, &cfg);
+            cudaGetLastError();
+            fits[p.splits] = (e == cudaSuccess && n > 0) ? 1 : -1;
+        }
+        if (fits[p.splits] < 0) goto apart;
+        p.cluster = 1;
+        cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+        if (pdl_enabled() && cudaStreamIsCapturing(stream, &cap) == cudaSuccess && cap == cudaStreamCaptureStatusNone) {
+            attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+            attr[1].val.programmaticStreamSerializationAllowed = 1;
+            cfg.numAttrs = 2;
+        }
+        cudaLaunchKernelEx(&cfg, attn_decode_bf16_kernel<HD>, map, p);
+        return launch_status();
+    }
+apart:
+    p.cluster = 0;
+    if (p.splits > 1 && p.part_o == nullptr) return CVB_E_SCRATCH;
+    launch_kernel(attn_decode_bf16_kernel<HD>, dim3(grid), dim3(kThreads), decode_smem<HD>(), stream, map, p);
+    if (p.splits > 1) launch_kernel(attn_decode_merge_kernel<HD>, dim3(mgrid), dim3(HD), 0, stream, p);
+    return launch_status();
 }
 
 static int check_common(int S, int H, int KV, int hd, int page_size, int table_width, int num_pages) {
@@ -664,7 +756,7 @@ extern "C" int cvb_attn_prefill_bf16(void* out, const void* q, const void* cache
 extern "C" int cvb_attn_decode_bf16(void* out, const void* q, const void* cache, const int* block_tables,
                                     int table_width, const int* cu_seqlens, const int* positions, int S, int H,
                                     int KV, int hd, int page_size, int window, float scale, int num_pages,
-                                    int splits, float* scratch, int64_t scratch_floats, int* err_flag,
+                                    int splits, float* scratch, int64_t scratch_floats, int cluster_merge, int* err_flag,
                                     cudaStream_t stream) {
     if (splits < 1 || splits > 65535) return CVB_E_SIZE;
     AttnParams p{};
@@ -672,25 +764,16 @@ extern "C" int cvb_attn_decode_bf16(void* out, const void* q, const void* cache,
     const int rc = fill_params(p, map, out, q, cache, block_tables, table_width, cu_seqlens, positions, S, H, KV, hd,
                                page_size, window, scale, num_pages, err_flag);
     if (rc != CVB_OK) return rc;
-    if (splits > 1 && (scratch == nullptr || scratch_floats < cvb_attn_decode_scratch_floats(S, KV, hd, splits)))
+    if (cluster_merge && splits > kMaxClusterSplits) cluster_merge = 0;
+    if (splits > 1 && !cluster_merge && (scratch == nullptr || scratch_floats < cvb_attn_decode_scratch_floats(S, KV, hd, splits)))
         return CVB_E_SCRATCH;
     p.splits = splits;
     p.part_o = scratch;
     p.part_ml = scratch ? scratch + static_cast<int64_t>(S) * KV * splits * 16 * hd : nullptr;
     dim3 grid(static_cast<unsigned>(S), static_cast<unsigned>(KV), static_cast<unsigned>(splits));
     dim3 mgrid(static_cast<unsigned>(S), static_cast<unsigned>(H));
-    if (hd == 128) {
-        static bool set = false;
-        if (!set) { cudaFuncSetAttribute(attn_decode_bf16_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem<128>()); set = true; }
-        launch_kernel(attn_decode_bf16_kernel<128>, dim3(grid), dim3(kThreads), decode_smem<128>(), stream, map, p);
-        if (splits > 1) launch_kernel(attn_decode_merge_kernel<128>, dim3(mgrid), dim3(128), 0, stream, p);
-    } else {
-        static bool set = false;
-        if (!set) { cudaFuncSetAttribute(attn_decode_bf16_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem<64>()); set = true; }
-        launch_kernel(attn_decode_bf16_kernel<64>, dim3(grid), dim3(kThreads), decode_smem<64>(), stream, map, p);
-        if (splits > 1) launch_kernel(attn_decode_merge_kernel<64>, dim3(mgrid), dim3(64), 0, stream, p);
-    }
-    return launch_status();
+    if (hd == 128) return launch_decode<128>(map, p, grid, mgrid, cluster_merge != 0, stream);
+    return launch_decode<64>(map, p, grid, mgrid, cluster_merge != 0, stream);
 }
 
 // ---- split-KV decode attention without any allocation ---------------------------------------------------------------

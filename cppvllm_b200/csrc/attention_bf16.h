@@ -17,11 +17,13 @@ int cvb_attn_prefill_bf16(void* out, const void* q, const void* cache, const int
 // Floats of scratch that cvb_attn_decode_bf16 needs for S requests, KV heads and `splits` chunks (0 for one chunk).
 int64_t cvb_attn_decode_scratch_floats(int S, int KV, int hd, int splits);
 
-// Split-KV attention for requests that bring one token; `scratch` holds the partial results of the chunks.
+// Split-KV attention for requests that bring one token.  With `cluster_merge` and 2 to 16 chunks, the chunks of a request
+// and kv head run as one thread-block cluster and are merged through distributed shared memory (`scratch` is not used);
+// otherwise `scratch` holds the partial results of the chunks and a second kernel merges them.
 int cvb_attn_decode_bf16(void* out, const void* q, const void* cache, const int* block_tables, int table_width,
                          const int* cu_seqlens, const int* positions, int S, int H, int KV, int hd, int page_size,
                          int window, float scale, int num_pages, int splits, float* scratch, int64_t scratch_floats,
-                         int* err_flag, cudaStream_t stream);
+                         int cluster_merge, int* err_flag, cudaStream_t stream);
 
 // The same attention for callers that cannot allocate device memory (no cudaMalloc in their loop, a fixed memory
 // budget owned by someone else): its scratch is a static device array inside the library, at most

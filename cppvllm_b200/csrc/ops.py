@@ -334,7 +334,10 @@ def attn_decode_scratch_floats(num_seqs: int, num_kv_heads: int, head_dim: int, 
 
 def attn_decode_bf16(out, q, cache, block_tables, cu_seqlens, positions, num_seqs: int, num_heads: int,
                      num_kv_heads: int, head_dim: int, page_size: int, scale: float, splits: int,
-                     scratch: Optional[torch.Tensor], window: int = 0):
+                     scratch: Optional[torch.Tensor], window: int = 0, cluster_merge: bool = True):
+    """Split-KV attention of single decoded tokens.  With `cluster_merge` (and up to 16 splits) the splits of a request
+    and kv head run as one thread-block cluster and merge their parts through distributed shared memory; otherwise the
+    parts go through `scratch` and a second kernel merges them."""
     _attn_common_checks(out, q, cache, block_tables, cu_seqlens, positions)
     if scratch is not None and (scratch.dtype != torch.float32 or not scratch.is_cuda or not scratch.is_contiguous()):
         raise KernelError("attn_decode_bf16: scratch must be a contiguous float32 CUDA tensor")
@@ -343,8 +346,9 @@ def attn_decode_bf16(out, q, cache, block_tables, cu_seqlens, positions, num_seq
         _ptr(out), _ptr(q), _ptr(cache), _ptr(block_tables), c_int(block_tables.shape[1]), _ptr(cu_seqlens),
         _ptr(positions), c_int(num_seqs), c_int(num_heads), c_int(num_kv_heads), c_int(head_dim), c_int(page_size),
         c_int(window), c_float(scale), c_int(num_pages), c_int(splits), _ptr(scratch),
-        c_int64(scratch.numel() if scratch is not None else 0), _ptr(error_flag(q.device)), _stream()), "attn_decode_bf16",
-        kernels=2 if splits > 1 else 1)
+        c_int64(scratch.numel() if scratch is not None else 0), c_int(1 if cluster_merge else 0),
+        _ptr(error_flag(q.device)), _stream()), "attn_decode_bf16",
+        kernels=2 if splits > 1 and not (cluster_merge and splits <= 16) else 1)
     return out
 
 

@@ -381,22 +381,24 @@ def test_tensor_core_attention_mixed_portions_and_single_tokens(ops, H, KV, hd, 
         ops.attn_prefill_bf16(out, q.view(T, -1).to(d), cache.to(d), tables.to(d), cu_t, pos_t, len(reqs),
                               ops.prefill_tiles(q_lens, H, KV), H, KV, hd, page, scale, window=window)
     results = {}
-    for splits in (1, 3, 7):
+    for splits, cluster in ((1, True), (3, True), (7, True), (7, False), (12, True), (20, True)):
         o2 = out.clone()
         n = ops.attn_decode_scratch_floats(len(reqs), KV, hd, splits)
         scratch = torch.full((max(n, 1),), float("nan"), device=d) if splits > 1 else None
         ops.attn_decode_bf16(o2, q.view(T, -1).to(d), cache.to(d), tables.to(d), cu_t, pos_t, len(reqs), H, KV, hd, page,
-                             scale, splits, scratch, window=window)
-        results[splits] = o2.float().cpu().view(T, H, hd)
+                             scale, splits, scratch, window=window, cluster_merge=cluster)
+        results[(splits, cluster)] = o2.float().cpu().view(T, H, hd)
     ops.check_device_errors(d)
     ref = attention_ref(q, [seqs_k[s] for s in seq_of], [seqs_v[s] for s in seq_of], None, positions, H, KV, hd, scale, window)
-    for splits, got in results.items():
+    for _, got in results.items():
         torch.testing.assert_close(got, rnd(ref, dt), atol=2e-2, rtol=2e-2)
+    # merged in the cluster's shared memory or by the second kernel: the same sums in the same order
+    assert torch.equal(results[(7, True)], results[(7, False)])
     # and against the general kernel of the package
     gen = torch.empty_like(out)
     ops.paged_attention_general(gen, q.view(T, -1).to(d), cache.to(d), tables.to(d), torch.tensor(seq_of, dtype=torch.int32, device=d),
                                 pos_t, H, KV, hd, page, scale, window=window)
-    torch.testing.assert_close(results[3], gen.float().cpu().view(T, H, hd), atol=2e-2, rtol=2e-2)
+    torch.testing.assert_close(results[(3, True)], gen.float().cpu().view(T, H, hd), atol=2e-2, rtol=2e-2)
 
 
 def test_tensor_core_attention_finds_one_far_key(ops):
@@ -435,7 +437,8 @@ def test_tensor_core_attention_refuses_what_it_does_not_cover(ops):
     assert not ops.fast_attention_supported(torch.float32, 4, 2, 128) and not ops.fast_attention_supported(torch.bfloat16, 4, 2, 96)
     z = torch.zeros(1, 2 * 64, dtype=torch.bfloat16, device=d)
     with pytest.raises(ops.KernelError, match="scratch"):
-        ops.attn_decode_bf16(z, z, torch.zeros(2, 2, 1, 16, 64, dtype=torch.bfloat16, device=d), i.view(1, 2), i, i, 1, 2, 1, 64, 16, 0.1, 4, None)
+        ops.attn_decode_bf16(z, z, torch.zeros(2, 2, 1, 16, 64, dtype=torch.bfloat16, device=d), i.view(1, 2), i, i, 1, 2, 1, 64, 16, 0.1, 4, None,
+                             cluster_merge=False)
 
 
 # ---- weight-streaming products for a few rows -----------------------------------------------------------------
