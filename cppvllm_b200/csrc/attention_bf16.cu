@@ -116,6 +116,18 @@ struct AttnParams {
     float* part_ml;                     // [S, KV, splits, 16, 2]
     int splits;
     int cluster;                        // 1: the splits of a (request, kv head) are one thread-block cluster
+    // decode with the projection's raw output (qkv != nullptr): queries are normed and rotated in the kernel, the new
+    // key and value are written to the cache by the block whose keys include the token's own position
+    const __nv_bfloat16* qkv;           // [T, H + 2 KV, HD]
+    const float* q_w;                   // [HD] per-head norm weights, or nullptr for no norm
+    const float* k_w;
+    const float* cos_t;                 // [max_pos, HD / 2], or nullptr for no rotation
+    const float* sin_t;
+    const int* slots;                   // [T] cache slot (page * page_size + offset) of each token
+    __nv_bfloat16* cache;               // the pages the tensor map describes
+    int64_t cache_elems;
+    int max_pos;
+    float qk_eps;
 };
 
 // Issued by ONE thread: fetch keys [key0, key0 + 64) of one kv head, K then V, into a stage.  `stage` points at
@@ -446,14 +458,108 @@ attn_decode_bf16_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnPa
             for (int i = 0; i < kDecStages; ++i) { mbar_init(full + i, 1); mbar_init(empty + i, kConsumers / 32); }
             mbar_fence_init();
         }
-        for (int i = threadIdx.x; i < 16 * CPR; i += kThreads) {
-            const int r = i / CPR, c = i % CPR;
-            const bool valid = r < g;
-            const __nv_bfloat16* src = valid ? p.q + ((static_cast<int64_t>(cu0) * p.H + kvh * g + r) * HD + c * 8) : p.q;
-            cp_async16(sm.q + swz<HD>(r, c), src, valid);
+        __nv_bfloat16* newkv = reinterpret_cast<__nv_bfloat16*>(reinterpret_cast<unsigned char*>(sm.bars) + 64);   // [2][HD]
+        const int tile_of_pos = pos / kBN;
+        const bool owns_pos = p.qkv != nullptr && tile_of_pos >= tile_begin && tile_of_pos < tile_begin + n_tiles;
+        if (p.qkv == nullptr) {
+            for (int i = threadIdx.x; i < 16 * CPR; i += kThreads) {
+                const int r = i / CPR, c = i % CPR;
+                const bool valid = r < g;
+                const __nv_bfloat16* src = valid ? p.q + ((static_cast<int64_t>(cu0) * p.H + kvh * g + r) * HD + c * 8) : p.q;
+                cp_async16(sm.q + swz<HD>(r, c), src, valid);
+            }
+            cp_async_commit();
+            cp_async_wait<0>();
+        } else if (threadIdx.x < kConsumers) {
+            // Per-head norm and rotation of this kv head's queries, straight from the projection; CPR neighbouring lanes
+            // own one head vector (16-byte chunks).  The block that owns the token's own position does the same for the
+            // new key, copies the new value, and writes both to the cache and to shared memory.
+            const int c = threadIdx.x % CPR, sub = threadIdx.x / CPR;
+            constexpr int kPerPass = kConsumers / CPR;
+            const bool first = c < CPR / 2;
+            float cs[8], sn[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) { cs[i] = 1.f; sn[i] = 0.f; }
+            if (p.cos_t != nullptr) {
+                int rp = pos;
+                if (rp < 0 || rp >= p.max_pos) {
+                    if (threadIdx.x == 0) atomicExch(p.err, 3);
+                    rp = rp < 0 ? 0 : p.max_pos - 1;
+                }
+                const int e0 = (first ? c : c - CPR / 2) * 8;
+                const float4* cr = reinterpret_cast<const float4*>(p.cos_t + static_cast<int64_t>(rp) * (HD / 2) + e0);
+                const float4* sr = reinterpret_cast<const float4*>(p.sin_t + static_cast<int64_t>(rp) * (HD / 2) + e0);
+                const float4 a0 = cr[0], a1 = cr[1], b0 = sr[0], b1 = sr[1];
+                cs[0] = a0.x; cs[1] = a0.y; cs[2] = a0.z; cs[3] = a0.w; cs[4] = a1.x; cs[5] = a1.y; cs[6] = a1.z; cs[7] = a1.w;
+                sn[0] = b0.x; sn[1] = b0.y; sn[2] = b0.z; sn[3] = b0.w; sn[4] = b1.x; sn[5] = b1.y; sn[6] = b1.z; sn[7] = b1.w;
+                if (first) {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) sn[i] = -sn[i];
+                }
+            }
+            int64_t k_elem = -1;                                           // where the new key goes in the cache
+            if (owns_pos) {
+                const int slot = p.slots[cu0];
+                if (slot >= 0) {
+                    const int64_t page = slot / p.page_size, off = slot % p.page_size;
+                    k_elem = (((page * 2) * p.KV + kvh) * p.page_size + off) * HD;
+                    if (k_elem + static_cast<int64_t>(p.KV) * p.page_size * HD + HD > p.cache_elems) {
+                        if (threadIdx.x == 0) atomicExch(p.err, 2);
+                        k_elem = -1;
+                    }
+                }
+            }
+            const int n_tasks = g + (owns_pos ? 2 : 0);                    // g query heads, then the new key, then the value
+            const int n_heads = p.H + 2 * p.KV;
+            for (int t0 = 0; t0 < n_tasks; t0 += kPerPass) {
+                const int task = t0 + sub;
+                const bool active = task < n_tasks;
+                const bool is_k = task == g, is_v = task == g + 1;
+                const int head = task < g ? kvh * g + task : (is_k ? p.H + kvh : p.H + p.KV + kvh);
+                float x[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) x[i] = 0.f;
+                uint4 raw = make_uint4(0, 0, 0, 0);
+                if (active) {
+                    raw = *reinterpret_cast<const uint4*>(p.qkv + (static_cast<int64_t>(cu0) * n_heads + head) * HD + c * 8);
+                    const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) { const float2 f = __bfloat1622float2(h2[i]); x[2 * i] = f.x; x[2 * i + 1] = f.y; }
+                }
+                if (active && is_v) {
+                    *reinterpret_cast<uint4*>(newkv + HD + c * 8) = raw;
+                    if (k_elem >= 0) *reinterpret_cast<uint4*>(p.cache + k_elem + static_cast<int64_t>(p.KV) * p.page_size * HD + c * 8) = raw;
+                }
+                float ss = 0.f;
+#pragma unroll
+                for (int i = 0; i < 8; ++i) ss += x[i] * x[i];
+#pragma unroll
+                for (int o = CPR / 2; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+                if (p.q_w != nullptr) {
+                    const float inv = rsqrtf(ss / static_cast<float>(HD) + p.qk_eps);
+                    const float* w = is_k ? p.k_w : p.q_w;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) x[i] = rnd<__nv_bfloat16>(rnd<__nv_bfloat16>(x[i] * inv) * w[c * 8 + i]);
+                }
+                float other[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) other[i] = __shfl_xor_sync(0xffffffffu, x[i], CPR / 2);
+                if (!active || is_v) continue;
+                uint4 packed;
+                uint32_t* pw = reinterpret_cast<uint32_t*>(&packed);
+#pragma unroll
+                for (int i = 0; i < 4; ++i)
+                    pw[i] = pack_bf16(x[2 * i] * cs[2 * i] + other[2 * i] * sn[2 * i], x[2 * i + 1] * cs[2 * i + 1] + other[2 * i + 1] * sn[2 * i + 1]);
+                if (is_k) {
+                    *reinterpret_cast<uint4*>(newkv + c * 8) = packed;
+                    if (k_elem >= 0) *reinterpret_cast<uint4*>(p.cache + k_elem + c * 8) = packed;
+                } else {
+                    *reinterpret_cast<uint4*>(sm.q + swz<HD>(task, c)) = packed;
+                }
+            }
+            for (int i = threadIdx.x; i < (16 - g) * CPR; i += kConsumers)    // rows without a query head are zero
+                *reinterpret_cast<uint4*>(sm.q + swz<HD>(g + i / CPR, i % CPR)) = make_uint4(0, 0, 0, 0);
         }
-        cp_async_commit();
-        cp_async_wait<0>();
         __syncthreads();
         if (warp == kConsumers / 32) {                                     // ---- producer warp ----
             if (lane == 0) {
@@ -475,6 +581,17 @@ attn_decode_bf16_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnPa
                 const int st = it % kDecStages;
                 const int key0 = (tile_begin + it) * kBN + warp * 16;      // each warp takes 16 of the tile's 64 keys
                 mbar_wait(full + st, (it / kDecStages) & 1, p.err);       // also when this warp's keys are all outside
+                if (owns_pos && tile_begin + it == tile_of_pos && warp == (pos % kBN) / 16) {
+                    // the token's own key and value are not in the cache's copy of this tile yet (they are being
+                    // written by this very kernel): the warp that owns the row puts them into the tile
+                    __nv_bfloat16* tile = sm.stages + st * Plan::kStageElems;
+                    if (lane < 2 * CPR) {
+                        const int which = lane / CPR, cc = lane % CPR;
+                        *reinterpret_cast<uint4*>(tile + which * kBN * HD + kv_off(pos % kBN, cc)) =
+                            *reinterpret_cast<const uint4*>(newkv + which * HD + cc * 8);
+                    }
+                    __syncwarp();
+                }
                 if (key0 <= key_hi && key0 + 15 >= key_lo) {
                     const __nv_bfloat16* sK = sm.stages + st * Plan::kStageElems;
                     const __nv_bfloat16* sV = sK + kBN * HD;
@@ -638,7 +755,8 @@ static int kv_tensor_map(CUtensorMap* out, const void* cache, int64_t rows, int 
 template <int HD> constexpr size_t prefill_smem() { return SmemPlan<HD, kPreStages, 64>::kBytes; }
 template <int HD> constexpr size_t decode_smem() {
     const size_t red = 1024 + static_cast<size_t>(5 * 16) * (HD + 2) * sizeof(float);
-    return SmemPlan<HD, kDecStages, 16>::kBytes > red ? SmemPlan<HD, kDecStages, 16>::kBytes : red;
+    const size_t plan = SmemPlan<HD, kDecStages, 16>::kBytes + 64 + 2 * HD * sizeof(__nv_bfloat16);   // + the new key and value
+    return plan > red ? plan : red;
 }
 
 constexpr int kMaxClusterSplits = 16;       // 8 is the portable cluster size; up to 16 blocks with the opt-in attribute
@@ -774,6 +892,41 @@ extern "C" int cvb_attn_decode_bf16(void* out, const void* q, const void* cache,
     dim3 mgrid(static_cast<unsigned>(S), static_cast<unsigned>(H));
     if (hd == 128) return launch_decode<128>(map, p, grid, mgrid, cluster_merge != 0, stream);
     return launch_decode<64>(map, p, grid, mgrid, cluster_merge != 0, stream);
+}
+
+// Decode attention straight from the projection's output: per-head norm and rotation of the queries, norm, rotation and
+// cache write of the new key, cache write of the new value, and the attention itself in one kernel.  `qkv` is
+// [T, H + 2 KV, hd]; `slots[t]` is the cache slot of token t; `q_w`/`k_w` are the per-head norm weights (both null: no
+// norm) and `cos_t`/`sin_t` the rotation tables over the whole head in rotate-half pairing (both null: no rotation).
+extern "C" int cvb_attn_decode_fused_bf16(void* out, const void* qkv, void* cache, const int* block_tables, int table_width,
+                                          const int* cu_seqlens, const int* positions, const int* slots, int S, int H,
+                                          int KV, int hd, int page_size, int window, float scale, int num_pages,
+                                          int splits, float* scratch, int64_t scratch_floats, const float* q_w,
+                                          const float* k_w, float qk_eps, const float* cos_t, const float* sin_t,
+                                          int max_pos, int* err_flag, cudaStream_t stream) {
+    if (splits < 1 || splits > 65535) return CVB_E_SIZE;
+    if (qkv == nullptr || slots == nullptr || (q_w == nullptr) != (k_w == nullptr)) return CVB_E_SHAPE;
+    if ((cos_t == nullptr) != (sin_t == nullptr) || (cos_t != nullptr && max_pos <= 0)) return CVB_E_SHAPE;
+    auto al = [](const void* q) { return q == nullptr || (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+    if (!al(qkv) || !al(cos_t) || !al(sin_t) || !al(cache)) return CVB_E_ALIGN;
+    AttnParams p{};
+    CUtensorMap map;
+    const int rc = fill_params(p, map, out, qkv, cache, block_tables, table_width, cu_seqlens, positions, S, H, KV, hd,
+                               page_size, window, scale, num_pages, err_flag);
+    if (rc != CVB_OK) return rc;
+    const bool cluster = splits <= kMaxClusterSplits;
+    if (splits > 1 && !cluster && (scratch == nullptr || scratch_floats < cvb_attn_decode_scratch_floats(S, KV, hd, splits)))
+        return CVB_E_SCRATCH;
+    p.splits = splits;
+    p.part_o = scratch;
+    p.part_ml = scratch ? scratch + static_cast<int64_t>(S) * KV * splits * 16 * hd : nullptr;
+    p.qkv = (const __nv_bfloat16*)qkv; p.q_w = q_w; p.k_w = k_w; p.qk_eps = qk_eps; p.cos_t = cos_t; p.sin_t = sin_t;
+    p.max_pos = max_pos; p.slots = slots; p.cache = (__nv_bfloat16*)cache;
+    p.cache_elems = static_cast<int64_t>(num_pages) * 2 * KV * page_size * hd;
+    dim3 grid(static_cast<unsigned>(S), static_cast<unsigned>(KV), static_cast<unsigned>(splits));
+    dim3 mgrid(static_cast<unsigned>(S), static_cast<unsigned>(H));
+    if (hd == 128) return launch_decode<128>(map, p, grid, mgrid, cluster, stream);
+    return launch_decode<64>(map, p, grid, mgrid, cluster, stream);
 }
 
 // ---- split-KV decode attention without any allocation ---------------------------------------------------------------

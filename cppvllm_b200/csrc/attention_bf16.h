@@ -25,6 +25,15 @@ int cvb_attn_decode_bf16(void* out, const void* q, const void* cache, const int*
                          int window, float scale, int num_pages, int splits, float* scratch, int64_t scratch_floats,
                          int cluster_merge, int* err_flag, cudaStream_t stream);
 
+// Decode attention straight from the projection's output qkv [T, H + 2 KV, hd]: per-head norm (weights q_w, k_w; both
+// null for none) and rotate-half rotation over the whole head (tables cos_t, sin_t [max_pos, hd / 2]; both null for none)
+// of the queries and of the new key, the cache write of the new key and value at `slots[t]`, and the attention.
+int cvb_attn_decode_fused_bf16(void* out, const void* qkv, void* cache, const int* block_tables, int table_width,
+                               const int* cu_seqlens, const int* positions, const int* slots, int S, int H, int KV,
+                               int hd, int page_size, int window, float scale, int num_pages, int splits, float* scratch,
+                               int64_t scratch_floats, const float* q_w, const float* k_w, float qk_eps,
+                               const float* cos_t, const float* sin_t, int max_pos, int* err_flag, cudaStream_t stream);
+
 // The same attention for callers that cannot allocate device memory (no cudaMalloc in their loop, a fixed memory
 // budget owned by someone else): its scratch is a static device array inside the library, at most
 // cvb_attn_decode_static_scratch_floats() floats (8 MiB) per launch; larger launches are refused with CVB_E_SCRATCH.

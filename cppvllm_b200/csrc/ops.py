@@ -352,6 +352,47 @@ def attn_decode_bf16(out, q, cache, block_tables, cu_seqlens, positions, num_seq
     return out
 
 
+DECODE_CLUSTER_SPLITS = 16      # up to this many splits merge inside a thread-block cluster and need no scratch
+
+
+def attn_decode_fused_bf16(out, qkv, cache, block_tables, cu_seqlens, positions, slots, num_seqs: int, num_heads: int,
+                           num_kv_heads: int, head_dim: int, page_size: int, scale: float, splits: int,
+                           scratch: Optional[torch.Tensor], q_weight: Optional[torch.Tensor], k_weight: Optional[torch.Tensor],
+                           qk_eps: float, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], window: int = 0):
+    """Attention of single decoded tokens from the projection's raw output qkv [T, (H + 2 KV) hd]: per-head norm and
+    rotation of queries and of the new key, the cache write of the new key and value, and the attention, one kernel."""
+    _attn_common_checks(out, qkv, cache, block_tables, cu_seqlens, positions)
+    _cuda(slots, q_weight, k_weight, cos, sin, scratch)
+    _contig(slots, q_weight, k_weight, cos, sin, scratch)
+    T = qkv.shape[0]
+    if qkv.shape[1] != (num_heads + 2 * num_kv_heads) * head_dim or out.shape != (T, num_heads * head_dim):
+        raise KernelError("attn_decode_fused_bf16: qkv must be [T, (H + 2 KV) hd] and out [T, H hd]")
+    if slots.dtype != torch.int32 or slots.numel() < T:
+        raise KernelError("attn_decode_fused_bf16: slots must be int32 [T]")
+    for w in (q_weight, k_weight):
+        if w is not None and (w.dtype != torch.float32 or w.numel() != head_dim):
+            raise KernelError("attn_decode_fused_bf16: norm weights must be float32 [head_dim]")
+    max_pos = 0
+    if cos is not None:
+        if sin is None or cos.dtype != torch.float32 or sin.dtype != torch.float32 or cos.shape != sin.shape \
+                or cos.dim() != 2 or cos.shape[1] != head_dim // 2:
+            raise KernelError("attn_decode_fused_bf16: cos and sin must be float32 [max_pos, head_dim / 2]")
+        max_pos = cos.shape[0]
+    if scratch is not None and scratch.dtype != torch.float32:
+        raise KernelError("attn_decode_fused_bf16: scratch must be float32")
+    num_pages = cache.numel() // (2 * num_kv_heads * page_size * head_dim)
+    lib = attn_bf16()
+    lib.cvb_attn_decode_fused_bf16.restype = c_int
+    _check(lib.cvb_attn_decode_fused_bf16(
+        _ptr(out), _ptr(qkv), _ptr(cache), _ptr(block_tables), c_int(block_tables.shape[1]), _ptr(cu_seqlens),
+        _ptr(positions), _ptr(slots), c_int(num_seqs), c_int(num_heads), c_int(num_kv_heads), c_int(head_dim),
+        c_int(page_size), c_int(window), c_float(scale), c_int(num_pages), c_int(splits), _ptr(scratch),
+        c_int64(scratch.numel() if scratch is not None else 0), _ptr(q_weight), _ptr(k_weight), c_float(qk_eps),
+        _ptr(cos), _ptr(sin), c_int(max_pos), _ptr(error_flag(qkv.device)), _stream()), "attn_decode_fused_bf16",
+        kernels=2 if splits > 16 else 1)
+    return out
+
+
 _gemv = None
 
 GEMV_MAX_ROWS = 8

@@ -26,7 +26,7 @@ class PagedAttention(Mixer):
     def __init__(self, runtime, prefix="", names=None, *, hidden_size: int, num_heads: int, num_kv_heads: int,
                  head_dim: int, qk_norm: bool = True, qk_norm_eps: float = 1e-6, window: int = 0,
                  scale: Optional[float] = None, position=None, force_general: bool = False,
-                 prefill_kernel: str = "tcgen05"):
+                 prefill_kernel: str = "tcgen05", fuse_decode_attention: bool = True):
         super().__init__(runtime, prefix, names)
         if num_heads % num_kv_heads:
             raise ValueError(f"{num_heads} query heads are not a multiple of {num_kv_heads} key/value heads")
@@ -37,6 +37,8 @@ class PagedAttention(Mixer):
         if prefill_kernel not in ("tcgen05", "mma"):
             raise ValueError("prefill_kernel must be 'tcgen05' or 'mma'")
         self.prefill_kernel = prefill_kernel         # which tensor-core kernel runs prompt portions
+        self.fuse_decode_attention = bool(fuse_decode_attention)   # decode-only steps: norm, rotation, cache write and
+                                                                   # attention in one kernel (else three kernels)
         self.position = position            # a RotaryEmbedding part or None
         if self.position is not None and self.position.rotary_dim > self.head_dim:
             raise ValueError("rotary_dim exceeds head_dim")
@@ -141,18 +143,36 @@ class PagedAttention(Mixer):
         H, KV, hd = self.num_heads, self.num_kv_heads, self.head_dim
         ws = self.rt.workspace
         g = ctx.groups[cache.group]
-        q = ws.rows("attn_q", T, H * hd, x.dtype)
         pos = self.position
-        ops.qk_norm_rope_kv(
-            q, qkv, self.q_norm_w, self.k_norm_w,
-            pos.cos if pos is not None else None, pos.sin if pos is not None else None, ctx.positions,
-            g.slot_mapping if cache.writes else None, cache.pages if cache.writes else None,
-            H, KV, hd, g.page_size, self.qk_norm_eps,
-            rotary_dim=pos.rotary_dim if pos is not None else 0,
-            interleaved=pos.interleaved if pos is not None else False)
         att = ws.rows("attn_out", T, H * hd, x.dtype)
-        self.attend(att, q, ctx, cache, g)
+        if self._decode_from_projection(ctx, cache, g):
+            # single decoded tokens only: per-head norm, rotation, cache write and attention in one kernel
+            S = ctx.num_seqs
+            splits = self.decode_splits(S, ctx.max_kv_len)
+            scratch = None
+            if splits > ops.DECODE_CLUSTER_SPLITS:
+                scratch = ws.flat("attn_decode_scratch", self.scratch_floats(), torch.float32)
+            ops.attn_decode_fused_bf16(att, qkv, cache.pages, g.block_tables, ctx.cu_seqlens, ctx.positions, g.slot_mapping,
+                                       S, H, KV, hd, g.page_size, self.scale, splits, scratch, self.q_norm_w, self.k_norm_w,
+                                       self.qk_norm_eps, pos.cos if pos is not None else None,
+                                       pos.sin if pos is not None else None, window=self.window)
+        else:
+            q = ws.rows("attn_q", T, H * hd, x.dtype)
+            ops.qk_norm_rope_kv(
+                q, qkv, self.q_norm_w, self.k_norm_w,
+                pos.cos if pos is not None else None, pos.sin if pos is not None else None, ctx.positions,
+                g.slot_mapping if cache.writes else None, cache.pages if cache.writes else None,
+                H, KV, hd, g.page_size, self.qk_norm_eps,
+                rotary_dim=pos.rotary_dim if pos is not None else 0,
+                interleaved=pos.interleaved if pos is not None else False)
+            self.attend(att, q, ctx, cache, g)
         return ops.project_rows(att, self.w_o, ws.rows("attn_proj", T, self.hidden_size, x.dtype), T)
+
+    def _decode_from_projection(self, ctx, cache, g) -> bool:
+        pos = self.position
+        return (ctx.all_decode and cache.writes and not self.force_general and self.fuse_decode_attention
+                and ops.fast_attention_supported(self.rt.dtype, self.num_heads, self.num_kv_heads, self.head_dim, g.page_size)
+                and (pos is None or (pos.rotary_dim == self.head_dim and not pos.interleaved)))
 
     # target number of blocks for the split-KV decode kernel: two per SM of a B200
     DECODE_TARGET_BLOCKS = 296

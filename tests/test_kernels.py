@@ -401,6 +401,51 @@ def test_tensor_core_attention_mixed_portions_and_single_tokens(ops, H, KV, hd, 
     torch.testing.assert_close(results[(3, True)], gen.float().cpu().view(T, H, hd), atol=2e-2, rtol=2e-2)
 
 
+@pytest.mark.parametrize("H,KV,hd,page,window,norm,rope", [(16, 8, 128, 32, 0, True, True), (6, 2, 64, 16, 0, True, True),
+                                                          (16, 1, 128, 16, 0, False, True), (4, 4, 64, 64, 70, True, False)])
+def test_decode_attention_from_the_projection(ops, H, KV, hd, page, window, norm, rope):
+    """Norm, rotation, cache write and attention of decoded tokens in one kernel against the three kernels it replaces:
+    the same outputs and the same cache contents, at contexts that put the new token at the start, in the middle and at
+    the end of a tile and of a page, for several split counts."""
+    dt = torch.bfloat16
+    g = torch.Generator().manual_seed(H + hd + page)
+    ctxs = [0, 1, 15, 16, 63, 64, 65, 127, 500, 1000]             # tokens already in the cache, one new token each
+    S = len(ctxs)
+    seqs_k = [torch.randn(c + 1, KV, hd, generator=g).to(dt) for c in ctxs]
+    seqs_v = [torch.randn(c + 1, KV, hd, generator=g).to(dt) for c in ctxs]
+    total_pages = sum((c + 1 + page - 1) // page for c in ctxs) + 2
+    cache, tables = build_paged(seqs_k, seqs_v, page, total_pages, KV, hd, dt, g)
+    d = dev()
+    qkv = (torch.randn(S, (H + 2 * KV) * hd, generator=g) * 1.5).to(dt).to(d)
+    qw = (1 + 0.2 * torch.randn(hd, generator=g)).to(d) if norm else None
+    kw = (1 + 0.2 * torch.randn(hd, generator=g)).to(d) if norm else None
+    cos = sin = None
+    if rope:
+        inv = 1.0 / (10000.0 ** (torch.arange(0, hd, 2, dtype=torch.float64) / hd))
+        ang = torch.arange(1100, dtype=torch.float64)[:, None] * inv[None, :]
+        cos, sin = ang.cos().float().to(d), ang.sin().float().to(d)
+    cu = torch.arange(S + 1, dtype=torch.int32, device=d)
+    pos = torch.tensor(ctxs, dtype=torch.int32, device=d)
+    slots = torch.tensor([int(tables[s, c // page]) * page + c % page for s, c in enumerate(ctxs)], dtype=torch.int32, device=d)
+    scale = 1 / math.sqrt(hd)
+    tables_d = tables.to(d)
+    # the three kernels
+    cache_a = cache.clone().to(d)
+    q = torch.empty(S, H * hd, dtype=dt, device=d)
+    ops.qk_norm_rope_kv(q, qkv, qw, kw, cos, sin, pos, slots, cache_a, H, KV, hd, page, 1e-6)
+    want = torch.zeros(S, H * hd, dtype=dt, device=d)
+    scratch = torch.zeros(ops.attn_decode_scratch_floats(S, KV, hd, 20), device=d)
+    ops.attn_decode_bf16(want, q, cache_a, tables_d, cu, pos, S, H, KV, hd, page, scale, 3, scratch, window=window)
+    for splits in (1, 3, 8, 20):
+        cache_b = cache.clone().to(d)
+        got = torch.zeros(S, H * hd, dtype=dt, device=d)
+        ops.attn_decode_fused_bf16(got, qkv, cache_b, tables_d, cu, pos, slots, S, H, KV, hd, page, scale, splits, scratch,
+                                   qw, kw, 1e-6, cos, sin, window=window)
+        ops.check_device_errors(d)
+        assert torch.equal(cache_a, cache_b)
+        torch.testing.assert_close(got.float(), want.float(), atol=2e-2, rtol=2e-2)
+
+
 def test_tensor_core_attention_finds_one_far_key(ops):
     dt = torch.bfloat16
     H, KV, hd, page = 4, 2, 128, 16
