@@ -454,23 +454,36 @@ attn_decode_bf16_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnPa
     if (n_tiles > 0) {
         uint64_t* full = sm.bars;
         uint64_t* empty = sm.bars + kDecStages;
-        if (threadIdx.x == 0) {
-            for (int i = 0; i < kDecStages; ++i) { mbar_init(full + i, 1); mbar_init(empty + i, kConsumers / 32); }
-            mbar_fence_init();
-        }
         __nv_bfloat16* newkv = reinterpret_cast<__nv_bfloat16*>(reinterpret_cast<unsigned char*>(sm.bars) + 64);   // [2][HD]
         const int tile_of_pos = pos / kBN;
         const bool owns_pos = p.qkv != nullptr && tile_of_pos >= tile_begin && tile_of_pos < tile_begin + n_tiles;
-        if (p.qkv == nullptr) {
-            for (int i = threadIdx.x; i < 16 * CPR; i += kThreads) {
-                const int r = i / CPR, c = i % CPR;
-                const bool valid = r < g;
-                const __nv_bfloat16* src = valid ? p.q + ((static_cast<int64_t>(cu0) * p.H + kvh * g + r) * HD + c * 8) : p.q;
-                cp_async16(sm.q + swz<HD>(r, c), src, valid);
+        if (warp == kConsumers / 32) {                                     // ---- producer warp ----
+            // it sets up the barriers itself and starts fetching keys while the other warps prepare the queries
+            if (lane == 0) {
+                for (int i = 0; i < kDecStages; ++i) { mbar_init(full + i, 1); mbar_init(empty + i, kConsumers / 32); }
+                mbar_fence_init();
             }
-            cp_async_commit();
-            cp_async_wait<0>();
-        } else if (threadIdx.x < kConsumers) {
+            __syncwarp();
+            asm volatile("bar.arrive 1, %0;\n" ::"n"(kThreads) : "memory");
+            if (lane == 0) {
+                for (int it = 0; it < n_tiles; ++it) {
+                    const int st = it % kDecStages;
+                    if (it >= kDecStages) mbar_wait(empty + st, ((it / kDecStages) - 1) & 1, p.err);
+                    tma_issue_tile<HD>(sm.stages + st * Plan::kStageElems, full + st, &kv_map, p, table, kvh,
+                                       (tile_begin + it) * kBN, key_lo, key_hi);
+                }
+            }
+        } else {                                                           // ---- consumer warps ----
+            if (p.qkv == nullptr) {
+                for (int i = threadIdx.x; i < 16 * CPR; i += kConsumers) {
+                    const int r = i / CPR, c = i % CPR;
+                    const bool valid = r < g;
+                    const __nv_bfloat16* src = valid ? p.q + ((static_cast<int64_t>(cu0) * p.H + kvh * g + r) * HD + c * 8) : p.q;
+                    cp_async16(sm.q + swz<HD>(r, c), src, valid);
+                }
+                cp_async_commit();
+                cp_async_wait<0>();
+            } else {
             // Per-head norm and rotation of this kv head's queries, straight from the projection; CPR neighbouring lanes
             // own one head vector (16-byte chunks).  The block that owns the token's own position does the same for the
             // new key, copies the new value, and writes both to the cache and to shared memory.
@@ -559,18 +572,8 @@ attn_decode_bf16_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnPa
             }
             for (int i = threadIdx.x; i < (16 - g) * CPR; i += kConsumers)    // rows without a query head are zero
                 *reinterpret_cast<uint4*>(sm.q + swz<HD>(g + i / CPR, i % CPR)) = make_uint4(0, 0, 0, 0);
-        }
-        __syncthreads();
-        if (warp == kConsumers / 32) {                                     // ---- producer warp ----
-            if (lane == 0) {
-                for (int it = 0; it < n_tiles; ++it) {
-                    const int st = it % kDecStages;
-                    if (it >= kDecStages) mbar_wait(empty + st, ((it / kDecStages) - 1) & 1, p.err);
-                    tma_issue_tile<HD>(sm.stages + st * Plan::kStageElems, full + st, &kv_map, p, table, kvh,
-                                       (tile_begin + it) * kBN, key_lo, key_hi);
-                }
             }
-        } else {                                                           // ---- consumer warps ----
+            asm volatile("bar.sync 1, %0;\n" ::"n"(kThreads) : "memory");     // all queries; and the producer's barriers exist
             const int row_lo[2] = {key_lo, key_lo};
             const int row_hi[2] = {key_hi, key_hi};         // rows >= g hold zero queries and are never stored
             uint32_t qf[HD / 16][4];
