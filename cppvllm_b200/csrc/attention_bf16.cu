@@ -435,8 +435,9 @@ attn_decode_bf16_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnPa
     const int g = p.H / p.KV;
     const int seq = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int cu0 = p.cu_seqlens[seq];
-    if (p.cu_seqlens[seq + 1] - cu0 != 1) return;                          // not a single decoded token
+    // with the projection's raw output every request brings exactly one token: token s belongs to request s
+    const int cu0 = p.qkv != nullptr ? seq : p.cu_seqlens[seq];
+    if (p.qkv == nullptr && p.cu_seqlens[seq + 1] - cu0 != 1) return;      // not a single decoded token
     const int pos = p.positions[cu0];
     const int key_lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
     const int key_hi = pos;
@@ -689,8 +690,8 @@ __global__ void attn_decode_merge_kernel(const AttnParams p) {
     pdl_trigger();
     pdl_wait();
     const int seq = blockIdx.x, h = blockIdx.y;
-    const int cu0 = p.cu_seqlens[seq];
-    if (p.cu_seqlens[seq + 1] - cu0 != 1) return;
+    const int cu0 = p.qkv != nullptr ? seq : p.cu_seqlens[seq];
+    if (p.qkv == nullptr && p.cu_seqlens[seq + 1] - cu0 != 1) return;
     const int g = p.H / p.KV, kvh = h / g, r = h % g;
     const int64_t base = ((static_cast<int64_t>(seq) * p.KV + kvh) * p.splits) * 16 + r;
     float mm = -INFINITY;
@@ -898,8 +899,8 @@ extern "C" int cvb_attn_decode_bf16(void* out, const void* q, const void* cache,
 }
 
 // Decode attention straight from the projection's output: per-head norm and rotation of the queries, norm, rotation and
-// cache write of the new key, cache write of the new value, and the attention itself in one kernel.  `qkv` is
-// [T, H + 2 KV, hd]; `slots[t]` is the cache slot of token t; `q_w`/`k_w` are the per-head norm weights (both null: no
+// cache write of the new key, cache write of the new value, and the attention itself in one kernel.  Every request brings
+// exactly one token (T = S, token s belongs to request s; `cu_seqlens` is not read).  `qkv` is [T, H + 2 KV, hd]; `slots[t]` is the cache slot of token t; `q_w`/`k_w` are the per-head norm weights (both null: no
 // norm) and `cos_t`/`sin_t` the rotation tables over the whole head in rotate-half pairing (both null: no rotation).
 extern "C" int cvb_attn_decode_fused_bf16(void* out, const void* qkv, void* cache, const int* block_tables, int table_width,
                                           const int* cu_seqlens, const int* positions, const int* slots, int S, int H,

@@ -365,6 +365,8 @@ def attn_decode_fused_bf16(out, qkv, cache, block_tables, cu_seqlens, positions,
     _cuda(slots, q_weight, k_weight, cos, sin, scratch)
     _contig(slots, q_weight, k_weight, cos, sin, scratch)
     T = qkv.shape[0]
+    if T != num_seqs:
+        raise KernelError("attn_decode_fused_bf16: every request brings exactly one token (qkv has one row per request)")
     if qkv.shape[1] != (num_heads + 2 * num_kv_heads) * head_dim or out.shape != (T, num_heads * head_dim):
         raise KernelError("attn_decode_fused_bf16: qkv must be [T, (H + 2 KV) hd] and out [T, H hd]")
     if slots.dtype != torch.int32 or slots.numel() < T:
