@@ -103,6 +103,9 @@ gemv_mma_kernel(const GemvParams p) {
     pdl_wait();
 
     // ---- activations into shared memory ----
+    // Loads come in batches of kStage per thread, all issued before the first of them is used: the staging then costs
+    // about one trip to the L2 instead of one per loop iteration.
+    constexpr int kStage = NORM ? 4 : 8;
     if constexpr (NORM) {
         // one warp per row: add, round, sum of squares, scale; the row passes through shared memory in between
         for (int m = warp; m < kBatch; m += n_warps) {
@@ -110,48 +113,84 @@ gemv_mma_kernel(const GemvParams p) {
                 for (int c = lane; c < chunks; c += 32) *reinterpret_cast<uint4*>(xs + m * xstride + c * 8) = make_uint4(0, 0, 0, 0);
                 continue;
             }
+            const uint4* xg = reinterpret_cast<const uint4*>(p.x + static_cast<int64_t>(m) * K);
+            const uint4* dg = p.delta != nullptr ? reinterpret_cast<const uint4*>(p.delta + static_cast<int64_t>(m) * K) : nullptr;
             float ss = 0.f;
-            for (int c = lane; c < chunks; c += 32) {
-                float v[8];
-                unpack8(*reinterpret_cast<const uint4*>(p.x + static_cast<int64_t>(m) * K + c * 8), v);
-                if (p.delta != nullptr) {
-                    float d[8];
-                    unpack8(*reinterpret_cast<const uint4*>(p.delta + static_cast<int64_t>(m) * K + c * 8), d);
+            for (int c0 = lane; c0 < chunks; c0 += 32 * kStage) {
+                uint4 xv[kStage], dv[kStage];
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) v[i] = rnd<__nv_bfloat16>(v[i] + d[i]);
+                for (int u = 0; u < kStage; ++u) {
+                    const int c = c0 + u * 32;
+                    xv[u] = c < chunks ? xg[c] : zero;
+                    dv[u] = (dg != nullptr && c < chunks) ? dg[c] : zero;
                 }
-                uint4 packed;
-                __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&packed);
 #pragma unroll
-                for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
-                *reinterpret_cast<uint4*>(xs + m * xstride + c * 8) = packed;
-                if (p.delta != nullptr && blockIdx.x == 0)
-                    *reinterpret_cast<uint4*>(p.resid_out + static_cast<int64_t>(m) * K + c * 8) = packed;
+                for (int u = 0; u < kStage; ++u) {
+                    const int c = c0 + u * 32;
+                    if (c >= chunks) break;
+                    float v[8];
+                    unpack8(xv[u], v);
+                    if (dg != nullptr) {
+                        float d[8];
+                        unpack8(dv[u], d);
 #pragma unroll
-                for (int i = 0; i < 8; ++i) ss += v[i] * v[i];
+                        for (int i = 0; i < 8; ++i) v[i] = rnd<__nv_bfloat16>(v[i] + d[i]);
+                    }
+                    uint4 packed;
+                    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+                    *reinterpret_cast<uint4*>(xs + m * xstride + c * 8) = packed;
+                    if (dg != nullptr && blockIdx.x == 0)
+                        *reinterpret_cast<uint4*>(p.resid_out + static_cast<int64_t>(m) * K + c * 8) = packed;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) ss += v[i] * v[i];
+                }
             }
             ss = warp_sum(ss);
             const float inv = rsqrtf(ss / static_cast<float>(K) + p.eps);
-            for (int c = lane; c < chunks; c += 32) {          // each lane re-reads the chunks it wrote itself
-                float v[8];
-                unpack8(*reinterpret_cast<const uint4*>(xs + m * xstride + c * 8), v);
-                const float4 w0 = *reinterpret_cast<const float4*>(p.norm_w + c * 8);
-                const float4 w1 = *reinterpret_cast<const float4*>(p.norm_w + c * 8 + 4);
-                const float w[8] = {w0.x, w0.y, w0.z, w0.w, w1.x, w1.y, w1.z, w1.w};
-                uint4 packed;
-                __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&packed);
+            for (int c0 = lane; c0 < chunks; c0 += 32 * kStage) {  // each lane re-reads the chunks it wrote itself
+                float4 w0[kStage], w1[kStage];
 #pragma unroll
-                for (int i = 0; i < 4; ++i)
-                    h[i] = __floats2bfloat162_rn(rnd<__nv_bfloat16>(v[2 * i] * inv) * w[2 * i],
-                                                 rnd<__nv_bfloat16>(v[2 * i + 1] * inv) * w[2 * i + 1]);
-                *reinterpret_cast<uint4*>(xs + m * xstride + c * 8) = packed;
+                for (int u = 0; u < kStage; ++u) {
+                    const int c = min(c0 + u * 32, chunks - 1);
+                    w0[u] = *reinterpret_cast<const float4*>(p.norm_w + c * 8);
+                    w1[u] = *reinterpret_cast<const float4*>(p.norm_w + c * 8 + 4);
+                }
+#pragma unroll
+                for (int u = 0; u < kStage; ++u) {
+                    const int c = c0 + u * 32;
+                    if (c >= chunks) break;
+                    float v[8];
+                    unpack8(*reinterpret_cast<const uint4*>(xs + m * xstride + c * 8), v);
+                    const float w[8] = {w0[u].x, w0[u].y, w0[u].z, w0[u].w, w1[u].x, w1[u].y, w1[u].z, w1[u].w};
+                    uint4 packed;
+                    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                        h[i] = __floats2bfloat162_rn(rnd<__nv_bfloat16>(v[2 * i] * inv) * w[2 * i],
+                                                     rnd<__nv_bfloat16>(v[2 * i + 1] * inv) * w[2 * i + 1]);
+                    *reinterpret_cast<uint4*>(xs + m * xstride + c * 8) = packed;
+                }
             }
         }
     } else {
-        for (int i = threadIdx.x; i < kBatch * chunks; i += blockDim.x) {
-            const int m = i / chunks, c = i - m * chunks;
-            *reinterpret_cast<uint4*>(xs + m * xstride + c * 8) =
-                m < p.M ? *reinterpret_cast<const uint4*>(p.x + static_cast<int64_t>(m) * K + c * 8) : make_uint4(0, 0, 0, 0);
+        const int total = kBatch * chunks;
+        for (int i0 = threadIdx.x; i0 < total; i0 += blockDim.x * kStage) {
+            uint4 v[kStage];
+#pragma unroll
+            for (int u = 0; u < kStage; ++u) {
+                const int i = i0 + u * blockDim.x;
+                const int m = i / chunks, c = i - m * chunks;
+                v[u] = (i < total && m < p.M) ? *reinterpret_cast<const uint4*>(p.x + static_cast<int64_t>(m) * K + c * 8) : zero;
+            }
+#pragma unroll
+            for (int u = 0; u < kStage; ++u) {
+                const int i = i0 + u * blockDim.x;
+                if (i >= total) break;
+                const int m = i / chunks, c = i - m * chunks;
+                *reinterpret_cast<uint4*>(xs + m * xstride + c * 8) = v[u];
+            }
         }
     }
     __syncthreads();
@@ -213,7 +252,7 @@ static int launch_gemv(GemvParams p, cudaStream_t stream) {
     const int n_out = SWIGLU ? p.N / 2 : p.N;
     const int tiles = (n_out + OUT_PER_TILE - 1) / OUT_PER_TILE;
     const int slabs = (p.K + 31) / 32;
-    p.warps_k = max(1, min(8, (slabs + kJBatch - 1) / kJBatch));          // about one batch of loads per warp
+    p.warps_k = max(1, min(16, (slabs + kJBatch - 1) / kJBatch));         // about one batch of loads per warp
     p.tiles_per_block = max(1, 8 / p.warps_k);
     while (p.tiles_per_block > 1 && (tiles + p.tiles_per_block - 1) / p.tiles_per_block < 120) p.tiles_per_block >>= 1;
     p.n_tiles = tiles;
