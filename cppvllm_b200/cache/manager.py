@@ -268,6 +268,15 @@ class CacheManager:
             need.append(max(0, self.num_pages_for(upto_len) - first))
         return need
 
+    def covered(self, request_id, upto_len: int) -> bool:
+        """Whether the request's tables already reach `upto_len` in every group (nothing to reserve): the common case
+        of a decoding request, checked without looking at the pools."""
+        need = (upto_len + self.page_size - 1) // self.page_size
+        for table in self.leases[request_id].tables:
+            if len(table) < need:
+                return False
+        return True
+
     def can_reserve(self, request_id, upto_len: int) -> bool:
         return all(n <= p.num_free for n, p in zip(self.pages_missing(request_id, upto_len), self.pools))
 

@@ -142,6 +142,9 @@ class ModelRunner:
         self._logits = torch.empty((self.max_seqs, self.vocab_size), dtype=torch.float32, device=self.device)
         self._graphs: Dict[int, tuple] = {}
         self._graph_launches: Dict[int, int] = {}
+        self._tab_mirror = [np.full((n_slots + 1, self.table_width), -1, dtype=np.int32) for _ in self.group_specs]
+        self._mirror_owner = [[None] * (n_slots + 1) for _ in self.group_specs]
+        self._mirror_len = [[0] * (n_slots + 1) for _ in self.group_specs]
         self._shape_graphs: "OrderedDict[tuple, tuple]" = OrderedDict()
         self._shape_seen: Dict[tuple, int] = {}
         self._feed = None
@@ -195,6 +198,29 @@ class ModelRunner:
             ev.synchronize()                                  # the copy that last read this buffer is done
         return i, self._stage_np[i]
 
+    def _mirror_row(self, lease, W: int) -> int:
+        """Block tables are mirrored on the host as integer arrays, one row per state slot, and brought up to date only
+        where a request's table has grown: a step then copies whole rows instead of converting every list again.
+        Returns the row of `lease`."""
+        row = lease.state_slot
+        for g in range(len(self.group_specs)):
+            tab = lease.tables[g]
+            n = len(tab)
+            if n > W:
+                raise ValueError("a request's block table is wider than the staged width")
+            mirror = self._tab_mirror[g]
+            if self._mirror_owner[g][row] is not lease:
+                mirror[row, :] = -1
+                self._mirror_owner[g][row] = lease
+                self._mirror_len[g][row] = 0
+            have = self._mirror_len[g][row]
+            if self.group_specs[g][0].window > 0:
+                have = 0                                      # a windowed group also gives pages back: copy the whole row
+            if have < n:
+                mirror[row, have:n] = tab[have:n]
+                self._mirror_len[g][row] = n
+        return row
+
     def _fill(self, entries: Sequence[StepEntry], T: int, S: int, R: int, W: int, pad_to: int = 0):
         """Write the step's index arrays into a pinned buffer and start its copy to the device."""
         S_pad = max(S, pad_to)
@@ -216,32 +242,56 @@ class ModelRunner:
             tb.fill(-1)
         t = r = 0
         cu[0] = 0
+        G = len(self.group_specs)
+        mirror_rows = []
         for s, e in enumerate(entries):
             n = len(e.tokens)
             lease = self.cache.lease(e.request_id)
-            tokens[t:t + n] = e.tokens
-            positions[t:t + n] = np.arange(e.start, e.start + n, dtype=np.int32)
-            seq_of[t:t + n] = s
+            start = e.start
             cu[s + 1] = t + n
-            kvl[s] = e.start + n
+            kvl[s] = start + n
             sts[s] = lease.state_slot
+            mirror_rows.append(self._mirror_row(lease, W))
+            if n == 1:                                        # a decoded token: plain integers instead of arrays
+                tokens[t] = e.tokens[0]
+                positions[t] = start
+                seq_of[t] = s
+                for w in e.want:
+                    rows[r] = t + w
+                    r += 1
+                for g in range(G):
+                    tab = lease.tables[g]
+                    i = start // ps
+                    if i >= len(tab):
+                        raise RuntimeError(f"request {e.request_id!r}: pages for positions up to {start} were "
+                                           f"not reserved in group {g}")
+                    page = tab[i]
+                    if page < 0:
+                        raise RuntimeError(f"request {e.request_id!r}: a token of this step has no page in group {g}")
+                    slots[g][t] = page * ps + start % ps
+                t += 1
+                continue
+            tokens[t:t + n] = e.tokens
+            positions[t:t + n] = np.arange(start, start + n, dtype=np.int32)
+            seq_of[t:t + n] = s
             for w in e.want:
                 rows[r] = t + w
                 r += 1
-            for g in range(len(self.group_specs)):
+            for g in range(G):
                 tab = lease.tables[g]
-                if len(tab) > W:
-                    raise ValueError("a request's block table is wider than the staged width")
-                if e.start + n > len(tab) * ps:
-                    raise RuntimeError(f"request {e.request_id!r}: pages for positions up to {e.start + n - 1} were "
+                if start + n > len(tab) * ps:
+                    raise RuntimeError(f"request {e.request_id!r}: pages for positions up to {start + n - 1} were "
                                        f"not reserved in group {g}")
-                tables[g][s, :len(tab)] = tab
                 pos = positions[t:t + n]
                 page_of = np.asarray(tab, dtype=np.int32)[pos // ps]
                 if (page_of < 0).any():
                     raise RuntimeError(f"request {e.request_id!r}: a token of this step has no page in group {g}")
                 slots[g][t:t + n] = page_of * ps + pos % ps
             t += n
+        if entries:
+            idx_rows = np.asarray(mirror_rows, dtype=np.int64)
+            for g in range(G):
+                tables[g][:S, :] = self._tab_mirror[g][idx_rows, :W]
         for s in range(S, S_pad):                             # padding rows of a captured graph
             tokens[t] = 0
             positions[t] = 0

@@ -160,7 +160,8 @@ class Scheduler:
                 kept.append(seq)
                 continue
             yielded = stuck = False
-            while not self.cache.can_reserve(seq.seq_id, len(seq)):
+            covered = self.cache.covered(seq.seq_id, len(seq))     # most decode steps need no new page
+            while not covered and not self.cache.can_reserve(seq.seq_id, len(seq)):
                 if not allow_preempt:
                     stuck = True
                     break
@@ -179,7 +180,8 @@ class Scheduler:
                 continue
             if yielded:
                 continue
-            self.cache.reserve(seq.seq_id, len(seq))
+            if not covered:
+                self.cache.reserve(seq.seq_id, len(seq))
             push(seq, want)
             kept.append(seq)
         self.running = kept
