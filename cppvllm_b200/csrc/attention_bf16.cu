@@ -130,28 +130,33 @@ struct AttnParams {
     float qk_eps;
 };
 
-// Issued by ONE thread: fetch keys [key0, key0 + 64) of one kv head, K then V, into a stage.  `stage` points at
-// the K tile; the V tile follows it.
+// Issued by one WARP: fetch keys [key0, key0 + 64) of one kv head, K then V, into a stage.  `stage` points at the K
+// tile; the V tile follows it.  Each lane issues one TMA box (a page or 64 keys, a 64-column half, K or V), so the
+// block-table reads of a tile are in flight together.  Lane 0 waits for the stage to be free (`empty`, unless null) and
+// arms the barrier before anyone copies.
 template <int HD>
-__device__ __forceinline__ void tma_issue_tile(__nv_bfloat16* stage, uint64_t* bar, const CUtensorMap* map,
-                                               const AttnParams& p, const int* table, int kvh, int key0,
-                                               int key_lo, int key_hi) {
+__device__ __forceinline__ void tma_issue_tile(__nv_bfloat16* stage, uint64_t* bar, uint64_t* empty, uint32_t empty_parity,
+                                               const CUtensorMap* map, const AttnParams& p, const int* table, int kvh,
+                                               int key0, int key_lo, int key_hi, int lane) {
     constexpr int kTileElems = kBN * HD;
-    mbar_expect_tx(bar, 2u * kTileElems * sizeof(__nv_bfloat16));
-    for (int b0 = 0; b0 < kBN; b0 += p.box_rows) {
-        int key = min(max(key0 + b0, key_lo), key_hi);            // outside the range: the nearest key inside it
-        key -= key % p.box_rows;                                  // boxes start on multiples of their size
+    const int per_kv = (kBN / p.box_rows) * (HD / 64);            // boxes of K (and of V) in a tile: 1 to 8
+    const int which = lane / per_kv;                              // 0: K, 1: V, above: idle lanes
+    const int box = (lane % per_kv) / (HD / 64), half = lane % (HD / 64);
+    int row = 0;
+    if (which < 2) {
+        int key = min(max(key0 + box * p.box_rows, key_lo), key_hi);   // outside the range: the nearest key inside it
+        key -= key % p.box_rows;                                      // boxes start on multiples of their size
         const int slot = key / p.page_size;
         int page = slot < p.table_width ? table[slot] : -1;
         if (page < 0 || page >= p.num_pages) { atomicExch(p.err, 4); page = 0; }
-        const int row_k = ((page * 2 + 0) * p.KV + kvh) * p.page_size + key % p.page_size;
-        const int row_v = row_k + p.KV * p.page_size;
-#pragma unroll
-        for (int half = 0; half < HD / 64; ++half) {
-            tma_load_2d(stage + half * 4096 + b0 * 64, map, bar, half * 64, row_k);
-            tma_load_2d(stage + kTileElems + half * 4096 + b0 * 64, map, bar, half * 64, row_v);
-        }
+        row = ((page * 2 + which) * p.KV + kvh) * p.page_size + key % p.page_size;
     }
+    if (lane == 0) {
+        if (empty != nullptr) mbar_wait(empty, empty_parity, p.err);
+        mbar_expect_tx(bar, 2u * kTileElems * sizeof(__nv_bfloat16));
+    }
+    __syncwarp();
+    if (which < 2) tma_load_2d(stage + which * kTileElems + half * 4096 + box * p.box_rows * 64, map, bar, half * 64, row);
 }
 
 // One warp: S[16 x NT*8] = Q[16 x HD] * K^T over NT/2 groups of 16 keys starting at tile row `krow0`.
@@ -329,13 +334,10 @@ attn_prefill_bf16_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnP
     __syncthreads();                                      // barriers are initialised, the query tile is in place
 
     if (warp == kConsumers / 32) {                        // ---- producer warp ----
-        if (lane == 0) {
-            for (int it = 0; it < n_tiles; ++it) {
-                const int st = it % kPreStages;
-                if (it >= kPreStages) mbar_wait(empty + st, ((it / kPreStages) - 1) & 1, p.err);
-                tma_issue_tile<HD>(sm.stages + st * Plan::kStageElems, full + st, &kv_map, p, table, kvh,
-                                   (tile_begin + it) * kBN, key_lo, key_hi);
-            }
+        for (int it = 0; it < n_tiles; ++it) {
+            const int st = it % kPreStages;
+            tma_issue_tile<HD>(sm.stages + st * Plan::kStageElems, full + st, it >= kPreStages ? empty + st : nullptr,
+                               ((it / kPreStages) - 1) & 1, &kv_map, p, table, kvh, (tile_begin + it) * kBN, key_lo, key_hi, lane);
         }
         return;
     }
@@ -466,13 +468,10 @@ attn_decode_bf16_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnPa
             }
             __syncwarp();
             asm volatile("bar.arrive 1, %0;\n" ::"n"(kThreads) : "memory");
-            if (lane == 0) {
-                for (int it = 0; it < n_tiles; ++it) {
-                    const int st = it % kDecStages;
-                    if (it >= kDecStages) mbar_wait(empty + st, ((it / kDecStages) - 1) & 1, p.err);
-                    tma_issue_tile<HD>(sm.stages + st * Plan::kStageElems, full + st, &kv_map, p, table, kvh,
-                                       (tile_begin + it) * kBN, key_lo, key_hi);
-                }
+            for (int it = 0; it < n_tiles; ++it) {
+                const int st = it % kDecStages;
+                tma_issue_tile<HD>(sm.stages + st * Plan::kStageElems, full + st, it >= kDecStages ? empty + st : nullptr,
+                                   ((it / kDecStages) - 1) & 1, &kv_map, p, table, kvh, (tile_begin + it) * kBN, key_lo, key_hi, lane);
             }
         } else {                                                           // ---- consumer warps ----
             if (p.qkv == nullptr) {
