@@ -1,0 +1,196 @@
+"""Parts that this architecture does not have, defined and registered here, in the test, and run through the
+framework's model, cache and step function as they are: a feed-forward that routes every token to one of a few
+small experts, and a position encoding with scaled positions.  They stand for what another architecture would bring;
+they are toys and no model of anyone's."""
+import json
+import os
+
+import pytest
+import torch
+
+import plain_qwen3 as plain
+import tiny_models
+
+pytestmark = pytest.mark.gpu
+
+
+def test_a_toy_feed_forward_with_routing_can_be_registered_built_and_stepped(tmp_path):
+    """Top-1 routing over four experts: router logits and their softmax in float32, the token goes to the expert with
+    the largest logit and its output is scaled by that expert's probability.  The part names its tensors per expert,
+    the loader checks them, the random-weights writer fills them; the model's other parts are the framework's own.
+    Steps that cut the sequence anywhere and put another request beside it must give what one whole step gives, and
+    the part alone must give what a loop over tokens gives."""
+    from cppvllm_b200.config.registry import register_architecture, unregister_architecture
+    from cppvllm_b200.engine.runner import ModelRunner, StepEntry
+    from cppvllm_b200.parts.base import FeedForward, WeightSpec, register_part, unregister_part
+    from cppvllm_b200.parts.spec import LayerSpec, ModelSpec, PartSpec
+    from cppvllm_b200.weights.random_init import write_random_model
+    from cppvllm_b200.weights.safetensors_io import SafetensorsFile
+
+    class RoutedFFN(FeedForward):
+        def __init__(self, runtime, prefix="", names=None, *, hidden_size, expert_size, num_experts):
+            super().__init__(runtime, prefix, names)
+            self.D, self.I, self.E = hidden_size, expert_size, num_experts
+            self.router = self.w_in = self.w_out = None
+
+        def weight_specs(self):
+            specs = {self.full_name("router.weight"): WeightSpec((self.E, self.D))}
+            for e in range(self.E):
+                specs[self.full_name(f"experts.{e}.in.weight")] = WeightSpec((self.I, self.D))
+                specs[self.full_name(f"experts.{e}.out.weight")] = WeightSpec((self.D, self.I))
+            return specs
+
+        def bind(self, tensors):
+            self.router = tensors[self.full_name("router.weight")].float()
+            self.w_in = torch.stack([tensors[self.full_name(f"experts.{e}.in.weight")] for e in range(self.E)]).float()
+            self.w_out = torch.stack([tensors[self.full_name(f"experts.{e}.out.weight")] for e in range(self.E)]).float()
+
+        def forward(self, x, ctx):
+            xf = x.float()
+            prob = torch.softmax(xf @ self.router.t(), dim=-1)                  # router logits and softmax in float32
+            gate, expert = prob.max(dim=-1)
+            out = torch.zeros_like(xf)
+            for e in range(self.E):                                              # tokens of one expert run together
+                rows = (expert == e).nonzero().flatten()
+                if rows.numel():
+                    out[rows] = torch.relu(xf[rows] @ self.w_in[e].t()) @ self.w_out[e].t() * gate[rows, None]
+            return out.to(x.dtype)
+
+    def build(cfg):
+        D, V, H, KV, hd = cfg["hidden_size"], cfg["vocab_size"], cfg["heads"], cfg["kv_heads"], cfg["head_dim"]
+        layers = [LayerSpec(
+            mixer=PartSpec("paged_attention", dict(hidden_size=D, num_heads=H, num_kv_heads=KV, head_dim=hd, qk_norm=True,
+                                                   qk_norm_eps=1e-6, position="rope"), prefix=f"toy.layers.{i}.attn."),
+            ffn=PartSpec("routed_toy", dict(hidden_size=D, expert_size=cfg["expert_size"], num_experts=cfg["num_experts"]),
+                         prefix=f"toy.layers.{i}.moe."),
+            mixer_norm=PartSpec("rmsnorm", dict(size=D, eps=1e-6), prefix=f"toy.layers.{i}.norm1."),
+            ffn_norm=PartSpec("rmsnorm", dict(size=D, eps=1e-6), prefix=f"toy.layers.{i}.norm2.")) for i in range(cfg["num_layers"])]
+        return ModelSpec("ToyRoutedForCausalLM", D, V,
+                         embedding=PartSpec("token_embedding", dict(vocab_size=V, hidden_size=D), prefix="toy.embed."),
+                         layers=layers, final_norm=PartSpec("rmsnorm", dict(size=D, eps=1e-6, buffer="head_normed"), prefix="toy.norm."),
+                         lm_head=PartSpec("lm_head", dict(vocab_size=V, hidden_size=D), prefix="toy.head."),
+                         positions={"rope": PartSpec("rotary", dict(rotary_dim=hd, theta=10000.0, max_positions=256, pairing="half"))},
+                         max_positions=256)
+
+    register_part("ffn", "routed_toy", RoutedFFN)
+    register_architecture("ToyRoutedForCausalLM", dict, build)
+    try:
+        cfg = dict(architectures=["ToyRoutedForCausalLM"], hidden_size=48, vocab_size=90, heads=4, kv_heads=2, head_dim=16,
+                   expert_size=40, num_experts=4, num_layers=2)
+        d = write_random_model(str(tmp_path / "toy"), cfg, seed=5, std=0.3, store_dtype=torch.float32)
+        names = SafetensorsFile(os.path.join(d, "model.safetensors")).names()
+        assert "toy.layers.1.moe.experts.3.out.weight" in names and "toy.layers.0.moe.router.weight" in names
+
+        def runner():
+            return ModelRunner(d, dtype=torch.float32, page_size=16, num_pages=12, max_step_tokens=64, max_seqs=4, max_model_len=128)
+
+        toks = {"a": tiny_models.random_tokens(90, 50, 1), "b": tiny_models.random_tokens(90, 21, 2)}
+
+        def whole(rid):
+            rr = runner()
+            rr.cache.admit(rid)
+            rr.cache.reserve(rid, len(toks[rid]))
+            return rr.step([StepEntry(rid, toks[rid], 0, list(range(len(toks[rid]))))]).cpu().clone()
+
+        ref = {k: whole(k) for k in toks}
+        r = runner()
+        got, fed = {k: [] for k in toks}, {k: 0 for k in toks}
+        for step in ([("a", 9), ("b", 2)], [("a", 1), ("b", 13)], [("a", 30)], [("b", 6), ("a", 2)], [("a", 8)]):
+            entries = []
+            for rid, n in step:
+                if rid not in r.cache.leases:
+                    r.cache.admit(rid)
+                r.cache.reserve(rid, fed[rid] + n)
+                entries.append(StepEntry(rid, toks[rid][fed[rid]:fed[rid] + n], fed[rid], list(range(n))))
+            out = r.step(entries).cpu()
+            o = 0
+            for rid, n in step:
+                got[rid].append(out[o:o + n].clone())
+                o += n
+                fed[rid] += n
+        r.check_errors()
+        for k in toks:
+            g = torch.cat(got[k])
+            assert g.shape == ref[k].shape
+            assert (g - ref[k]).abs().max() < 1e-4 * max(1.0, ref[k].abs().max())
+
+        # the part alone against a loop over tokens; and the router does send tokens to different experts
+        ffn = r.model.blocks[0].ffn
+        x = torch.randn(23, 48, device=r.device)
+        y = ffn.forward(x, None).cpu()
+        used = set()
+        for t in range(23):
+            xt = x[t].cpu().float()
+            prob = torch.softmax(xt @ ffn.router.cpu().t(), dim=-1)
+            e = int(prob.argmax())
+            used.add(e)
+            want = torch.relu(xt @ ffn.w_in[e].cpu().t()) @ ffn.w_out[e].cpu().t() * prob[e]
+            assert (y[t] - want).abs().max() < 1e-4 * max(1.0, float(want.abs().max()))
+        assert len(used) >= 2
+    finally:
+        unregister_part("ffn", "routed_toy")
+        unregister_architecture("ToyRoutedForCausalLM")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_a_toy_position_encoding_can_be_registered_and_used(model_dirs, dtype, monkeypatch):
+    """Rotary tables whose positions are divided by four (positions 0..3 share an angle), as a part of its own kind:
+    tiny_c's weights, the framework's attention reading this part's tables.  The plain implementation with the same
+    tables gives the reference; with the architecture's own tables the logits differ."""
+    from cppvllm_b200.config.model_config import Qwen3Config
+    from cppvllm_b200.config.registry import register_architecture, unregister_architecture
+    from cppvllm_b200.engine.runner import ModelRunner, StepEntry
+    from cppvllm_b200.models.qwen3 import build_qwen3_spec
+    from cppvllm_b200.parts.base import PositionEncoding, register_part, unregister_part
+    from cppvllm_b200.parts.spec import PartSpec
+
+    FACTOR = 4.0
+
+    def scaled_tables(hd, theta, max_pos):
+        idx = torch.arange(0, hd, 2, dtype=torch.float64)
+        inv_freq = torch.pow(torch.tensor(theta, dtype=torch.float64), idx / hd).reciprocal()
+        angle = torch.outer(torch.arange(max_pos, dtype=torch.float64) / FACTOR, inv_freq)
+        return angle.cos().float(), angle.sin().float()
+
+    class ScaledRotary(PositionEncoding):
+        def __init__(self, runtime, prefix="", names=None, *, rotary_dim, theta, max_positions):
+            super().__init__(runtime, prefix, names)
+            self.rotary_dim, self.interleaved = rotary_dim, False
+            cos, sin = scaled_tables(rotary_dim, theta, max_positions)
+            self.cos, self.sin = cos.contiguous().to(runtime.device), sin.contiguous().to(runtime.device)
+
+    def build(cfg):
+        spec = build_qwen3_spec(cfg)
+        spec.positions = {"rope": PartSpec("scaled_rotary_toy", dict(rotary_dim=cfg.head_dim, theta=cfg.rope_theta,
+                                                                      max_positions=cfg.max_position_embeddings))}
+        return spec
+
+    register_part("position", "scaled_rotary_toy", ScaledRotary)
+    register_architecture("ToyScaledRopeForCausalLM", Qwen3Config.from_dict, build)
+    try:
+        name = "tiny_c"
+        d = model_dirs[name] + "_toy_scaled_rope"
+        os.makedirs(d, exist_ok=True)
+        json.dump(dict(tiny_models.config(name), architectures=["ToyScaledRopeForCausalLM"]), open(os.path.join(d, "config.json"), "w"))
+        if not os.path.exists(os.path.join(d, "model.safetensors")):
+            os.symlink(os.path.join(model_dirs[name], "model.safetensors"), os.path.join(d, "model.safetensors"))
+        act = "float32" if dtype == torch.float32 else "bfloat16"
+        toks = tiny_models.random_tokens(tiny_models.config(name)["vocab_size"], 90, 12)
+        own = plain.forward(model_dirs[name], toks, act)
+        monkeypatch.setattr(plain, "rope_tables", scaled_tables)
+        ref = plain.forward(model_dirs[name], toks, act)
+        assert (own - ref).abs().max() > 1e-2                      # the encoding matters
+        r = ModelRunner(d, dtype=dtype, page_size=16, num_pages=12, max_step_tokens=128, max_seqs=4, max_model_len=256)
+        r.cache.admit("a")
+        got, pos = [], 0
+        for n in (50, 3, 1, 1, 35):                                # a portion, a short one, decoded tokens, the rest
+            r.cache.reserve("a", pos + n)
+            got.append(r.step([StepEntry("a", toks[pos:pos + n], pos, list(range(n)))]).float().cpu().clone())
+            pos += n
+        r.check_errors()
+        got = torch.cat(got)
+        tol = 1e-5 if dtype == torch.float32 else 2e-2
+        assert (got - ref).abs().max() <= tol * max(1.0, float(ref.abs().max()))
+    finally:
+        unregister_part("position", "scaled_rotary_toy")
+        unregister_architecture("ToyScaledRopeForCausalLM")
