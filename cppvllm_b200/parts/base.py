@@ -93,8 +93,12 @@ class Workspace:
         self.max_tokens = max_tokens
         self.max_seqs = max_seqs or max_tokens
         self._buffers: Dict[str, torch.Tensor] = {}
+        self._views: Dict[tuple, torch.Tensor] = {}
 
     def rows(self, name: str, n_rows: int, width, dtype: torch.dtype) -> torch.Tensor:
+        hit = self._views.get((name, n_rows, width, dtype))       # the same view object for the same request
+        if hit is not None:
+            return hit
         widths = tuple(width) if isinstance(width, (tuple, list)) else (width,)
         key = f"{name}|{widths}|{dtype}"
         buf = self._buffers.get(key)
@@ -103,7 +107,12 @@ class Workspace:
             self._buffers[key] = buf
         if n_rows > self.max_tokens:
             raise ValueError(f"a step of {n_rows} tokens exceeds the workspace of {self.max_tokens}")
-        return buf[:n_rows]
+        view = buf[:n_rows]
+        if not isinstance(width, list):
+            if len(self._views) > 4096:
+                self._views.clear()
+            self._views[(name, n_rows, width, dtype)] = view
+        return view
 
     def flat(self, name: str, numel: int, dtype: torch.dtype, zero: bool = False) -> torch.Tensor:
         """A named scratch buffer of a fixed number of elements (allocated once, at its first use; `zero`: zero-filled)."""
