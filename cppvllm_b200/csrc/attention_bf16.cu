@@ -3,8 +3,11 @@
 //   cvb_attn_prefill_bf16  prompt portions (requests with more than one token in the step): flash attention with a
 //                          causal offset, reading ALL keys (earlier portions' and the step's own) from the pages.
 //   cvb_attn_decode_bf16   single decoded tokens: the key range of every (request, kv head) is cut into `splits`
-//                          chunks that run in parallel; partial (max, sum, output) triples go to scratch memory
-//                          and cvb_attn_decode_merge (launched by the same entry point) combines them.
+//                          chunks that run in parallel.  Up to 16 chunks are the blocks of one thread-block cluster and
+//                          merge their partial (max, sum, output) triples through distributed shared memory; more go
+//                          through scratch memory and cvb_attn_decode_merge (launched by the same entry point).
+//   cvb_attn_decode_fused_bf16  the same from the projection's raw output: the kernel also norms and rotates the
+//                          queries and the new key and writes the new key and value to the cache.
 //
 // Both kernels put the query heads that share a kv head next to each other in the M dimension of the matrix
 // product (row r = token r / g, head kvh * g + r % g), so a key/value tile is loaded once for the whole group.
@@ -18,7 +21,7 @@
 // consumer warps that a tile has landed, "empty" barriers (one arrival per consumer warp) give the stage back.  A box whose keys lie outside
 // the request's range is fetched from the nearest page inside it, so every tile brings the same number of
 // bytes and never touches a page the request does not own; such keys are excluded by the mask.  Waits on the
-// mbarrier are bounded: if one runs out, the block records error 5 and leaves without computing.  The query tile
+// mbarrier are bounded: if one runs out, the block records error 5 and carries on to its end.  The query tile
 // comes by cp.async.  The matrix products are mma.sync.m16n8k16 (bf16 in, float accumulate); ldmatrix reads the
 // swizzled tiles without bank conflicts.
 #include "common.cuh"

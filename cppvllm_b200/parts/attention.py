@@ -7,7 +7,8 @@ rotary position encoding (reference model/model_architecture.cpp:155-178):
     y = att Wo^T
 
 Prompt portions and decoded tokens run through the same code: every token attends to its request's pages,
-which already hold the step's own keys.  All sizes are parameters; `scale` defaults to 1/sqrt(head_dim)
+which already hold the step's own keys.  A step of decoded tokens only takes a shorter way through the same
+arithmetic: one kernel norms, rotates, writes the cache and attends (`fuse_decode_attention`).  All sizes are parameters; `scale` defaults to 1/sqrt(head_dim)
 (model_architecture.cpp:134).  The part does not know how many layers exist or which model it serves.
 """
 from __future__ import annotations
