@@ -27,6 +27,7 @@ def _engine_flags(p: argparse.ArgumentParser, util: float) -> None:
     p.add_argument("--block-size", type=int, default=32)
     p.add_argument("--enforce-eager", action="store_true")
     p.add_argument("--enable-prefix-caching", action="store_true")
+    p.add_argument("--use-ref-kernels", action="store_true")
     p.add_argument("--seed", type=int, default=0)
 
 
@@ -38,7 +39,7 @@ def _engine(args):
         max_num_seqs=args.max_num_seqs, max_chunk_tokens=args.max_chunk_tokens, max_model_len=args.max_model_len,
         gpu_memory_utilization=args.gpu_memory_utilization, num_kv_blocks=args.num_kv_blocks,
         block_size=args.block_size, enforce_eager=args.enforce_eager, enable_prefix_caching=args.enable_prefix_caching,
-        seed=args.seed))
+        use_ref_kernels=args.use_ref_kernels, seed=args.seed))
 
 
 def example_main(argv=None) -> int:

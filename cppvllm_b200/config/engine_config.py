@@ -7,7 +7,9 @@ Added here: ``block_size`` (tokens per cache page; the reference fixes 16 in seq
 because a TMA box is one page of one head and boxes of 32 rows reach the full HBM rate where boxes of 16 reach 3/4)
 ``pipeline_depth`` (steps in flight: 2 as the reference's ``kDepth``, engine/llm_engine.h:51, or 1 to wait for
 every step's samples before the next step is scheduled) and ``enable_prefix_caching`` (requests share the cache pages
-of a common prefix; always on in the reference, engine/block_manager.cpp:71-143; off by default here).
+of a common prefix; always on in the reference, engine/block_manager.cpp:71-143; off by default here) and
+``use_ref_kernels`` (every part uses its plain twin kernels: the general attention kernel, library products with separate
+norm and activation kernels; for comparing the fast kernels with, inside the whole engine).
 """
 from __future__ import annotations
 
@@ -48,6 +50,7 @@ class EngineConfig:
     block_size: int = 32
     pipeline_depth: int = 2
     enable_prefix_caching: bool = False
+    use_ref_kernels: bool = False
     device: str = "cuda:0"
 
     def __post_init__(self):

@@ -62,7 +62,7 @@ class ModelRunner:
     def __init__(self, model_dir: str, dtype=torch.bfloat16, device="cuda:0", page_size: int = 32,
                  num_pages: Optional[int] = None, max_step_tokens: int = 4096, max_seqs: int = 256,
                  max_model_len: int = 4096, gpu_memory_utilization: float = 0.90, enforce_eager: bool = False,
-                 num_state_slots: Optional[int] = None, enable_prefix_caching: bool = False):
+                 num_state_slots: Optional[int] = None, enable_prefix_caching: bool = False, use_ref_kernels: bool = False):
         if not torch.cuda.is_available():
             raise RuntimeError("cppvllm_b200 runs on a CUDA device only; torch.cuda.is_available() is False")
         self.device = torch.device(device)
@@ -81,7 +81,7 @@ class ModelRunner:
         spec = self.arch.build_spec(self.config)
         self.max_model_len = int(min(max_model_len, spec.max_positions) if spec.max_positions else max_model_len)
         self.workspace = Workspace(self.device, self.max_step_tokens, self.max_seqs)
-        self.rt = Runtime(self.device, dtype, self.workspace)
+        self.rt = Runtime(self.device, dtype, self.workspace, plain_kernels=bool(use_ref_kernels))
         self.model = CausalLM(spec, self.rt)
         self.model.bind(load_weights(self.model, model_dir, self.device, dtype))
         self.vocab_size = self.model.vocab_size

@@ -36,6 +36,7 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--block-size", type=int, default=32, help="tokens per cache page (must divide 64)")
     p.add_argument("--max-num-seqs", type=int, default=16, help="most requests in one step")
     p.add_argument("--enforce-eager", action="store_true", help="never replay CUDA graphs for decode-only steps")
+    p.add_argument("--use-ref-kernels", action="store_true", help="plain twin kernels only (general attention, library products)")
     return p
 
 
@@ -57,7 +58,7 @@ def main(argv=None) -> int:
     runner = ModelRunner(args.model, dtype=parse_dtype(args.dtype), device="cuda:0", page_size=ps,
                          num_pages=num_pages, max_step_tokens=max(64, min(args.max_tokens, 32768)),
                          max_seqs=args.max_num_seqs, max_model_len=max(64, args.max_tokens),
-                         enforce_eager=args.enforce_eager)
+                         enforce_eager=args.enforce_eager, use_ref_kernels=args.use_ref_kernels)
     for line in sys.stdin:
         line = line.strip()
         if not line:

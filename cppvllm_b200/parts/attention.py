@@ -34,7 +34,7 @@ class PagedAttention(Mixer):
         self.hidden_size, self.num_heads, self.num_kv_heads, self.head_dim = map(int, (hidden_size, num_heads, num_kv_heads, head_dim))
         self.qk_norm, self.qk_norm_eps, self.window = bool(qk_norm), float(qk_norm_eps), int(window)
         self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(self.head_dim)
-        self.force_general = bool(force_general)     # always use the general kernel (tests compare the two)
+        self.force_general = bool(force_general) or runtime.plain_kernels   # always use the general kernel
         if prefill_kernel not in ("tcgen05", "mma"):
             raise ValueError("prefill_kernel must be 'tcgen05' or 'mma'")
         self.prefill_kernel = prefill_kernel         # which tensor-core kernel runs prompt portions
@@ -85,13 +85,13 @@ class PagedAttention(Mixer):
     def forward(self, x, ctx, cache, state):
         T = x.shape[0]
         H, KV, hd = self.num_heads, self.num_kv_heads, self.head_dim
-        qkv = ops.project_rows(x, self.w_qkv, self.rt.workspace.rows("attn_qkv", T, (H + 2 * KV) * hd, x.dtype), T)
+        qkv = self._project(x, self.w_qkv, self.rt.workspace.rows("attn_qkv", T, (H + 2 * KV) * hd, x.dtype), T)
         return self._after_projection(qkv, ctx, cache)
 
     def can_fuse_norm(self, norm, ctx) -> bool:
         """A step of a few tokens can take the preceding RMSNorm (and the residual add before it) into the
         projection's weight-streaming kernel."""
-        return (getattr(norm, "weight", None) is not None and hasattr(norm, "eps")
+        return (not self.rt.plain_kernels and getattr(norm, "weight", None) is not None and hasattr(norm, "eps")
                 and ops.gemv_supported(self.rt.dtype, self.w_qkv, ctx.num_tokens)
                 and not ops.gemv_splitk_preferred(self.rt.dtype, self.w_qkv, ctx.num_tokens)
                 and ops.gemv_supported(self.rt.dtype, self.w_o, ctx.num_tokens))
@@ -112,7 +112,7 @@ class PagedAttention(Mixer):
     # ---- decode steps: norm + projection + rotary + cache write in one persistent kernel ----
     def can_fuse_decode_head(self, norm, ctx, cache) -> bool:
         pos = self.position
-        return (cache is not None and cache.writes and getattr(norm, "weight", None) is not None and hasattr(norm, "eps")
+        return (not self.rt.plain_kernels and cache is not None and cache.writes and getattr(norm, "weight", None) is not None and hasattr(norm, "eps")
                 and self.w_qkv.dtype == torch.bfloat16 and self.w_o.dtype == torch.bfloat16
                 and (pos is None or (pos.rotary_dim == self.head_dim and not pos.interleaved))
                 and ops.decode_fusion_supported(self.rt.dtype, ctx.num_tokens, (self.hidden_size,), self.head_dim))
@@ -167,7 +167,10 @@ class PagedAttention(Mixer):
                 rotary_dim=pos.rotary_dim if pos is not None else 0,
                 interleaved=pos.interleaved if pos is not None else False)
             self.attend(att, q, ctx, cache, g)
-        return ops.project_rows(att, self.w_o, ws.rows("attn_proj", T, self.hidden_size, x.dtype), T)
+        return self._project(att, self.w_o, ws.rows("attn_proj", T, self.hidden_size, x.dtype), T)
+
+    def _project(self, x, w, out, rows):
+        return ops.linear(x, w, out=out) if self.rt.plain_kernels else ops.project_rows(x, w, out, rows)
 
     def _decode_from_projection(self, ctx, cache, g) -> bool:
         pos = self.position

@@ -128,10 +128,14 @@ class Workspace:
 
 @dataclass
 class Runtime:
-    """What parts are built against: the device, the activation element type and the shared workspace."""
+    """What parts are built against: the device, the activation element type and the shared workspace.
+    `plain_kernels`: parts use their plain twin kernels only (the general attention kernel, library products with
+    separate norm and activation kernels; no tensor-core attention, no weight-streaming products, no fusions): the
+    path to compare the fast kernels with, inside the whole engine."""
     device: torch.device
     dtype: torch.dtype
     workspace: Workspace
+    plain_kernels: bool = False
 
 
 class Part:

@@ -39,15 +39,18 @@ class SwiGLUMLP(FeedForward):
     def forward(self, x, ctx):
         T = x.shape[0]
         ws = self.rt.workspace
-        gu = ops.project_rows(x, self.w_gate_up, ws.rows("ffn_gate_up", T, 2 * self.intermediate_size, x.dtype), T)
+        gu = self._project(x, self.w_gate_up, ws.rows("ffn_gate_up", T, 2 * self.intermediate_size, x.dtype), T)
         act = ops.swiglu(ws.rows("ffn_act", T, self.intermediate_size, x.dtype), gu)
         return self._down(act, T)
 
     def _down(self, act, T):
-        return ops.project_rows(act, self.w_down, self.rt.workspace.rows("ffn_out", T, self.hidden_size, act.dtype), T)
+        return self._project(act, self.w_down, self.rt.workspace.rows("ffn_out", T, self.hidden_size, act.dtype), T)
+
+    def _project(self, x, w, out, rows):
+        return ops.linear(x, w, out=out) if self.rt.plain_kernels else ops.project_rows(x, w, out, rows)
 
     def can_fuse_norm(self, norm, ctx) -> bool:
-        return (getattr(norm, "weight", None) is not None and hasattr(norm, "eps")
+        return (not self.rt.plain_kernels and getattr(norm, "weight", None) is not None and hasattr(norm, "eps")
                 and ops.gemv_supported(self.rt.dtype, self.w_gate_up, ctx.num_tokens)
                 and not ops.gemv_splitk_preferred(self.rt.dtype, self.w_gate_up, ctx.num_tokens)
                 and ops.gemv_supported(self.rt.dtype, self.w_down, ctx.num_tokens))

@@ -122,6 +122,49 @@ def test_requests_that_share_a_prefix_read_the_same_pages_and_generate_the_same_
                 assert row[tok] >= row.max() - 0.02 * max(1.0, float(row.abs().max()))
 
 
+def test_plain_twin_kernels_give_the_same_logits_as_the_fast_ones(model_dirs):
+    """use_ref_kernels: the general attention kernel and library products with separate norm and activation kernels, in
+    place of the tensor-core attention kernels, the weight-streaming products and the fusions.  Same steps (a prompt
+    portion, short portions, decoded tokens of two requests), bfloat16: the logits agree to rounding, and both agree
+    with the plain implementation."""
+    from cppvllm_b200.csrc import ops
+    from cppvllm_b200.engine.runner import ModelRunner, StepEntry
+    name = "tiny_c"
+    d = model_dirs[name]
+    vocab = tiny_models.config(name)["vocab_size"]
+    a, b = tiny_models.random_tokens(vocab, 100, 3), tiny_models.random_tokens(vocab, 40, 4)
+    ref = {"a": plain.forward(d, a, "bfloat16"), "b": plain.forward(d, b, "bfloat16")}
+    plan = [[("a", 70)], [("a", 5), ("b", 30)], [("a", 1), ("b", 1)], [("a", 1), ("b", 1)], [("b", 8)], [("a", 23)]]
+    rows = {}
+    for twin in (False, True):
+        r = ModelRunner(d, dtype=torch.bfloat16, page_size=16, num_pages=24, max_step_tokens=128, max_seqs=4,
+                        max_model_len=256, use_ref_kernels=twin)
+        before = ops.launches()
+        pos, seqs, got = {"a": 0, "b": 0}, {"a": a, "b": b}, []
+        for rid in pos:
+            r.cache.admit(rid)
+        for step in plan:
+            entries = []
+            for rid, n in step:
+                r.cache.reserve(rid, pos[rid] + n)
+                entries.append(StepEntry(rid, seqs[rid][pos[rid]:pos[rid] + n], pos[rid], list(range(n))))
+            out = r.step(entries).float().cpu().clone()
+            k = 0
+            for rid, n in step:
+                for w in range(n):
+                    got.append((rid, pos[rid] + w, out[k]))
+                    k += 1
+                pos[rid] += n
+        r.check_errors()
+        rows[twin] = got
+        assert ops.launches() > before
+    for (rid, p_, fast), (_, _, twin) in zip(rows[False], rows[True]):
+        want = ref[rid][p_]
+        scale = max(1.0, float(want.abs().max()))
+        assert (fast - want).abs().max() <= 2e-2 * scale and (twin - want).abs().max() <= 2e-2 * scale
+        assert (fast - twin).abs().max() <= 2e-2 * scale
+
+
 def test_overlapped_and_step_by_step_engines_generate_the_same_tokens(model_dirs):
     """pipeline_depth 2 schedules step n + 1 before the samples of step n are read back (the tokens travel on the
     device); depth 1 waits for every step.  Same tokens, greedy and sampled, also when pages run out."""
