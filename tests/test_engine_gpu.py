@@ -72,12 +72,14 @@ def test_temperature_sampling_is_reproducible_and_independent_of_batching(model_
     assert greedy[1].token_ids != together[1].token_ids            # temperature 0.7 really samples
 
 
-def test_pages_run_out_requests_are_preempted_recomputed_and_still_right(model_dirs):
+@pytest.mark.parametrize("prefix_cache", [False, True])
+def test_pages_run_out_requests_are_preempted_recomputed_and_still_right(model_dirs, prefix_cache):
+    """With the prefix cache a preempted request may find its first pages again and recompute less; the tokens are the same."""
     from cppvllm_b200 import SamplingParams
     d = model_dirs["tiny_a"]
     prompts = [tiny_models.random_tokens(256, n, 80 + n) for n in (30, 31, 29, 12)]
     sp = SamplingParams(temperature=0.0, max_tokens=20, ignore_eos=True)
-    llm = engine(d, "tiny_a", num_kv_blocks=7)                      # 112 tokens for four requests of up to 51
+    llm = engine(d, "tiny_a", num_kv_blocks=7, enable_prefix_caching=prefix_cache)   # 112 tokens for four requests of up to 51
     outs = llm.generate(prompts, sp)
     assert llm.stats().preemptions > 0
     for p, o in zip(prompts, outs):
