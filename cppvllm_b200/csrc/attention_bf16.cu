@@ -24,10 +24,9 @@
 // mbarrier are bounded: if one runs out, the block records error 5 and carries on to its end.  The query tile
 // comes by cp.async.  The matrix products are mma.sync.m16n8k16 (bf16 in, float accumulate); ldmatrix reads the
 // swizzled tiles without bank conflicts.
-#include "common.cuh"
+#include "sm100.cuh"
 #include "attention_bf16.h"
 
-#include <cuda.h>
 #include <mutex>
 #include <unordered_map>
 
@@ -37,15 +36,6 @@ constexpr int kBN = 64;                 // keys per tile
 constexpr int kConsumers = 128;         // 4 warps that compute
 constexpr int kThreads = kConsumers + 32; // plus one warp that issues the TMA copies
 constexpr float kLog2e = 1.4426950408889634f;
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
-
-__device__ __forceinline__ void cp_async16(void* smem, const void* gmem, bool valid) {
-    const int n = valid ? 16 : 0;       // src-size 0: nothing is read, the 16 bytes are zero-filled
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(smem_u32(smem)), "l"(gmem), "r"(n));
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
-template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
 
 __device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], const void* p) {
     asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
@@ -71,38 +61,6 @@ template <int HD> __device__ __forceinline__ int swz(int r, int c) { return r * 
 // element offset of chunk `c` of key row `r` in a key/value tile as TMA lays it out: HD/64 halves of
 // [64 rows][64 columns], each 128-byte row with its 16-byte chunks XOR-ed by (row & 7) (the 128-byte swizzle)
 __device__ __forceinline__ int kv_off(int r, int c) { return ((c >> 3) << 12) + (r << 6) + (((c & 7) ^ (r & 7)) << 3); }
-
-// ---- mbarrier and TMA ------------------------------------------------------------------------------------
-__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%1], %0;\n" ::"r"(count), "r"(smem_u32(bar)));
-}
-__device__ __forceinline__ void mbar_fence_init() { asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory"); }
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%1], %0;\n" ::"r"(bytes), "r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile("{\n.reg .pred P1;\nmbarrier.try_wait.parity.shared::cta.b64 P1, [%1], %2;\nselp.b32 %0, 1, 0, P1;\n}\n"
-                 : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
-    return ok != 0;
-}
-// Bounded wait (about 20 ms of clock cycles): if the barrier does not complete, error 5 is recorded and the
-// caller goes on with whatever the stage holds.  No thread leaves early, so block-wide barriers stay matched
-// and the kernel always ends; the host sees the error flag and discards the step.
-__device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, int* err) {
-    if (mbar_try_wait(bar, parity)) return;
-    const long long t0 = clock64();
-    while (!mbar_try_wait(bar, parity)) {
-        if (clock64() - t0 > 40000000LL) { atomicExch(err, 5); return; }
-    }
-}
-__device__ __forceinline__ void tma_load_2d(void* smem, const CUtensorMap* map, uint64_t* bar, int x, int y) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
-                 ::"r"(smem_u32(smem)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
-}
 
 struct AttnParams {
     __nv_bfloat16* out;                 // [T, H, HD]
@@ -414,19 +372,6 @@ attn_prefill_bf16_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnP
 // ---- decode ----------------------------------------------------------------------------------------------------
 
 constexpr int kDecStages = 3;
-
-// barrier over all threads of the cluster; what they wrote to shared memory before it is visible after it
-__device__ __forceinline__ void cluster_sync() {
-    asm volatile("barrier.cluster.arrive.release.aligned;\nbarrier.cluster.wait.acquire.aligned;\n" ::: "memory");
-}
-// the float at the same shared-memory address in block `rank` of the cluster
-__device__ __forceinline__ float ld_cluster(const float* local, int rank) {
-    uint32_t remote;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(remote) : "r"(smem_u32(local)), "r"(rank));
-    float v;
-    asm volatile("ld.shared::cluster.f32 %0, [%1];\n" : "=f"(v) : "r"(remote) : "memory");
-    return v;
-}
 
 template <int HD>
 __global__ void __launch_bounds__(kThreads)

@@ -24,9 +24,8 @@
 // Buffers are handed over with mbarriers: TMA transaction counts, tcgen05.commit arrivals from the tensor core, and
 // plain arrivals from the softmax threads.  Every wait is bounded by a cycle count; a wait that runs out records
 // error 5 and the block runs on to its end (tensor memory is always given back).
-#include "common.cuh"
+#include "sm100.cuh"
 
-#include <cuda.h>
 #include <mutex>
 #include <unordered_map>
 
@@ -37,86 +36,6 @@ constexpr int kTN = 128;                      // keys per tile
 constexpr int kKStages = 3;
 constexpr int kVStages = 2;
 constexpr float kLog2eF = 1.4426950408889634f;
-
-__device__ __forceinline__ uint32_t saddr(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
-__device__ __forceinline__ void mb_init(uint64_t* bar, int count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%1], %0;\n" ::"r"(count), "r"(saddr(bar)));
-}
-__device__ __forceinline__ void mb_expect_tx(uint64_t* bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%1], %0;\n" ::"r"(bytes), "r"(saddr(bar)) : "memory");
-}
-__device__ __forceinline__ void mb_arrive(uint64_t* bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];\n" ::"r"(saddr(bar)) : "memory");
-}
-__device__ __forceinline__ bool mb_try_wait(uint64_t* bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile("{\n.reg .pred P1;\nmbarrier.try_wait.parity.shared::cta.b64 P1, [%1], %2;\nselp.b32 %0, 1, 0, P1;\n}\n"
-                 : "=r"(ok) : "r"(saddr(bar)), "r"(parity) : "memory");
-    return ok != 0;
-}
-__device__ __forceinline__ void mb_wait(uint64_t* bar, uint32_t parity, int* err) {
-    if (mb_try_wait(bar, parity)) return;
-    const long long t0 = clock64();
-    while (!mb_try_wait(bar, parity)) {
-        if (clock64() - t0 > 40000000LL) { atomicExch(err, 5); return; }
-    }
-}
-__device__ __forceinline__ void tma_2d(void* smem, const CUtensorMap* map, uint64_t* bar, int x, int y) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
-                 ::"r"(saddr(smem)), "l"(reinterpret_cast<uint64_t>(map)), "r"(saddr(bar)), "r"(x), "r"(y) : "memory");
-}
-__device__ __forceinline__ void cpa16(void* smem, const void* gmem, bool valid) {
-    const int n = valid ? 16 : 0;
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;\n" ::"r"(saddr(smem)), "l"(gmem), "r"(n));
-}
-
-// Shared-memory matrix descriptors, 128-byte swizzle, rows of 128 bytes in 1024-byte atoms of 8 rows.
-//   K-major operand ([rows][64 elements] per half): stride byte offset 1024 between 8-row groups.
-//   MN-major operand (V: [keys][64 head elements] per half): the 64 contiguous elements run along N, keys along K;
-//   stride byte offset 1024 between groups of 8 keys, leading byte offset = distance between the 64-column halves.
-__device__ __forceinline__ uint64_t desc_sw128(uint32_t addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
-    uint64_t d = 0;
-    d |= static_cast<uint64_t>((addr >> 4) & 0x3FFF);
-    d |= static_cast<uint64_t>((lbo_bytes >> 4) & 0x3FFF) << 16;
-    d |= static_cast<uint64_t>((sbo_bytes >> 4) & 0x3FFF) << 32;
-    d |= static_cast<uint64_t>(1) << 46;
-    d |= static_cast<uint64_t>(2) << 61;
-    return d;
-}
-__host__ __device__ constexpr uint32_t idesc_bf16(int m, int n, bool b_mn_major) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | (b_mn_major ? (1u << 16) : 0u) | (static_cast<uint32_t>(n >> 3) << 17) |
-           (static_cast<uint32_t>(m >> 4) << 24);
-}
-__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
-                 ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void commit_to(uint64_t* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(saddr(bar)) : "memory");
-}
-__device__ __forceinline__ void tm_load32(uint32_t taddr, uint32_t (&v)[32]) {
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
-                 "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
-                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
-                   "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
-                   "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
-                   "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-                 : "r"(taddr));
-}
-__device__ __forceinline__ void tm_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
-__device__ __forceinline__ void tc_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
-__device__ __forceinline__ void tc_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
-__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;\n" ::: "memory"); }
-__device__ __forceinline__ float max3(float a, float b, float c) {
-    float d;
-    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
-    return d;
-}
-__device__ __forceinline__ float ex2(float x) {
-    float y;
-    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
-    return y;
-}
 
 // element offset of 16-byte chunk c of row r in a [128 rows][HD] tile stored as HD/64 halves of [128][64], swizzled
 __device__ __forceinline__ int tile_off(int r, int c) { return ((c >> 3) << 13) + (r << 6) + (((c & 7) ^ (r & 7)) << 3); }
@@ -141,21 +60,6 @@ struct TcSmem {
     static constexpr size_t kBytes = static_cast<size_t>(kTile) * (2 + kKStages + kVStages) + kNumBars * 8 + 16;
 };
 
-__device__ __forceinline__ void umma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}\n"
-                 ::"r"(tmem_d), "r"(tmem_a), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void tm_store32(uint32_t taddr, const uint32_t (&v)[32]) {
-    asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
-                 "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};\n"
-                 ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]),
-                   "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]), "r"(v[17]),
-                   "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]), "r"(v[25]), "r"(v[26]),
-                   "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
-                 : "memory");
-}
-__device__ __forceinline__ void tm_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;\n" ::: "memory"); }
-
 constexpr float kRescaleStep = 8.f;            // log2 of the growth of a row's maximum that forces a rescale
 
 template <int HD>
@@ -164,7 +68,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, const Tc
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     using L = TcSmem<HD>;
     pdl_trigger();
-    if ((saddr(smem_raw) & 1023u) != 0) {
+    if ((smem_u32(smem_raw) & 1023u) != 0) {
         if (threadIdx.x == 0) atomicExch(p.err, 6);
         return;
     }
@@ -214,7 +118,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, const Tc
             const int tok = x * tok_per_tile + r / g;
             const bool valid = r / g < n_tok[x];
             const __nv_bfloat16* src = valid ? p.q + ((static_cast<int64_t>(cu0 + q0 + tok) * p.H + kvh * g + r % g) * HD + c * 8) : p.q;
-            cpa16(reinterpret_cast<__nv_bfloat16*>(sQ + x * L::kTile) + tile_off(r, c), src, valid);
+            cp_async16(reinterpret_cast<__nv_bfloat16*>(sQ + x * L::kTile) + tile_off(r, c), src, valid);
         }
         asm volatile("cp.async.commit_group;\n" ::: "memory");
     }
@@ -238,16 +142,16 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, const Tc
 
     if (warp == 0) {
         if (lane == 0) {
-            for (int i = 0; i < kKStages; ++i) { mb_init(k_full + i, 1); mb_init(k_empty + i, 1); }
-            for (int i = 0; i < kVStages; ++i) { mb_init(v_full + i, 1); mb_init(v_empty + i, 1); }
-            for (int i = 0; i < 2; ++i) { mb_init(s_ready + i, 1); mb_init(p_ready + i, 128); mb_init(o_done + i, 1); }
-            asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
+            for (int i = 0; i < kKStages; ++i) { mbar_init(k_full + i, 1); mbar_init(k_empty + i, 1); }
+            for (int i = 0; i < kVStages; ++i) { mbar_init(v_full + i, 1); mbar_init(v_empty + i, 1); }
+            for (int i = 0; i < 2; ++i) { mbar_init(s_ready + i, 1); mbar_init(p_ready + i, 128); mbar_init(o_done + i, 1); }
+            mbar_fence_init();
         }
         __syncwarp();
         asm volatile("bar.arrive 1, %0;\n" ::"n"(kTcThreads) : "memory");       // the others wait for this below
     } else {
         if (warp == 1) {
-            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(saddr(tmem_slot)), "r"(512));
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(tmem_slot)), "r"(512));
             asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
         }
         asm volatile("cp.async.wait_group 0;\n" ::: "memory");
@@ -280,17 +184,17 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, const Tc
                 row = ((page * 2 + which) * p.KV + kvh) * p.page_size + key % p.page_size;
             }
             if (lane == 0) {
-                if (i >= kKStages) mb_wait(k_empty + ks, ((i / kKStages) - 1) & 1, p.err);
-                mb_expect_tx(k_full + ks, L::kTile);
+                if (i >= kKStages) mbar_wait(k_empty + ks, ((i / kKStages) - 1) & 1, p.err);
+                mbar_expect_tx(k_full + ks, L::kTile);
             }
             __syncwarp();
-            if (which == 0) tma_2d(sK + ks * L::kTile + half * 16384 + box * p.box_rows * 128, &kv_map, k_full + ks, half * 64, row);
+            if (which == 0) tma_load_2d(sK + ks * L::kTile + half * 16384 + box * p.box_rows * 128, &kv_map, k_full + ks, half * 64, row);
             if (lane == 0) {
-                if (i >= kVStages) mb_wait(v_empty + vs, ((i / kVStages) - 1) & 1, p.err);
-                mb_expect_tx(v_full + vs, L::kTile);
+                if (i >= kVStages) mbar_wait(v_empty + vs, ((i / kVStages) - 1) & 1, p.err);
+                mbar_expect_tx(v_full + vs, L::kTile);
             }
             __syncwarp();
-            if (which == 1) tma_2d(sV + vs * L::kTile + half * 16384 + box * p.box_rows * 128, &kv_map, v_full + vs, half * 64, row);
+            if (which == 1) tma_load_2d(sV + vs * L::kTile + half * 16384 + box * p.box_rows * 128, &kv_map, v_full + vs, half * 64, row);
         }
     } else if (warp == 1) {
         if (lane == 0) {                             // ---- tensor-core issue ----
@@ -299,17 +203,17 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, const Tc
             auto active = [&](int x, int j) { return j >= t_lo[x] && j < t_hi[x]; };
             auto issue_s = [&](int x, int j) {       // S_j(X); the K tile has been waited for
                 const int ks = (j - j_lo) % kKStages;
-                const uint32_t q_addr = saddr(sQ + x * L::kTile), k_addr = saddr(sK + ks * L::kTile);
+                const uint32_t q_addr = smem_u32(sQ + x * L::kTile), k_addr = smem_u32(sK + ks * L::kTile);
 #pragma unroll
                 for (int k = 0; k < HD / 16; ++k) {
                     const uint32_t off = (k >> 2) * 16384 + (k & 3) * 32;
                     umma(tS[x], desc_sw128(q_addr + off, 16, 1024), desc_sw128(k_addr + off, 16, 1024), idesc_s, k > 0 ? 1u : 0u);
                 }
-                commit_to(s_ready + x);
+                tc_commit(s_ready + x);
             };
             auto wait_k = [&](int j) {
                 const int i = j - j_lo;
-                mb_wait(k_full + i % kKStages, (i / kKStages) & 1, p.err);
+                mbar_wait(k_full + i % kKStages, (i / kKStages) & 1, p.err);
                 tc_after();
             };
             {
@@ -317,7 +221,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, const Tc
 #pragma unroll
                 for (int x = 0; x < 2; ++x)
                     if (active(x, j_lo)) issue_s(x, j_lo);
-                commit_to(k_empty + 0);
+                tc_commit(k_empty + 0);
             }
             for (int j = j_lo; j < j_hi; ++j) {
                 const int i = j - j_lo, vs = i % kVStages;
@@ -332,10 +236,10 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, const Tc
                         }
                         continue;
                     }
-                    mb_wait(p_ready + x, (j - t_lo[x]) & 1, p.err);
-                    if (!have_v) { mb_wait(v_full + vs, (i / kVStages) & 1, p.err); have_v = true; }
+                    mbar_wait(p_ready + x, (j - t_lo[x]) & 1, p.err);
+                    if (!have_v) { mbar_wait(v_full + vs, (i / kVStages) & 1, p.err); have_v = true; }
                     tc_after();
-                    const uint32_t v_addr = saddr(sV + vs * L::kTile);
+                    const uint32_t v_addr = smem_u32(sV + vs * L::kTile);
 #pragma unroll
                     for (int k = 0; k < kTN / 16; ++k)   // P: 16 keys = 8 columns of packed pairs; V: 16 keys further down
                         umma_ts(tO[x], tS[x] + k * 8, desc_sw128(v_addr + k * 16 * 128, 16384, 1024), idesc_pv,
@@ -344,14 +248,14 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, const Tc
                         if (!have_k) { wait_k(j + 1); have_k = true; }
                         issue_s(x, j + 1);
                     } else {
-                        commit_to(o_done + x);
+                        tc_commit(o_done + x);
                     }
                 }
-                if (!have_v) mb_wait(v_full + vs, (i / kVStages) & 1, p.err);    // nobody needed it: hand it back in order
-                commit_to(v_empty + vs);
+                if (!have_v) mbar_wait(v_full + vs, (i / kVStages) & 1, p.err);    // nobody needed it: hand it back in order
+                tc_commit(v_empty + vs);
                 if (j + 1 < j_hi) {
                     if (!have_k) wait_k(j + 1);          // nobody needs it: still hand the stage back in order
-                    commit_to(k_empty + (i + 1) % kKStages);
+                    tc_commit(k_empty + (i + 1) % kKStages);
                 }
             }
         }
@@ -371,7 +275,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, const Tc
             for (int j = t_lo[x]; j < t_hi[x]; ++j) {
                 const int i = j - t_lo[x];
                 const int key0 = j * kTN;
-                mb_wait(s_ready + x, i & 1, p.err);
+                mbar_wait(s_ready + x, i & 1, p.err);
                 tc_after();
                 uint32_t v[128];
 #pragma unroll
@@ -430,9 +334,9 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, const Tc
                 l += (sum2[0].x + sum2[0].y) + (sum2[1].x + sum2[1].y);
                 tm_wait_st();
                 tc_before();
-                mb_arrive(p_ready + x);
+                mbar_arrive(p_ready + x);
             }
-            mb_wait(o_done + x, 0, p.err);
+            mbar_wait(o_done + x, 0, p.err);
             tc_after();
             const bool valid = r / g < n_tok[x];
             const float inv = l > 0.f ? 1.f / l : 0.f;

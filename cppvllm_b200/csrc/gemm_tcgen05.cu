@@ -17,9 +17,8 @@
 //            epilogue in float, rounds to bf16 once and stores rows to global memory.
 // Every wait on an mbarrier is bounded by a cycle count; a wait that runs out records error 5 and the block carries
 // on to its end (tensor memory is always given back).  No cluster launch, no multicast.
-#include "common.cuh"
+#include "sm100.cuh"
 
-#include <cuda.h>
 #include <mutex>
 #include <unordered_map>
 
@@ -28,70 +27,6 @@ namespace cvb {
 constexpr int kBM = 128;
 constexpr int kBK = 64;                       // one 128-byte swizzle span of bf16
 constexpr int kGemmThreads = 192;
-
-__device__ __forceinline__ uint32_t smem_addr(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%1], %0;\n" ::"r"(count), "r"(smem_addr(bar)));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%1], %0;\n" ::"r"(bytes), "r"(smem_addr(bar)) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile("{\n.reg .pred P1;\nmbarrier.try_wait.parity.shared::cta.b64 P1, [%1], %2;\nselp.b32 %0, 1, 0, P1;\n}\n"
-                 : "=r"(ok) : "r"(smem_addr(bar)), "r"(parity) : "memory");
-    return ok != 0;
-}
-__device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, int* err) {
-    if (mbar_try_wait(bar, parity)) return;
-    const long long t0 = clock64();
-    while (!mbar_try_wait(bar, parity)) {
-        if (clock64() - t0 > 40000000LL) { atomicExch(err, 5); return; }
-    }
-}
-__device__ __forceinline__ void tma_load_2d(void* smem, const CUtensorMap* map, uint64_t* bar, int x, int y) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];\n"
-                 ::"r"(smem_addr(smem)), "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_addr(bar)), "r"(x), "r"(y) : "memory");
-}
-
-// Shared-memory matrix descriptor of a K-major tile whose rows are 128 bytes, swizzled in 1024-byte atoms of 8 rows
-// (what TMA writes with CU_TENSOR_MAP_SWIZZLE_128B): start address / 16, leading byte offset (unused with a swizzle) 1,
-// stride byte offset 1024 / 16 between 8-row groups, descriptor version 1, layout type 2 = 128-byte swizzle.
-__device__ __forceinline__ uint64_t umma_desc_k_sw128(uint32_t addr) {
-    uint64_t d = 0;
-    d |= static_cast<uint64_t>((addr >> 4) & 0x3FFF);
-    d |= static_cast<uint64_t>(1) << 16;
-    d |= static_cast<uint64_t>(1024 >> 4) << 32;
-    d |= static_cast<uint64_t>(1) << 46;
-    d |= static_cast<uint64_t>(2) << 61;
-    return d;
-}
-
-// Instruction descriptor of kind::f16 with bf16 operands (both K-major) and a float accumulator.
-__host__ __device__ constexpr uint32_t umma_idesc_bf16(int m, int n) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
-}
-
-__device__ __forceinline__ void umma_bf16(uint32_t tmem_d, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile("{\n.reg .pred p;\nsetp.ne.b32 p, %4, 0;\ntcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
-                 ::"r"(tmem_d), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void umma_commit(uint64_t* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n" ::"r"(smem_addr(bar)) : "memory");
-}
-__device__ __forceinline__ void tmem_load_32(uint32_t taddr, uint32_t (&v)[32]) {
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
-                 "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];\n"
-                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
-                   "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
-                   "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
-                   "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
-                 : "r"(taddr));
-}
-__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;\n" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;\n" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;\n" ::: "memory"); }
 
 struct GemmParams {
     __nv_bfloat16* out;       // [M, n_out]
@@ -116,7 +51,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     using L = GemmSmem<BN, STAGES>;
     pdl_trigger();
-    const uint32_t raw_addr = smem_addr(smem_raw);
+    const uint32_t raw_addr = smem_u32(smem_raw);
     unsigned char* base = smem_raw + ((1024u - (raw_addr & 1023u)) & 1023u);
     unsigned char* stages = base;
     uint64_t* full = reinterpret_cast<uint64_t*>(base + static_cast<size_t>(STAGES) * L::kStageBytes);
@@ -136,12 +71,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         asm volatile("fence.mbarrier_init.release.cluster;\n" ::: "memory");
     }
     if (warp == 1) {                                   // one warp allocates the accumulator's columns
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_addr(tmem_slot)), "r"(BN));
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(tmem_slot)), "r"(BN));
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
     }
-    tc_fence_before();
+    tc_before();
     __syncthreads();
-    tc_fence_after();
+    tc_after();
     const uint32_t tmem_d = *tmem_slot;
     pdl_wait();                                        // the activations come from the kernel before this one
 
@@ -165,33 +100,33 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
         }
     } else if (warp == 1) {
         if (lane == 0) {                               // ---- tensor-core issue ----
-            constexpr uint32_t idesc = umma_idesc_bf16(kBM, BN);
+            constexpr uint32_t idesc = idesc_bf16(kBM, BN, false);
             for (int kb = 0; kb < num_kb; ++kb) {
                 const int s = kb % STAGES;
                 mbar_wait(full + s, (kb / STAGES) & 1, p.err);
-                tc_fence_after();
-                const uint32_t a_addr = smem_addr(stages + static_cast<size_t>(s) * L::kStageBytes);
+                tc_after();
+                const uint32_t a_addr = smem_u32(stages + static_cast<size_t>(s) * L::kStageBytes);
                 const uint32_t b_addr = a_addr + L::kABytes;
 #pragma unroll
                 for (int k = 0; k < kBK / 16; ++k) {
-                    umma_bf16(tmem_d, umma_desc_k_sw128(a_addr + k * 32), umma_desc_k_sw128(b_addr + k * 32), idesc,
+                    umma(tmem_d, desc_sw128(a_addr + k * 32, 16, 1024), desc_sw128(b_addr + k * 32, 16, 1024), idesc,
                               (kb > 0 || k > 0) ? 1u : 0u);
                 }
-                umma_commit(empty + s);                // the stage is free once these products have read it
+                tc_commit(empty + s);                // the stage is free once these products have read it
             }
-            umma_commit(accum_ready);
+            tc_commit(accum_ready);
         }
     } else {                                           // ---- epilogue: warps 2..5 own lanes 32 * (warp % 4) .. +31 ----
         const int quarter = warp & 3;
         const int row = m0 + quarter * 32 + lane;
         mbar_wait(accum_ready, 0, p.err);
-        tc_fence_after();
+        tc_after();
         __nv_bfloat16* out_row = p.out + static_cast<int64_t>(row) * p.n_out;
         for (int c0 = 0; c0 < OUT_COLS; c0 += 32) {
             uint32_t v[32], u[32];
-            tmem_load_32(tmem_d + (static_cast<uint32_t>(quarter * 32) << 16) + c0, v);
-            if constexpr (SWIGLU) tmem_load_32(tmem_d + (static_cast<uint32_t>(quarter * 32) << 16) + OUT_COLS + c0, u);
-            tmem_wait_ld();
+            tm_load32(tmem_d + (static_cast<uint32_t>(quarter * 32) << 16) + c0, v);
+            if constexpr (SWIGLU) tm_load32(tmem_d + (static_cast<uint32_t>(quarter * 32) << 16) + OUT_COLS + c0, u);
+            tm_wait_ld();
             if (row < p.M) {
 #pragma unroll
                 for (int j = 0; j < 32; j += 8) {
@@ -221,10 +156,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             }
         }
     }
-    tc_fence_before();
+    tc_before();
     __syncthreads();
     if (warp == 1) {
-        tc_fence_after();
+        tc_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;\n" ::"r"(tmem_d), "r"(BN));
     }
 }
