@@ -25,10 +25,8 @@
 // comes by cp.async.  The matrix products are mma.sync.m16n8k16 (bf16 in, float accumulate); ldmatrix reads the
 // swizzled tiles without bank conflicts.
 #include "sm100.cuh"
+#include "tensor_map.cuh"
 #include "attention_bf16.h"
-
-#include <mutex>
-#include <unordered_map>
 
 namespace cvb {
 
@@ -657,50 +655,10 @@ __global__ void attn_decode_merge_kernel(const AttnParams p) {
 
 // ---- host side --------------------------------------------------------------------------------------------------
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_tiled_fn() {
-    static EncodeTiledFn fn = nullptr;
-    static std::once_flag once;
-    std::call_once(once, [] {
-        void* ptr = nullptr;
-        cudaDriverEntryPointQueryResult qres;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
-            qres == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(ptr);
-    });
-    return fn;
-}
-
 // A tensor map of one cache unit seen as [rows = pages * 2 * KV * page_size][head_dim] bf16, fetched in boxes of
-// [box_rows][64 columns] with the 128-byte swizzle.  Maps are kept per (address, shape).
+// [box_rows][64 columns] with the 128-byte swizzle.
 static int kv_tensor_map(CUtensorMap* out, const void* cache, int64_t rows, int hd, int box_rows) {
-    struct Key { const void* p; int64_t rows; int hd, box; bool operator==(const Key& o) const { return p == o.p && rows == o.rows && hd == o.hd && box == o.box; } };
-    struct Hash { size_t operator()(const Key& k) const { return std::hash<const void*>()(k.p) ^ (std::hash<int64_t>()(k.rows) * 31) ^ (k.hd * 131) ^ (k.box * 7); } };
-    static std::unordered_map<Key, CUtensorMap, Hash> maps;
-    static std::mutex mu;
-    std::lock_guard<std::mutex> lock(mu);
-    const Key key{cache, rows, hd, box_rows};
-    auto it = maps.find(key);
-    if (it == maps.end()) {
-        EncodeTiledFn fn = encode_tiled_fn();
-        if (fn == nullptr) return CVB_E_UNSUPPORTED;
-        if ((reinterpret_cast<uintptr_t>(cache) & 15) != 0) return CVB_E_ALIGN;
-        CUtensorMap m;
-        const cuuint64_t dims[2] = {static_cast<cuuint64_t>(hd), static_cast<cuuint64_t>(rows)};
-        const cuuint64_t strides[1] = {static_cast<cuuint64_t>(hd) * sizeof(__nv_bfloat16)};
-        const cuuint32_t box[2] = {64u, static_cast<cuuint32_t>(box_rows)};
-        const cuuint32_t estr[2] = {1u, 1u};
-        const CUresult r = fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(cache), dims, strides, box, estr,
-                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-        if (r != CUDA_SUCCESS) return CVB_E_SHAPE;
-        it = maps.emplace(key, m).first;
-    }
-    *out = it->second;
-    return CVB_OK;
+    return cached_bf16_map(out, cache, rows, hd, 64, box_rows);
 }
 
 template <int HD> constexpr size_t prefill_smem() { return SmemPlan<HD, kPreStages, 64>::kBytes; }
@@ -957,18 +915,9 @@ extern "C" int cvb_attn_decode_bf16_static(void* out, const void* q, const void*
     p.part_ml = scratch + static_cast<int64_t>(S) * KV * splits * 16 * hd;
 
     // the tensor map is encoded into a local variable: no table, no heap
-    EncodeTiledFn fn = encode_tiled_fn();
-    if (fn == nullptr) return CVB_E_UNSUPPORTED;
-    if ((reinterpret_cast<uintptr_t>(cache) & 15) != 0) return CVB_E_ALIGN;
     CUtensorMap map;
-    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(hd), static_cast<cuuint64_t>(num_pages) * 2 * KV * page_size};
-    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(hd) * sizeof(__nv_bfloat16)};
-    const cuuint32_t box[2] = {64u, static_cast<cuuint32_t>(p.box_rows)};
-    const cuuint32_t estr[2] = {1u, 1u};
-    if (fn(&map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(cache), dims, strides, box, estr,
-           CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-        return CVB_E_SHAPE;
+    rc = encode_bf16_map(&map, cache, static_cast<int64_t>(num_pages) * 2 * KV * page_size, hd, 64, p.box_rows);
+    if (rc != CVB_OK) return rc;
 
     dim3 grid(static_cast<unsigned>(S), static_cast<unsigned>(KV), static_cast<unsigned>(splits));
     dim3 mgrid(static_cast<unsigned>(S), static_cast<unsigned>(H));

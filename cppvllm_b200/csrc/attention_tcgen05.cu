@@ -25,9 +25,7 @@
 // plain arrivals from the softmax threads.  Every wait is bounded by a cycle count; a wait that runs out records
 // error 5 and the block runs on to its end (tensor memory is always given back).
 #include "sm100.cuh"
-
-#include <mutex>
-#include <unordered_map>
+#include "tensor_map.cuh"
 
 namespace cvb {
 
@@ -370,48 +368,8 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, const Tc
 
 // ---- host side ------------------------------------------------------------------------------------------------
 
-typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                             const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                             CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeFn encode_fn() {
-    static EncodeFn fn = nullptr;
-    static std::once_flag once;
-    std::call_once(once, [] {
-        void* ptr = nullptr;
-        cudaDriverEntryPointQueryResult qres;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
-            qres == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeFn>(ptr);
-    });
-    return fn;
-}
-
 static int kv_map_for(CUtensorMap* out, const void* cache, int64_t rows, int hd, int box_rows) {
-    struct Key { const void* p; int64_t rows; int hd, box; bool operator==(const Key& o) const { return p == o.p && rows == o.rows && hd == o.hd && box == o.box; } };
-    struct Hash { size_t operator()(const Key& k) const { return std::hash<const void*>()(k.p) ^ (std::hash<int64_t>()(k.rows) * 31) ^ (k.hd * 131) ^ (k.box * 7); } };
-    static std::unordered_map<Key, CUtensorMap, Hash> maps;
-    static std::mutex mu;
-    std::lock_guard<std::mutex> lock(mu);
-    const Key key{cache, rows, hd, box_rows};
-    auto it = maps.find(key);
-    if (it == maps.end()) {
-        EncodeFn fn = encode_fn();
-        if (fn == nullptr) return CVB_E_UNSUPPORTED;
-        if ((reinterpret_cast<uintptr_t>(cache) & 15) != 0) return CVB_E_ALIGN;
-        CUtensorMap m;
-        const cuuint64_t dims[2] = {static_cast<cuuint64_t>(hd), static_cast<cuuint64_t>(rows)};
-        const cuuint64_t strides[1] = {static_cast<cuuint64_t>(hd) * sizeof(__nv_bfloat16)};
-        const cuuint32_t box[2] = {64u, static_cast<cuuint32_t>(box_rows)};
-        const cuuint32_t estr[2] = {1u, 1u};
-        if (fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(cache), dims, strides, box, estr,
-               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-            return CVB_E_SHAPE;
-        it = maps.emplace(key, m).first;
-    }
-    *out = it->second;
-    return CVB_OK;
+    return cached_bf16_map(out, cache, rows, hd, 64, box_rows);
 }
 
 }  // namespace cvb

@@ -40,7 +40,7 @@ LIBRARIES: Dict[str, List[str]] = {
     "attn_tcgen05": ["attention_tcgen05.cu"],
 }
 
-_HEADERS = ["common.cuh", "sm100.cuh", "attention_bf16.h"]
+_HEADERS = ["common.cuh", "sm100.cuh", "tensor_map.cuh", "attention_bf16.h"]
 _loaded: Dict[str, ctypes.CDLL] = {}
 _lock = threading.Lock()
 

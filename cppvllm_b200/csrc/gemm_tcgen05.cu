@@ -18,9 +18,7 @@
 // Every wait on an mbarrier is bounded by a cycle count; a wait that runs out records error 5 and the block carries
 // on to its end (tensor memory is always given back).  No cluster launch, no multicast.
 #include "sm100.cuh"
-
-#include <mutex>
-#include <unordered_map>
+#include "tensor_map.cuh"
 
 namespace cvb {
 
@@ -166,50 +164,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
 // ---- host side ------------------------------------------------------------------------------------------------
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_tiled_fn() {
-    static EncodeTiledFn fn = nullptr;
-    static std::once_flag once;
-    std::call_once(once, [] {
-        void* ptr = nullptr;
-        cudaDriverEntryPointQueryResult qres;
-        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
-            qres == cudaDriverEntryPointSuccess)
-            fn = reinterpret_cast<EncodeTiledFn>(ptr);
-    });
-    return fn;
-}
-
 // Tensor map of a row-major bf16 matrix [rows, cols], fetched in boxes of [128 rows, 64 columns], 128-byte swizzle,
-// zero fill outside the matrix.  Kept per (address, shape).
+// zero fill outside the matrix.
 static int matrix_map(CUtensorMap* out, const void* ptr, int64_t rows, int64_t cols) {
-    struct Key { const void* p; int64_t r, c; bool operator==(const Key& o) const { return p == o.p && r == o.r && c == o.c; } };
-    struct Hash { size_t operator()(const Key& k) const { return std::hash<const void*>()(k.p) ^ (std::hash<int64_t>()(k.r) * 1315423911u) ^ (std::hash<int64_t>()(k.c) * 2654435761u); } };
-    static std::unordered_map<Key, CUtensorMap, Hash> maps;
-    static std::mutex mu;
-    std::lock_guard<std::mutex> lock(mu);
-    const Key key{ptr, rows, cols};
-    auto it = maps.find(key);
-    if (it == maps.end()) {
-        EncodeTiledFn fn = encode_tiled_fn();
-        if (fn == nullptr) return CVB_E_UNSUPPORTED;
-        CUtensorMap m;
-        const cuuint64_t dims[2] = {static_cast<cuuint64_t>(cols), static_cast<cuuint64_t>(rows)};
-        const cuuint64_t strides[1] = {static_cast<cuuint64_t>(cols) * sizeof(__nv_bfloat16)};
-        const cuuint32_t box[2] = {static_cast<cuuint32_t>(kBK), 128u};
-        const cuuint32_t estr[2] = {1u, 1u};
-        if (fn(&m, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, estr,
-               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-            return CVB_E_SHAPE;
-        if (maps.size() > 4096) maps.clear();          // activations of many different lengths: start over
-        it = maps.emplace(key, m).first;
-    }
-    *out = it->second;
-    return CVB_OK;
+    return cached_bf16_map(out, ptr, rows, cols, kBK, 128);
 }
 
 template <int BN, int STAGES, bool SWIGLU>
