@@ -22,6 +22,7 @@ namespace cvb {
 
 constexpr int kXPad = 32;              // elements of padding per activation row: rows land in different banks
 constexpr int kBatch = 8;              // columns of the B operand
+constexpr int kMaxRows = 16;           // activation rows a launch takes: one or two groups of kBatch
 constexpr int kJBatch = 8;             // 32-wide slabs fetched ahead per warp
 
 __device__ __forceinline__ void unpack8(const uint4& t, float (&v)[8]) {
@@ -51,14 +52,17 @@ struct GemvParams {
 };
 
 // TILE_ROWS: rows of W per tile (16, or 8 with the lower half of the A operand left zero).
-template <int TILE_ROWS, bool NORM, bool SWIGLU>
+// NB: activation rows in groups of eight (1 or 2): the B operand of a product holds eight rows, so sixteen rows take two
+// products per weight fragment; the weights are still read once.
+template <int TILE_ROWS, bool NORM, bool SWIGLU, int NB>
 __global__ void __launch_bounds__(512)
 gemv_mma_kernel(const GemvParams p) {
+    constexpr int kRows = kBatch * NB;                                   // activation rows staged and multiplied
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int K = p.K, chunks = K >> 3;
     const int xstride = K + kXPad;
     __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(smem_raw);                    // [8][K + pad]
-    float* red = reinterpret_cast<float*>(xs + kBatch * xstride);                      // [warps][16][8]
+    float* red = reinterpret_cast<float*>(xs + kRows * xstride);                       // [warps][16][kRows]
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = blockDim.x >> 5;
     pdl_trigger();
 
@@ -108,7 +112,7 @@ gemv_mma_kernel(const GemvParams p) {
     constexpr int kStage = NORM ? 4 : 8;
     if constexpr (NORM) {
         // one warp per row: add, round, sum of squares, scale; the row passes through shared memory in between
-        for (int m = warp; m < kBatch; m += n_warps) {
+        for (int m = warp; m < kRows; m += n_warps) {
             if (m >= p.M) {
                 for (int c = lane; c < chunks; c += 32) *reinterpret_cast<uint4*>(xs + m * xstride + c * 8) = make_uint4(0, 0, 0, 0);
                 continue;
@@ -175,7 +179,7 @@ gemv_mma_kernel(const GemvParams p) {
             }
         }
     } else {
-        const int total = kBatch * chunks;
+        const int total = kRows * chunks;
         for (int i0 = threadIdx.x; i0 < total; i0 += blockDim.x * kStage) {
             uint4 v[kStage];
 #pragma unroll
@@ -196,18 +200,25 @@ gemv_mma_kernel(const GemvParams p) {
     __syncthreads();
 
     // ---- the product, tile after tile ----
-    const uint4* x_row = reinterpret_cast<const uint4*>(xs + r * xstride);
+    const uint4* x_row[NB];
+#pragma unroll
+    for (int b = 0; b < NB; ++b) x_row[b] = reinterpret_cast<const uint4*>(xs + (r + 8 * b) * xstride);
     for (int round = 0; round < n_rounds; ++round) {
-        float acc[4] = {0.f, 0.f, 0.f, 0.f};
+        float acc[NB][4];
+#pragma unroll
+        for (int b = 0; b < NB; ++b) { acc[b][0] = acc[b][1] = acc[b][2] = acc[b][3] = 0.f; }
         for (int jb = j_begin; jb < j_end; jb += kJBatch) {
             if (jb != j_begin) fetch(jb);
 #pragma unroll
             for (int u = 0; u < kJBatch; ++u) {
                 const int c = (jb + u) * 4 + q;
                 if (jb + u >= j_end) break;
-                const uint4 xv = c < chunks ? x_row[c] : zero;
-                mma_16816(acc, wh[u].x, wl[u].x, wh[u].y, wl[u].y, xv.x, xv.y);
-                mma_16816(acc, wh[u].z, wl[u].z, wh[u].w, wl[u].w, xv.z, xv.w);
+#pragma unroll
+                for (int b = 0; b < NB; ++b) {
+                    const uint4 xv = c < chunks ? x_row[b][c] : zero;
+                    mma_16816(acc[b], wh[u].x, wl[u].x, wh[u].y, wl[u].y, xv.x, xv.y);
+                    mma_16816(acc[b], wh[u].z, wl[u].z, wh[u].w, wl[u].w, xv.z, xv.w);
+                }
             }
         }
         const int tile_base = (round * gridDim.x + blockIdx.x) * p.tiles_per_block;
@@ -215,25 +226,28 @@ gemv_mma_kernel(const GemvParams p) {
             set_tile(round + 1);                                         // while this one's parts are added up
             fetch(j_begin);
         }
-        // acc[0], acc[1]: (row r, batch 2q, 2q+1); acc[2], acc[3]: (row r + 8, same)
-        float* mine = red + warp * 128;
-        mine[r * 8 + 2 * q] = acc[0];
-        mine[r * 8 + 2 * q + 1] = acc[1];
-        mine[(r + 8) * 8 + 2 * q] = acc[2];
-        mine[(r + 8) * 8 + 2 * q + 1] = acc[3];
+        // acc[b][0], [1]: (row r, batch 8b + 2q, + 1); acc[b][2], [3]: (row r + 8, same)
+        float* mine = red + warp * (16 * kRows);
+#pragma unroll
+        for (int b = 0; b < NB; ++b) {
+            mine[r * kRows + 8 * b + 2 * q] = acc[b][0];
+            mine[r * kRows + 8 * b + 2 * q + 1] = acc[b][1];
+            mine[(r + 8) * kRows + 8 * b + 2 * q] = acc[b][2];
+            mine[(r + 8) * kRows + 8 * b + 2 * q + 1] = acc[b][3];
+        }
         __syncthreads();
 
         // ---- add the K parts of every tile and store ----
-        for (int i = threadIdx.x; i < p.tiles_per_block * OUT_PER_TILE * kBatch; i += blockDim.x) {
-            const int t = i / (OUT_PER_TILE * kBatch), rem = i % (OUT_PER_TILE * kBatch);
-            const int row = rem / kBatch, m = rem % kBatch;
+        for (int i = threadIdx.x; i < p.tiles_per_block * OUT_PER_TILE * kRows; i += blockDim.x) {
+            const int t = i / (OUT_PER_TILE * kRows), rem = i % (OUT_PER_TILE * kRows);
+            const int row = rem / kRows, m = rem % kRows;
             const int n = (tile_base + t) * OUT_PER_TILE + row;
             if (n >= n_out || m >= p.M) continue;
             float s0 = 0.f, s1 = 0.f;
             for (int w = 0; w < p.warps_k; ++w) {
-                const float* part = red + (t * p.warps_k + w) * 128;
-                s0 += part[row * 8 + m];
-                if constexpr (SWIGLU) s1 += part[(row + 8) * 8 + m];
+                const float* part = red + (t * p.warps_k + w) * (16 * kRows);
+                s0 += part[row * kRows + m];
+                if constexpr (SWIGLU) s1 += part[(row + 8) * kRows + m];
             }
             float y = s0;
             if constexpr (SWIGLU) {
@@ -246,8 +260,8 @@ gemv_mma_kernel(const GemvParams p) {
     }
 }
 
-template <int TILE_ROWS, bool NORM, bool SWIGLU>
-static int launch_gemv(GemvParams p, cudaStream_t stream) {
+template <int TILE_ROWS, bool NORM, bool SWIGLU, int NB>
+static int launch_gemv_nb(GemvParams p, cudaStream_t stream) {
     constexpr int OUT_PER_TILE = SWIGLU ? 8 : TILE_ROWS;
     const int n_out = SWIGLU ? p.N / 2 : p.N;
     const int tiles = (n_out + OUT_PER_TILE - 1) / OUT_PER_TILE;
@@ -257,7 +271,7 @@ static int launch_gemv(GemvParams p, cudaStream_t stream) {
     while (p.tiles_per_block > 1 && (tiles + p.tiles_per_block - 1) / p.tiles_per_block < 120) p.tiles_per_block >>= 1;
     p.n_tiles = tiles;
     auto smem_for = [&](int tpb) {
-        return static_cast<size_t>(kBatch) * (p.K + kXPad) * sizeof(__nv_bfloat16) + static_cast<size_t>(p.warps_k * tpb) * 128 * sizeof(float);
+        return static_cast<size_t>(kBatch * NB) * (p.K + kXPad) * sizeof(__nv_bfloat16) + static_cast<size_t>(p.warps_k * tpb) * 128 * NB * sizeof(float);
     };
     // Blocks stage all of the activations: with long rows few of them fit on an SM, and each then takes more warps
     // (up to 16) to keep as many loads in flight.  The grid is what the device holds at once; blocks walk the tiles.
@@ -271,11 +285,11 @@ static int launch_gemv(GemvParams p, cudaStream_t stream) {
     auto resident = [&](int tpb) {                                   // blocks of this shape that an SM holds
         const size_t smem = smem_for(tpb);
         if (smem > 48 * 1024 &&
-            cudaFuncSetAttribute(gemv_mma_kernel<TILE_ROWS, NORM, SWIGLU>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+            cudaFuncSetAttribute(gemv_mma_kernel<TILE_ROWS, NORM, SWIGLU, NB>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  static_cast<int>(smem)) != cudaSuccess)
             return 0;
         int n = 0;
-        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, gemv_mma_kernel<TILE_ROWS, NORM, SWIGLU>, p.warps_k * tpb * 32, smem) != cudaSuccess)
+        if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, gemv_mma_kernel<TILE_ROWS, NORM, SWIGLU, NB>, p.warps_k * tpb * 32, smem) != cudaSuccess)
             return 0;
         return n;
     };
@@ -289,8 +303,15 @@ static int launch_gemv(GemvParams p, cudaStream_t stream) {
     const int warps = p.warps_k * p.tiles_per_block;
     const int blocks = min((tiles + p.tiles_per_block - 1) / p.tiles_per_block, sms * per_sm);
     const size_t smem = smem_for(p.tiles_per_block);
-    launch_kernel(gemv_mma_kernel<TILE_ROWS, NORM, SWIGLU>, dim3(blocks), dim3(warps * 32), smem, stream, p);
+    launch_kernel(gemv_mma_kernel<TILE_ROWS, NORM, SWIGLU, NB>, dim3(blocks), dim3(warps * 32), smem, stream, p);
     return launch_status();
+}
+
+// up to 8 rows: one group of eight; up to 16: two
+template <int TILE_ROWS, bool NORM, bool SWIGLU>
+static int launch_gemv(const GemvParams& p, cudaStream_t stream) {
+    if (p.M <= kBatch) return launch_gemv_nb<TILE_ROWS, NORM, SWIGLU, 1>(p, stream);
+    return launch_gemv_nb<TILE_ROWS, NORM, SWIGLU, 2>(p, stream);
 }
 
 template <bool NORM>
@@ -410,7 +431,7 @@ using namespace cvb;
 extern "C" int cvb_gemv_bf16(void* out, const void* x, const void* delta, void* resid_out, const float* norm_w,
                              const void* W, int M, int N, int K, float eps, int mode, cudaStream_t stream) {
     if (M == 0) return CVB_OK;
-    if (M < 0 || M > kBatch || N <= 0 || K <= 0) return CVB_E_SIZE;
+    if (M < 0 || M > kMaxRows || N <= 0 || K <= 0) return CVB_E_SIZE;
     if (K % 8) return CVB_E_ALIGN;
     auto al = [](const void* q) { return q == nullptr || (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
     if (!al(out) || !al(x) || !al(delta) || !al(resid_out) || !al(W) || !al(norm_w)) return CVB_E_ALIGN;

@@ -405,13 +405,20 @@ def attn_decode_fused_bf16(out, qkv, cache, block_tables, cu_seqlens, positions,
 
 _gemv = None
 
-GEMV_MAX_ROWS = 8
+SPLITK_MIN_BYTES = 16 << 20
+GEMV_MAX_ROWS = 16           # the weight-streaming product: one or two groups of eight activation rows
+SPLITK_MAX_ROWS = 8          # its split-K form and the persistent decode kernels: one group
+DECODE_FUSED_MAX_ROWS = 8
 
 
 def gemv_supported(x_dtype: torch.dtype, weight: torch.Tensor, rows: int) -> bool:
-    """The weight-streaming product covers bf16 operands, up to 8 rows and inner sizes that are multiples of 8."""
+    """The weight-streaming product covers bf16 operands, up to 16 rows, and inner sizes that are multiples of 8 and whose
+    staged rows (8 or 16 of them) fit into shared memory.  More than 8 rows against a large weight are left to the
+    library: the split-K form takes 8 rows, and the plain form is slower than the library there."""
+    staged = 8 if rows <= 8 else 16
     return (x_dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and 0 < rows <= GEMV_MAX_ROWS
-            and weight.shape[1] % 8 == 0 and weight.shape[1] * 8 * 2 <= 200 * 1024)
+            and weight.shape[1] % 8 == 0 and weight.shape[1] * staged * 2 + 32 * 1024 <= 200 * 1024
+            and (rows <= 8 or weight.numel() * 2 < SPLITK_MIN_BYTES))
 
 
 def gemv_bf16(out: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, rows: int, norm_weight: Optional[torch.Tensor] = None,
@@ -448,13 +455,12 @@ def gemv_bf16(out: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, rows: in
     return out
 
 
-SPLITK_MIN_BYTES = 16 << 20
 _splitk_buffers: Dict[int, list] = {}
 
 
 def gemv_splitk_preferred(x_dtype: torch.dtype, weight: torch.Tensor, rows: int) -> bool:
     """Weights of 16 MB and more go through the kernel that splits the inner dimension over blocks as well."""
-    return (x_dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and 0 < rows <= GEMV_MAX_ROWS
+    return (x_dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and 0 < rows <= SPLITK_MAX_ROWS
             and weight.dim() == 2 and weight.shape[1] % 8 == 0 and weight.numel() * 2 >= SPLITK_MIN_BYTES)
 
 
@@ -554,7 +560,7 @@ def decode_fusion_supported(dtype: torch.dtype, rows: int, widths, head_dim: int
     """The persistent decode kernels cover bf16 steps of up to 8 tokens, widths that are multiples of 8 and fit into
     shared memory eight rows at a time, and head sizes of 16, 32, 64, 128 or 256."""
     ch = head_dim // 8
-    return (dtype == torch.bfloat16 and 0 < rows <= GEMV_MAX_ROWS and all(w % 8 == 0 for w in widths)
+    return (dtype == torch.bfloat16 and 0 < rows <= DECODE_FUSED_MAX_ROWS and all(w % 8 == 0 for w in widths)
             and 8 * (max(widths) + 32) * 2 + 8 * 128 * 4 <= 200 * 1024
             and head_dim % 8 == 0 and 2 <= ch <= 32 and ch & (ch - 1) == 0)
 

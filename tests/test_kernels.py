@@ -488,7 +488,7 @@ def test_tensor_core_attention_refuses_what_it_does_not_cover(ops):
 
 # ---- weight-streaming products for a few rows -----------------------------------------------------------------
 
-@pytest.mark.parametrize("M", [1, 3, 8])
+@pytest.mark.parametrize("M", [1, 3, 8, 9, 16])
 @pytest.mark.parametrize("N,K", [(1024, 2048), (4096, 1024), (40, 72), (1000, 3064)])
 def test_gemv_plain_norm_and_swiglu_forms(ops, M, N, K):
     dt = torch.bfloat16
@@ -496,7 +496,9 @@ def test_gemv_plain_norm_and_swiglu_forms(ops, M, N, K):
     d = dev()
     W = (torch.randn(N, K, generator=g) * 0.05).to(dt).to(d)
     x = torch.randn(M, K, generator=g).to(dt).to(d)
-    assert ops.gemv_supported(dt, W, M) and not ops.gemv_supported(dt, W, 9) and not ops.gemv_supported(torch.float32, W, 1)
+    assert ops.gemv_supported(dt, W, M) and not ops.gemv_supported(dt, W, 17) and not ops.gemv_supported(torch.float32, W, 1)
+    big = torch.empty(8192, 2048, dtype=dt, device="meta")                       # 32 MB: more than 8 rows go to the library
+    assert ops.gemv_supported(dt, big, 8) and not ops.gemv_supported(dt, big, 9)
     # plain
     out = torch.full((M, N), float("nan"), dtype=dt, device=d)
     ops.gemv_bf16(out, x, W, M)
