@@ -7,7 +7,9 @@
 // once for the whole group and for both query tiles.  Keys are walked in tiles of 128.  The tensor core alternates
 // between the two query tiles: while the softmax of one runs, the products of the other do.  Roles, by warp:
 //   warp 0     producer: one lane per TMA box (a page or 64 keys, times 64-column half, times K and V; 128-byte swizzle),
-//              K ring of three stages, V ring of two; the block-table reads of a tile are in flight together;
+//              two stages, each with the keys of tile j + 1 and the values of tile j (what one round of the tensor core
+//              reads), so a round costs the issuing thread one wait and one commit for its operands; the block-table
+//              reads of a load are in flight together;
 //   warp 1     allocates 512 columns of tensor memory; one thread issues, per key tile j and query tile X,
 //                  PV_j(X)    = P_j(X) V_j        (M 128, N = head size, K 128; P from tensor memory, V MN-major)
 //                  S_{j+1}(X) = Q(X) K_{j+1}^T    (M 128, N 128, K = head size; both operands K-major)
@@ -31,8 +33,7 @@ namespace cvb {
 
 constexpr int kTM = 128;                      // query rows per block
 constexpr int kTN = 128;                      // keys per tile
-constexpr int kKStages = 3;
-constexpr int kVStages = 2;
+constexpr int kStages = 2;                    // each holds the keys of tile j + 1 and the values of tile j
 constexpr float kLog2eF = 1.4426950408889634f;
 
 // element offset of 16-byte chunk c of row r in a [128 rows][HD] tile stored as HD/64 halves of [128][64], swizzled
@@ -54,8 +55,8 @@ constexpr int kTcThreads = 128 + 256;         // one warpgroup of helpers (two w
 template <int HD>
 struct TcSmem {
     static constexpr int kTile = 128 * HD * 2;
-    static constexpr int kNumBars = 2 * kKStages + 2 * kVStages + 2 + 2 + 2;
-    static constexpr size_t kBytes = static_cast<size_t>(kTile) * (2 + kKStages + kVStages) + kNumBars * 8 + 16;
+    static constexpr int kNumBars = 2 * kStages + 2 + 2 + 2;
+    static constexpr size_t kBytes = static_cast<size_t>(kTile) * (2 + 2 * kStages) + kNumBars * 8 + 16;
 };
 
 constexpr float kRescaleStep = 8.f;            // log2 of the growth of a row's maximum that forces a rescale
@@ -71,14 +72,11 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, const Tc
         return;
     }
     unsigned char* sQ = smem_raw;                                   // two tiles
-    unsigned char* sK = sQ + 2 * L::kTile;
-    unsigned char* sV = sK + kKStages * L::kTile;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sV + kVStages * L::kTile);
-    uint64_t* k_full = bars;                       // [3]  TMA
-    uint64_t* k_empty = k_full + kKStages;         // [3]  tensor core
-    uint64_t* v_full = k_empty + kKStages;         // [2]  TMA
-    uint64_t* v_empty = v_full + kVStages;         // [2]  tensor core
-    uint64_t* s_ready = v_empty + kVStages;        // [2 tiles]  tensor core: S_j(X) and everything issued before it is done
+    unsigned char* sKV = sQ + 2 * L::kTile;                         // stage s: keys at (2 s) tiles, values at (2 s + 1) tiles
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sKV + 2 * kStages * L::kTile);
+    uint64_t* kv_full = bars;                      // [2]  TMA: the stage's keys and values have landed
+    uint64_t* kv_empty = kv_full + kStages;        // [2]  tensor core: the products that read the stage are done
+    uint64_t* s_ready = kv_empty + kStages;        // [2 tiles]  tensor core: S_j(X) and everything issued before it is done
     uint64_t* p_ready = s_ready + 2;               // [2 tiles]  128 softmax threads: P_j(X) is in tensor memory
     uint64_t* o_done = p_ready + 2;                // [2 tiles]  tensor core: the last PV(X) is done
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_done + 2);
@@ -140,8 +138,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, const Tc
 
     if (warp == 0) {
         if (lane == 0) {
-            for (int i = 0; i < kKStages; ++i) { mbar_init(k_full + i, 1); mbar_init(k_empty + i, 1); }
-            for (int i = 0; i < kVStages; ++i) { mbar_init(v_full + i, 1); mbar_init(v_empty + i, 1); }
+            for (int i = 0; i < kStages; ++i) { mbar_init(kv_full + i, 1); mbar_init(kv_empty + i, 1); }
             for (int i = 0; i < 2; ++i) { mbar_init(s_ready + i, 1); mbar_init(p_ready + i, 128); mbar_init(o_done + i, 1); }
             mbar_fence_init();
         }
@@ -170,10 +167,15 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, const Tc
         const int boxes = kTN / p.box_rows, per_tile = boxes * (HD / 64);
         const int which = lane / per_tile;           // 0: K, 1: V, above: idle lanes
         const int box = (lane % per_tile) / (HD / 64), half = lane % (HD / 64);
-        for (int j = j_lo; j < j_hi; ++j) {
-            const int i = j - j_lo, ks = i % kKStages, vs = i % kVStages;
+        // Load i (0 .. n) brings the keys of tile j_lo + i and the values of tile j_lo + i - 1: what step j_lo + i - 1 of
+        // the tensor core reads (its PV and the S of the next tile), so one barrier covers a step.
+        const int n = j_hi - j_lo;
+        for (int i = 0; i <= n; ++i) {
+            const int st = i % kStages;
+            const bool has = which == 0 ? i < n : (which == 1 && i >= 1);
             int row = 0;
-            if (which < 2) {
+            if (has) {
+                const int j = j_lo + i - which;
                 int key = min(max(j * kTN + box * p.box_rows, key_lo), key_hi);      // outside the range: the nearest key inside it
                 key -= key % p.box_rows;
                 const int slot = key / p.page_size;
@@ -182,26 +184,20 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, const Tc
                 row = ((page * 2 + which) * p.KV + kvh) * p.page_size + key % p.page_size;
             }
             if (lane == 0) {
-                if (i >= kKStages) mbar_wait(k_empty + ks, ((i / kKStages) - 1) & 1, p.err);
-                mbar_expect_tx(k_full + ks, L::kTile);
+                if (i >= kStages) mbar_wait(kv_empty + st, ((i / kStages) - 1) & 1, p.err);
+                mbar_expect_tx(kv_full + st, L::kTile * ((i < n ? 1 : 0) + (i >= 1 ? 1 : 0)));
             }
             __syncwarp();
-            if (which == 0) tma_load_2d(sK + ks * L::kTile + half * 16384 + box * p.box_rows * 128, &kv_map, k_full + ks, half * 64, row);
-            if (lane == 0) {
-                if (i >= kVStages) mbar_wait(v_empty + vs, ((i / kVStages) - 1) & 1, p.err);
-                mbar_expect_tx(v_full + vs, L::kTile);
-            }
-            __syncwarp();
-            if (which == 1) tma_load_2d(sV + vs * L::kTile + half * 16384 + box * p.box_rows * 128, &kv_map, v_full + vs, half * 64, row);
+            if (has) tma_load_2d(sKV + (2 * st + which) * L::kTile + half * 16384 + box * p.box_rows * 128, &kv_map, kv_full + st, half * 64, row);
         }
     } else if (warp == 1) {
         if (lane == 0) {                             // ---- tensor-core issue ----
             constexpr uint32_t idesc_s = idesc_bf16(kTM, kTN, false);
             constexpr uint32_t idesc_pv = idesc_bf16(kTM, HD, true);
             auto active = [&](int x, int j) { return j >= t_lo[x] && j < t_hi[x]; };
-            auto issue_s = [&](int x, int j) {       // S_j(X); the K tile has been waited for
-                const int ks = (j - j_lo) % kKStages;
-                const uint32_t q_addr = smem_u32(sQ + x * L::kTile), k_addr = smem_u32(sK + ks * L::kTile);
+            auto issue_s = [&](int x, int j) {       // S_j(X); the stage with K_j has been waited for
+                const int st = (j - j_lo) % kStages;
+                const uint32_t q_addr = smem_u32(sQ + x * L::kTile), k_addr = smem_u32(sKV + 2 * st * L::kTile);
 #pragma unroll
                 for (int k = 0; k < HD / 16; ++k) {
                     const uint32_t off = (k >> 2) * 16384 + (k & 3) * 32;
@@ -209,52 +205,32 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, const Tc
                 }
                 tc_commit(s_ready + x);
             };
-            auto wait_k = [&](int j) {
-                const int i = j - j_lo;
-                mbar_wait(k_full + i % kKStages, (i / kKStages) & 1, p.err);
-                tc_after();
-            };
-            {
-                wait_k(j_lo);
+            mbar_wait(kv_full + 0, 0, p.err);        // the bytes came through the async proxy: the wait itself orders them
 #pragma unroll
-                for (int x = 0; x < 2; ++x)
-                    if (active(x, j_lo)) issue_s(x, j_lo);
-                tc_commit(k_empty + 0);
-            }
+            for (int x = 0; x < 2; ++x)
+                if (active(x, j_lo)) issue_s(x, j_lo);
+            tc_commit(kv_empty + 0);
             for (int j = j_lo; j < j_hi; ++j) {
-                const int i = j - j_lo, vs = i % kVStages;
-                bool have_v = false, have_k = false;
+                const int i = j - j_lo + 1, st = i % kStages;                  // load i: V_j and K_{j+1}
+                mbar_wait(kv_full + st, (i / kStages) & 1, p.err);
 #pragma unroll
                 for (int x = 0; x < 2; ++x) {
                     if (!active(x, j)) {
                         // a tile that starts later (window): its first S belongs to the round before its first PV
-                        if (j + 1 < j_hi && active(x, j + 1)) {
-                            if (!have_k) { wait_k(j + 1); have_k = true; }
-                            issue_s(x, j + 1);
-                        }
+                        if (j + 1 < j_hi && active(x, j + 1)) issue_s(x, j + 1);
                         continue;
                     }
                     mbar_wait(p_ready + x, (j - t_lo[x]) & 1, p.err);
-                    if (!have_v) { mbar_wait(v_full + vs, (i / kVStages) & 1, p.err); have_v = true; }
                     tc_after();
-                    const uint32_t v_addr = smem_u32(sV + vs * L::kTile);
+                    const uint32_t v_addr = smem_u32(sKV + (2 * st + 1) * L::kTile);
 #pragma unroll
                     for (int k = 0; k < kTN / 16; ++k)   // P: 16 keys = 8 columns of packed pairs; V: 16 keys further down
                         umma_ts(tO[x], tS[x] + k * 8, desc_sw128(v_addr + k * 16 * 128, 16384, 1024), idesc_pv,
                                 (j > t_lo[x] || k > 0) ? 1u : 0u);
-                    if (active(x, j + 1)) {
-                        if (!have_k) { wait_k(j + 1); have_k = true; }
-                        issue_s(x, j + 1);
-                    } else {
-                        tc_commit(o_done + x);
-                    }
+                    if (active(x, j + 1)) issue_s(x, j + 1);
+                    else tc_commit(o_done + x);
                 }
-                if (!have_v) mbar_wait(v_full + vs, (i / kVStages) & 1, p.err);    // nobody needed it: hand it back in order
-                tc_commit(v_empty + vs);
-                if (j + 1 < j_hi) {
-                    if (!have_k) wait_k(j + 1);          // nobody needs it: still hand the stage back in order
-                    tc_commit(k_empty + (i + 1) % kKStages);
-                }
+                tc_commit(kv_empty + st);
             }
         }
     }
