@@ -105,15 +105,23 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, const Tc
     int n_tok[2];
 #pragma unroll
     for (int x = 0; x < 2; ++x) n_tok[x] = max(0, min(tok_per_tile, q_len - q0 - x * tok_per_tile));
+    // r / g for r < 256 without a division (g <= 16): exact with this multiplier
+    const uint32_t g_mul = ((1u << 20) + g - 1) / g;
+    auto row_tok = [&](int r) { return static_cast<int>((static_cast<uint32_t>(r) * g_mul) >> 20); };
     // query rows: row r of tile x = (token x * tok_per_tile + r / g, head kvh * g + r % g); rows past the portion are zero.
-    // Warp 0 takes no part: it starts fetching keys as soon as the barriers exist.
+    // Warp 0 takes no part: it starts fetching keys as soon as the barriers exist.  Warp 1 asks for the tensor memory first.
     if (warp > 0) {
+        if (warp == 1) {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(tmem_slot)), "r"(512));
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
+        }
+        const __nv_bfloat16* q_base = p.q + (static_cast<int64_t>(cu0 + q0) * p.H + kvh * g) * HD;
         for (int i = threadIdx.x - 32; i < 2 * kTM * CPR; i += kTcThreads - 32) {
             const int row = i / CPR, c = i % CPR;
             const int x = row >> 7, r = row & 127;
-            const int tok = x * tok_per_tile + r / g;
-            const bool valid = r / g < n_tok[x];
-            const __nv_bfloat16* src = valid ? p.q + ((static_cast<int64_t>(cu0 + q0 + tok) * p.H + kvh * g + r % g) * HD + c * 8) : p.q;
+            const int t = row_tok(r), h = r - t * g;
+            const bool valid = t < n_tok[x];
+            const __nv_bfloat16* src = valid ? q_base + (static_cast<int64_t>(x * tok_per_tile + t) * p.H + h) * HD + c * 8 : p.q;
             cp_async16(reinterpret_cast<__nv_bfloat16*>(sQ + x * L::kTile) + tile_off(r, c), src, valid);
         }
         asm volatile("cp.async.commit_group;\n" ::: "memory");
@@ -145,10 +153,6 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, const Tc
         __syncwarp();
         asm volatile("bar.arrive 1, %0;\n" ::"n"(kTcThreads) : "memory");       // the others wait for this below
     } else {
-        if (warp == 1) {
-            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(tmem_slot)), "r"(512));
-            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
-        }
         asm volatile("cp.async.wait_group 0;\n" ::: "memory");
         fence_async_smem();                                         // the tensor core reads what these threads wrote
         tc_before();
@@ -164,9 +168,11 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, const Tc
     if (warp == 0) {
         // ---- producer: one lane per TMA box (page or 64 keys, times 64-column half, times K and V), so that the
         // block-table reads of a tile are in flight together instead of one after the other ----
-        const int boxes = kTN / p.box_rows, per_tile = boxes * (HD / 64);
-        const int which = lane / per_tile;           // 0: K, 1: V, above: idle lanes
-        const int box = (lane % per_tile) / (HD / 64), half = lane % (HD / 64);
+        // page size and box rows are powers of two: shifts and masks instead of divisions
+        const int box_shift = 31 - __clz(p.box_rows), page_shift = 31 - __clz(p.page_size);
+        const int per_tile_shift = (7 - box_shift) + (HD == 128 ? 1 : 0);          // boxes of a tile times 64-column halves
+        const int which = lane >> per_tile_shift;    // 0: K, 1: V, above: idle lanes
+        const int box = (lane & ((1 << per_tile_shift) - 1)) / (HD / 64), half = lane % (HD / 64);
         // Load i (0 .. n) brings the keys of tile j_lo + i and the values of tile j_lo + i - 1: what step j_lo + i - 1 of
         // the tensor core reads (its PV and the S of the next tile), so one barrier covers a step.
         const int n = j_hi - j_lo;
@@ -177,11 +183,11 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, const Tc
             if (has) {
                 const int j = j_lo + i - which;
                 int key = min(max(j * kTN + box * p.box_rows, key_lo), key_hi);      // outside the range: the nearest key inside it
-                key -= key % p.box_rows;
-                const int slot = key / p.page_size;
+                key &= ~(p.box_rows - 1);
+                const int slot = key >> page_shift;
                 int page = slot < p.table_width ? table[slot] : -1;
                 if (page < 0 || page >= p.num_pages) { atomicExch(p.err, 4); page = 0; }
-                row = ((page * 2 + which) * p.KV + kvh) * p.page_size + key % p.page_size;
+                row = (((page * 2 + which) * p.KV + kvh) << page_shift) + (key & (p.page_size - 1));
             }
             if (lane == 0) {
                 if (i >= kStages) mbar_wait(kv_empty + st, ((i / kStages) - 1) & 1, p.err);
@@ -241,7 +247,8 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, const Tc
         const int r = quarter * 32 + lane;           // row within the tile
         const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
         if (t_lo[x] < t_hi[x]) {
-            const int tok_in_tile = min(r / g, n_tok[x] - 1);
+            const int r_tok = row_tok(r);
+            const int tok_in_tile = min(r_tok, n_tok[x] - 1);
             const int tok = x * tok_per_tile + tok_in_tile;
             const int row_pos = p.positions[cu0 + q0 + tok];
             const int row_lo = p.window > 0 ? max(0, row_pos - p.window + 1) : 0;
@@ -255,12 +262,15 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, const Tc
 #pragma unroll
                 for (int c = 0; c < 4; ++c) tm_load32(tS[x] + lane_base + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&v[c * 32]));
                 tm_wait_ld();
-                if (key0 + 127 > row_pos || key0 < row_lo) {
+                if (key0 + 127 > row_pos) {                                    // keys after the row's own: -inf
+                    const int n_keep = row_pos - key0 + 1;
 #pragma unroll
-                    for (int c = 0; c < 128; ++c) {
-                        const int key = key0 + c;
-                        if (key > row_pos || key < row_lo) v[c] = 0xff800000u;     // -inf
-                    }
+                    for (int c = 0; c < 128; ++c) v[c] = c < n_keep ? v[c] : 0xff800000u;
+                }
+                if (key0 < row_lo) {                                           // keys before the row's window
+                    const int n_drop = row_lo - key0;
+#pragma unroll
+                    for (int c = 0; c < 128; ++c) v[c] = c < n_drop ? 0xff800000u : v[c];
                 }
                 float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};       // four chains of three-input maxima
 #pragma unroll
@@ -312,25 +322,37 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, const Tc
             }
             mbar_wait(o_done + x, 0, p.err);
             tc_after();
-            const bool valid = r / g < n_tok[x];
+            // The rows go through shared memory (over the query tile, which no product reads any more, in its swizzled
+            // layout) so that the stores to global memory are whole rows side by side: a thread that stored its own row
+            // would touch 32 lines with every instruction.
             const float inv = l > 0.f ? 1.f / l : 0.f;
-            __nv_bfloat16* dst = p.out + (static_cast<int64_t>(cu0 + q0 + tok) * p.H + kvh * g + r % g) * HD;
+            __nv_bfloat16* stage = reinterpret_cast<__nv_bfloat16*>(sQ + x * L::kTile);
+            uint32_t o[HD];
 #pragma unroll
-            for (int c = 0; c < HD; c += 32) {
-                uint32_t o[32];
-                tm_load32(tO[x] + lane_base + c, o);
-                tm_wait_ld();
-                if (valid) {
+            for (int c = 0; c < HD; c += 32) tm_load32(tO[x] + lane_base + c, *reinterpret_cast<uint32_t(*)[32]>(&o[c]));
+            tm_wait_ld();
 #pragma unroll
-                    for (int k = 0; k < 32; k += 8) {
-                        uint4 t;
-                        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&t);
+            for (int k = 0; k < HD; k += 8) {
+                uint4 t;
+                __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&t);
 #pragma unroll
-                        for (int e = 0; e < 4; ++e)
-                            h[e] = __floats2bfloat162_rn(__uint_as_float(o[k + 2 * e]) * inv, __uint_as_float(o[k + 2 * e + 1]) * inv);
-                        *reinterpret_cast<uint4*>(dst + c + k) = t;
-                    }
-                }
+                for (int e = 0; e < 4; ++e)
+                    h[e] = __floats2bfloat162_rn(__uint_as_float(o[k + 2 * e]) * inv, __uint_as_float(o[k + 2 * e + 1]) * inv);
+                *reinterpret_cast<uint4*>(stage + tile_off(r, k >> 3)) = t;
+            }
+            asm volatile("bar.sync %0, 128;\n" ::"r"(2 + x) : "memory");       // the 128 threads of this query tile
+            __nv_bfloat16* out_base = p.out + ((static_cast<int64_t>(cu0 + q0) + x * tok_per_tile) * p.H + kvh * g) * HD;
+            // thread r takes chunk r % CPR of the rows r / CPR + k * (128 / CPR): a row's chunks lie in neighbouring lanes
+            constexpr int kRowsPerPass = kTM / CPR;
+            const int c = r % CPR;
+            uint4 held[CPR];
+#pragma unroll
+            for (int k = 0; k < CPR; ++k) held[k] = *reinterpret_cast<const uint4*>(stage + tile_off(r / CPR + k * kRowsPerPass, c));
+#pragma unroll
+            for (int k = 0; k < CPR; ++k) {
+                const int row = r / CPR + k * kRowsPerPass;
+                const int t = row_tok(row), h = row - t * g;
+                if (t < n_tok[x]) *reinterpret_cast<uint4*>(out_base + (static_cast<int64_t>(t) * p.H + h) * HD + c * 8) = held[k];
             }
         }
     }
