@@ -280,8 +280,9 @@ class CacheManager:
     def can_reserve(self, request_id, upto_len: int) -> bool:
         return all(n <= p.num_free for n, p in zip(self.pages_missing(request_id, upto_len), self.pools))
 
-    def reserve(self, request_id, upto_len: int) -> None:
-        """Cover positions below `upto_len` with pages, in every group.  All or nothing."""
+    def reserve(self, request_id, upto_len: int) -> int:
+        """Cover positions below `upto_len` with pages, in every group.  All or nothing.  Returns how many tokens the
+        request's tables cover now (in every group), so that a caller can skip the call while it stays within that."""
         lease = self.lease(request_id)
         need = self.pages_missing(request_id, upto_len)
         for g, n in enumerate(need):
@@ -293,6 +294,7 @@ class CacheManager:
             first = self._first_needed_page(g, lease.computed)
             while len(table) < target:
                 table.append(self.pools[g].take() if len(table) >= first else -1)
+        return min((len(t) for t in lease.tables), default=target) * self.page_size
 
     def advance(self, request_id, computed: int) -> None:
         """Record that the request's first `computed` tokens are in the cache; windowed groups give back the

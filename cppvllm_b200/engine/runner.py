@@ -244,7 +244,33 @@ class ModelRunner:
         cu[0] = 0
         G = len(self.group_specs)
         mirror_rows = []
-        for s, e in enumerate(entries):
+        decode_only = bool(entries) and T == S and R == S and all(len(e.want) == 1 for e in entries)
+        if decode_only:
+            # decoded tokens only, each with its logits wanted: the arrays are filled whole instead of entry by entry
+            leases = [self.cache.lease(e.request_id) for e in entries]
+            mirror_rows = [self._mirror_row(lease, W) for lease in leases]
+            starts = np.fromiter((e.start for e in entries), dtype=np.int32, count=S)
+            ar = np.arange(S, dtype=np.int32)
+            tokens[:S] = [e.tokens[0] for e in entries]
+            positions[:S] = starts
+            seq_of[:S] = ar
+            rows[:S] = ar
+            cu[1:S + 1] = ar + 1
+            kvl[:S] = starts + 1
+            sts[:S] = mirror_rows                              # a request's mirror row is its state slot
+            page_idx = starts // ps
+            if (page_idx >= W).any():
+                raise RuntimeError("pages for a decoded token's position were not reserved")
+            idx_rows = np.asarray(mirror_rows, dtype=np.int64)
+            for g in range(G):
+                tables[g][:S, :] = self._tab_mirror[g][idx_rows, :W]
+                page = tables[g][ar, page_idx]
+                if (page < 0).any():
+                    bad = entries[int(np.argmax(page < 0))]
+                    raise RuntimeError(f"request {bad.request_id!r}: a token of this step has no page in group {g}")
+                slots[g][:S] = page * ps + starts % ps
+            t = r = S
+        for s, e in enumerate(() if decode_only else entries):
             n = len(e.tokens)
             lease = self.cache.lease(e.request_id)
             start = e.start
@@ -288,7 +314,7 @@ class ModelRunner:
                     raise RuntimeError(f"request {e.request_id!r}: a token of this step has no page in group {g}")
                 slots[g][t:t + n] = page_of * ps + pos % ps
             t += n
-        if entries:
+        if entries and not decode_only:
             idx_rows = np.asarray(mirror_rows, dtype=np.int64)
             for g in range(G):
                 tables[g][:S, :] = self._tab_mirror[g][idx_rows, :W]

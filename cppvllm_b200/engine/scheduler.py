@@ -46,7 +46,7 @@ PENDING = -1        # placeholder for a token that was sampled on the device but
 class Sequence:
     """One request: its tokens (prompt, then generated), how many are in the cache, and its options."""
     __slots__ = ("seq_id", "token_ids", "num_prompt_tokens", "num_cached_tokens", "num_scheduled_tokens",
-                 "params", "status", "stopped_on_eos", "row_seed", "num_preemptions", "num_inflight")
+                 "params", "status", "stopped_on_eos", "row_seed", "num_preemptions", "num_inflight", "capacity")
 
     def __init__(self, seq_id: int, prompt: Seq[int], params: Optional[SamplingParams] = None):
         if len(prompt) == 0:
@@ -62,6 +62,7 @@ class Sequence:
         self.row_seed = 0
         self.num_preemptions = 0
         self.num_inflight = 0
+        self.capacity = 0            # tokens that the pages reserved for it cover (the scheduler's copy of the cache's answer)
 
     def __len__(self) -> int:
         return len(self.token_ids)
@@ -130,6 +131,7 @@ class Scheduler:
         seq.num_cached_tokens = 0
         seq.num_scheduled_tokens = 0
         seq.num_preemptions += 1
+        seq.capacity = 0
         self.waiting.appendleft(seq)
         self.num_preemptions += 1
 
@@ -152,15 +154,17 @@ class Scheduler:
         blocked = False
         while pending:
             seq = pending.popleft()
-            if seq.num_completion_tokens > 0 and seq.num_completion_tokens >= seq.params.max_tokens:
+            n_tok = len(seq.token_ids)
+            done = n_tok - seq.num_prompt_tokens
+            if done > 0 and done >= seq.params.max_tokens:
                 kept.append(seq)                       # its last token is still in flight
                 continue
-            want = min(seq.num_uncached_tokens, budget, cap)
+            want = min(n_tok - seq.num_cached_tokens, budget, cap)
             if want <= 0 or len(out.seqs) >= self.cfg.max_num_seqs:
                 kept.append(seq)
                 continue
             yielded = stuck = False
-            covered = self.cache.covered(seq.seq_id, len(seq))     # most decode steps need no new page
+            covered = n_tok <= seq.capacity                        # most decode steps need no new page
             while not covered and not self.cache.can_reserve(seq.seq_id, len(seq)):
                 if not allow_preempt:
                     stuck = True
@@ -181,7 +185,7 @@ class Scheduler:
             if yielded:
                 continue
             if not covered:
-                self.cache.reserve(seq.seq_id, len(seq))
+                seq.capacity = self.cache.reserve(seq.seq_id, n_tok)
             push(seq, want)
             kept.append(seq)
         self.running = kept
@@ -195,7 +199,7 @@ class Scheduler:
             self.waiting.popleft()
             lease = self.cache.admit(seq.seq_id, seq.token_ids)      # with the prefix cache: shared pages count as computed
             seq.num_cached_tokens = lease.computed
-            self.cache.reserve(seq.seq_id, len(seq))
+            seq.capacity = self.cache.reserve(seq.seq_id, len(seq))
             seq.status = RUNNING
             self.running.append(seq)
             push(seq, min(seq.num_uncached_tokens, budget, cap))
