@@ -168,7 +168,7 @@ def main():
     t_build = time.time()
     model_dir = write_random_model(os.path.join(tmp, "qwen3_0p6b_random"), cfg, seed=0, std=0.02, norm_spread=0.0)
     max_b = B if args.no_points else max(B, 256)                # 256: the reference's throughput workload (bench.cpp)
-    max_len = CTX + 64
+    max_len = max(CTX + 64, PREFILL_TOKENS)              # the prefill point needs its 2,048 positions at any --context
     page = 32
     llm = LLMEngine(EngineConfig(model_path=model_dir, dtype="bfloat16", max_num_batched_tokens=8192, max_num_seqs=max_b,
                                  max_chunk_tokens=4096, max_model_len=max_len, block_size=page,

@@ -79,8 +79,11 @@ class Sampler:
         self._temps[slot][:R].copy_(self._host_f[slot][:R], non_blocking=True)
         self._pos[slot][:R].copy_(self._host_p[slot][:R], non_blocking=True)
         self._seeds[slot][:R].copy_(self._host_s[slot][:R], non_blocking=True)
-        # a large vocabulary is searched by several blocks per row, unless the rows alone fill the device
-        chunks = self._chunks if logits.shape[1] >= 16384 and R <= 64 else 0
+        # a large vocabulary is searched by several blocks per row: 32 at few rows, fewer at many, so that there are
+        # a couple of thousand blocks (one block per row reads its 600 KB of logits at a seventh of the bandwidth)
+        chunks = max(1, min(self._chunks, 2048 // max(R, 1))) if logits.shape[1] >= 16384 else 0
+        if chunks < 2:
+            chunks = 0
         ops.sample(self._out[slot][:R], logits, None, self._temps[slot], self._seeds[slot], self._pos[slot], num_rows=R,
                    scratch=self._scratch if chunks else None, chunks=chunks)
         self._out_host[slot][:R].copy_(self._out[slot][:R], non_blocking=True)
