@@ -9,7 +9,9 @@ because a TMA box is one page of one head and boxes of 32 rows reach the full HB
 every step's samples before the next step is scheduled) and ``enable_prefix_caching`` (requests share the cache pages
 of a common prefix; always on in the reference, engine/block_manager.cpp:71-143; off by default here) and
 ``use_ref_kernels`` (every part uses its plain twin kernels: the general attention kernel, library products with separate
-norm and activation kernels; for comparing the fast kernels with, inside the whole engine).
+norm and activation kernels; for comparing the fast kernels with, inside the whole engine) and ``native_cache_manager``
+(the cache manager in C++, as the reference's block manager is, engine/block_manager.cpp; false = its plain twin in
+Python, which the tests compare it with).
 """
 from __future__ import annotations
 
@@ -51,6 +53,7 @@ class EngineConfig:
     pipeline_depth: int = 2
     enable_prefix_caching: bool = False
     use_ref_kernels: bool = False
+    native_cache_manager: bool = True
     device: str = "cuda:0"
 
     def __post_init__(self):

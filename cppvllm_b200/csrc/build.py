@@ -38,6 +38,7 @@ LIBRARIES: Dict[str, List[str]] = {
     "gemm_bf16": ["gemm_tcgen05.cu"],
     "decode_fused": ["decode_fused.cu"],
     "attn_tcgen05": ["attention_tcgen05.cu"],
+    "runtime": ["cache_runtime.cpp"],          # host code only (the cache manager); nvcc hands it to the host compiler
 }
 
 _HEADERS = ["common.cuh", "sm100.cuh", "tensor_map.cuh", "attention_bf16.h"]

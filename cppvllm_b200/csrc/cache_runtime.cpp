@@ -1,0 +1,432 @@
+// Host-side bookkeeping of the paged cache in C++: page pools, block tables, state slots and the optional prefix cache,
+// with the policy of cache/manager.py (which states it and remains the plain twin that the tests compare this with).
+// No device memory is touched here.  After the reference's BlockManager (engine/block_manager.cpp): pages are handed out
+// least-recently-freed first (:35-69), a request's pages are given back last-logical-page first (:145-153), a page that is
+// given back keeps what it was registered as until it is taken for other contents (:52-69), and the prefix cache chains
+// the keys of full pages (:10-24, 71-143).
+//
+// What differs from the Python twin is the shape of the data, chosen for the step function that reads it every step:
+// the block tables of all live requests of a group are ONE dense int32 array [state slot][table width], -1 where nothing
+// is held, so a step copies whole rows to its staging buffer instead of converting lists; a request is known by its state
+// slot (the Python wrapper maps request ids to slots).  Every entry point is plain C (called through ctypes) and returns
+// a status; nothing throws across the boundary.
+#include <cstdint>
+#include <cstring>
+#include <queue>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+namespace {
+
+constexpr int kOk = 0;
+constexpr int kErrMisuse = -1;      // unknown or double admission, double free, shrinking length
+constexpr int kErrOutOfPages = -2;  // a reservation needs more pages than a group has free
+constexpr int kErrWidth = -3;       // a table would grow beyond the width of the dense array
+constexpr int kErrNoSlot = -4;      // no free state slot
+constexpr int kErrArgument = -5;
+
+inline uint64_t mix64(uint64_t x) {  // splitmix64 finaliser
+    x += 0x9e3779b97f4a7c15ULL;
+    x = (x ^ (x >> 30)) * 0xbf58476d1ce4e5b9ULL;
+    x = (x ^ (x >> 27)) * 0x94d049bb133111ebULL;
+    return x ^ (x >> 31);
+}
+
+// Pages of one group.  The free list is a doubly linked list threaded through the page numbers (a registered page that
+// lies on it can be taken out of its middle when a new request shares it).
+struct Pool {
+    int n = 0, page_size = 0;
+    bool keyed = false;                       // prefix cache on: pages can be registered
+    std::vector<int> refs, prev, next;
+    std::vector<char> on_free;
+    int head = -1, tail = -1, free_count = 0;
+    std::vector<char> has_key;
+    std::vector<uint64_t> key;
+    std::vector<int> tokens;                  // [n][page_size], contents of registered pages
+    std::unordered_map<uint64_t, int> by_key;
+
+    void init(int num_pages, int ps, bool with_keys) {
+        n = num_pages; page_size = ps; keyed = with_keys;
+        refs.assign(n, 0); prev.assign(n, -1); next.assign(n, -1); on_free.assign(n, 0);
+        has_key.assign(n, 0); key.assign(n, 0);
+        if (keyed) tokens.assign(static_cast<size_t>(n) * ps, 0);
+        head = tail = -1; free_count = 0;
+        for (int p = 0; p < n; ++p) push_tail(p);
+    }
+    void push_tail(int p) {
+        prev[p] = tail; next[p] = -1;
+        if (tail >= 0) next[tail] = p; else head = p;
+        tail = p; on_free[p] = 1; ++free_count;
+    }
+    void unlink(int p) {
+        if (prev[p] >= 0) next[prev[p]] = next[p]; else head = next[p];
+        if (next[p] >= 0) prev[next[p]] = prev[p]; else tail = prev[p];
+        prev[p] = next[p] = -1; on_free[p] = 0; --free_count;
+    }
+    // a page for new contents: the least recently freed one; what it was registered as is forgotten
+    int take() {
+        if (head < 0) return -1;
+        const int p = head;
+        unlink(p);
+        if (has_key[p]) {
+            auto it = by_key.find(key[p]);
+            if (it != by_key.end() && it->second == p) by_key.erase(it);
+            has_key[p] = 0;
+        }
+        refs[p] = 1;
+        return p;
+    }
+    bool give_back(int p) {
+        if (p < 0 || p >= n || refs[p] <= 0) return false;
+        if (--refs[p] == 0) push_tail(p);     // to the tail; it keeps its key until taken again
+        return true;
+    }
+    void share(int p) {                       // one more holder of a registered page
+        if (refs[p] == 0) unlink(p);
+        ++refs[p];
+    }
+    uint64_t chain_key(bool has_prefix, uint64_t prefix, const int* toks) const {
+        uint64_t h = mix64(has_prefix ? prefix ^ 0x5851f42d4c957f2dULL : 0x2545f4914f6cdd1dULL);
+        for (int i = 0; i < page_size; ++i) h = mix64(h ^ static_cast<uint64_t>(static_cast<uint32_t>(toks[i])));
+        return h;
+    }
+    // the page registered for these tokens after that prefix, or -1; the key either way
+    int find(bool has_prefix, uint64_t prefix, const int* toks, uint64_t* key_out) const {
+        const uint64_t k = chain_key(has_prefix, prefix, toks);
+        *key_out = k;
+        auto it = by_key.find(k);
+        if (it == by_key.end()) return -1;
+        const int p = it->second;
+        if (std::memcmp(&tokens[static_cast<size_t>(p) * page_size], toks, sizeof(int) * page_size) != 0) return -1;
+        return p;
+    }
+    // record what a held page contains; the first page registered under a key keeps it
+    uint64_t register_page(int p, bool has_prefix, uint64_t prefix, const int* toks) {
+        if (!has_key[p]) {
+            const uint64_t k = chain_key(has_prefix, prefix, toks);
+            key[p] = k; has_key[p] = 1;
+            std::memcpy(&tokens[static_cast<size_t>(p) * page_size], toks, sizeof(int) * page_size);
+            by_key.emplace(k, p);             // keeps an earlier page of the same key
+        }
+        return key[p];
+    }
+};
+
+struct Manager {
+    int page_size = 0, width = 0, num_slots = 0, num_groups = 0;
+    bool prefix_caching = false;
+    long long prefix_hits = 0;
+    std::vector<int> window;
+    std::vector<Pool> pools;
+    std::vector<std::vector<int>> tables;     // per group [num_slots][width], -1 where nothing is held
+    std::vector<std::vector<int>> table_len;  // per group [num_slots]
+    std::vector<std::vector<int>> first_held; // per group [num_slots]: first logical page still held (windowed groups)
+    std::vector<char> held;                   // per slot
+    std::vector<int> computed, registered;    // per slot
+    std::priority_queue<int, std::vector<int>, std::greater<int>> free_slots;   // lowest number first
+    std::vector<int> fresh;
+    std::string message;                      // of the last failed self-check
+
+    int pages_for(int length) const { return (length + page_size - 1) / page_size; }
+    int first_needed(int g, int comp) const {
+        const int w = window[g];
+        if (w <= 0) return 0;
+        const int lo = comp - w + 1;           // the next token sits at `comp` and reads positions >= comp - w + 1
+        return (lo > 0 ? lo : 0) / page_size;
+    }
+    int* row(int g, int slot) { return &tables[g][static_cast<size_t>(slot) * width]; }
+    bool live(int slot) const { return slot >= 0 && slot < num_slots && held[slot]; }
+    // pages to take in group g so that positions first_needed .. upto_len - 1 are covered
+    int missing(int g, int slot, int upto_len) const {
+        const int have = table_len[g][slot];
+        const int fn = first_needed(g, computed[slot]);
+        const int first = have > fn ? have : fn;
+        const int need = pages_for(upto_len) - first;
+        return need > 0 ? need : 0;
+    }
+    // [(page, key)] of the longest registered chain that matches the prefix of the tokens
+    int prefix_pages(const int* toks, int n, std::vector<int>* pages) const {
+        pages->clear();
+        if (!prefix_caching || toks == nullptr) return 0;
+        const Pool& pool = pools[0];
+        bool has = false;
+        uint64_t key = 0;
+        for (int i = 0; i < (n - 1) / page_size; ++i) {     // at least one token is always computed
+            const int* chunk = toks + static_cast<size_t>(i) * page_size;
+            bool known = true;
+            for (int k = 0; k < page_size; ++k) known = known && chunk[k] >= 0;
+            if (!known) break;
+            uint64_t k2;
+            const int p = pool.find(has, key, chunk, &k2);
+            if (p < 0) break;
+            pages->push_back(p);
+            has = true; key = k2;
+        }
+        return static_cast<int>(pages->size());
+    }
+};
+
+inline Manager* M(void* h) { return static_cast<Manager*>(h); }
+
+}  // namespace
+
+extern "C" {
+
+void* cvb_cm_create(int num_groups, const int* num_pages, const int* windows, int page_size, int num_slots, int width,
+                    int prefix_caching) {
+    if (num_groups <= 0 || page_size <= 0 || num_slots <= 0 || width <= 0) return nullptr;
+    if (prefix_caching && !(num_groups == 1 && windows[0] <= 0)) return nullptr;
+    for (int g = 0; g < num_groups; ++g)
+        if (num_pages[g] <= 0) return nullptr;
+    Manager* m = new Manager();
+    m->page_size = page_size; m->width = width; m->num_slots = num_slots; m->num_groups = num_groups;
+    m->prefix_caching = prefix_caching != 0;
+    m->window.assign(windows, windows + num_groups);
+    m->pools.resize(num_groups);
+    m->tables.resize(num_groups); m->table_len.resize(num_groups); m->first_held.resize(num_groups);
+    for (int g = 0; g < num_groups; ++g) {
+        m->pools[g].init(num_pages[g], page_size, m->prefix_caching);
+        m->tables[g].assign(static_cast<size_t>(num_slots) * width, -1);
+        m->table_len[g].assign(num_slots, 0);
+        m->first_held[g].assign(num_slots, 0);
+    }
+    m->held.assign(num_slots, 0); m->computed.assign(num_slots, 0); m->registered.assign(num_slots, 0);
+    for (int s = 0; s < num_slots; ++s) m->free_slots.push(s);
+    return m;
+}
+
+void cvb_cm_destroy(void* h) { delete M(h); }
+
+// Arrays that the wrapper reads in place (they never move): a group's dense block tables and their lengths, and the
+// per-slot counters.
+int* cvb_cm_tables(void* h, int g) { return M(h)->tables[g].data(); }
+int* cvb_cm_table_len(void* h, int g) { return M(h)->table_len[g].data(); }
+int* cvb_cm_computed(void* h) { return M(h)->computed.data(); }
+int* cvb_cm_registered(void* h) { return M(h)->registered.data(); }
+int cvb_cm_num_free(void* h, int g) { return M(h)->pools[g].free_count; }
+int cvb_cm_num_free_slots(void* h) { return static_cast<int>(M(h)->free_slots.size()); }
+int cvb_cm_refs(void* h, int g, int page) {
+    Manager* m = M(h);
+    return page >= 0 && page < m->pools[g].n ? m->pools[g].refs[page] : -1;
+}
+long long cvb_cm_prefix_hits(void* h) { return M(h)->prefix_hits; }
+
+// Whether a request with these tokens could be admitted and covered up to `upto_len` now.  Registered pages that somebody
+// holds cost nothing; registered pages on the free list are counted as taken from it.
+int cvb_cm_can_admit(void* h, const int* tokens, int n_tokens, int upto_len) {
+    Manager* m = M(h);
+    if (m->free_slots.empty()) return 0;
+    std::vector<int> pages;
+    m->prefix_pages(tokens, n_tokens, &pages);
+    int shared = 0;
+    for (int p : pages) shared += m->pools[0].refs[p] > 0 ? 1 : 0;
+    const int need = m->pages_for(upto_len);
+    for (int g = 0; g < m->num_groups; ++g)
+        if ((g == 0 ? need - shared : need) > m->pools[g].free_count) return 0;
+    return 1;
+}
+
+// A new request: returns its state slot.  With the prefix cache and the request's tokens, the pages of its longest
+// registered prefix are shared with it and count as computed.
+int cvb_cm_admit(void* h, const int* tokens, int n_tokens) {
+    Manager* m = M(h);
+    if (m->free_slots.empty()) return kErrNoSlot;
+    std::vector<int> pages;
+    m->prefix_pages(tokens, n_tokens, &pages);
+    if (static_cast<int>(pages.size()) > m->width) return kErrWidth;
+    const int slot = m->free_slots.top();
+    m->free_slots.pop();
+    m->held[slot] = 1;
+    for (int g = 0; g < m->num_groups; ++g) { m->table_len[g][slot] = 0; m->first_held[g][slot] = 0; }
+    int* tab = m->row(0, slot);
+    for (size_t i = 0; i < pages.size(); ++i) {
+        m->pools[0].share(pages[i]);
+        tab[i] = pages[i];
+    }
+    m->table_len[0][slot] = static_cast<int>(pages.size());
+    m->registered[slot] = m->prefix_caching ? static_cast<int>(pages.size()) : 0;
+    m->computed[slot] = m->registered[slot] * m->page_size;
+    m->prefix_hits += m->registered[slot];
+    m->fresh.push_back(slot);
+    return slot;
+}
+
+// Register the request's full pages whose keys are in the cache and whose tokens are all known.
+int cvb_cm_commit(void* h, int slot, const int* tokens, int n_tokens) {
+    Manager* m = M(h);
+    if (!m->prefix_caching) return kOk;
+    if (!m->live(slot)) return kErrMisuse;
+    Pool& pool = m->pools[0];
+    const int* tab = m->row(0, slot);
+    const int upto = m->computed[slot] < n_tokens ? m->computed[slot] : n_tokens;
+    const int full = upto / m->page_size;
+    int i = m->registered[slot];
+    while (i < full) {
+        const int* chunk = tokens + static_cast<size_t>(i) * m->page_size;
+        bool known = true;
+        for (int k = 0; k < m->page_size; ++k) known = known && chunk[k] >= 0;
+        if (!known) break;                                 // a token that is not known on the host yet
+        const bool has_prefix = i > 0 && pool.has_key[tab[i - 1]];
+        pool.register_page(tab[i], has_prefix, has_prefix ? pool.key[tab[i - 1]] : 0, chunk);
+        ++i;
+    }
+    m->registered[slot] = i;
+    return kOk;
+}
+
+int cvb_cm_take_fresh_slots(void* h, int* out, int max_out) {
+    Manager* m = M(h);
+    int n = 0;
+    for (int s : m->fresh)
+        if (n < max_out) out[n++] = s;
+    m->fresh.clear();
+    return n;
+}
+
+int cvb_cm_pages_missing(void* h, int slot, int upto_len, int* out) {
+    Manager* m = M(h);
+    if (!m->live(slot)) return kErrMisuse;
+    for (int g = 0; g < m->num_groups; ++g) out[g] = m->missing(g, slot, upto_len);
+    return kOk;
+}
+
+int cvb_cm_covered(void* h, int slot, int upto_len) {
+    Manager* m = M(h);
+    if (!m->live(slot)) return kErrMisuse;
+    const int need = m->pages_for(upto_len);
+    for (int g = 0; g < m->num_groups; ++g)
+        if (m->table_len[g][slot] < need) return 0;
+    return 1;
+}
+
+int cvb_cm_can_reserve(void* h, int slot, int upto_len) {
+    Manager* m = M(h);
+    if (!m->live(slot)) return kErrMisuse;
+    for (int g = 0; g < m->num_groups; ++g)
+        if (m->missing(g, slot, upto_len) > m->pools[g].free_count) return 0;
+    return 1;
+}
+
+// Cover positions below `upto_len` with pages, in every group; all or nothing.  Returns how many tokens the request's
+// tables cover now, or an error.
+int cvb_cm_reserve(void* h, int slot, int upto_len) {
+    Manager* m = M(h);
+    if (!m->live(slot)) return kErrMisuse;
+    const int target = m->pages_for(upto_len);
+    for (int g = 0; g < m->num_groups; ++g)
+        if (m->missing(g, slot, upto_len) > m->pools[g].free_count) return kErrOutOfPages;
+    if (target > m->width) return kErrWidth;
+    int covered = 0x7fffffff;
+    for (int g = 0; g < m->num_groups; ++g) {
+        int* tab = m->row(g, slot);
+        int& len = m->table_len[g][slot];
+        const int first = m->first_needed(g, m->computed[slot]);
+        while (len < target) {
+            tab[len] = len >= first ? m->pools[g].take() : -1;
+            ++len;
+        }
+        if (len < covered) covered = len;
+    }
+    return covered * m->page_size;
+}
+
+// The request's first `computed` tokens are in the cache; windowed groups give back the pages that no later token can
+// read.
+int cvb_cm_advance(void* h, int slot, int computed) {
+    Manager* m = M(h);
+    if (!m->live(slot) || computed < m->computed[slot]) return kErrMisuse;
+    m->computed[slot] = computed;
+    for (int g = 0; g < m->num_groups; ++g) {
+        if (m->window[g] <= 0) continue;
+        int* tab = m->row(g, slot);
+        const int len = m->table_len[g][slot];
+        int upto = m->first_needed(g, computed);
+        if (upto > len) upto = len;
+        for (int i = m->first_held[g][slot]; i < upto; ++i)
+            if (tab[i] >= 0) {
+                m->pools[g].give_back(tab[i]);
+                tab[i] = -1;
+            }
+        if (upto > m->first_held[g][slot]) m->first_held[g][slot] = upto;
+    }
+    return kOk;
+}
+
+int cvb_cm_release(void* h, int slot) {
+    Manager* m = M(h);
+    if (!m->live(slot)) return kErrMisuse;
+    for (int g = 0; g < m->num_groups; ++g) {
+        int* tab = m->row(g, slot);
+        for (int i = m->table_len[g][slot] - 1; i >= 0; --i) {   // last logical page first: prefix pages survive longest
+            if (tab[i] >= 0) m->pools[g].give_back(tab[i]);
+            tab[i] = -1;
+        }
+        m->table_len[g][slot] = 0;
+        m->first_held[g][slot] = 0;
+    }
+    m->held[slot] = 0;
+    m->computed[slot] = 0;
+    m->registered[slot] = 0;
+    m->free_slots.push(slot);
+    for (size_t i = 0; i < m->fresh.size(); ++i)
+        if (m->fresh[i] == slot) { m->fresh.erase(m->fresh.begin() + i); break; }
+    return kOk;
+}
+
+// Every page is either free exactly once or held, by as many requests as its reference count says and by each at most
+// once (more than one holder only with the prefix cache); no state slot is lost.  0 if so; else the message tells.
+int cvb_cm_check(void* h) {
+    Manager* m = M(h);
+    m->message.clear();
+    auto fail = [&](const std::string& s) { m->message = s; return -1; };
+    for (int g = 0; g < m->num_groups; ++g) {
+        Pool& pool = m->pools[g];
+        std::vector<int> on_list(pool.n, 0), holders(pool.n, 0);
+        int count = 0, last = -1;
+        for (int p = pool.head; p >= 0; p = pool.next[p]) {
+            if (++count > pool.n) return fail("group " + std::to_string(g) + ": the free list has a cycle");
+            if (on_list[p]++) return fail("group " + std::to_string(g) + ": a page is in the free list twice");
+            if (pool.prev[p] != last) return fail("group " + std::to_string(g) + ": the free list's links disagree");
+            last = p;
+        }
+        if (count != pool.free_count || last != pool.tail) return fail("group " + std::to_string(g) + ": the free list's count or tail is off");
+        for (int s = 0; s < m->num_slots; ++s) {
+            const int* tab = m->row(g, s);
+            if (!m->held[s]) {
+                for (int i = 0; i < m->width; ++i)
+                    if (tab[i] != -1) return fail("a slot that nobody holds has a page in its table");
+                continue;
+            }
+            std::vector<int> mine;
+            for (int i = 0; i < m->width; ++i) {
+                if (i >= m->table_len[g][s] && tab[i] != -1) return fail("a table has a page beyond its length");
+                if (tab[i] >= 0) {
+                    for (int q : mine)
+                        if (q == tab[i]) return fail("group " + std::to_string(g) + ": a request holds a page twice");
+                    mine.push_back(tab[i]);
+                    ++holders[tab[i]];
+                }
+            }
+        }
+        for (int p = 0; p < pool.n; ++p) {
+            if (holders[p] != pool.refs[p])
+                return fail("group " + std::to_string(g) + ": page " + std::to_string(p) + " is held by " + std::to_string(holders[p]) +
+                            " requests but counts " + std::to_string(pool.refs[p]));
+            if ((holders[p] == 0) != (on_list[p] == 1))
+                return fail("group " + std::to_string(g) + ": page " + std::to_string(p) + " is free and held, or neither");
+            if (holders[p] > 1 && !m->prefix_caching) return fail("group " + std::to_string(g) + ": a page is held by several requests");
+        }
+        for (auto& kv : pool.by_key)
+            if (!pool.has_key[kv.second] || pool.key[kv.second] != kv.first)
+                return fail("group " + std::to_string(g) + ": key of a page and the key table disagree");
+    }
+    int held = 0;
+    for (int s = 0; s < m->num_slots; ++s) held += m->held[s] ? 1 : 0;
+    if (held + static_cast<int>(m->free_slots.size()) != m->num_slots) return fail("a state slot is lost");
+    return 0;
+}
+
+const char* cvb_cm_message(void* h) { return M(h)->message.c_str(); }
+
+}  // extern "C"

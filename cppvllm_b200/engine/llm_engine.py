@@ -66,7 +66,7 @@ class LLMEngine:
             max_step_tokens=config.max_num_batched_tokens, max_seqs=config.max_num_seqs,
             max_model_len=config.max_model_len, gpu_memory_utilization=config.gpu_memory_utilization,
             enforce_eager=config.enforce_eager, enable_prefix_caching=config.enable_prefix_caching,
-            use_ref_kernels=config.use_ref_kernels)
+            use_ref_kernels=config.use_ref_kernels, native_cache_manager=config.native_cache_manager)
         eos = tuple(getattr(self.runner.config, "eos_token_ids", ()) or ())
         self.scheduler = Scheduler(SchedulerConfig(
             max_num_batched_tokens=config.max_num_batched_tokens, max_num_seqs=config.max_num_seqs,

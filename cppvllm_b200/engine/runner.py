@@ -28,6 +28,7 @@ import numpy as np
 import torch
 
 from ..cache.manager import CacheManager, GroupConfig
+from ..cache.native import NativeCacheManager
 from ..config.model_config import read_config_json
 from ..config.registry import resolve_architecture
 from ..csrc import ops
@@ -62,7 +63,8 @@ class ModelRunner:
     def __init__(self, model_dir: str, dtype=torch.bfloat16, device="cuda:0", page_size: int = 32,
                  num_pages: Optional[int] = None, max_step_tokens: int = 4096, max_seqs: int = 256,
                  max_model_len: int = 4096, gpu_memory_utilization: float = 0.90, enforce_eager: bool = False,
-                 num_state_slots: Optional[int] = None, enable_prefix_caching: bool = False, use_ref_kernels: bool = False):
+                 num_state_slots: Optional[int] = None, enable_prefix_caching: bool = False, use_ref_kernels: bool = False,
+                 native_cache_manager: bool = True):
         if not torch.cuda.is_available():
             raise RuntimeError("cppvllm_b200 runs on a CUDA device only; torch.cuda.is_available() is False")
         self.device = torch.device(device)
@@ -116,8 +118,12 @@ class ModelRunner:
             print("[cppvllm_b200] the prefix cache is off: it needs one group of cache units that keeps all keys and "
                   "no per-request state", file=sys.stderr, flush=True)
             enable_prefix_caching = False
-        self.cache = CacheManager([GroupConfig(self.num_pages, cs.window, tuple(m)) for cs, m in self.group_specs],
-                                  page_size, n_slots, prefix_caching=enable_prefix_caching)
+        groups = [GroupConfig(self.num_pages, cs.window, tuple(m)) for cs, m in self.group_specs]
+        if native_cache_manager and groups:
+            # the C++ manager keeps the block tables as dense arrays that the steps read in place
+            self.cache = NativeCacheManager(groups, page_size, n_slots, self.table_width, prefix_caching=enable_prefix_caching)
+        else:
+            self.cache = CacheManager(groups, page_size, n_slots, prefix_caching=enable_prefix_caching)
         self.scratch_slot = n_slots
         self.states = {i: torch.zeros((n_slots + 1,) + tuple(ss.shape), dtype=ss.dtype, device=self.device)
                        for i, ss in enumerate(self.state_specs) if ss is not None}
@@ -142,7 +148,10 @@ class ModelRunner:
         self._logits = torch.empty((self.max_seqs, self.vocab_size), dtype=torch.float32, device=self.device)
         self._graphs: Dict[int, tuple] = {}
         self._graph_launches: Dict[int, int] = {}
-        self._tab_mirror = [np.full((n_slots + 1, self.table_width), -1, dtype=np.int32) for _ in self.group_specs]
+        if getattr(self.cache, "native", False):
+            self._tab_mirror = list(self.cache.tables)        # the manager's own arrays: nothing to mirror
+        else:
+            self._tab_mirror = [np.full((n_slots + 1, self.table_width), -1, dtype=np.int32) for _ in self.group_specs]
         self._mirror_owner = [[None] * (n_slots + 1) for _ in self.group_specs]
         self._mirror_len = [[0] * (n_slots + 1) for _ in self.group_specs]
         self._shape_graphs: "OrderedDict[tuple, tuple]" = OrderedDict()
@@ -203,6 +212,8 @@ class ModelRunner:
         where a request's table has grown: a step then copies whole rows instead of converting every list again.
         Returns the row of `lease`."""
         row = lease.state_slot
+        if getattr(self.cache, "native", False):
+            return row                                        # a row of the manager's dense table (never wider than W)
         for g in range(len(self.group_specs)):
             tab = lease.tables[g]
             n = len(tab)

@@ -188,6 +188,43 @@ def test_overlapped_and_step_by_step_engines_generate_the_same_tokens(model_dirs
         assert all(len(t) == sp.max_tokens for t in outs[2])
 
 
+@pytest.mark.parametrize("prefix_cache", [False, True])
+def test_cache_manager_in_cpp_and_in_python_run_the_same_engine(model_dirs, prefix_cache):
+    """The engine with the cache manager in C++ (the default) and with its plain twin in Python: the same tokens, the
+    same preemptions and prefix hits, and the same pages in every request's table after every step."""
+    from cppvllm_b200 import SamplingParams
+    from cppvllm_b200.cache.native import NativeCacheManager
+    d = model_dirs["tiny_b"]
+    stem = tiny_models.random_tokens(320, 70, 5)
+    prompts = [stem + tiny_models.random_tokens(320, n, 90 + n) for n in (1, 31, 40, 3)] + [tiny_models.random_tokens(320, 50, 8)]
+    sp = SamplingParams(temperature=0.7, max_tokens=24, ignore_eos=True, seed=11)
+    llms = [engine(d, "tiny_b", num_kv_blocks=11, enable_prefix_caching=prefix_cache, native_cache_manager=native)
+            for native in (True, False)]
+    assert isinstance(llms[0].runner.cache, NativeCacheManager) and not isinstance(llms[1].runner.cache, NativeCacheManager)
+    for llm in llms:
+        for pr in prompts:
+            llm.add_request(pr, sp)
+    steps = 0
+    while not llms[0].is_finished():
+        for llm in llms:
+            llm.step()
+        a, b = (llm.runner.cache for llm in llms)
+        assert set(a.leases) == set(b.leases) and a.num_free_pages() == b.num_free_pages()
+        for rid in a.leases:
+            assert a.block_table(rid, 0) == b.block_table(rid, 0) and a.lease(rid).computed == b.lease(rid).computed
+        steps += 1
+        assert steps < 500
+    assert llms[1].is_finished()
+    outs = [sorted((o.request_id, tuple(o.token_ids)) for o in llm.take_finished()) for llm in llms]
+    assert outs[0] == outs[1] and len(outs[0]) == len(prompts)
+    assert llms[0].stats().preemptions == llms[1].stats().preemptions > 0
+    assert llms[0].stats().prefix_hit_pages == llms[1].stats().prefix_hit_pages
+    assert (llms[0].stats().prefix_hit_pages > 0) == prefix_cache
+    for llm in llms:
+        llm.runner.cache.check_invariants()
+        assert llm.runner.cache.num_free_pages() == llm.num_kv_blocks
+
+
 def test_end_of_sequence_stops_a_request(model_dirs, tmp_path):
     from cppvllm_b200 import SamplingParams
     d = model_dirs["tiny_a"]

@@ -14,8 +14,25 @@ from cppvllm_b200.sampling.params import SamplingParams
 GOLDEN = os.path.join(os.path.dirname(__file__), "golden", "scheduler_golden.json")
 
 
+_KIND = "python"
+
+
+@pytest.fixture(autouse=True, params=["python", "native"])
+def manager_kind(request):
+    """Every test of this file runs with the cache manager in Python and with the one in C++."""
+    global _KIND
+    _KIND = request.param
+    yield
+    _KIND = "python"
+
+
 def make(blocks, budget, chunk, max_seqs, page=16, max_model_len=4096, eos=(), prefix_caching=False):
-    cache = CacheManager([GroupConfig(blocks)], page, max(8, max_seqs), prefix_caching=prefix_caching)
+    if _KIND == "native":
+        from cppvllm_b200.cache.native import NativeCacheManager
+        cache = NativeCacheManager([GroupConfig(blocks)], page, max(8, max_seqs), (max_model_len + page - 1) // page,
+                                   prefix_caching=prefix_caching)
+    else:
+        cache = CacheManager([GroupConfig(blocks)], page, max(8, max_seqs), prefix_caching=prefix_caching)
     return Scheduler(SchedulerConfig(budget, max_seqs, chunk, max_model_len, tuple(eos)), cache), cache
 
 
