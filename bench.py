@@ -266,7 +266,7 @@ def main():
     for _ in range(B):
         llm.add_request(rand_tokens(ctx0), sp)
     guard = 0
-    while any(s.num_completion_tokens == 0 for s in llm._live.values()) and guard < 1000:
+    while llm.num_without_first_token() > 0 and guard < 1000:
         llm.step()                                              # prompt portions until every request has sampled once
         guard += 1
     for _ in range(W - 1):

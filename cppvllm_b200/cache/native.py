@@ -234,6 +234,17 @@ class NativeCacheManager:
         if rc < 0:
             self._raise(rc, request_id, "release")
 
+    # ---- requests that the scheduler in C++ admits and releases itself ---------------------------------------
+    def adopt(self, request_id, state_slot: int) -> NativeLease:
+        """The library admitted a request on its own (csrc/scheduler_runtime.cpp): make it known here by its id."""
+        lease = NativeLease(self, request_id, int(state_slot))
+        self.leases[request_id] = lease
+        return lease
+
+    def drop(self, request_id) -> None:
+        """The library released a request on its own."""
+        self.leases.pop(request_id, None)
+
     # ---- what a step needs -------------------------------------------------------------------------------
     def block_table(self, request_id, group: int) -> List[int]:
         return [int(p) for p in self.lease(request_id).tables[group]]

@@ -11,7 +11,8 @@ of a common prefix; always on in the reference, engine/block_manager.cpp:71-143;
 ``use_ref_kernels`` (every part uses its plain twin kernels: the general attention kernel, library products with separate
 norm and activation kernels; for comparing the fast kernels with, inside the whole engine) and ``native_cache_manager``
 (the cache manager in C++, as the reference's block manager is, engine/block_manager.cpp; false = its plain twin in
-Python, which the tests compare it with).
+Python, which the tests compare it with) and ``native_scheduler`` (the scheduler and the requests in C++ as well, as
+the reference's are, engine/scheduler.cpp; it needs the cache manager in C++; false = its plain twin in Python).
 """
 from __future__ import annotations
 
@@ -54,6 +55,7 @@ class EngineConfig:
     enable_prefix_caching: bool = False
     use_ref_kernels: bool = False
     native_cache_manager: bool = True
+    native_scheduler: bool = True
     device: str = "cuda:0"
 
     def __post_init__(self):

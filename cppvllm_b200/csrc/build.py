@@ -38,10 +38,11 @@ LIBRARIES: Dict[str, List[str]] = {
     "gemm_bf16": ["gemm_tcgen05.cu"],
     "decode_fused": ["decode_fused.cu"],
     "attn_tcgen05": ["attention_tcgen05.cu"],
-    "runtime": ["cache_runtime.cpp"],          # host code only (the cache manager); nvcc hands it to the host compiler
+    # host code only (the cache manager and the scheduler); nvcc hands it to the host compiler
+    "runtime": ["cache_runtime.cpp", "scheduler_runtime.cpp"],
 }
 
-_HEADERS = ["common.cuh", "sm100.cuh", "tensor_map.cuh", "attention_bf16.h"]
+_HEADERS = ["common.cuh", "sm100.cuh", "tensor_map.cuh", "attention_bf16.h", "runtime.hpp"]
 _loaded: Dict[str, ctypes.CDLL] = {}
 _lock = threading.Lock()
 

@@ -19,6 +19,7 @@ from ..config.engine_config import EngineConfig
 from ..sampling.params import SamplingParams
 from ..sampling.sampler import Sampler, mix_seed
 from .runner import ModelRunner, StepEntry
+from .native_scheduler import NativeScheduler
 from .scheduler import FINISHED, PENDING, ScheduledBatch, Scheduler, SchedulerConfig, Sequence
 
 
@@ -68,10 +69,12 @@ class LLMEngine:
             enforce_eager=config.enforce_eager, enable_prefix_caching=config.enable_prefix_caching,
             use_ref_kernels=config.use_ref_kernels, native_cache_manager=config.native_cache_manager)
         eos = tuple(getattr(self.runner.config, "eos_token_ids", ()) or ())
-        self.scheduler = Scheduler(SchedulerConfig(
+        sched_cfg = SchedulerConfig(
             max_num_batched_tokens=config.max_num_batched_tokens, max_num_seqs=config.max_num_seqs,
-            max_chunk_tokens=config.max_chunk_tokens, max_model_len=self.runner.max_model_len,
-            eos_token_ids=eos), self.runner.cache)
+            max_chunk_tokens=config.max_chunk_tokens, max_model_len=self.runner.max_model_len, eos_token_ids=eos)
+        # the scheduler in C++ keeps the requests itself and works on the cache manager in C++; else the twins in Python
+        self._native = bool(config.native_scheduler and getattr(self.runner.cache, "native", False))
+        self.scheduler = NativeScheduler(sched_cfg, self.runner.cache) if self._native else Scheduler(sched_cfg, self.runner.cache)
         self.sampler = Sampler(self.runner.device, config.max_num_seqs)
         self._live: Dict[int, Sequence] = {}
         self._finished: Dict[int, GenerationOutput] = {}
@@ -79,6 +82,7 @@ class LLMEngine:
         self._stats = EngineStats()
         self._empty_steps = 0
         self._inflight: List[dict] = []
+        self._forget_later: List[int] = []
         self._slot = 0
 
     # ---- requests ------------------------------------------------------------------------------------
@@ -89,12 +93,27 @@ class LLMEngine:
             if not (0 <= int(t) < vocab):
                 raise ValueError(f"prompt token {t} lies outside the vocabulary of {vocab}")
         rid = self._next_id
-        seq = Sequence(rid, prompt, params)
-        seq.row_seed = mix_seed(self.config.seed, params.seed if params.seed is not None else rid)
-        self.scheduler.add_request(seq)
+        row_seed = mix_seed(self.config.seed, params.seed if params.seed is not None else rid)
+        if self._native:
+            self.scheduler.add_request(rid, prompt, params, row_seed)
+            self._live[rid] = None
+        else:
+            seq = Sequence(rid, prompt, params)
+            seq.row_seed = row_seed
+            self.scheduler.add_request(seq)
+            self._live[rid] = seq
         self._next_id += 1
-        self._live[rid] = seq
         return rid
+
+    def num_without_first_token(self) -> int:
+        """Live requests that have not sampled their first token yet."""
+        if self._native:
+            n = 0
+            for rid in self._live:
+                d = self.scheduler.info(rid)
+                n += 1 if d["num_tokens"] <= d["num_prompt_tokens"] else 0
+            return n
+        return sum(1 for s in self._live.values() if s.num_completion_tokens == 0)
 
     def is_finished(self) -> bool:
         return not self._inflight and self.scheduler.is_finished()
@@ -116,6 +135,8 @@ class LLMEngine:
         if self.scheduler.is_finished():
             self.sync(info)
             return info
+        if self._native:
+            return self._step_native(info, t0)
         batch = self.scheduler.schedule(allow_preempt=not self._inflight)
         self._stats.preemptions = self.scheduler.num_preemptions
         self._stats.prefix_hit_pages = self.runner.cache.prefix_hits
@@ -164,6 +185,47 @@ class LLMEngine:
         self._account(info, t0)
         return info
 
+    def _step_native(self, info: StepInfo, t0: float) -> StepInfo:
+        """The same step with the scheduler in C++: it hands out the step as arrays (which requests, where their tokens
+        start, the tokens, which rows of the step in flight feed them, the sampling rows' options)."""
+        b = self.scheduler.schedule(allow_preempt=not self._inflight)
+        self._stats.preemptions = self.scheduler.num_preemptions
+        self._stats.prefix_hit_pages = self.runner.cache.prefix_hits
+        if not b.ids:
+            if self._inflight:
+                self.sync(info)
+                self._account(info, t0)
+                return info
+            self._empty_steps += 1
+            if self._empty_steps > 2:
+                raise RuntimeError("the scheduler produced no work although requests are pending")
+            return info
+        self._empty_steps = 0
+        prev = self._inflight[-1] if self._inflight else None
+        entries, o = [], 0
+        for rid, c, n, smp in zip(b.ids, b.starts, b.counts, b.samples):
+            entries.append(StepEntry(rid, b.tokens[o:o + n], c, (n - 1,) if smp else ()))
+            o += n
+        feed = (prev["sampled"], b.feed_src) if b.need_feed else None
+        logits = self.runner.step(entries, feed=feed)
+        slot = self._slot
+        self._slot ^= 1
+        rows = len(b.temps)
+        sampled_dev = self.sampler.sample_async(logits, b.temps, b.seeds, b.generated, slot=slot) if rows else None
+        if self.scheduler.on_launched() != rows:
+            raise RuntimeError("the scheduler and the step disagree on the sampling rows")
+        self._inflight.append({"slot": slot, "n": rows, "sampled": sampled_dev})
+        info.num_seqs, info.num_tokens = len(b.ids), b.total_tokens
+        self._stats.steps += 1
+        self._stats.tokens_processed += b.total_tokens
+        if b.blocked:
+            self.sync(info)
+        else:
+            while len(self._inflight) >= self.config.pipeline_depth:
+                self._retire_oldest(info)
+        self._account(info, t0)
+        return info
+
     def _account(self, info: StepInfo, t0: float) -> None:
         self._stats.tokens_generated += info.num_sampled
         self._stats.seconds += time.perf_counter() - t0
@@ -171,6 +233,21 @@ class LLMEngine:
     def _retire_oldest(self, info: StepInfo) -> None:
         rec = self._inflight.pop(0)
         tokens = self.sampler.collect(rec["n"], slot=rec["slot"]) if rec["n"] else []
+        if self._native:
+            finished = self.scheduler.postprocess(tokens)
+            for rid in finished:
+                d = self.scheduler.info(rid)
+                toks = self.scheduler.tokens(rid)
+                out = GenerationOutput(rid, toks[:d["num_prompt_tokens"]], toks[d["num_prompt_tokens"]:], d["stopped_on_eos"])
+                if out.stopped_on_eos and out.token_ids:
+                    out.token_ids.pop()                      # the end-of-sequence token itself is not returned
+                self._finished[rid] = out
+                self._live.pop(rid, None)
+            # the library keeps a finished request while a step in flight still names it
+            self._forget_later = [r for r in self._forget_later + finished if not self.scheduler.forget(r)]
+            info.num_sampled += len(tokens)
+            info.num_finished += len(finished)
+            return
         finished = self.scheduler.postprocess(rec["batch"], rec["flags"], tokens)
         for seq in finished:
             self._harvest(seq)
