@@ -28,6 +28,8 @@ def _engine_flags(p: argparse.ArgumentParser, util: float) -> None:
     p.add_argument("--enforce-eager", action="store_true")
     p.add_argument("--enable-prefix-caching", action="store_true")
     p.add_argument("--use-ref-kernels", action="store_true")
+    p.add_argument("--python-runtime", action="store_true",
+                   help="the cache manager and the scheduler in Python (their plain twins) instead of C++")
     p.add_argument("--seed", type=int, default=0)
 
 
@@ -39,7 +41,8 @@ def _engine(args):
         max_num_seqs=args.max_num_seqs, max_chunk_tokens=args.max_chunk_tokens, max_model_len=args.max_model_len,
         gpu_memory_utilization=args.gpu_memory_utilization, num_kv_blocks=args.num_kv_blocks,
         block_size=args.block_size, enforce_eager=args.enforce_eager, enable_prefix_caching=args.enable_prefix_caching,
-        use_ref_kernels=args.use_ref_kernels, seed=args.seed))
+        use_ref_kernels=args.use_ref_kernels, native_cache_manager=not args.python_runtime,
+        native_scheduler=not args.python_runtime, seed=args.seed))
 
 
 def example_main(argv=None) -> int:

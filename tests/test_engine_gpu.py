@@ -256,6 +256,11 @@ def test_command_lines(model_dirs):
                         "--max-num-seqs", "4", "--max-num-batched-tokens", "64"], capture_output=True, text=True, env=env)
     assert r.returncode == 0, r.stderr[-2000:]
     assert "Throughput:" in r.stdout and "KV blocks: 12" in r.stdout
+    r = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "example"), d, "--dtype", "float32", "--max-tokens", "5",
+                        "--temperature", "0", "--prompt", "1,2,3", "--max-model-len", "64", "--num-kv-blocks", "16",
+                        "--max-num-seqs", "4", "--ignore-eos", "--python-runtime"], capture_output=True, text=True, env=env)
+    assert r.returncode == 0, r.stderr[-2000:]
+    assert f"Completion: {plain.greedy_generate(d, [1, 2, 3], 5)}" in r.stdout
     r = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "example")], capture_output=True, text=True, env=env)
     assert r.returncode == 2 and "usage: example <model_dir>" in r.stderr
 
