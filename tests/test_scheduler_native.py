@@ -25,11 +25,16 @@ def sample(rid: int, pos: int) -> int:
     return (rid * 31 + pos * 7 + (pos * pos) % 11) % 50
 
 
+def groups_of(blocks, window):
+    """One group that keeps all keys; with a window, a second, smaller one that gives pages back as the window passes."""
+    return [GroupConfig(blocks)] + ([GroupConfig(max(4, blocks // 2), window=window)] if window else [])
+
+
 class PythonLoop:
     """The engine's loop (engine/llm_engine.py: step, _retire_oldest) around the scheduler in Python."""
 
-    def __init__(self, cfg, blocks, page, slots, prefix, depth):
-        self.cache = CacheManager([GroupConfig(blocks)], page, slots, prefix_caching=prefix)
+    def __init__(self, cfg, blocks, page, slots, prefix, depth, window=0):
+        self.cache = CacheManager(groups_of(blocks, window), page, slots, prefix_caching=prefix)
         self.sched = Scheduler(cfg, self.cache)
         self.depth, self.inflight, self.results, self.seqs = depth, [], {}, {}
 
@@ -83,8 +88,8 @@ class PythonLoop:
 class NativeLoop:
     """The same loop around the scheduler in C++."""
 
-    def __init__(self, cfg, blocks, page, slots, prefix, depth):
-        self.cache = NativeCacheManager([GroupConfig(blocks)], page, slots, (cfg.max_model_len + page - 1) // page,
+    def __init__(self, cfg, blocks, page, slots, prefix, depth, window=0):
+        self.cache = NativeCacheManager(groups_of(blocks, window), page, slots, (cfg.max_model_len + page - 1) // page,
                                         prefix_caching=prefix)
         self.sched = NativeScheduler(cfg, self.cache)
         self.depth, self.inflight, self.results = depth, [], {}
@@ -133,8 +138,8 @@ class NativeLoop:
         return (rows, b.preempted, b.blocked)
 
 
-def run_both(cfg, blocks, page, slots, requests, prefix=False, depth=2, arrivals=None, max_steps=5000):
-    loops = [PythonLoop(cfg, blocks, page, slots, prefix, depth), NativeLoop(cfg, blocks, page, slots, prefix, depth)]
+def run_both(cfg, blocks, page, slots, requests, prefix=False, depth=2, arrivals=None, max_steps=5000, window=0):
+    loops = [PythonLoop(cfg, blocks, page, slots, prefix, depth, window), NativeLoop(cfg, blocks, page, slots, prefix, depth, window)]
     arrivals = arrivals or {}
     pending = list(enumerate(requests))
     steps = 0
@@ -158,6 +163,7 @@ def run_both(cfg, blocks, page, slots, requests, prefix=False, depth=2, arrivals
     same_state(loops[0].cache, loops[1].cache)
     assert loops[0].results == loops[1].results and len(loops[0].results) == len(requests)
     assert loops[1].cache.num_free_pages() == blocks and not loops[1].cache.leases
+    assert all(loops[1].cache.num_free_pages(g) == gc.num_pages for g, gc in enumerate(loops[1].cache.groups))
     return loops, steps
 
 
@@ -191,6 +197,20 @@ def test_pages_run_out_and_requests_are_preempted_in_both():
     requests = [([i + 1] * n, SamplingParams(max_tokens=40, ignore_eos=True)) for i, n in enumerate((30, 25, 20, 28))]
     loops, _ = run_both(cfg, blocks=10, page=16, slots=4, requests=requests, depth=2)
     assert loops[1].sched.num_preemptions > 0
+
+
+@pytest.mark.parametrize("seed", range(4))
+def test_two_groups_of_pages_one_with_a_window(seed):
+    """A second group of cache units that looks back only `window` positions: it holds few pages per request and gives
+    them back as decoding goes on, so the two groups run out at different times."""
+    rng = random.Random(50 + seed)
+    page, blocks = 8, rng.randint(14, 24)
+    cfg = SchedulerConfig(48, 4, 16, blocks * page // 2, ())
+    requests = [([rng.randint(0, 49) for _ in range(rng.randint(1, 5 * page))],
+                 SamplingParams(max_tokens=rng.randint(1, 4 * page), ignore_eos=True)) for _ in range(8)]
+    requests = [(p[:cfg.max_model_len - sp.max_tokens] or [1], sp) for p, sp in requests]
+    loops, _ = run_both(cfg, blocks, page, 6, requests, depth=2, window=rng.choice([page, 2 * page + 3]),
+                        arrivals={i: rng.randint(0, 12) for i in range(8)})
 
 
 def test_requests_are_refused_as_the_twin_refuses_them():
