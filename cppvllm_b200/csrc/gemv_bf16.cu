@@ -1,4 +1,4 @@
-// Matrix products for a handful of tokens (decode steps of up to 8 rows), bf16 weights and activations:
+// Matrix products for a handful of tokens (decode steps of up to 16 rows), bf16 weights and activations:
 //   y[m, n] = sum_k x[m, k] * W[n, k]
 // With so few rows the product is a stream of the weight matrix through the SMs; a library GEMM leaves most of the
 // HBM bandwidth unused at these shapes and cannot take the neighbouring elementwise work along.
