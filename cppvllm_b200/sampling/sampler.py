@@ -80,7 +80,7 @@ class Sampler:
         self._pos[slot][:R].copy_(self._host_p[slot][:R], non_blocking=True)
         self._seeds[slot][:R].copy_(self._host_s[slot][:R], non_blocking=True)
         # a large vocabulary is searched by several blocks per row: 32 at few rows, fewer at many, so that there are
-        # a couple of thousand blocks (one block per row reads its 600 KB of logits at a seventh of the bandwidth)
+        # a couple of thousand blocks (one block per row read its 600 KB of logits at about a fifth of the bandwidth)
         chunks = max(1, min(self._chunks, 2048 // max(R, 1))) if logits.shape[1] >= 16384 else 0
         if chunks < 2:
             chunks = 0
