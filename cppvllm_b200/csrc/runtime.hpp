@@ -15,7 +15,6 @@ constexpr int kErrMisuse = -1;      // unknown or double admission, double free,
 constexpr int kErrOutOfPages = -2;  // a reservation needs more pages than a group has free
 constexpr int kErrWidth = -3;       // a table would grow beyond the width of the dense array
 constexpr int kErrNoSlot = -4;      // no free state slot
-constexpr int kErrArgument = -5;
 
 inline uint64_t mix64(uint64_t x) {  // splitmix64 finaliser
     x += 0x9e3779b97f4a7c15ULL;

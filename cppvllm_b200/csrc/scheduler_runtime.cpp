@@ -41,9 +41,7 @@ struct Sched {
     long long num_preemptions = 0;
     // the batch that schedule() made last, until on_launched() takes it
     std::vector<int> batch, batch_preempted, batch_admitted;
-    bool batch_blocked = false;
     std::deque<Launched> inflight;
-    std::vector<int> finished_now;     // of the last postprocess()
 
     Seq& at(int id) { return seqs.find(id)->second; }
     void preempt(Seq& s) {
@@ -143,7 +141,6 @@ int cvb_sched_schedule(void* h, int allow_preempt, int* info) {
         kept.push_back(q.id);
     }
     s->running.swap(kept);
-    s->batch_blocked = blocked;
     while (!preempted_now && !blocked && !s->waiting.empty() && budget > 0 && static_cast<int>(s->running.size()) < s->max_seqs &&
            static_cast<int>(s->batch.size()) < s->max_seqs) {
         Seq& q = s->at(s->waiting.front());
