@@ -53,7 +53,9 @@ class EngineStats:
 
 
 class LLMEngine:
-    def __init__(self, config: Union[EngineConfig, str, None] = None, **kwargs):
+    def __init__(self, config: Union[EngineConfig, str, None] = None, *, runner=None, sampler=None, **kwargs):
+        """`runner` and `sampler`: objects to use instead of a ModelRunner and a Sampler built from the configuration (the
+        tests of the engine's loop on the CPU hand in stand-ins that need no device)."""
         if isinstance(config, str):
             config = EngineConfig(model_path=config, **kwargs)
         elif config is None:
@@ -61,7 +63,7 @@ class LLMEngine:
         elif kwargs:
             raise TypeError("pass either an EngineConfig or keyword options, not both")
         self.config = config
-        self.runner = ModelRunner(
+        self.runner = runner if runner is not None else ModelRunner(
             config.model_path, dtype=config.dtype, device=config.device, page_size=config.block_size,
             num_pages=config.num_kv_blocks if config.num_kv_blocks > 0 else None,
             max_step_tokens=config.max_num_batched_tokens, max_seqs=config.max_num_seqs,
@@ -75,7 +77,7 @@ class LLMEngine:
         # the scheduler in C++ keeps the requests itself and works on the cache manager in C++; else the twins in Python
         self._native = bool(config.native_scheduler and getattr(self.runner.cache, "native", False))
         self.scheduler = NativeScheduler(sched_cfg, self.runner.cache) if self._native else Scheduler(sched_cfg, self.runner.cache)
-        self.sampler = Sampler(self.runner.device, config.max_num_seqs)
+        self.sampler = sampler if sampler is not None else Sampler(self.runner.device, config.max_num_seqs)
         self._live: Dict[int, Sequence] = {}
         self._finished: Dict[int, GenerationOutput] = {}
         self._next_id = 0
