@@ -4,7 +4,7 @@ cap), ``max_model_len`` (4096), ``gpu_memory_utilization`` (0.90), ``num_kv_bloc
 memory), ``enforce_eager`` (false = decode steps replay CUDA graphs), ``dtype`` and ``seed``.
 ``tensor_parallel_size`` exists only so that a value other than 1 is refused: this engine runs on one GPU.
 Added here: ``block_size`` (tokens per cache page; the reference fixes 16 in sequence.h:28; the default here is 32,
-because a TMA box is one page of one head and boxes of 32 rows reach the full HBM rate where boxes of 16 reach 3/4)
+because a TMA box is one page of one head and boxes of 32 rows come out a few percent faster than boxes of 16),
 ``pipeline_depth`` (steps in flight: 2 as the reference's ``kDepth``, engine/llm_engine.h:51, or 1 to wait for
 every step's samples before the next step is scheduled) and ``enable_prefix_caching`` (requests share the cache pages
 of a common prefix; always on in the reference, engine/block_manager.cpp:71-143; off by default here) and
