@@ -47,6 +47,7 @@ def _library():
         lib.cvb_cm_pages_missing.argtypes = [c_void_p, c_int, c_int, POINTER(c_int)]
         for name in ("cvb_cm_covered", "cvb_cm_can_reserve", "cvb_cm_reserve", "cvb_cm_advance"):
             getattr(lib, name).argtypes = [c_void_p, c_int, c_int]
+        lib.cvb_cm_advance_many.argtypes = [c_void_p, c_void_p, c_void_p, c_int]
         lib.cvb_cm_release.argtypes = [c_void_p, c_int]
         lib.cvb_cm_check.argtypes = [c_void_p]
         _lib = lib
@@ -225,6 +226,18 @@ class NativeCacheManager:
         rc = int(self._lib.cvb_cm_advance(self._h, self.lease(request_id).state_slot, int(computed)))
         if rc < 0:
             raise CacheError("a request's computed length cannot shrink")
+
+    def advance_many(self, request_ids, computed) -> None:
+        """advance() for the requests of a step in one call into the library."""
+        n = len(request_ids)
+        try:
+            slots = np.fromiter((self.leases[r].state_slot for r in request_ids), dtype=np.int32, count=n)
+        except KeyError as e:
+            raise CacheError(f"request {e.args[0]!r} is not admitted") from None
+        upto = np.asarray(computed, dtype=np.int32)
+        bad = int(self._lib.cvb_cm_advance_many(self._h, slots.ctypes.data_as(c_void_p), upto.ctypes.data_as(c_void_p), n))
+        if bad >= 0:
+            raise CacheError(f"request {request_ids[bad]!r}: a request's computed length cannot shrink")
 
     def release(self, request_id) -> None:
         lease = self.leases.pop(request_id, None)

@@ -202,6 +202,13 @@ int cvb_cm_advance(void* h, int slot, int computed) {
     return kOk;
 }
 
+// advance() for several requests in one call; returns the index of the first request that was refused, or -1.
+int cvb_cm_advance_many(void* h, const int* slots, const int* computed, int n) {
+    for (int i = 0; i < n; ++i)
+        if (cvb_cm_advance(h, slots[i], computed[i]) != kOk) return i;
+    return -1;
+}
+
 int cvb_cm_release(void* h, int slot) {
     Manager* m = M(h);
     if (!m->live(slot)) return kErrMisuse;

@@ -442,11 +442,19 @@ class ModelRunner:
                 (R, self.vocab_size), dtype=torch.float32, device=self.device)
             logits = self.model.forward(ctx, self.cache_views, self.states, out)[:R] if R > 0 else \
                 self._forward_no_logits(ctx)
-        for e in entries:
-            self.cache.advance(e.request_id, e.start + len(e.tokens))
+        self._advance(entries)
         self.stats["steps"] += 1
         self.stats["tokens"] += T
         return logits
+
+    def _advance(self, entries: Sequence[StepEntry]) -> None:
+        """The step's tokens are in the cache now (windowed groups give pages back)."""
+        many = getattr(self.cache, "advance_many", None)
+        if many is not None:
+            many([e.request_id for e in entries], [e.start + len(e.tokens) for e in entries])
+        else:
+            for e in entries:
+                self.cache.advance(e.request_id, e.start + len(e.tokens))
 
     def _forward_no_logits(self, ctx) -> torch.Tensor:
         self.model.forward_hidden(ctx, self.cache_views, self.states)

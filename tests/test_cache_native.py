@@ -177,6 +177,23 @@ def test_prefix_cache_under_random_orders_gives_the_same_sharing(seed):
     assert py.prefix_hits > 0                                 # the stems were shared at all
 
 
+def test_advance_many_is_advance_for_each():
+    py, nat = pair([GroupConfig(30), GroupConfig(20, window=9)], 4, 4, 16)
+    for rid, n in (("a", 30), ("b", 11), ("c", 4)):
+        for m in (py, nat):
+            m.admit(rid)
+            m.reserve(rid, n)
+    for rid, n in (("a", 30), ("b", 11), ("c", 4)):
+        py.advance(rid, n)
+    nat.advance_many(["a", "b", "c"], [30, 11, 4])
+    same_state(py, nat)
+    with pytest.raises(CacheError):
+        nat.advance_many(["a", "b"], [30, 5])                 # b would shrink; a's call before it stands
+    with pytest.raises(CacheError):
+        nat.advance_many(["nobody"], [1])
+    same_state(py, nat)
+
+
 def test_tables_are_read_in_place():
     """The dense arrays belong to the library and follow every call without being fetched again."""
     nat = NativeCacheManager([GroupConfig(10)], 8, 3, 6)

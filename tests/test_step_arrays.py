@@ -95,8 +95,10 @@ def test_index_arrays_are_the_same_with_either_cache_manager(seed, monkeypatch):
                 x, y = a._stage_np[ia][o:o + n], b._stage_np[ib][o:o + n]
                 if name == "feed_src": continue
                 assert (x == y).all(), (trial, step, name, x, y)
+            for r in (a, b):
+                r._advance(entries)                          # the runner's own step end: one call into the C++ manager
             for e in entries:
-                for r in (a, b): r.cache.advance(e.request_id, e.start + len(e.tokens))
+                assert a.cache.lease(e.request_id).computed == b.cache.lease(e.request_id).computed == e.start + len(e.tokens)
                 pos[e.request_id] = e.start + len(e.tokens)
             if rng.random() < 0.15:
                 rid = rng.choice(list(pos))
