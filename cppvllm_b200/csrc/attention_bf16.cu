@@ -374,8 +374,13 @@ constexpr int kDecStages = 3;
 template <int HD>
 __global__ void __launch_bounds__(kThreads)
 attn_decode_bf16_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnParams p) {
-    pdl_trigger();
-    pdl_wait();
+    // With the projection's raw output (the fused form) nothing that this kernel reads from the cache was written by
+    // the kernels directly in front of it: the keys of earlier positions are older than this step, and the token's own
+    // key and value are made here.  So the producer warp starts fetching keys at once, ahead of the dependency, and only
+    // what reads the projection (and everything that writes) comes behind the wait.  Without the fused form the kernel in
+    // front of this one has just written the new key into the cache: all of it waits.
+    const bool fused = p.qkv != nullptr;
+    if (!fused) pdl_wait();
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     using Plan = SmemPlan<HD, kDecStages, 16>;
     Plan sm(smem_raw);
@@ -430,6 +435,7 @@ attn_decode_bf16_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnPa
                 cp_async_commit();
                 cp_async_wait<0>();
             } else {
+            pdl_wait();
             // Per-head norm and rotation of this kv head's queries, straight from the projection; CPR neighbouring lanes
             // own one head vector (16-byte chunks).  The block that owns the token's own position does the same for the
             // new key, copies the new value, and writes both to the cache and to shared memory.
@@ -562,6 +568,10 @@ attn_decode_bf16_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnPa
         l[half] += __shfl_xor_sync(0xffffffffu, l[half], 1);
         l[half] += __shfl_xor_sync(0xffffffffu, l[half], 2);
     }
+    if (fused && (n_tiles == 0 || warp == kConsumers / 32)) pdl_wait();    // every thread has waited before anything is written
+    // The kernel behind this one may start now: its blocks arrive when most of this kernel's blocks have left their SMs, so
+    // they spread evenly, and what they fetch ahead of their own wait overlaps the merge below.
+    pdl_trigger();
     // combine the four warps through shared memory (the tiles are no longer needed)
     __syncthreads();
     float* red_o = reinterpret_cast<float*>(sm.stages);                    // [4][16][HD]
@@ -705,7 +715,8 @@ static int launch_decode(const CUtensorMap& map, AttnParams p, dim3 grid, dim3 m
         if (fits[p.splits] < 0) goto apart;
         p.cluster = 1;
         cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
-        if (pdl_enabled() && cudaStreamIsCapturing(stream, &cap) == cudaSuccess && cap == cudaStreamCaptureStatusNone) {
+        if (pdl_enabled() && (p.qkv != nullptr ||
+                              (cudaStreamIsCapturing(stream, &cap) == cudaSuccess && cap == cudaStreamCaptureStatusNone))) {
             attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
             attr[1].val.programmaticStreamSerializationAllowed = 1;
             cfg.numAttrs = 2;

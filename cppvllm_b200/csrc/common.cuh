@@ -98,8 +98,28 @@ inline void launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_
     cfg.numAttrs = 0;
     if (pdl_enabled()) {
         cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
-        if (cudaStreamIsCapturing(stream, &cap) == cudaSuccess && cap == cudaStreamCaptureStatusNone) cfg.numAttrs = 1;
+        static const bool in_graph = [] { const char* e = getenv("CVB_PDL_GRAPH"); return e && e[0] == '1'; }();
+        if (in_graph || (cudaStreamIsCapturing(stream, &cap) == cudaSuccess && cap == cudaStreamCaptureStatusNone)) cfg.numAttrs = 1;
     }
+    cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
+// The same launch with the attribute decided by the caller: kernels written for a chain of dependent launches (they ask
+// for what depends on no kernel before griddepcontrol.wait, and size their blocks so that the blocks of two neighbouring
+// kernels share an SM evenly) take it inside captured graphs as well.
+template <typename... KArgs, typename... Args>
+inline void launch_kernel_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, bool dependent,
+                                    Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = (dependent && pdl_enabled()) ? 1 : 0;
     cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
 

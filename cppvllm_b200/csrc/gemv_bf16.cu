@@ -17,6 +17,7 @@
 //             the block stores T( rnd(silu(T(g))) * T(u) )                                      (:210-220)
 // The result is rounded to bf16 once, as a library product with bf16 output is.
 #include "common.cuh"
+#include "sm100.cuh"
 
 namespace cvb {
 
@@ -423,9 +424,363 @@ gemv_splitk_kernel(const SplitKParams p) {
     if (threadIdx.x == 0) p.counters[blockIdx.x] = 0;
 }
 
+
+// ---- small models: one block per SM, the block's weights by bulk copy ahead of the dependency ------------------------
+// When a weight matrix is a few megabytes, every block's share (N / #SMs rows of K elements) fits into its shared memory
+// at once.  The kernel then asks for all of it with one bulk copy per row BEFORE it waits for the kernel in front of it
+// (programmatic dependent launch: weights depend on no kernel), so that the weights travel while the predecessor still
+// runs, and it lets its own successor start as soon as it has passed that wait.  What is left on the chain of dependent
+// kernels is the trip of the activations through the L2 and the products themselves.  Blocks ask for about half of an
+// SM's shared memory, so the blocks of two neighbouring kernels fit an SM together, one each.
+// Rows land in shared memory with 64 bytes of padding, which makes the lanes' 16-byte reads (same k permutation as
+// above) free of bank conflicts.  Arithmetic and rounding are those of the kernel above.
+constexpr int kStWarps = 16;
+constexpr int kStThreads = kStWarps * 32;
+
+struct StreamParams {
+    __nv_bfloat16* out;            // [M, N] (SWIGLU: [M, N / 2])
+    const __nv_bfloat16* x;        // [M, K]
+    const __nv_bfloat16* delta;    // NORM: added to the residual first, or nullptr
+    __nv_bfloat16* resid_out;      // NORM with delta: receives rnd(x + delta)
+    const float* norm_w;           // NORM: [K]
+    const __nv_bfloat16* W;        // [N, K]
+    const unsigned char* prefetch; // bytes that a later kernel will stream: asked into the L2 by this one (or nullptr)
+    long long prefetch_bytes;
+    int* err;
+    int M, N, K;
+    int opb;                       // outputs per block
+    int n_tiles;                   // tiles of 16 weight rows per block
+    int warps_k;                   // warps that share one tile's K range
+    int warps_per_row;             // NORM: warps that share one activation row (16 / rows, a power of two)
+    int late_trigger;              // 1: the successor may start only when this block's products are done
+    float eps;
+};
+
+// A load that the compiler may not move: issued where it stands (ahead of the dependency), used much later.
+__device__ __forceinline__ float4 ld_early(const float* p) {
+    float4 v;
+    asm volatile("ld.global.nc.v4.f32 {%0, %1, %2, %3}, [%4];\n" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "l"(p));
+    return v;
+}
+
+__device__ __forceinline__ void bulk_row_to_smem(void* smem, const void* gmem, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n"
+                 ::"r"(static_cast<uint32_t>(__cvta_generic_to_shared(smem))), "l"(gmem), "r"(bytes),
+                   "r"(static_cast<uint32_t>(__cvta_generic_to_shared(bar))) : "memory");
+}
+
+// What runs after the wait is the chain that every decode step passes through once per product, so it is kept short:
+// everything that can be worked out before the wait (addresses, which rows and outputs a thread owns, quotients) is,
+// and no thread divides by a run-time number behind it.
+template <bool NORM, bool SWIGLU>
+__global__ void __launch_bounds__(kStThreads, 2)
+gemv_stream_kernel(const StreamParams p) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    const int K = p.K, chunks = K >> 3, stride = K + kXPad;
+    const int n_out = SWIGLU ? p.N / 2 : p.N;
+    const int o0 = blockIdx.x * p.opb, n_mine = min(p.opb, n_out - o0);           // this block's outputs
+    const int w_rows = SWIGLU ? 2 * n_mine : n_mine;
+    uint64_t* bar = reinterpret_cast<uint64_t*>(smem_raw);
+    float* row_ss = reinterpret_cast<float*>(smem_raw + 16);                       // [8 rows][16 parts]
+    __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(smem_raw + 16 + kBatch * kStWarps * sizeof(float));   // [8][K + pad]
+    __nv_bfloat16* ws = xs + kBatch * stride;                                      // [rows of W][K + pad]
+    float* red = reinterpret_cast<float*>(ws + static_cast<size_t>(SWIGLU ? 2 : 1) * p.opb * stride);   // [item][16][8]
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const uint4 zero = make_uint4(0, 0, 0, 0);
+
+    // ---- before the dependency: the weights ----
+    if (threadIdx.x == 0) {
+        mbar_init(bar, 1);
+        mbar_fence_init();
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) mbar_expect_tx(bar, static_cast<uint32_t>(w_rows) * K * 2u);
+    // One copy per row.  A warp issues the copies of its lanes one after the other, so the rows go round the warps.  (The
+    // barrier's byte count may run ahead of the expectation above: its phase cannot end before thread 0 has arrived.)
+    for (int r = warp + lane * kStWarps; r < w_rows; r += 32 * kStWarps) {
+        const int grow = SWIGLU ? (r < n_mine ? o0 + r : n_out + o0 + (r - n_mine)) : o0 + r;
+        bulk_row_to_smem(ws + static_cast<size_t>(r) * stride, p.W + static_cast<int64_t>(grow) * K, K * 2u, bar);
+    }
+    // ---- before the dependency: who does what afterwards ----
+    // Activation row m belongs to the warps m * wpr .. m * wpr + wpr - 1 (wpr = 16 / rows, a power of two), each with a
+    // range of the row's 16-byte chunks; a lane takes the chunks c_begin + lane, + 32, ...
+    constexpr int kStage = 2;
+    const int wpr = p.warps_per_row;
+    const int my_row = warp / wpr, my_part = warp - my_row * wpr;
+    const int per_part = (chunks + wpr - 1) / wpr;
+    const int c_begin = my_part * per_part, c_end = min(chunks, c_begin + per_part);
+    const bool has_row = my_row < p.M;
+    const uint4* xg = reinterpret_cast<const uint4*>(p.x + static_cast<int64_t>(has_row ? my_row : 0) * K);
+    const uint4* dg = (NORM && p.delta != nullptr) ? reinterpret_cast<const uint4*>(p.delta + static_cast<int64_t>(has_row ? my_row : 0) * K) : nullptr;
+    uint4* xs_row = reinterpret_cast<uint4*>(xs + my_row * stride);
+    float4 nw0[kStage], nw1[kStage];
+    if constexpr (NORM) {
+#pragma unroll
+        for (int u = 0; u < kStage; ++u) {
+            const int c = min(c_begin + lane + u * 32, chunks - 1);
+            nw0[u] = ld_early(p.norm_w + c * 8);
+            nw1[u] = ld_early(p.norm_w + c * 8 + 4);
+        }
+    }
+    // the products: a warp's first (tile, K range) item and the rows of W behind the two halves of the A operand
+    constexpr int OUT_PER_TILE = SWIGLU ? 8 : 16;
+    const int r = lane >> 2, q = lane & 3;
+    const int slabs = (K + 31) >> 5;
+    const int per_warp = (slabs + p.warps_k - 1) / p.warps_k;
+    const int items = p.n_tiles * p.warps_k;
+    // B operand: column r of a product is activation row r; columns without a token repeat the last row and are not stored
+    const uint4* x_row = reinterpret_cast<const uint4*>(xs + min(r, p.M - 1) * stride);
+    auto rows_of = [&](int tile, const uint4*& w_hi, const uint4*& w_lo) {
+        int row_hi, row_lo;
+        if constexpr (SWIGLU) {
+            row_hi = min(tile * 8 + r, n_mine - 1);
+            row_lo = n_mine + row_hi;
+        } else {
+            row_hi = min(tile * 16 + r, n_mine - 1);
+            row_lo = min(tile * 16 + r + 8, n_mine - 1);
+        }
+        w_hi = reinterpret_cast<const uint4*>(ws + static_cast<size_t>(row_hi) * stride);
+        w_lo = reinterpret_cast<const uint4*>(ws + static_cast<size_t>(row_lo) * stride);
+    };
+    int tile = warp / p.warps_k, wk = warp - tile * p.warps_k;
+    const uint4 *w_hi, *w_lo;
+    rows_of(tile, w_hi, w_lo);
+    // the store: thread i takes output i % n_mine of row i / n_mine
+    int e_m = threadIdx.x / n_mine, e_o = threadIdx.x - e_m * n_mine;
+    const float inv_k = 1.f / static_cast<float>(K);
+    pdl_wait();
+
+    // ---- activations into shared memory (read past the L1: another kernel wrote them while this block was resident) ----
+    if constexpr (NORM) {
+        float ss = 0.f;
+        uint4 keep[kStage];                                              // the first pass's chunks stay in registers
+        if (has_row) {
+            for (int c0 = c_begin + lane; c0 < c_end; c0 += 32 * kStage) {
+                uint4 xv[kStage], dv[kStage];
+#pragma unroll
+                for (int u = 0; u < kStage; ++u) {
+                    const int c = c0 + u * 32;
+                    xv[u] = c < c_end ? __ldcg(xg + c) : zero;
+                    dv[u] = (dg != nullptr && c < c_end) ? __ldcg(dg + c) : zero;
+                }
+#pragma unroll
+                for (int u = 0; u < kStage; ++u) {
+                    const int c = c0 + u * 32;
+                    float v[8];
+                    unpack8(xv[u], v);
+                    if (dg != nullptr) {
+                        float d[8];
+                        unpack8(dv[u], d);
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) v[i] = rnd<__nv_bfloat16>(v[i] + d[i]);
+                    }
+                    uint4 packed;
+                    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+                    if (c0 == c_begin + lane) keep[u] = packed;
+                    else if (c < c_end) xs_row[c] = packed;              // later passes wait in shared memory
+                    if (dg != nullptr && blockIdx.x == 0 && c < c_end)
+                        *reinterpret_cast<uint4*>(p.resid_out + static_cast<int64_t>(my_row) * K + c * 8) = packed;
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) ss += v[i] * v[i];       // chunks past the end are zero
+                }
+            }
+            ss = warp_sum(ss);
+            if (lane == 0) row_ss[my_row * kStWarps + my_part] = ss;
+        }
+        __syncthreads();
+        if (has_row) {
+            float part[kStWarps];
+#pragma unroll
+            for (int i = 0; i < kStWarps; ++i) part[i] = i < wpr ? row_ss[my_row * kStWarps + i] : 0.f;
+            float total = 0.f;
+#pragma unroll
+            for (int i = 0; i < kStWarps; ++i) total += part[i];         // in part order, whichever warp adds
+            const float inv = rsqrtf(total * inv_k + p.eps);
+            for (int c0 = c_begin + lane; c0 < c_end; c0 += 32 * kStage) {
+                const bool first = c0 == c_begin + lane;
+                if (!first) {
+#pragma unroll
+                    for (int u = 0; u < kStage; ++u) {
+                        const int c = min(c0 + u * 32, chunks - 1);
+                        nw0[u] = __ldg(reinterpret_cast<const float4*>(p.norm_w + c * 8));
+                        nw1[u] = __ldg(reinterpret_cast<const float4*>(p.norm_w + c * 8 + 4));
+                    }
+                }
+#pragma unroll
+                for (int u = 0; u < kStage; ++u) {
+                    const int c = c0 + u * 32;
+                    if (c >= c_end) break;
+                    float v[8];
+                    unpack8(first ? keep[u] : xs_row[c], v);
+                    const float w[8] = {nw0[u].x, nw0[u].y, nw0[u].z, nw0[u].w, nw1[u].x, nw1[u].y, nw1[u].z, nw1[u].w};
+                    uint4 packed;
+                    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+                    for (int i = 0; i < 4; ++i)
+                        h[i] = __floats2bfloat162_rn(rnd<__nv_bfloat16>(v[2 * i] * inv) * w[2 * i],
+                                                     rnd<__nv_bfloat16>(v[2 * i + 1] * inv) * w[2 * i + 1]);
+                    xs_row[c] = packed;
+                }
+            }
+        }
+    } else {
+        if (has_row) {
+            constexpr int kCopy = 4;
+            for (int c0 = c_begin + lane; c0 < c_end; c0 += 32 * kCopy) {
+                uint4 v[kCopy];
+#pragma unroll
+                for (int u = 0; u < kCopy; ++u) v[u] = c0 + u * 32 < c_end ? __ldcg(xg + c0 + u * 32) : zero;
+#pragma unroll
+                for (int u = 0; u < kCopy; ++u)
+                    if (c0 + u * 32 < c_end) xs_row[c0 + u * 32] = v[u];
+            }
+        }
+    }
+    __syncthreads();
+    // The successor's blocks arrive on this SM and ask for their weights at once: only now, when this block's own
+    // activations have come in, so that they do not queue behind those weights.
+    if (!p.late_trigger) pdl_trigger();
+    if (p.prefetch != nullptr && threadIdx.x == 32) {
+        // this block's share of what a later kernel streams, in pieces of at most 64 KB
+        const long long share = ((p.prefetch_bytes + gridDim.x - 1) / gridDim.x + 15) & ~15LL;
+        const long long begin = share * blockIdx.x, end = min(p.prefetch_bytes & ~15LL, begin + share);
+        for (long long o = begin; o < end; o += 65536) {
+            const uint32_t n = static_cast<uint32_t>(min(65536LL, end - o));
+            asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;\n" ::"l"(p.prefetch + o), "r"(n) : "memory");
+        }
+    }
+    mbar_wait(bar, 0, p.err);
+
+    // ---- the products: a warp takes (tile, K range) items; four independent chains of products ----
+    for (int item = warp; item < items; item += kStWarps) {
+        if (item != warp) {
+            tile = item / p.warps_k;
+            wk = item - tile * p.warps_k;
+            rows_of(tile, w_hi, w_lo);
+        }
+        float acc[4][4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f; }
+        const int j_end = min(slabs, (wk + 1) * per_warp);
+        int c = wk * per_warp * 4 + q;
+        for (int j0 = wk * per_warp; j0 < j_end; j0 += 2, c += 8) {
+            const bool ok0 = c < chunks, ok1 = j0 + 1 < j_end && c + 4 < chunks;
+            const uint4 wh0 = ok0 ? w_hi[c] : zero, wl0 = ok0 ? w_lo[c] : zero, xv0 = ok0 ? x_row[c] : zero;
+            const uint4 wh1 = ok1 ? w_hi[c + 4] : zero, wl1 = ok1 ? w_lo[c + 4] : zero, xv1 = ok1 ? x_row[c + 4] : zero;
+            mma_16816(acc[0], wh0.x, wl0.x, wh0.y, wl0.y, xv0.x, xv0.y);
+            mma_16816(acc[1], wh0.z, wl0.z, wh0.w, wl0.w, xv0.z, xv0.w);
+            mma_16816(acc[2], wh1.x, wl1.x, wh1.y, wl1.y, xv1.x, xv1.y);
+            mma_16816(acc[3], wh1.z, wl1.z, wh1.w, wl1.w, xv1.z, xv1.w);
+        }
+        // acc[.][0], [1]: (row r, batch 2q, 2q + 1); acc[.][2], [3]: (row r + 8, same)
+        float* mine = red + item * 128;
+        mine[r * 8 + 2 * q] = (acc[0][0] + acc[1][0]) + (acc[2][0] + acc[3][0]);
+        mine[r * 8 + 2 * q + 1] = (acc[0][1] + acc[1][1]) + (acc[2][1] + acc[3][1]);
+        mine[(r + 8) * 8 + 2 * q] = (acc[0][2] + acc[1][2]) + (acc[2][2] + acc[3][2]);
+        mine[(r + 8) * 8 + 2 * q + 1] = (acc[0][3] + acc[1][3]) + (acc[2][3] + acc[3][3]);
+    }
+    __syncthreads();
+    if (p.late_trigger) pdl_trigger();
+
+    // ---- add the K parts and store: consecutive threads, consecutive outputs ----
+    for (int i = threadIdx.x; i < p.M * n_mine; i += kStThreads) {
+        if (i != static_cast<int>(threadIdx.x)) { e_m = i / n_mine; e_o = i - e_m * n_mine; }
+        const int t = e_o / OUT_PER_TILE, row = e_o - t * OUT_PER_TILE;
+        const float* part = red + t * p.warps_k * 128 + row * 8 + e_m;
+        float s0 = 0.f, s1 = 0.f;
+        for (int w = 0; w < p.warps_k; ++w) {
+            s0 += part[w * 128];
+            if constexpr (SWIGLU) s1 += part[w * 128 + 64];
+        }
+        float y = s0;
+        if constexpr (SWIGLU) {
+            const float g = rnd<__nv_bfloat16>(s0), u = rnd<__nv_bfloat16>(s1);
+            y = rnd<__nv_bfloat16>(g / (1.f + expf(-g))) * u;
+        }
+        p.out[static_cast<int64_t>(e_m) * n_out + o0 + e_o] = __float2bfloat16_rn(y);
+    }
+}
+
+// The plan of a launch: outputs per block, tiles, warps per tile and shared memory; false if the shape is not for this
+// kernel (the block's rows do not fit into about half an SM's shared memory).
+struct StreamPlan { int blocks, opb, n_tiles, warps_k; size_t smem; };
+static bool stream_plan(int N, int K, bool swiglu, StreamPlan* plan) {
+    static int sms = 0;
+    if (sms == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (sms <= 0) sms = 148;
+    }
+    const int n_out = swiglu ? N / 2 : N;
+    if (n_out <= 0 || K <= 0 || (K % 8) || (swiglu && (N % 2))) return false;
+    const int opb = (n_out + sms - 1) / sms;
+    const int per_tile = swiglu ? 8 : 16;
+    const int n_tiles = (opb + per_tile - 1) / per_tile;
+    const int slabs = (K + 31) / 32;
+    const int warps_k = max(1, min(slabs, kStWarps / n_tiles));
+    const size_t row = static_cast<size_t>(K + kXPad) * sizeof(__nv_bfloat16);
+    const size_t smem = 16 + kBatch * kStWarps * sizeof(float) + row * (kBatch + static_cast<size_t>(swiglu ? 2 : 1) * opb) +
+                        static_cast<size_t>(n_tiles) * warps_k * 128 * sizeof(float);
+    if (smem > 113 * 1024 || static_cast<size_t>(swiglu ? 2 : 1) * opb * K * 2 >= (1u << 20)) return false;
+    plan->blocks = (n_out + opb - 1) / opb; plan->opb = opb; plan->n_tiles = n_tiles; plan->warps_k = warps_k; plan->smem = smem;
+    return true;
+}
+
 }  // namespace cvb
 
 using namespace cvb;
+
+// 1 if cvb_gemv_stream_bf16 takes a weight of N rows and K columns in this mode (0 plain, 1 norm, 2 norm + SwiGLU).
+extern "C" int cvb_gemv_stream_supported(int N, int K, int mode) {
+    StreamPlan plan;
+    return stream_plan(N, K, mode == 2, &plan) ? 1 : 0;
+}
+
+// out[:M] = x[:M] W^T for up to 8 rows and a weight whose per-SM share fits into shared memory; modes as cvb_gemv_bf16.
+// `prefetch` (or null) names bytes that a later kernel will stream; this one asks them into the L2.  With `late_trigger`
+// the kernel behind this one starts when this one's products are done rather than as early as possible.  The launch
+// always carries the programmatic-dependent-launch attribute unless `pdl` is 0.
+extern "C" int cvb_gemv_stream_bf16(void* out, const void* x, const void* delta, void* resid_out, const float* norm_w,
+                                    const void* W, int M, int N, int K, float eps, int mode, const void* prefetch,
+                                    long long prefetch_bytes, int late_trigger, int pdl, int* err, cudaStream_t stream) {
+    if (M == 0) return CVB_OK;
+    if (M < 0 || M > kBatch || N <= 0 || K <= 0) return CVB_E_SIZE;
+    if (K % 8) return CVB_E_ALIGN;
+    auto al = [](const void* q) { return q == nullptr || (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+    if (!al(out) || !al(x) || !al(delta) || !al(resid_out) || !al(W) || !al(norm_w) || !al(prefetch)) return CVB_E_ALIGN;
+    if (mode != 0 && norm_w == nullptr) return CVB_E_SHAPE;
+    if (mode < 0 || mode > 2 || err == nullptr) return CVB_E_SHAPE;
+    if (delta != nullptr && (resid_out == nullptr || resid_out == x)) return CVB_E_SHAPE;
+    StreamPlan plan;
+    if (!stream_plan(N, K, mode == 2, &plan)) return CVB_E_UNSUPPORTED;
+    StreamParams p{};
+    p.out = (__nv_bfloat16*)out; p.x = (const __nv_bfloat16*)x; p.delta = (const __nv_bfloat16*)delta;
+    p.resid_out = (__nv_bfloat16*)resid_out; p.norm_w = norm_w; p.W = (const __nv_bfloat16*)W;
+    p.prefetch = (const unsigned char*)prefetch; p.prefetch_bytes = prefetch != nullptr ? prefetch_bytes : 0; p.err = err;
+    p.M = M; p.N = N; p.K = K; p.opb = plan.opb; p.n_tiles = plan.n_tiles; p.warps_k = plan.warps_k;
+    p.late_trigger = late_trigger ? 1 : 0; p.eps = eps;
+    p.warps_per_row = M <= 1 ? 16 : (M <= 2 ? 8 : (M <= 4 ? 4 : 2));
+    static bool set[3] = {false, false, false};                       // the three kernels share one pointer type: one flag per mode
+    auto go = [&](void (*kernel)(StreamParams)) {
+        if (!set[mode]) {
+            if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 113 * 1024) != cudaSuccess) { cudaGetLastError(); return CVB_E_SIZE; }
+            // all kernels of the chain ask for the largest shared-memory partition, so that a block of the next kernel
+            // can join a running block on its SM without the partition having to change
+            cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+            cudaGetLastError();
+            set[mode] = true;
+        }
+        launch_kernel_dependent(kernel, dim3(plan.blocks), dim3(kStThreads), plan.smem, stream, pdl != 0, p);
+        return launch_status();
+    };
+    if (mode == 0) return go(gemv_stream_kernel<false, false>);
+    if (mode == 1) return go(gemv_stream_kernel<true, false>);
+    return go(gemv_stream_kernel<true, true>);
+}
+
 
 // mode: 0 = plain product, 1 = norm(+add) prologue, 2 = norm(+add) prologue and SwiGLU epilogue.
 extern "C" int cvb_gemv_bf16(void* out, const void* x, const void* delta, void* resid_out, const float* norm_w,

@@ -8,7 +8,7 @@ from __future__ import annotations
 
 import ctypes
 from ctypes import c_int, c_int64, c_float, c_void_p
-from typing import Optional
+from typing import Dict, Optional
 
 import torch
 
@@ -427,14 +427,7 @@ def gemv_bf16(out: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, rows: in
     """out[:rows] = x[:rows] @ weight^T for a few rows.  With `norm_weight`, x is the residual stream: `delta` (if given)
     is added first and the sum written to `resid_out`, then the RMSNorm with `norm_weight` is applied before the
     product.  With `swiglu`, weight holds gate rows over up rows and out receives silu(gate) * up."""
-    global _gemv
-    if _gemv is None:
-        lib = load_library("gemv_bf16")
-        lib.cvb_gemv_bf16.restype = c_int
-        lib.cvb_gemv_splitk_bf16.restype = c_int
-        lib.cvb_gemv_splitk_scratch_floats.restype = c_int64
-        lib.cvb_gemv_splitk_counters.restype = c_int
-        _gemv = lib
+    _gemv_lib()
     _cuda(out, x, weight, norm_weight, delta, resid_out)
     _contig(out, x, weight, norm_weight, delta, resid_out)
     N, K = weight.shape
@@ -455,6 +448,68 @@ def gemv_bf16(out: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, rows: in
     return out
 
 
+def _gemv_lib():
+    global _gemv
+    if _gemv is None:
+        lib = load_library("gemv_bf16")
+        for name in ("cvb_gemv_bf16", "cvb_gemv_splitk_bf16", "cvb_gemv_splitk_counters", "cvb_gemv_stream_bf16",
+                     "cvb_gemv_stream_supported"):
+            getattr(lib, name).restype = c_int
+        lib.cvb_gemv_splitk_scratch_floats.restype = c_int64
+        _gemv = lib
+    return _gemv
+
+
+STREAM_MAX_ROWS = 8
+_stream_ok: Dict[tuple, bool] = {}
+
+
+def gemv_stream_supported(x_dtype: torch.dtype, weight: torch.Tensor, rows: int, swiglu: bool = False) -> bool:
+    """The product that runs one block per SM and fetches the block's whole share of the weight ahead of its dependency
+    covers bf16 operands, up to 8 rows, and weights whose share per SM (rows / #SMs, whole rows) fits into about half an
+    SM's shared memory beside the staged activations: matrices of a few megabytes."""
+    if not (x_dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and weight.dim() == 2 and 0 < rows <= STREAM_MAX_ROWS):
+        return False
+    key = (weight.shape[0], weight.shape[1], swiglu)
+    ok = _stream_ok.get(key)
+    if ok is None:
+        ok = bool(_gemv_lib().cvb_gemv_stream_supported(c_int(key[0]), c_int(key[1]), c_int(2 if swiglu else 0)))
+        _stream_ok[key] = ok
+    return ok
+
+
+def gemv_stream_bf16(out: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, rows: int, norm_weight: Optional[torch.Tensor] = None,
+                     eps: float = 0.0, delta: Optional[torch.Tensor] = None, resid_out: Optional[torch.Tensor] = None,
+                     swiglu: bool = False, prefetch: Optional[torch.Tensor] = None, late_trigger: bool = False,
+                     dependent: bool = True) -> torch.Tensor:
+    """Same contract as gemv_bf16 for shapes that gemv_stream_supported accepts.  `prefetch`: a tensor that a later kernel
+    will stream (asked into the L2 by this kernel).  `late_trigger`: the next kernel on the stream may start only when
+    this one's products are done (for successors whose blocks should find the SMs free).  `dependent=False` launches
+    without the programmatic-dependent-launch attribute."""
+    lib = _gemv_lib()
+    _cuda(out, x, weight, norm_weight, delta, resid_out, prefetch)
+    _contig(out, x, weight, norm_weight, delta, resid_out, prefetch)
+    N, K = weight.shape
+    if x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or x.shape[1] != K:
+        raise KernelError("gemv_stream_bf16: x [M, K], weight [N, K] and out must be bf16")
+    if out.shape[1] != (N // 2 if swiglu else N) or out.shape[0] < rows or x.shape[0] < rows:
+        raise KernelError("gemv_stream_bf16: out must be [M, N] (or [M, N / 2] with swiglu)")
+    if swiglu and norm_weight is None:
+        raise KernelError("gemv_stream_bf16: the SwiGLU form comes with the norm prologue")
+    if norm_weight is not None and (norm_weight.dtype != torch.float32 or norm_weight.numel() != K):
+        raise KernelError("gemv_stream_bf16: norm_weight must be float32 [K]")
+    if delta is not None and (norm_weight is None or resid_out is None or delta.dtype != torch.bfloat16
+                              or resid_out.dtype != torch.bfloat16 or resid_out.data_ptr() == x.data_ptr()):
+        raise KernelError("gemv_stream_bf16: delta needs the norm prologue and a resid_out buffer other than x")
+    mode = 0 if norm_weight is None else (2 if swiglu else 1)
+    _check(lib.cvb_gemv_stream_bf16(_ptr(out), _ptr(x), _ptr(delta), _ptr(resid_out), _ptr(norm_weight), _ptr(weight), c_int(rows),
+                                    c_int(N), c_int(K), c_float(eps), c_int(mode), _ptr(prefetch),
+                                    ctypes.c_longlong(prefetch.numel() * prefetch.element_size() if prefetch is not None else 0),
+                                    c_int(1 if late_trigger else 0), c_int(1 if dependent else 0),
+                                    _ptr(error_flag(x.device)), _stream()), "gemv_stream_bf16")
+    return out
+
+
 _splitk_buffers: Dict[int, list] = {}
 
 
@@ -468,14 +523,7 @@ def gemv_splitk_bf16(out: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, r
     """out[:rows] = x[:rows] @ weight^T for up to 8 rows and a large weight.  The scratch for the partial sums and the
     counters belong to the device and grow with the largest weight seen; they are made at the first call with a weight
     (a warm-up before any graph capture, as the runner does, sizes them)."""
-    global _gemv
-    if _gemv is None:
-        lib = load_library("gemv_bf16")
-        lib.cvb_gemv_bf16.restype = c_int
-        lib.cvb_gemv_splitk_bf16.restype = c_int
-        lib.cvb_gemv_splitk_scratch_floats.restype = c_int64
-        lib.cvb_gemv_splitk_counters.restype = c_int
-        _gemv = lib
+    _gemv_lib()
     _cuda(out, x, weight)
     _contig(out, x, weight)
     N, K = weight.shape
@@ -498,9 +546,12 @@ def gemv_splitk_bf16(out: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, r
     return out
 
 
-def project_rows(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, rows: int) -> torch.Tensor:
+def project_rows(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, rows: int, dependent: bool = True) -> torch.Tensor:
     """out = x @ weight^T by the kernel that suits the step: the weight-streaming kernels for a few bf16 rows (split over
-    the inner dimension when the weight is large), the library product otherwise."""
+    the inner dimension when the weight is large), the library product otherwise.  `dependent=False` keeps a kernel that
+    would otherwise start ahead of its predecessor's end (and fetch its weights meanwhile) behind it."""
+    if gemv_stream_supported(x.dtype, weight, rows):
+        return gemv_stream_bf16(out, x, weight, rows, dependent=dependent)
     if gemv_splitk_preferred(x.dtype, weight, rows):
         return gemv_splitk_bf16(out, x, weight, rows)
     if gemv_supported(x.dtype, weight, rows):

@@ -105,8 +105,10 @@ class PagedAttention(Mixer):
         if pending is not None:
             h_new = ws.rows("residual_alt" if h.data_ptr() == ws.rows("residual", T, h.shape[1], h.dtype).data_ptr()
                             else "residual", T, h.shape[1], h.dtype)
-        qkv = ops.gemv_bf16(ws.rows("attn_qkv", T, (H + 2 * KV) * hd, h.dtype), h, self.w_qkv, T, norm_weight=norm.weight,
-                            eps=norm.eps, delta=pending, resid_out=h_new if pending is not None else None)
+        product = ops.gemv_stream_bf16 if ops.gemv_stream_supported(h.dtype, self.w_qkv, T) else ops.gemv_bf16
+        extra = {}
+        qkv = product(ws.rows("attn_qkv", T, (H + 2 * KV) * hd, h.dtype), h, self.w_qkv, T, norm_weight=norm.weight,
+                      eps=norm.eps, delta=pending, resid_out=h_new if pending is not None else None, **extra)
         return self._after_projection(qkv, ctx, cache), h_new
 
     # ---- decode steps: norm + projection + rotary + cache write in one persistent kernel ----
@@ -167,10 +169,12 @@ class PagedAttention(Mixer):
                 rotary_dim=pos.rotary_dim if pos is not None else 0,
                 interleaved=pos.interleaved if pos is not None else False)
             self.attend(att, q, ctx, cache, g)
-        return self._project(att, self.w_o, ws.rows("attn_proj", T, self.hidden_size, x.dtype), T)
+        # Behind the attention kernel the product starts only when that kernel has ended: measured, blocks of the product
+        # that arrive among the attention kernel's last blocks cost more (4 us a layer) than their early weights save.
+        return self._project(att, self.w_o, ws.rows("attn_proj", T, self.hidden_size, x.dtype), T, dependent=False)
 
-    def _project(self, x, w, out, rows):
-        return ops.linear(x, w, out=out) if self.rt.plain_kernels else ops.project_rows(x, w, out, rows)
+    def _project(self, x, w, out, rows, dependent=True):
+        return ops.linear(x, w, out=out) if self.rt.plain_kernels else ops.project_rows(x, w, out, rows, dependent=dependent)
 
     def _decode_from_projection(self, ctx, cache, g) -> bool:
         pos = self.position

@@ -64,7 +64,8 @@ class SwiGLUMLP(FeedForward):
         if pending is not None:
             h_new = ws.rows("residual_alt" if h.data_ptr() == ws.rows("residual", T, h.shape[1], h.dtype).data_ptr()
                             else "residual", T, h.shape[1], h.dtype)
-        act = ops.gemv_bf16(ws.rows("ffn_act", T, self.intermediate_size, h.dtype), h, self.w_gate_up, T,
-                            norm_weight=norm.weight, eps=norm.eps, delta=pending,
-                            resid_out=h_new if pending is not None else None, swiglu=True)
+        product = ops.gemv_stream_bf16 if ops.gemv_stream_supported(h.dtype, self.w_gate_up, T, swiglu=True) else ops.gemv_bf16
+        act = product(ws.rows("ffn_act", T, self.intermediate_size, h.dtype), h, self.w_gate_up, T,
+                      norm_weight=norm.weight, eps=norm.eps, delta=pending,
+                      resid_out=h_new if pending is not None else None, swiglu=True)
         return self._down(act, T), h_new

@@ -526,6 +526,45 @@ def test_gemv_plain_norm_and_swiglu_forms(ops, M, N, K):
         ops.gemv_bf16(out, x, W, M, norm_weight=nw, eps=eps, delta=delta, resid_out=x)
 
 
+@pytest.mark.parametrize("dependent", [True, False])
+@pytest.mark.parametrize("M", [1, 3, 8])
+@pytest.mark.parametrize("N,K", [(1024, 2048), (4096, 1024), (6144, 1024), (1024, 3072), (40, 72), (1000, 3064), (3, 8), (302, 40)])
+def test_gemv_stream_forms(ops, M, N, K, dependent):
+    """The product that fetches its block's weights by bulk copy ahead of its dependency (one block per SM): plain, with the
+    norm prologue and residual add, with the SwiGLU epilogue; row counts per block that are no multiple of a tile, inner
+    sizes that are no multiple of 32; twice in a row; with and without the dependent-launch attribute; against float32."""
+    dt = torch.bfloat16
+    g = torch.Generator().manual_seed(M * 37 + N + K)
+    d = dev()
+    W = (torch.randn(N, K, generator=g) * 0.05).to(dt).to(d)
+    assert ops.gemv_stream_supported(dt, W, M) and not ops.gemv_stream_supported(dt, W, 9)
+    assert not ops.gemv_stream_supported(torch.float32, W, 1)
+    assert not ops.gemv_stream_supported(dt, torch.empty(8192, 4096, dtype=dt, device="meta"), 1)    # 64 MB: not in one piece
+    for rep in range(2):
+        x = torch.randn(M, K, generator=g).to(dt).to(d)
+        out = torch.full((M, N), float("nan"), dtype=dt, device=d)
+        ops.gemv_stream_bf16(out, x, W, M, dependent=dependent, prefetch=W if rep else None, late_trigger=bool(rep))
+        torch.testing.assert_close(out.float(), rnd(x.float() @ W.float().t(), dt), atol=2e-2, rtol=2e-2)
+        delta = (torch.randn(M, K, generator=g) * 0.3).to(dt).to(d)
+        nw = (1 + 0.2 * torch.randn(K, generator=g)).to(d)
+        eps = 1e-5
+        h2 = torch.zeros_like(x)
+        ops.gemv_stream_bf16(out, x, W, M, norm_weight=nw, eps=eps, delta=delta, resid_out=h2, dependent=dependent)
+        s_ = rnd(x.float() + delta.float(), dt)
+        assert torch.equal(h2.float(), s_)
+        xn = rnd(rnd(s_ * torch.rsqrt((s_ * s_).mean(-1, keepdim=True) + eps), dt) * nw, dt)
+        torch.testing.assert_close(out.float(), rnd(xn @ W.float().t(), dt), atol=3e-2, rtol=3e-2)
+        if N % 2 == 0:
+            out2 = torch.full((M, N // 2), float("nan"), dtype=dt, device=d)
+            ops.gemv_stream_bf16(out2, x, W, M, norm_weight=nw, eps=eps, swiglu=True, dependent=dependent)
+            xf = x.float()
+            xn = rnd(rnd(xf * torch.rsqrt((xf * xf).mean(-1, keepdim=True) + eps), dt) * nw, dt)
+            gu = rnd(xn @ W.float().t(), dt)
+            gate, up = gu[:, :N // 2], gu[:, N // 2:]
+            torch.testing.assert_close(out2.float(), rnd(rnd(gate / (1 + torch.exp(-gate)), dt) * up, dt), atol=3e-2, rtol=3e-2)
+    ops.check_device_errors(d)
+
+
 @pytest.mark.parametrize("M,N,K", [(1, 200, 1000), (5, 128, 512), (8, 1031, 2056), (3, 4096, 4096)])
 def test_split_k_weight_streaming_product(ops, M, N, K):
     """The product for large weights (inner dimension split over blocks, last block adds the parts) at sizes that are no
