@@ -127,14 +127,16 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, const Tc
         asm volatile("cp.async.commit_group;\n" ::: "memory");
     }
     // per query tile: the range of key tiles it needs, t_lo <= j < t_hi (none if t_lo >= t_hi)
-    int t_lo[2], t_hi[2], key_hi = 0;
+    int t_lo[2], t_hi[2], key_hi = 0, key_lo = 0x3fffffff;
 #pragma unroll
     for (int x = 0; x < 2; ++x) {
         if (n_tok[x] > 0) {
             const int first = p.positions[cu0 + q0 + x * tok_per_tile];
             const int last = p.positions[cu0 + q0 + x * tok_per_tile + n_tok[x] - 1];
-            t_lo[x] = (p.window > 0 ? max(0, first - p.window + 1) : 0) / kTN;
+            const int first_key = p.window > 0 ? max(0, first - p.window + 1) : 0;   // the oldest key any of its tokens sees
+            t_lo[x] = first_key / kTN;
             t_hi[x] = last / kTN + 1;
+            key_lo = min(key_lo, first_key);
             key_hi = last;                                          // the block's last token
         } else {
             t_lo[x] = 0x3fffffff;
@@ -142,7 +144,9 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, const Tc
         }
     }
     const int j_lo = min(t_lo[0], t_lo[1]), j_hi = max(t_hi[0], t_hi[1]);
-    const int key_lo = j_lo * kTN;                                  // keys that exist for the clamp of the loads
+    // Loads are clamped to [key_lo, key_hi], the keys that the block's tokens see: a page below the window may have been
+    // given back by its request already (its table entry is -1) and is never looked up; rounding a key down to its box
+    // stays inside the page that holds it.
 
     if (warp == 0) {
         if (lane == 0) {

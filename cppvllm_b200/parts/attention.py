@@ -106,7 +106,8 @@ class PagedAttention(Mixer):
             h_new = ws.rows("residual_alt" if h.data_ptr() == ws.rows("residual", T, h.shape[1], h.dtype).data_ptr()
                             else "residual", T, h.shape[1], h.dtype)
         product = ops.gemv_stream_bf16 if ops.gemv_stream_supported(h.dtype, self.w_qkv, T) else ops.gemv_bf16
-        extra = {}
+        # the O product starts behind the attention kernel; its weights are asked into the L2 from here, ahead of it
+        extra = {"prefetch": self.w_o} if product is ops.gemv_stream_bf16 and self.w_o.dtype == torch.bfloat16 else {}
         qkv = product(ws.rows("attn_qkv", T, (H + 2 * KV) * hd, h.dtype), h, self.w_qkv, T, norm_weight=norm.weight,
                       eps=norm.eps, delta=pending, resid_out=h_new if pending is not None else None, **extra)
         return self._after_projection(qkv, ctx, cache), h_new

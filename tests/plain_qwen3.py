@@ -127,8 +127,9 @@ def lm_head(y: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
     return y @ w.t()
 
 
-def forward(model_dir: str, tokens, act: str = "float32", weights: dict = None, cfg: dict = None) -> torch.Tensor:
-    """Logits [T, V] at every position of one whole sequence (model_architecture.cpp:130-191, 222-236)."""
+def forward(model_dir: str, tokens, act: str = "float32", weights: dict = None, cfg: dict = None, rows=None) -> torch.Tensor:
+    """Logits [T, V] at every position of one whole sequence (model_architecture.cpp:130-191, 222-236); with `rows`,
+    only at those positions (the reference, too, picks rows before the final norm, :232-234)."""
     c = cfg or read_config(model_dir)
     w = weights or read_weights(model_dir)
     if act == "bfloat16":
@@ -155,6 +156,8 @@ def forward(model_dir: str, tokens, act: str = "float32", weights: dict = None, 
         u = linear(x, w[p + "mlp.up_proj.weight"], act)
         m = linear(swiglu(g, u, act), w[p + "mlp.down_proj.weight"], act)
         h = rnd(h + m, act)                                                            # residual 2 (:187-188)
+    if rows is not None:
+        h = h[torch.as_tensor(list(rows), dtype=torch.long)]
     y = rms_norm(h, w["model.norm.weight"], eps, act)
     head = w["model.embed_tokens.weight"] if c["tie"] else w["lm_head.weight"]
     return lm_head(y, head)

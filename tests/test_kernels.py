@@ -361,6 +361,13 @@ def test_tensor_core_attention_mixed_portions_and_single_tokens(ops, H, KV, hd, 
     seqs_v = [torch.randn(c + n, KV, hd, generator=g).to(dt) for c, n in reqs]
     total_pages = sum((c + n + page - 1) // page for c, n in reqs) + 3
     cache, tables = build_paged(seqs_k, seqs_v, page, total_pages, KV, hd, dt, g)
+    if window > 0:
+        # as in the engine: a request has given back the pages that lie wholly below its window (table entry -1), and
+        # someone else may have left anything in them (here NaN): no kernel may look them up or read them
+        for s, (c, n) in enumerate(reqs):
+            for slot in range(max(0, c - window + 1) // page):
+                cache[tables[s, slot]] = float("nan")
+                tables[s, slot] = -1
     cu, positions, seq_of = [0], [], []
     for s, (c, n) in enumerate(reqs):
         cu.append(cu[-1] + n)

@@ -148,6 +148,57 @@ def test_layers_differ_and_the_run_list_is_data(model_dirs):
         unregister_architecture("ToyWindowedForCausalLM")
 
 
+@pytest.mark.parametrize("prefill_kernel", ["tcgen05", "mma"])
+@pytest.mark.parametrize("window", [24, 150])
+def test_windowed_layers_in_bfloat16_through_the_tensor_core_kernels(model_dirs, window, prefill_kernel):
+    """tiny_c's weights (head size 64: the tensor-core attention kernels) with a window on every layer, pages of 16
+    tokens, bfloat16.  The prompt comes in portions longer than the window plus a page, so from the second portion on the
+    request has given back pages that lie below the window (their table entries are -1) while the kernels' first key tile
+    still starts below it; then single tokens are decoded past the window.  Logits against the plain windowed model;
+    no kernel may report a missing page."""
+    from cppvllm_b200.config.model_config import Qwen3Config
+    from cppvllm_b200.config.registry import register_architecture, unregister_architecture
+    from cppvllm_b200.engine.runner import StepEntry
+    from cppvllm_b200.models.qwen3 import build_qwen3_spec
+
+    def build(cfg):
+        spec = build_qwen3_spec(cfg)
+        for layer in spec.layers:
+            layer.mixer.params["window"] = window
+            layer.mixer.params["prefill_kernel"] = prefill_kernel
+        return spec
+
+    arch = f"ToyWindowed{window}{prefill_kernel}ForCausalLM"
+    register_architecture(arch, Qwen3Config.from_dict, build)
+    try:
+        d = model_dirs["tiny_c"] + f"_toy_windowed_{window}_{prefill_kernel}"
+        os.makedirs(d, exist_ok=True)
+        json.dump(dict(tiny_models.TINY_C, architectures=[arch]), open(os.path.join(d, "config.json"), "w"))
+        if not os.path.exists(os.path.join(d, "model.safetensors")):
+            os.symlink(os.path.join(model_dirs["tiny_c"], "model.safetensors"), os.path.join(d, "model.safetensors"))
+        cuts = (60, 45, 70, 2, 41) if window == 24 else (180, 170, 2, 30)
+        n_decode = 40
+        toks = tiny_models.random_tokens(200, sum(cuts) + n_decode, 8)
+        r = make_runner(d, torch.bfloat16, 16, num_pages=40, max_step_tokens=256, max_model_len=512)
+        ref = _windowed_reference(model_dirs["tiny_c"], toks, window, "bfloat16")
+        r.cache.admit("a")
+        got, pos, freed = [], 0, 0
+        for n in cuts + (1,) * n_decode:
+            r.cache.reserve("a", pos + n)
+            got.append(r.step([StepEntry("a", toks[pos:pos + n], pos, list(range(n)))]).float().cpu().clone())
+            pos += n
+            table = r.cache.lease("a").tables[0]
+            freed = max(freed, sum(1 for i, p in enumerate(table) if p < 0 and i * 16 < pos))
+            r.check_errors()                                 # after every step: a missing page would show at once
+        assert freed >= (pos - window) // 16 - 1             # pages below the window really went back
+        got = torch.cat(got)
+        assert (got - ref).abs().max() <= 2e-2 * max(1.0, float(ref.abs().max()))
+        r.cache.release("a")
+        r.cache.check_invariants()
+    finally:
+        unregister_architecture(arch)
+
+
 @pytest.mark.parametrize("name", ["tiny_b", "tiny_c"])
 def test_blocks_with_the_persistent_decode_kernels_give_the_same_logits(model_dirs, name, monkeypatch):
     """A block's options are data (LayerSpec.block_params).  With fuse_decode, steps of up to eight tokens run
@@ -251,6 +302,43 @@ def test_steps_of_a_repeated_shape_replay_a_graph_and_stay_right(model_dirs, dty
         scale = max(1.0, float(want.abs().max()))
         assert (row - want).abs().max() <= tol * scale
         assert (row - row_e).abs().max() <= tol * scale
+
+
+def _windowed_reference(d, toks, window, act):
+    """The plain model (tests/plain_qwen3.py, same rounding places) with every layer's attention limited to the last
+    `window` positions."""
+    c, w = plain.read_config(d), plain.read_weights(d)
+    if act == "bfloat16":
+        w = {k: plain.rnd(t, act) for k, t in w.items()}
+    T = len(toks)
+    cos, sin = plain.rope_tables(c["hd"], c["theta"], c["max_pos"])
+    pos = torch.arange(T)
+    H, KV, hd, eps = c["H"], c["KV"], c["hd"], c["eps"]
+    h = plain.embedding(w["model.embed_tokens.weight"], torch.tensor(toks))
+    far = (pos[:, None] - pos[None, :]) >= window            # [query, key]: the key has left the window
+    future = pos[None, :] > pos[:, None]
+    for l in range(c["L"]):
+        p = f"model.layers.{l}."
+        x = plain.rms_norm(h, w[p + "input_layernorm.weight"], eps, act)
+        q = plain.apply_rope(plain.qk_norm(plain.linear(x, w[p + "self_attn.q_proj.weight"], act).view(T, H, hd),
+                                           w[p + "self_attn.q_norm.weight"], eps, act), cos, sin, pos, act)
+        k = plain.apply_rope(plain.qk_norm(plain.linear(x, w[p + "self_attn.k_proj.weight"], act).view(T, KV, hd),
+                                           w[p + "self_attn.k_norm.weight"], eps, act), cos, sin, pos, act)
+        v = plain.linear(x, w[p + "self_attn.v_proj.weight"], act).view(T, KV, hd)
+        att = torch.empty(T, H, hd)
+        for hh in range(H):
+            g = hh // (H // KV)
+            s_ = (q[:, hh] @ k[:, g].t()) / hd ** 0.5
+            s_ = s_.masked_fill(far | future, float("-inf"))
+            att[:, hh] = torch.softmax(s_, -1) @ v[:, g]
+        att = plain.rnd(att, act)
+        h = plain.rnd(h + plain.linear(att.reshape(T, -1), w[p + "self_attn.o_proj.weight"], act), act)
+        x = plain.rms_norm(h, w[p + "post_attention_layernorm.weight"], eps, act)
+        m = plain.linear(plain.swiglu(plain.linear(x, w[p + "mlp.gate_proj.weight"], act), plain.linear(x, w[p + "mlp.up_proj.weight"], act), act),
+                         w[p + "mlp.down_proj.weight"], act)
+        h = plain.rnd(h + m, act)
+    y = plain.rms_norm(h, w["model.norm.weight"], eps, act)
+    return plain.lm_head(y, w["model.embed_tokens.weight"] if c["tie"] else w["lm_head.weight"])
 
 
 def _toy_reference(d, toks):

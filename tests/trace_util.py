@@ -45,8 +45,35 @@ def run_trace(model_dir, dtype, steps, max_tokens, out_dir, extra=()):
     return out
 
 
-def rows_by_position(steps, outputs):
-    """{(request id, absolute position): logits row} from a trace and its outputs."""
+def run_trace_in_process(runner, steps):
+    """The same protocol as trace_run's loop, on a ModelRunner that the test holds (one model load for many traces).
+    Returns {step: float32 array [wanted, vocab]}."""
+    from cppvllm_b200.engine.runner import StepEntry
+    out = {}
+    for st in steps:
+        entries = []
+        for e in st["entries"]:
+            rid = e["id"]
+            if rid not in runner.cache.leases:
+                runner.cache.admit(rid)
+            start = runner.cache.lease(rid).computed
+            runner.cache.reserve(rid, start + len(e["tokens"]))
+            entries.append(StepEntry(rid, list(e["tokens"]), start, list(e["want"])))
+        if entries:
+            logits = runner.step(entries)
+            if logits.shape[0] > 0:
+                out[st["step"]] = logits.float().cpu().numpy().copy()
+            runner.check_errors()
+        for rid in st.get("end", []):
+            if rid in runner.cache.leases:
+                runner.cache.release(rid)
+    return out
+
+
+def rows_by_position(steps, outputs, repeats=False):
+    """{(request id, absolute position): logits row} from a trace and its outputs.  With `repeats`, a request that
+    was ended and fed again from its first token (dropped and recomputed) may produce a position twice: the values are
+    lists of rows."""
     fed = {}
     rows = {}
     for st in steps:
@@ -55,8 +82,11 @@ def rows_by_position(steps, outputs):
             base = fed.get(e["id"], 0)
             for w in e["want"]:
                 key = (e["id"], base + w)
-                assert key not in rows
-                rows[key] = outputs[st["step"]][r]
+                if repeats:
+                    rows.setdefault(key, []).append(outputs[st["step"]][r])
+                else:
+                    assert key not in rows
+                    rows[key] = outputs[st["step"]][r]
                 r += 1
             fed[e["id"]] = base + len(e["tokens"])
         for rid in st.get("end", []):
