@@ -26,33 +26,33 @@ __global__ void embed_kernel(T* __restrict__ out, const T* __restrict__ table, c
     for (int i = threadIdx.x; i < D; i += blockDim.x) dst[i] = src[i];
 }
 
-template <typename T, bool ADD>
-__global__ void rmsnorm_kernel(T* __restrict__ out, T* resid, const T* __restrict__ x, const float* __restrict__ w,
-                               int D, float eps) {
+// Rows of any length and alignment (the forms further down need 16-byte rows): a warp owns a row and its lanes walk
+// the row's elements; with `add`, the residual stream is updated in place on the first walk and read back on the second.
+constexpr int kRowWarps = 8;
+
+template <typename T>
+__global__ void __launch_bounds__(kRowWarps * 32)
+rmsnorm_rows_kernel(T* __restrict__ out, T* stream_io, const T* __restrict__ x, const float* __restrict__ w, int n_rows, int D,
+                    float eps, int add) {
     pdl_trigger();
     pdl_wait();
-    __shared__ float scratch[32];
-    const int64_t row = blockIdx.x;
-    const T* xin = x + row * D;
-    T* res = ADD ? resid + row * D : nullptr;
-    T* o = out + row * D;
-    float ss = 0.f;
-    for (int i = threadIdx.x; i < D; i += blockDim.x) {
-        float v;
-        if constexpr (ADD) {
-            v = rnd<T>(to_float(res[i]) + to_float(xin[i]));
-            res[i] = from_float<T>(v);
-        } else {
-            v = to_float(xin[i]);
+    const int lane = threadIdx.x & 31;
+    const int64_t row = static_cast<int64_t>(blockIdx.x) * kRowWarps + (threadIdx.x >> 5);
+    if (row >= n_rows) return;
+    const T* src = x + row * D;
+    T* sum_row = add ? stream_io + row * D : nullptr;
+    float sq = 0.f;
+    for (int i = lane; i < D; i += 32) {
+        float v = to_float(src[i]);
+        if (add) {
+            v = rnd<T>(to_float(sum_row[i]) + v);
+            sum_row[i] = from_float<T>(v);
         }
-        ss += v * v;
+        sq = fmaf(v, v, sq);
     }
-    ss = block_sum(ss, scratch);
-    const float inv = rsqrtf(ss / static_cast<float>(D) + eps);
-    for (int i = threadIdx.x; i < D; i += blockDim.x) {
-        const float v = ADD ? to_float(res[i]) : to_float(xin[i]);
-        o[i] = from_float<T>(rnd<T>(v * inv) * w[i]);
-    }
+    const float scale = rsqrtf(warp_sum(sq) / static_cast<float>(D) + eps);
+    const T* normed_from = add ? sum_row : src;             // lanes read back only what they wrote themselves
+    for (int i = lane; i < D; i += 32) out[row * D + i] = from_float<T>(rnd<T>(to_float(normed_from[i]) * scale) * w[i]);
 }
 
 template <typename T>
@@ -61,20 +61,6 @@ __global__ void add_kernel(T* __restrict__ resid, const T* __restrict__ x, int64
     pdl_wait();
     const int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (i < n) resid[i] = from_float<T>(to_float(resid[i]) + to_float(x[i]));
-}
-
-template <typename T>
-__global__ void swiglu_kernel(T* __restrict__ out, const T* __restrict__ gu, int64_t n, int I) {
-    pdl_trigger();
-    pdl_wait();
-    const int64_t k = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-    if (k >= n) return;
-    const int64_t r = k / I;
-    const int i = static_cast<int>(k - r * I);
-    const float g = to_float(gu[r * 2 * I + i]);
-    const float u = to_float(gu[r * 2 * I + I + i]);
-    const float silu = rnd<T>(g / (1.f + expf(-g)));
-    out[k] = from_float<T>(silu * u);
 }
 
 template <typename T>
@@ -120,7 +106,7 @@ template <> struct Vec16<__nv_bfloat16> {
 constexpr int kNormThreads = 128;
 constexpr int kNormMaxChunks = 8;      // per thread: rows up to 128 * 8 * (4 or 8) elements stay in registers
 
-// Same arithmetic as rmsnorm_kernel, one global read of the row: the (summed) row is kept in registers.
+// Same arithmetic as rmsnorm_rows_kernel, one global read of the row: the (summed) row is kept in registers.
 template <typename T, bool ADD>
 __global__ void __launch_bounds__(kNormThreads)
 rmsnorm_vec_kernel(T* __restrict__ out, T* resid, const T* __restrict__ x, const float* __restrict__ w, int D, float eps) {
@@ -248,6 +234,19 @@ __host__ bool launch_warp_norm(T* out, T* resid, const T* x, const float* w, int
 template <typename T> __device__ __forceinline__ float silu_of(float g) { return g / (1.f + expf(-g)); }
 template <> __device__ __forceinline__ float silu_of<__nv_bfloat16>(float g) { return __fdividef(g, 1.f + __expf(-g)); }
 
+// any width: blockIdx.y walks the rows, the block's threads a row's columns
+template <typename T>
+__global__ void swiglu_rows_kernel(T* __restrict__ out, const T* __restrict__ gu, int n_rows, int I) {
+    pdl_trigger();
+    pdl_wait();
+    for (int64_t row = blockIdx.y; row < n_rows; row += gridDim.y) {
+        const T* gate = gu + row * 2 * I;
+        T* dst = out + row * I;
+        for (int col = blockIdx.x * blockDim.x + threadIdx.x; col < I; col += gridDim.x * blockDim.x)
+            dst[col] = from_float<T>(rnd<T>(silu_of<T>(to_float(gate[col]))) * to_float(gate[I + col]));
+    }
+}
+
 template <typename T>
 __global__ void swiglu_vec_kernel(T* __restrict__ out, const T* __restrict__ gu, int64_t n_chunks, int I) {
     pdl_trigger();
@@ -295,7 +294,7 @@ extern "C" int cvb_rmsnorm(void* out, const void* x, const float* w, int T, int 
     else if (vec_ok<TY>(out, x, nullptr, D) && D <= kNormThreads * kNormMaxChunks * Vec16<TY>::N)             \
         launch_kernel(rmsnorm_vec_kernel<TY, false>, dim3(T), dim3(kNormThreads), 0, stream, (TY*)out, nullptr, (const TY*)x, w, D, eps); \
     else                                                                                                      \
-        launch_kernel(rmsnorm_kernel<TY, false>, dim3(T), dim3(256), 0, stream, (TY*)out, nullptr, (const TY*)x, w, D, eps)
+        launch_kernel(rmsnorm_rows_kernel<TY>, dim3((T + kRowWarps - 1) / kRowWarps), dim3(kRowWarps * 32), 0, stream, (TY*)out, nullptr, (const TY*)x, w, T, D, eps, 0)
     CVB_DISPATCH_DTYPE(dtype, CALL);
 #undef CALL
     return launch_status();
@@ -310,7 +309,7 @@ extern "C" int cvb_add_rmsnorm(void* out, void* resid, const void* x, const floa
     else if (vec_ok<TY>(out, x, resid, D) && D <= kNormThreads * kNormMaxChunks * Vec16<TY>::N)               \
         launch_kernel(rmsnorm_vec_kernel<TY, true>, dim3(T), dim3(kNormThreads), 0, stream, (TY*)out, (TY*)resid, (const TY*)x, w, D, eps); \
     else                                                                                                      \
-        launch_kernel(rmsnorm_kernel<TY, true>, dim3(T), dim3(256), 0, stream, (TY*)out, (TY*)resid, (const TY*)x, w, D, eps)
+        launch_kernel(rmsnorm_rows_kernel<TY>, dim3((T + kRowWarps - 1) / kRowWarps), dim3(kRowWarps * 32), 0, stream, (TY*)out, (TY*)resid, (const TY*)x, w, T, D, eps, 1)
     CVB_DISPATCH_DTYPE(dtype, CALL);
 #undef CALL
     return launch_status();
@@ -330,13 +329,12 @@ extern "C" int cvb_swiglu(void* out, const void* gate_up, int T, int I, int dtyp
     if (T == 0) return CVB_OK;
     if (T < 0 || I <= 0) return CVB_E_SIZE;
     const int64_t n = static_cast<int64_t>(T) * I;
-    const unsigned blocks = static_cast<unsigned>((n + 255) / 256);
 #define CALL(TY)                                                                                              \
     if (vec_ok<TY>(out, gate_up, nullptr, I)) {                                                               \
         const int64_t nc = n / Vec16<TY>::N;                                                                  \
         launch_kernel(swiglu_vec_kernel<TY>, dim3(static_cast<unsigned>((nc + 255) / 256)), dim3(256), 0, stream, (TY*)out, (const TY*)gate_up, nc, I); \
     } else                                                                                                    \
-        launch_kernel(swiglu_kernel<TY>, dim3(blocks), dim3(256), 0, stream, (TY*)out, (const TY*)gate_up, n, I)
+        launch_kernel(swiglu_rows_kernel<TY>, dim3(static_cast<unsigned>(min(64, (I + 255) / 256)), static_cast<unsigned>(min(T, 65535))), dim3(256), 0, stream, (TY*)out, (const TY*)gate_up, T, I)
     CVB_DISPATCH_DTYPE(dtype, CALL);
 #undef CALL
     return launch_status();

@@ -32,153 +32,103 @@ __device__ __forceinline__ float uniform01(uint32_t x) {
     return (static_cast<float>(x >> 8) + 0.5f) * (1.0f / 16777216.0f);
 }
 
-struct Best { float v; int i; };
-__device__ __forceinline__ bool better(float v, int i, const Best& b) { return v > b.v || (v == b.v && i < b.i); }
-
 constexpr uint32_t kSampleTag = 0x53414D50u;
 
+// A candidate (score, vocabulary index) as one 64-bit word whose unsigned order is the sampler's order: the higher
+// score wins, among equal scores the lower index.  0 stands for "no candidate"; a NaN score is no candidate.
+__device__ __forceinline__ unsigned long long candidate(float score, int index) {
+    if (score != score) return 0ull;
+    uint32_t bits = __float_as_uint(score);
+    bits = (bits & 0x80000000u) ? ~bits : (bits | 0x80000000u);          // floats in their order, as unsigned numbers
+    return (static_cast<unsigned long long>(bits) << 32) | static_cast<uint32_t>(0x7fffffff - index);
+}
+__device__ __forceinline__ int candidate_token(unsigned long long c, int V) {
+    const int index = 0x7fffffff - static_cast<int>(static_cast<uint32_t>(c));
+    return (c != 0ull && index >= 0 && index < V) ? index : 0;           // a row of NaNs yields token 0, never an index >= V
+}
+__device__ __forceinline__ unsigned long long best_of_warp(unsigned long long c) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const unsigned long long other = __shfl_xor_sync(0xffffffffu, c, o);
+        c = other > c ? other : c;
+    }
+    return c;
+}
+
+// What a sampled row needs, read once per block.
+struct RowDraw {
+    const float* logits;
+    float inv_temp;
+    bool greedy;
+    uint32_t key_lo, key_hi, out_pos;
+};
+__device__ __forceinline__ RowDraw row_draw(int r, const float* logits, const int* rows, const float* temps,
+                                            const uint64_t* seeds, const int* out_positions, int V, int n_logit_rows) {
+    int src = rows != nullptr ? rows[r] : r;
+    src = max(0, min(src, n_logit_rows - 1));
+    const float temp = temps[r];
+    const uint64_t seed = seeds[r];
+    return RowDraw{logits + static_cast<int64_t>(src) * V, 1.0f / fmaxf(temp, 1e-5f), temp <= 0.f,
+                   static_cast<uint32_t>(seed), static_cast<uint32_t>(seed >> 32), static_cast<uint32_t>(out_positions[r])};
+}
+
+// The best candidate among the groups of four vocabulary entries g_begin + threadIdx.x, + blockDim.x, ... below g_end.
+// One Philox call serves a group; the counter names the group, so a score does not depend on who computes it.
+__device__ __forceinline__ unsigned long long best_of_groups(const RowDraw& d, int V, int g_begin, int g_end) {
+    unsigned long long best = 0ull;
+    for (int group = g_begin + threadIdx.x; group < g_end; group += blockDim.x) {
+        uint32_t bits[4] = {0u, 0u, 0u, 0u};
+        if (!d.greedy) {
+            const Philox4 p = philox4x32_10(Philox4{static_cast<uint32_t>(group), d.out_pos, kSampleTag, 0u}, d.key_lo, d.key_hi);
+            bits[0] = p.x; bits[1] = p.y; bits[2] = p.z; bits[3] = p.w;
+        }
+        const int first = group << 2, n = min(4, V - first);
+        for (int j = 0; j < n; ++j) {
+            float score = d.logits[first + j];
+            if (!d.greedy) score = score * d.inv_temp - logf(fmaxf(-logf(uniform01(bits[j])), 1e-10f));   // Gumbel-max
+            const unsigned long long c = candidate(score, first + j);
+            best = c > best ? c : best;
+        }
+    }
+    return best;
+}
+
+// Grid (rows, chunks): block (r, chunk) searches its share of row r's vocabulary.  With one chunk the block writes
+// the token; with more it leaves its best candidate in `part[r * n_chunks + chunk]` for sample_pick_kernel.  Either
+// way a row's token is the largest candidate over the whole vocabulary, so every chunk count gives the same token.
 __global__ void __launch_bounds__(1024)
-sample_kernel(int* __restrict__ out, const float* __restrict__ logits, const int* __restrict__ rows,
-              const float* __restrict__ temps, const uint64_t* __restrict__ seeds,
-              const int* __restrict__ out_positions, int V, int n_logit_rows) {
+sample_search_kernel(int* __restrict__ out, unsigned long long* __restrict__ part, const float* __restrict__ logits,
+                     const int* __restrict__ rows, const float* __restrict__ temps, const uint64_t* __restrict__ seeds,
+                     const int* __restrict__ out_positions, int V, int n_logit_rows, int n_chunks) {
     pdl_trigger();
     pdl_wait();
-    const int r = blockIdx.x;
-    int src = rows ? rows[r] : r;
-    if (src < 0) src = 0;
-    if (src >= n_logit_rows) src = n_logit_rows - 1;
-    const float* row = logits + static_cast<int64_t>(src) * V;
-    const float temp = temps[r];
-    const bool greedy = temp <= 0.f;
-    const float inv_t = 1.0f / fmaxf(temp, 1e-5f);
-    const uint64_t seed = seeds[r];
-    const uint32_t opos = static_cast<uint32_t>(out_positions[r]);
-
-    Best best{-INFINITY, 0x7fffffff};
-    for (int base = threadIdx.x * 4; base < V; base += blockDim.x * 4) {
-        uint32_t rn[4] = {0, 0, 0, 0};
-        if (!greedy) {
-            const Philox4 g = philox4x32_10(Philox4{static_cast<uint32_t>(base >> 2), opos, kSampleTag, 0u},
-                                            static_cast<uint32_t>(seed), static_cast<uint32_t>(seed >> 32));
-            rn[0] = g.x; rn[1] = g.y; rn[2] = g.z; rn[3] = g.w;
-        }
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            if (base + j >= V) break;
-            const float x = row[base + j];
-            float s = x;
-            if (!greedy) {
-                const float e = fmaxf(-logf(uniform01(rn[j])), 1e-10f);
-                s = x * inv_t - logf(e);
-            }
-            if (better(s, base + j, best)) { best.v = s; best.i = base + j; }
-        }
-    }
-#pragma unroll
-    for (int d = 16; d > 0; d >>= 1) {
-        const float ov = __shfl_down_sync(0xffffffffu, best.v, d);
-        const int oi = __shfl_down_sync(0xffffffffu, best.i, d);
-        if (better(ov, oi, best)) { best.v = ov; best.i = oi; }
-    }
-    __shared__ float sv[32];
-    __shared__ int si[32];
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = (blockDim.x + 31) >> 5;
-    if (lane == 0) { sv[warp] = best.v; si[warp] = best.i; }
-    __syncthreads();
-    if (warp == 0) {
-        best.v = lane < n_warps ? sv[lane] : -INFINITY;
-        best.i = lane < n_warps ? si[lane] : 0x7fffffff;
-#pragma unroll
-        for (int d = 16; d > 0; d >>= 1) {
-            const float ov = __shfl_down_sync(0xffffffffu, best.v, d);
-            const int oi = __shfl_down_sync(0xffffffffu, best.i, d);
-            if (better(ov, oi, best)) { best.v = ov; best.i = oi; }
-        }
-        if (lane == 0) out[r] = best.i < V ? best.i : 0;   // a row of NaNs yields token 0, never an index >= V
-    }
-}
-
-// Two-phase form for large vocabularies: phase 1 gives every row `n_chunks` blocks, each of which finds the best
-// (score, index) of its slice of the vocabulary; phase 2 picks the best of a row's partial results.  Scores, random
-// numbers and tie-breaking are those of sample_kernel, so both forms return the same token.
-__global__ void __launch_bounds__(256)
-sample_partial_kernel(float* __restrict__ part_v, int* __restrict__ part_i, const float* __restrict__ logits,
-                      const int* __restrict__ rows, const float* __restrict__ temps, const uint64_t* __restrict__ seeds,
-                      const int* __restrict__ out_positions, int V, int n_logit_rows, int n_chunks) {
-    pdl_trigger();
-    pdl_wait();
+    __shared__ unsigned long long per_warp[32];
     const int r = blockIdx.x, chunk = blockIdx.y;
-    int src = rows ? rows[r] : r;
-    if (src < 0) src = 0;
-    if (src >= n_logit_rows) src = n_logit_rows - 1;
-    const float* row = logits + static_cast<int64_t>(src) * V;
-    const float temp = temps[r];
-    const bool greedy = temp <= 0.f;
-    const float inv_t = 1.0f / fmaxf(temp, 1e-5f);
-    const uint64_t seed = seeds[r];
-    const uint32_t opos = static_cast<uint32_t>(out_positions[r]);
-    const int groups = (V + 3) >> 2;                                  // groups of four vocabulary entries
-    const int per = (groups + n_chunks - 1) / n_chunks;
-    const int g_begin = chunk * per, g_end = min(groups, g_begin + per);
-
-    Best best{-INFINITY, 0x7fffffff};
-    for (int gi = g_begin + threadIdx.x; gi < g_end; gi += blockDim.x) {
-        const int base = gi << 2;
-        uint32_t rn[4] = {0, 0, 0, 0};
-        if (!greedy) {
-            const Philox4 g = philox4x32_10(Philox4{static_cast<uint32_t>(gi), opos, kSampleTag, 0u},
-                                            static_cast<uint32_t>(seed), static_cast<uint32_t>(seed >> 32));
-            rn[0] = g.x; rn[1] = g.y; rn[2] = g.z; rn[3] = g.w;
-        }
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            if (base + j >= V) break;
-            const float x = row[base + j];
-            float sc = x;
-            if (!greedy) {
-                const float e = fmaxf(-logf(uniform01(rn[j])), 1e-10f);
-                sc = x * inv_t - logf(e);
-            }
-            if (better(sc, base + j, best)) { best.v = sc; best.i = base + j; }
-        }
-    }
-#pragma unroll
-    for (int d = 16; d > 0; d >>= 1) {
-        const float ov = __shfl_down_sync(0xffffffffu, best.v, d);
-        const int oi = __shfl_down_sync(0xffffffffu, best.i, d);
-        if (better(ov, oi, best)) { best.v = ov; best.i = oi; }
-    }
-    __shared__ float sv[8];
-    __shared__ int si[8];
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    if (lane == 0) { sv[warp] = best.v; si[warp] = best.i; }
+    const RowDraw d = row_draw(r, logits, rows, temps, seeds, out_positions, V, n_logit_rows);
+    const int groups = (V + 3) >> 2;
+    const int share = (groups + n_chunks - 1) / n_chunks;
+    unsigned long long best = best_of_warp(best_of_groups(d, V, chunk * share, min(groups, (chunk + 1) * share)));
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = (blockDim.x + 31) >> 5;
+    if (lane == 0) per_warp[warp] = best;
     __syncthreads();
-    if (threadIdx.x == 0) {
-        for (int w = 1; w < (blockDim.x >> 5); ++w)
-            if (better(sv[w], si[w], best)) { best.v = sv[w]; best.i = si[w]; }
-        part_v[r * n_chunks + chunk] = best.v;
-        part_i[r * n_chunks + chunk] = best.i;
-    }
+    if (warp != 0) return;
+    best = best_of_warp(lane < n_warps ? per_warp[lane] : 0ull);
+    if (lane != 0) return;
+    if (n_chunks == 1) out[r] = candidate_token(best, V);
+    else part[static_cast<int64_t>(r) * n_chunks + chunk] = best;
 }
 
-__global__ void sample_final_kernel(int* __restrict__ out, const float* __restrict__ part_v, const int* __restrict__ part_i,
-                                    int V, int n_chunks) {
+__global__ void sample_pick_kernel(int* __restrict__ out, const unsigned long long* __restrict__ part, int V, int n_chunks) {
     pdl_trigger();
     pdl_wait();
     const int r = blockIdx.x;
-    Best best{-INFINITY, 0x7fffffff};
+    unsigned long long best = 0ull;
     for (int c = threadIdx.x; c < n_chunks; c += 32) {
-        const float v = part_v[r * n_chunks + c];
-        const int i = part_i[r * n_chunks + c];
-        if (better(v, i, best)) { best.v = v; best.i = i; }
+        const unsigned long long other = part[static_cast<int64_t>(r) * n_chunks + c];
+        best = other > best ? other : best;
     }
-#pragma unroll
-    for (int d = 16; d > 0; d >>= 1) {
-        const float ov = __shfl_down_sync(0xffffffffu, best.v, d);
-        const int oi = __shfl_down_sync(0xffffffffu, best.i, d);
-        if (better(ov, oi, best)) { best.v = ov; best.i = oi; }
-    }
-    if (threadIdx.x == 0) out[r] = best.i < V ? best.i : 0;
+    best = best_of_warp(best);
+    if (threadIdx.x == 0) out[r] = candidate_token(best, V);
 }
 
 // tokens[i] = sampled[src[i]] where src[i] >= 0: hands the previous step's samples to this step's inputs on
@@ -202,22 +152,24 @@ extern "C" int cvb_sample(int* out, const float* logits, const int* rows, const 
                           cudaStream_t stream) {
     if (R == 0) return CVB_OK;
     if (R < 0 || V <= 0 || n_logit_rows <= 0) return CVB_E_SIZE;
-    launch_kernel(sample_kernel, dim3(R), dim3(1024), 0, stream, out, logits, rows, temps, seeds, out_positions, V, n_logit_rows);
+    launch_kernel(sample_search_kernel, dim3(R), dim3(1024), 0, stream, out, static_cast<unsigned long long*>(nullptr), logits, rows,
+                  temps, seeds, out_positions, V, n_logit_rows, 1);
     return launch_status();
 }
 
-// `scratch` holds R * n_chunks floats followed by R * n_chunks ints (n_chunks <= 64).
+// `scratch` holds R * n_chunks candidates of 8 bytes (n_chunks <= 64), 8-byte aligned.
 extern "C" int cvb_sample_chunked(int* out, const float* logits, const int* rows, const float* temps,
                                   const uint64_t* seeds, const int* out_positions, int R, int V, int n_logit_rows,
                                   int n_chunks, void* scratch, int64_t scratch_bytes, cudaStream_t stream) {
     if (R == 0) return CVB_OK;
     if (R < 0 || V <= 0 || n_logit_rows <= 0 || n_chunks < 1 || n_chunks > 64) return CVB_E_SIZE;
     if (scratch == nullptr || scratch_bytes < static_cast<int64_t>(R) * n_chunks * 8) return CVB_E_SCRATCH;
-    float* pv = static_cast<float*>(scratch);
-    int* pi = reinterpret_cast<int*>(pv + static_cast<int64_t>(R) * n_chunks);
+    if (reinterpret_cast<uintptr_t>(scratch) & 7) return CVB_E_ALIGN;
+    unsigned long long* part = static_cast<unsigned long long*>(scratch);
     dim3 grid(static_cast<unsigned>(R), static_cast<unsigned>(n_chunks));
-    launch_kernel(sample_partial_kernel, dim3(grid), dim3(256), 0, stream, pv, pi, logits, rows, temps, seeds, out_positions, V, n_logit_rows, n_chunks);
-    launch_kernel(sample_final_kernel, dim3(R), dim3(32), 0, stream, out, pv, pi, V, n_chunks);
+    launch_kernel(sample_search_kernel, dim3(grid), dim3(n_chunks == 1 ? 1024 : 256), 0, stream, out, part, logits, rows, temps, seeds,
+                  out_positions, V, n_logit_rows, n_chunks);
+    if (n_chunks > 1) launch_kernel(sample_pick_kernel, dim3(R), dim3(32), 0, stream, out, part, V, n_chunks);
     return launch_status();
 }
 

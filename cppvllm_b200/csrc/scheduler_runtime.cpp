@@ -4,6 +4,7 @@
 // device).  The decisions are those of engine/scheduler.py, which stays as the plain twin that the tests compare this
 // with step by step (and which is compared with the reference's own scheduler, engine/scheduler.cpp:36-151, through the
 // golden batches).  The cache manager is called directly (runtime.hpp).  Plain C entry points, called through ctypes.
+#include <algorithm>
 #include <deque>
 #include <unordered_set>
 
@@ -99,52 +100,75 @@ int cvb_sched_queue(void* h, int which, int* out, int max_out) {       // 0: wai
     return n;
 }
 
-// One step's decisions.  Running requests first, in their order: each takes what it still has to compute, within the
-// step's token budget and the cap on a portion; a request whose pages run out makes the last running request give up
-// everything it holds and wait again (itself, if it is the last), unless a step is in flight (allow_preempt 0), in which
-// case the batch is marked blocked.  Then waiting requests are admitted first come first served while pages, budget and
-// rows last.  info: [sequences, tokens, blocked, preempted, admitted].
-int cvb_sched_schedule(void* h, int allow_preempt, int* info) {
-    Sched* s = S(h);
-    s->batch.clear(); s->batch_preempted.clear(); s->batch_admitted.clear();
-    int budget = s->budget, total = 0;
-    const int cap = s->chunk_cap > 0 ? s->chunk_cap : 0x7fffffff;
-    std::deque<int> pending(s->running.begin(), s->running.end());
-    std::vector<int> kept;
-    bool preempted_now = false, blocked = false;
-    auto push = [&](Seq& q, int n) { q.scheduled = n; s->batch.push_back(q.id); total += n; budget -= n; };
-    while (!pending.empty()) {
-        Seq& q = s->at(pending.front());
-        pending.pop_front();
-        const int n_tok = q.len(), done = n_tok - q.prompt_len;
-        if (done > 0 && done >= q.max_tokens) { kept.push_back(q.id); continue; }      // its last token is in flight
-        int want = n_tok - q.cached;
-        if (budget < want) want = budget;
-        if (cap < want) want = cap;
-        if (want <= 0 || static_cast<int>(s->batch.size()) >= s->max_seqs) { kept.push_back(q.id); continue; }
-        bool yielded = false, stuck = false;
-        const bool covered = n_tok <= q.capacity;                                      // most decode steps need no new page
-        while (!covered && cvb_cm_can_reserve(s->cm, q.slot, n_tok) <= 0) {
-            if (!allow_preempt) { stuck = true; break; }
-            Seq* victim;
-            if (!pending.empty()) { victim = &s->at(pending.back()); pending.pop_back(); }
-            else { victim = &q; yielded = true; }
-            s->preempt(*victim);
-            s->batch_preempted.push_back(victim->id);
-            preempted_now = true;
-            if (yielded) break;
-        }
-        if (stuck) { blocked = true; kept.push_back(q.id); continue; }
-        if (yielded) continue;
-        if (!covered) q.capacity = cvb_cm_reserve(s->cm, q.slot, n_tok);
-        push(q, want);
-        kept.push_back(q.id);
+// ---- one step's decisions ---------------------------------------------------------------------------------------------
+// The step is planned in two passes over the queues.
+//   Pass 1, the running requests: the list is seen through a window [i, live).  Request i is served from the front; when
+//   its pages cannot grow, the request at the window's far end (live - 1) gives up everything it holds and waits again,
+//   which shrinks the window from behind; if the window has shrunk onto request i itself, it is the one that goes.  With a
+//   step in flight nobody may be taken out (allow_preempt 0): the request is left as it is and the plan is marked blocked.
+//   What is left of the window afterwards is the new running list.
+//   Pass 2, the waiting requests: admitted first come first served while rows, tokens and pages last; not at all in a step
+//   that took somebody out or was blocked.
+// The policy is the reference's (engine/scheduler.cpp:36-106); the golden batches under tests/golden hold it to that.
+struct StepPlan {
+    Sched* s;
+    int tokens_left;              // of the step's token budget
+    int portion_cap;              // longest portion of a prompt in one step
+    int total = 0;
+    bool blocked = false, took_out = false;
+
+    bool rows_full() const { return static_cast<int>(s->batch.size()) >= s->max_seqs; }
+    // how many of its tokens request q would run now: what it has not computed, cut to the cap and to the budget
+    int portion(const Seq& q) const { return std::min(std::min(q.len() - q.cached, portion_cap), tokens_left); }
+    void take(Seq& q, int n) {
+        q.scheduled = n;
+        s->batch.push_back(q.id);
+        total += n;
+        tokens_left -= n;
     }
-    s->running.swap(kept);
-    while (!preempted_now && !blocked && !s->waiting.empty() && budget > 0 && static_cast<int>(s->running.size()) < s->max_seqs &&
-           static_cast<int>(s->batch.size()) < s->max_seqs) {
+};
+
+enum class Room { kHasIt, kBlocked, kGaveWay };
+
+// Pages for all of q's tokens (q is running[i]).  May take requests out from the far end of the window.
+static Room make_room(StepPlan& plan, Seq& q, size_t i, size_t& live, bool allow_preempt) {
+    Sched* s = plan.s;
+    const int n_tok = q.len();
+    if (n_tok <= q.capacity) return Room::kHasIt;                       // most decode steps need no new page
+    while (cvb_cm_can_reserve(s->cm, q.slot, n_tok) <= 0) {
+        if (!allow_preempt) return Room::kBlocked;
+        Seq& last = s->at(s->running[--live]);                         // live - 1 >= i: at worst q itself
+        s->preempt(last);
+        s->batch_preempted.push_back(last.id);
+        plan.took_out = true;
+        if (live == i) return Room::kGaveWay;
+    }
+    q.capacity = cvb_cm_reserve(s->cm, q.slot, n_tok);
+    return Room::kHasIt;
+}
+
+static void serve_running(StepPlan& plan, bool allow_preempt) {
+    Sched* s = plan.s;
+    size_t live = s->running.size();
+    for (size_t i = 0; i < live; ++i) {
+        Seq& q = s->at(s->running[i]);
+        const int generated = q.len() - q.prompt_len;
+        if (generated > 0 && generated >= q.max_tokens) continue;      // complete but for the token still in flight
+        const int n = plan.portion(q);
+        if (n <= 0 || plan.rows_full()) continue;
+        const Room room = make_room(plan, q, i, live, allow_preempt);
+        if (room == Room::kBlocked) plan.blocked = true;
+        else if (room == Room::kHasIt) plan.take(q, n);
+    }
+    s->running.resize(live);
+}
+
+static void admit_waiting(StepPlan& plan) {
+    Sched* s = plan.s;
+    if (plan.took_out || plan.blocked) return;
+    while (!s->waiting.empty() && plan.tokens_left > 0 && static_cast<int>(s->running.size()) < s->max_seqs && !plan.rows_full()) {
         Seq& q = s->at(s->waiting.front());
-        if (!cvb_cm_can_admit(s->cm, q.tokens.data(), q.len(), q.len())) break;
+        if (!cvb_cm_can_admit(s->cm, q.tokens.data(), q.len(), q.len())) return;    // first come first served: nobody overtakes
         s->waiting.pop_front();
         q.slot = cvb_cm_admit(s->cm, q.tokens.data(), q.len());     // with the prefix cache: shared pages count as computed
         q.cached = cvb_rt::manager_computed(s->cm, q.slot);
@@ -152,12 +176,18 @@ int cvb_sched_schedule(void* h, int allow_preempt, int* info) {
         q.status = kRunning;
         s->running.push_back(q.id);
         s->batch_admitted.push_back(q.id);
-        int want = q.len() - q.cached;
-        if (budget < want) want = budget;
-        if (cap < want) want = cap;
-        push(q, want);
+        plan.take(q, plan.portion(q));
     }
-    info[0] = static_cast<int>(s->batch.size()); info[1] = total; info[2] = blocked ? 1 : 0;
+}
+
+// info: [sequences, tokens, blocked, preempted, admitted].
+int cvb_sched_schedule(void* h, int allow_preempt, int* info) {
+    Sched* s = S(h);
+    s->batch.clear(); s->batch_preempted.clear(); s->batch_admitted.clear();
+    StepPlan plan{s, s->budget, s->chunk_cap > 0 ? s->chunk_cap : 0x7fffffff};
+    serve_running(plan, allow_preempt != 0);
+    admit_waiting(plan);
+    info[0] = static_cast<int>(s->batch.size()); info[1] = plan.total; info[2] = plan.blocked ? 1 : 0;
     info[3] = static_cast<int>(s->batch_preempted.size()); info[4] = static_cast<int>(s->batch_admitted.size());
     return info[0];
 }

@@ -136,74 +136,79 @@ class Scheduler:
         self.num_preemptions += 1
 
     # ---- one step's decisions --------------------------------------------------------------------------
+    # Two passes, as in csrc/scheduler_runtime.cpp.  Pass 1 sees the running list through a window [i, live): request i
+    # is served from the front; when its pages cannot grow, the request at the far end of the window gives up what it
+    # holds and waits again (request i itself, once the window has shrunk onto it).  Pass 2 admits waiting requests first
+    # come first served, unless the step took somebody out or was blocked.  Policy of the reference's
+    # engine/scheduler.cpp:36-106, held to it by the golden batches.
     def schedule(self, allow_preempt: bool = True) -> ScheduledBatch:
         out = ScheduledBatch()
-        budget = self.cfg.max_num_batched_tokens
+        self._tokens_left = self.cfg.max_num_batched_tokens
+        self._took_out = False
+        self._serve_running(out, allow_preempt)
+        self._admit_waiting(out)
+        return out
+
+    def _portion(self, seq: Sequence) -> int:
+        """How many of its tokens the request would run now: what it has not computed, cut to the cap and to the budget."""
         cap = self.cfg.max_chunk_tokens if self.cfg.max_chunk_tokens > 0 else 1 << 62
-        pending: Deque[Sequence] = deque(self.running)
-        kept: List[Sequence] = []
-        preempted_now = False
+        return min(len(seq.token_ids) - seq.num_cached_tokens, cap, self._tokens_left)
 
-        def push(seq: Sequence, n: int) -> None:
-            nonlocal budget
-            seq.num_scheduled_tokens = n
-            out.seqs.append(seq)
-            out.total_tokens += n
-            budget -= n
+    def _take(self, out: ScheduledBatch, seq: Sequence, n: int) -> None:
+        seq.num_scheduled_tokens = n
+        out.seqs.append(seq)
+        out.total_tokens += n
+        self._tokens_left -= n
 
-        blocked = False
-        while pending:
-            seq = pending.popleft()
-            n_tok = len(seq.token_ids)
-            done = n_tok - seq.num_prompt_tokens
-            if done > 0 and done >= seq.params.max_tokens:
-                kept.append(seq)                       # its last token is still in flight
-                continue
-            want = min(n_tok - seq.num_cached_tokens, budget, cap)
-            if want <= 0 or len(out.seqs) >= self.cfg.max_num_seqs:
-                kept.append(seq)
-                continue
-            yielded = stuck = False
-            covered = n_tok <= seq.capacity                        # most decode steps need no new page
-            while not covered and not self.cache.can_reserve(seq.seq_id, len(seq)):
-                if not allow_preempt:
-                    stuck = True
-                    break
-                if pending:
-                    victim = pending.pop()
-                else:
-                    victim, yielded = seq, True
-                self._preempt(victim)
-                out.preempted.append(victim)
-                preempted_now = True
-                if yielded:
-                    break
-            if stuck:
-                blocked = True
-                kept.append(seq)
-                continue
-            if yielded:
-                continue
-            if not covered:
-                seq.capacity = self.cache.reserve(seq.seq_id, n_tok)
-            push(seq, want)
-            kept.append(seq)
-        self.running = kept
+    def _make_room(self, out: ScheduledBatch, i: int, live: int, allow_preempt: bool):
+        """Pages for all tokens of running[i].  Returns (outcome, live) with outcome 'has' | 'blocked' | 'gave_way'."""
+        seq = self.running[i]
+        n_tok = len(seq.token_ids)
+        if n_tok <= seq.capacity:                                  # most decode steps need no new page
+            return "has", live
+        while not self.cache.can_reserve(seq.seq_id, n_tok):
+            if not allow_preempt:
+                return "blocked", live
+            live -= 1                                              # live >= i: at worst the request itself
+            last = self.running[live]
+            self._preempt(last)
+            out.preempted.append(last)
+            self._took_out = True
+            if live == i:
+                return "gave_way", live
+        seq.capacity = self.cache.reserve(seq.seq_id, n_tok)
+        return "has", live
 
-        out.blocked = blocked
-        while (not preempted_now and not blocked and self.waiting and budget > 0 and len(self.running) < self.cfg.max_num_seqs
+    def _serve_running(self, out: ScheduledBatch, allow_preempt: bool) -> None:
+        live, i = len(self.running), 0
+        while i < live:
+            seq = self.running[i]
+            generated = len(seq.token_ids) - seq.num_prompt_tokens
+            n = 0 if (generated > 0 and generated >= seq.params.max_tokens) else self._portion(seq)   # complete but for a token in flight
+            if n > 0 and len(out.seqs) < self.cfg.max_num_seqs:
+                outcome, live = self._make_room(out, i, live, allow_preempt)
+                if outcome == "blocked":
+                    out.blocked = True
+                elif outcome == "has":
+                    self._take(out, seq, n)
+            i += 1
+        del self.running[live:]
+
+    def _admit_waiting(self, out: ScheduledBatch) -> None:
+        if self._took_out or out.blocked:
+            return
+        while (self.waiting and self._tokens_left > 0 and len(self.running) < self.cfg.max_num_seqs
                and len(out.seqs) < self.cfg.max_num_seqs):
             seq = self.waiting[0]
             if not self.cache.can_admit(seq.token_ids, len(seq)):
-                break
+                return                                             # first come first served: nobody overtakes
             self.waiting.popleft()
-            lease = self.cache.admit(seq.seq_id, seq.token_ids)      # with the prefix cache: shared pages count as computed
+            lease = self.cache.admit(seq.seq_id, seq.token_ids)    # with the prefix cache: shared pages count as computed
             seq.num_cached_tokens = lease.computed
             seq.capacity = self.cache.reserve(seq.seq_id, len(seq))
             seq.status = RUNNING
             self.running.append(seq)
-            push(seq, min(seq.num_uncached_tokens, budget, cap))
-        return out
+            self._take(out, seq, self._portion(seq))
 
     # ---- after the step ----------------------------------------------------------------------------------
     def on_launched(self, batch: ScheduledBatch) -> List[bool]:
