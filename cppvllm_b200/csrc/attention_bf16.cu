@@ -886,13 +886,15 @@ static int static_scratch_for_current_device(float** out) {
     std::lock_guard<std::mutex> lock(g_static_scratch_mu);
     if (g_static_scratch_ptr[dev] == nullptr) {
         float* ptr = nullptr;
+        // a failed call leaves its error behind in the runtime; it is taken out here (cudaGetLastError), so that the next
+        // launcher's status check does not report it against an unrelated kernel
         e = cudaGetSymbolAddress(reinterpret_cast<void**>(&ptr), g_static_decode_scratch);
-        if (e != cudaSuccess) return static_cast<int>(e);
+        if (e != cudaSuccess) { cudaGetLastError(); return static_cast<int>(e); }
         if (ptr == nullptr) return CVB_E_SCRATCH;
         e = cudaFuncSetAttribute(attn_decode_bf16_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem<128>());
-        if (e != cudaSuccess) return static_cast<int>(e);
+        if (e != cudaSuccess) { cudaGetLastError(); return static_cast<int>(e); }
         e = cudaFuncSetAttribute(attn_decode_bf16_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)decode_smem<64>());
-        if (e != cudaSuccess) return static_cast<int>(e);
+        if (e != cudaSuccess) { cudaGetLastError(); return static_cast<int>(e); }
         g_static_scratch_ptr[dev] = ptr;
     }
     *out = g_static_scratch_ptr[dev];

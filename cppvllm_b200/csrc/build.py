@@ -32,11 +32,10 @@ NVCC_FLAGS = [
 
 # library name -> source files
 LIBRARIES: Dict[str, List[str]] = {
-    "core": ["elementwise.cu", "qk_rope_kv.cu", "attention_general.cu", "sampling.cu"],
+    "core": ["elementwise.cu", "qk_rope_kv.cu", "attention_general.cu", "sampling.cu", "selftest.cu"],
     "attn_bf16": ["attention_bf16.cu"],
     "gemv_bf16": ["gemv_bf16.cu"],
     "gemm_bf16": ["gemm_tcgen05.cu"],
-    "decode_fused": ["decode_fused.cu"],
     "attn_tcgen05": ["attention_tcgen05.cu"],
     # host code only (the cache manager and the scheduler); nvcc hands it to the host compiler
     "runtime": ["cache_runtime.cpp", "scheduler_runtime.cpp"],
@@ -154,10 +153,13 @@ def build_library(name: str, verbose: bool = True) -> str:
 
 
 def load_library(name: str) -> ctypes.CDLL:
+    """The library `name`, built if need be.  CVB_LIBRARY_<NAME> in the environment names a file to load instead (a build
+    of the same sources with other flags, for instance the host runtime compiled with sanitizers)."""
     with _lock:
         lib = _loaded.get(name)
         if lib is None:
-            lib = ctypes.CDLL(build_library(name))
+            override = os.environ.get(f"CVB_LIBRARY_{name.upper()}")
+            lib = ctypes.CDLL(override if override else build_library(name))
             _loaded[name] = lib
         return lib
 

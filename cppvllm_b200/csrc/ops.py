@@ -128,6 +128,19 @@ def check_device_errors(device) -> None:
         raise KernelError(f"a kernel reported: {DEVICE_ERRORS.get(v, f'error {v}')}")
 
 
+def selftest_wait_runs_out(limit_cycles: int = 2_000_000) -> int:
+    """Launches a block that waits on a barrier nothing arrives on, with a limit of `limit_cycles` clock cycles (about a
+    millisecond by default).  Returns 1 if the wait gave up and the kernel ran to its end; the device error word then
+    holds 5 (check_device_errors raises "a bounded wait in a kernel ran out")."""
+    lib = core()
+    lib.cvb_selftest_wait_runs_out.restype = c_int
+    dev = torch.device("cuda", torch.cuda.current_device())
+    finished = torch.zeros(1, dtype=torch.int32, device=dev)
+    _check(lib.cvb_selftest_wait_runs_out(_ptr(error_flag(dev)), _ptr(finished), ctypes.c_longlong(limit_cycles), _stream()),
+           "selftest_wait_runs_out")
+    return int(finished.item())
+
+
 # ---- elementwise ------------------------------------------------------------------------------------------
 
 def embed(out: torch.Tensor, table: torch.Tensor, tokens: torch.Tensor) -> torch.Tensor:
@@ -407,8 +420,7 @@ _gemv = None
 
 SPLITK_MIN_BYTES = 16 << 20
 GEMV_MAX_ROWS = 16           # the weight-streaming product: one or two groups of eight activation rows
-SPLITK_MAX_ROWS = 8          # its split-K form and the persistent decode kernels: one group
-DECODE_FUSED_MAX_ROWS = 8
+SPLITK_MAX_ROWS = 8          # its split-K form: one group
 
 
 def gemv_supported(x_dtype: torch.dtype, weight: torch.Tensor, rows: int) -> bool:
@@ -592,65 +604,6 @@ def gemm_bf16_tcgen05(out: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, 
     _check(_gemm.cvb_gemm_bf16_tcgen05(_ptr(out), _ptr(x), _ptr(weight), c_int(M), c_int(N), c_int(K), c_int(1 if swiglu else 0),
                                        c_int(tile_n), _ptr(error_flag(x.device)), _stream()), "gemm_bf16_tcgen05")
     return out
-
-
-_fused = None
-
-
-def _fused_lib():
-    global _fused
-    if _fused is None:
-        lib = load_library("decode_fused")
-        lib.cvb_decode_block_tail.restype = c_int
-        lib.cvb_decode_block_head.restype = c_int
-        _fused = lib
-    return _fused
-
-
-def decode_fusion_supported(dtype: torch.dtype, rows: int, widths, head_dim: int) -> bool:
-    """The persistent decode kernels cover bf16 steps of up to 8 tokens, widths that are multiples of 8 and fit into
-    shared memory eight rows at a time, and head sizes of 16, 32, 64, 128 or 256."""
-    ch = head_dim // 8
-    return (dtype == torch.bfloat16 and 0 < rows <= DECODE_FUSED_MAX_ROWS and all(w % 8 == 0 for w in widths)
-            and 8 * (max(widths) + 32) * 2 + 8 * 128 * 4 <= 200 * 1024
-            and head_dim % 8 == 0 and 2 <= ch <= 32 and ch & (ch - 1) == 0)
-
-
-def decode_block_head(h_in, delta, h_out, norm_weight, eps, w_qkv, qkv, q_out, q_weight, k_weight, qk_eps, cos, sin, positions,
-                      slots, cache, rows: int, num_heads: int, num_kv_heads: int, head_dim: int, page_size: int, barrier):
-    """Residual add, RMSNorm, QKV product, per-head norm, rotary and cache write of a decode step in one persistent kernel."""
-    _cuda(h_in, delta, h_out, norm_weight, w_qkv, qkv, q_out, q_weight, k_weight, cos, sin, positions, slots, cache, barrier)
-    _contig(h_in, delta, h_out, norm_weight, w_qkv, qkv, q_out, q_weight, k_weight, cos, sin, positions, slots, cache, barrier)
-    D = h_in.shape[1]
-    if any(t.dtype != torch.bfloat16 for t in (h_in, w_qkv, qkv, q_out, cache)) or norm_weight.dtype != torch.float32:
-        raise KernelError("decode_block_head: activations, weights and pages must be bf16, norm weights float32")
-    if w_qkv.shape != ((num_heads + 2 * num_kv_heads) * head_dim, D) or barrier.dtype != torch.int32 or barrier.numel() < 2:
-        raise KernelError("decode_block_head: w_qkv must be [(H + 2 KV) hd, D]; barrier two int32")
-    if positions.dtype != torch.int32 or slots.dtype != torch.int32:
-        raise KernelError("decode_block_head: positions and slots must be int32")
-    _check(_fused_lib().cvb_decode_block_head(
-        _ptr(h_in), _ptr(delta), _ptr(h_out), _ptr(norm_weight), _ptr(w_qkv), _ptr(qkv), _ptr(q_out), _ptr(q_weight), _ptr(k_weight),
-        _ptr(cos), _ptr(sin), _ptr(positions), _ptr(slots), _ptr(cache), c_int(rows), c_int(D), c_int(num_heads),
-        c_int(num_kv_heads), c_int(head_dim), c_int(page_size), c_int(cos.shape[0] if cos is not None else 0),
-        c_int64(cache.numel()), c_float(eps), c_float(qk_eps), _ptr(barrier), _ptr(error_flag(h_in.device)), _stream()),
-        "decode_block_head")
-
-
-def decode_block_tail(att, w_o, y1, h_in, h_out, norm_weight, eps, w_gate_up, act, w_down, y2, rows: int, barrier):
-    """O product, residual add, RMSNorm, gate/up product with SwiGLU and down product of a decode step in one kernel."""
-    _cuda(att, w_o, y1, h_in, h_out, norm_weight, w_gate_up, act, w_down, y2, barrier)
-    _contig(att, w_o, y1, h_in, h_out, norm_weight, w_gate_up, act, w_down, y2, barrier)
-    D, Kq = w_o.shape
-    I = w_down.shape[1]
-    if any(t.dtype != torch.bfloat16 for t in (att, w_o, y1, h_in, h_out, w_gate_up, act, w_down, y2)) \
-            or norm_weight.dtype != torch.float32:
-        raise KernelError("decode_block_tail: activations and weights must be bf16, norm weights float32")
-    if w_gate_up.shape != (2 * I, D) or w_down.shape[0] != D or att.shape[1] != Kq or h_in.shape[1] != D:
-        raise KernelError("decode_block_tail: shapes of the weights do not fit one another")
-    _check(_fused_lib().cvb_decode_block_tail(
-        _ptr(att), _ptr(w_o), _ptr(y1), _ptr(h_in), _ptr(h_out), _ptr(norm_weight), _ptr(w_gate_up), _ptr(act), _ptr(w_down),
-        _ptr(y2), c_int(rows), c_int(D), c_int(Kq), c_int(I), c_float(eps), _ptr(barrier), _ptr(error_flag(att.device)),
-        _stream()), "decode_block_tail")
 
 
 # ---- sampling ----------------------------------------------------------------------------------------------

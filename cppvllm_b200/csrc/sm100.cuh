@@ -39,13 +39,15 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // Bounded wait (about 20 ms of clock cycles): if the barrier does not complete, error 5 is recorded and the caller goes
 // on with whatever it was waiting for.  No thread leaves early, so block-wide barriers stay matched and the kernel
 // always ends; the host sees the error flag and discards the step.
-__device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, int* err) {
-    if (mbar_try_wait(bar, parity)) return;
+__device__ __forceinline__ bool mbar_wait_cycles(uint64_t* bar, uint32_t parity, int* err, long long limit_cycles) {
+    if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     while (!mbar_try_wait(bar, parity)) {
-        if (clock64() - t0 > 40000000LL) { atomicExch(err, 5); return; }
+        if (clock64() - t0 > limit_cycles) { atomicExch(err, 5); return false; }
     }
+    return true;
 }
+__device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, int* err) { mbar_wait_cycles(bar, parity, err, 40000000LL); }
 
 // ---- TMA ---------------------------------------------------------------------------------------------------
 // One box of a 2-D tensor map into shared memory; completion is counted in bytes on `bar`.  x (the innermost

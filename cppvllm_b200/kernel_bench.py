@@ -174,51 +174,6 @@ def gemm(a) -> dict:
             "library_us": round(us_lib, 2), "library_TFLOPs": round(flops / us_lib / 1e6, 1)}
 
 
-def decode_block(a) -> dict:
-    """The two persistent kernels of a decode step against the separate kernels they replace (Qwen3-0.6B sizes by default)."""
-    from .csrc import ops
-    d = torch.device("cuda:0")
-    M, D, H, KV, hd, I = a.batch, a.cols, a.heads, a.kv_heads, a.head_dim, a.rows
-    N = (H + 2 * KV) * hd
-    copies = 12
-    rn = lambda *s: (torch.randn(*s, device=d) * 0.05).to(torch.bfloat16)
-    W = [dict(qkv=rn(N, D), o=rn(D, H * hd), gu=rn(2 * I, D), down=rn(D, I)) for _ in range(copies)]
-    h, delta, h2, h3 = rn(M, D), rn(M, D), rn(M, D), rn(M, D)
-    n1 = torch.ones(D, device=d)
-    qw = torch.ones(hd, device=d)
-    cos = torch.ones(4096, hd // 2, device=d)
-    sin = torch.zeros(4096, hd // 2, device=d)
-    pos = torch.arange(M, dtype=torch.int32, device=d)
-    slots = torch.arange(M, dtype=torch.int32, device=d) * 3
-    cache = torch.zeros(64, 2, KV, 32, hd, dtype=torch.bfloat16, device=d)
-    qkv, q, att = rn(M, N), rn(M, H * hd), rn(M, H * hd)
-    y1, act, y2 = rn(M, D), rn(M, I), rn(M, D)
-    barrier = torch.zeros(2, dtype=torch.int32, device=d)
-
-    def fused(i):
-        w = W[i % copies]
-        ops.decode_block_head(h, delta, h2, n1, 1e-6, w["qkv"], qkv, q, qw, qw, 1e-6, cos, sin, pos, slots, cache, M, H, KV, hd, 32, barrier)
-        ops.decode_block_tail(att, w["o"], y1, h2, h3, n1, 1e-6, w["gu"], act, w["down"], y2, M, barrier)
-
-    def separate(i):
-        w = W[i % copies]
-        ops.gemv_bf16(qkv, h, w["qkv"], M, norm_weight=n1, eps=1e-6, delta=delta, resid_out=h2)
-        ops.qk_norm_rope_kv(q, qkv, qw, qw, cos, sin, pos, slots, cache, H, KV, hd, 32, 1e-6)
-        ops.gemv_bf16(y1, att, w["o"], M)
-        ops.gemv_bf16(act, h2, w["gu"], M, norm_weight=n1, eps=1e-6, delta=y1, resid_out=h3, swiglu=True)
-        ops.gemv_bf16(y2, act, w["down"], M)
-
-    def head_only(i):
-        w = W[i % copies]
-        ops.decode_block_head(h, delta, h2, n1, 1e-6, w["qkv"], qkv, q, qw, qw, 1e-6, cos, sin, pos, slots, cache, M, H, KV, hd, 32, barrier)
-
-    us_f, us_s, us_h = _time(fused, a.iters), _time(separate, a.iters), _time(head_only, a.iters)
-    ops.check_device_errors(d)
-    nbytes = 2 * (N * D + D * H * hd + 2 * I * D + D * I)
-    return {"kernel": "decode block head + tail", "batch": M, "fused_us": round(us_f, 2), "head_us": round(us_h, 2),
-            "separate_us": round(us_s, 2), "weights_MB": round(nbytes / 1e6, 1), "fused_GBps": round(nbytes / us_f / 1e3, 1)}
-
-
 def elementwise(a) -> dict:
     """The memory-bound kernels of a prompt portion of --tokens tokens at the model's widths (--cols hidden, --rows
     intermediate): residual add + RMSNorm, SwiGLU, per-head norm + rotary + cache write.  Inputs stay in L2 between
@@ -253,7 +208,7 @@ def elementwise(a) -> dict:
 
 def main(argv=None) -> int:
     p = argparse.ArgumentParser(prog="kernel_bench")
-    p.add_argument("kernel", choices=["attn_decode", "attn_prefill", "gemv", "gemv_fused", "gemm", "decode_block", "elementwise"])
+    p.add_argument("kernel", choices=["attn_decode", "attn_prefill", "gemv", "gemv_fused", "gemm", "elementwise"])
     p.add_argument("--tile-n", type=int, default=0)
     p.add_argument("--impl", default="tcgen05", choices=["tcgen05", "mma"])
     p.add_argument("--form", default="plain", choices=["plain", "norm", "swiglu", "splitk"])

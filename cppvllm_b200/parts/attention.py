@@ -112,35 +112,6 @@ class PagedAttention(Mixer):
                       eps=norm.eps, delta=pending, resid_out=h_new if pending is not None else None, **extra)
         return self._after_projection(qkv, ctx, cache), h_new
 
-    # ---- decode steps: norm + projection + rotary + cache write in one persistent kernel ----
-    def can_fuse_decode_head(self, norm, ctx, cache) -> bool:
-        pos = self.position
-        return (not self.rt.plain_kernels and cache is not None and cache.writes and getattr(norm, "weight", None) is not None and hasattr(norm, "eps")
-                and self.w_qkv.dtype == torch.bfloat16 and self.w_o.dtype == torch.bfloat16
-                and (pos is None or (pos.rotary_dim == self.head_dim and not pos.interleaved))
-                and ops.decode_fusion_supported(self.rt.dtype, ctx.num_tokens, (self.hidden_size,), self.head_dim))
-
-    def decode_head(self, h, pending, norm, ctx, cache):
-        """Returns (attention output before the O product [T, H hd], residual stream)."""
-        T = ctx.num_tokens
-        H, KV, hd = self.num_heads, self.num_kv_heads, self.head_dim
-        ws = self.rt.workspace
-        g = ctx.groups[cache.group]
-        h_new = h
-        if pending is not None:
-            h_new = ws.rows("residual_alt" if h.data_ptr() == ws.rows("residual", T, h.shape[1], h.dtype).data_ptr()
-                            else "residual", T, h.shape[1], h.dtype)
-        qkv = ws.rows("attn_qkv", T, (H + 2 * KV) * hd, h.dtype)
-        q = ws.rows("attn_q", T, H * hd, h.dtype)
-        pos = self.position
-        ops.decode_block_head(h, pending, h_new if pending is not None else None, norm.weight, norm.eps, self.w_qkv, qkv, q,
-                              self.q_norm_w, self.k_norm_w, self.qk_norm_eps, pos.cos if pos is not None else None,
-                              pos.sin if pos is not None else None, ctx.positions, g.slot_mapping, cache.pages, T, H, KV, hd,
-                              g.page_size, ws.flat("grid_barrier", 2, torch.int32, zero=True))
-        att = ws.rows("attn_out", T, H * hd, h.dtype)
-        self.attend(att, q, ctx, cache, g)
-        return att, h_new
-
     def _after_projection(self, qkv, ctx, cache):
         T = qkv.shape[0]
         x = qkv

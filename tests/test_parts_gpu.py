@@ -199,11 +199,11 @@ def test_windowed_layers_in_bfloat16_through_the_tensor_core_kernels(model_dirs,
         unregister_architecture(arch)
 
 
-@pytest.mark.parametrize("name", ["tiny_b", "tiny_c"])
-def test_blocks_with_the_persistent_decode_kernels_give_the_same_logits(model_dirs, name, monkeypatch):
-    """A block's options are data (LayerSpec.block_params).  With fuse_decode, steps of up to eight tokens run
-    through the two persistent kernels; the logits agree with the blocks made of separate kernels to rounding, over
-    a prompt cut into small portions, decoded tokens and a second request beside them."""
+def test_a_parts_options_are_data(model_dirs, monkeypatch):
+    """A part's options travel in the specification (LayerSpec.mixer.params).  tiny_c's layers with the decode steps'
+    one-kernel attention switched off and the mma.sync prompt kernel chosen: the engine then runs other kernels (counted),
+    and the logits agree with the default choice to rounding, over a prompt cut into portions, decoded tokens and a
+    second request beside them."""
     from cppvllm_b200.config.model_config import Qwen3Config
     from cppvllm_b200.config.registry import register_architecture, unregister_architecture
     from cppvllm_b200.csrc import ops
@@ -213,29 +213,32 @@ def test_blocks_with_the_persistent_decode_kernels_give_the_same_logits(model_di
     def build(cfg):
         spec = build_qwen3_spec(cfg)
         for layer in spec.layers:
-            layer.block_params["fuse_decode"] = True
+            layer.mixer.params["fuse_decode_attention"] = False
+            layer.mixer.params["prefill_kernel"] = "mma"
         return spec
 
-    calls = {"head": 0, "tail": 0}
-    head, tail = ops.decode_block_head, ops.decode_block_tail
-    monkeypatch.setattr(ops, "decode_block_head", lambda *a, **k: (calls.__setitem__("head", calls["head"] + 1), head(*a, **k))[1])
-    monkeypatch.setattr(ops, "decode_block_tail", lambda *a, **k: (calls.__setitem__("tail", calls["tail"] + 1), tail(*a, **k))[1])
-    register_architecture("ToyFusedForCausalLM", Qwen3Config.from_dict, build)
+    calls = {"fused": 0, "mma": 0, "tcgen05": 0}
+    for key, fn_name in (("fused", "attn_decode_fused_bf16"), ("mma", "attn_prefill_bf16"), ("tcgen05", "attn_prefill_tcgen05")):
+        fn = getattr(ops, fn_name)
+        monkeypatch.setattr(ops, fn_name, lambda *a, _fn=fn, _k=key, **k: (calls.__setitem__(_k, calls[_k] + 1), _fn(*a, **k))[1])
+    register_architecture("ToyOptionsForCausalLM", Qwen3Config.from_dict, build)
     try:
-        d = model_dirs[name] + "_toy_fused"
+        name = "tiny_c"
+        d = model_dirs[name] + "_toy_options"
         os.makedirs(d, exist_ok=True)
-        cfg = dict(tiny_models.config(name), architectures=["ToyFusedForCausalLM"])
+        cfg = dict(tiny_models.config(name), architectures=["ToyOptionsForCausalLM"])
         json.dump(cfg, open(os.path.join(d, "config.json"), "w"))
         if not os.path.exists(os.path.join(d, "model.safetensors")):
             os.symlink(os.path.join(model_dirs[name], "model.safetensors"), os.path.join(d, "model.safetensors"))
         vocab = cfg["vocab_size"]
         a, b = tiny_models.random_tokens(vocab, 60, 5), tiny_models.random_tokens(vocab, 23, 6)
-        # (request, tokens) per step: whole portions, portions of 2 to 8 tokens, single tokens, two requests in a step
         plan = [[("a", 40)], [("a", 5)], [("a", 2), ("b", 6)], [("a", 1), ("b", 1)], [("b", 16)], [("a", 8)], [("a", 1)],
                 [("a", 3)]]
-        results = []
+        results, counted = [], []
         for folder in (model_dirs[name], d):
-            r = make_runner(folder, torch.bfloat16, tiny_models.page_size(name), enforce_eager=(folder == d))
+            for k in calls:
+                calls[k] = 0
+            r = make_runner(folder, torch.bfloat16, tiny_models.page_size(name), enforce_eager=True)
             pos = {"a": 0, "b": 0}
             seqs = {"a": a, "b": b}
             for rid in pos:
@@ -250,13 +253,14 @@ def test_blocks_with_the_persistent_decode_kernels_give_the_same_logits(model_di
                 got.append(r.step(entries).float().cpu().clone())
             r.check_errors()
             results.append(torch.cat(got))
-        layers = cfg["num_hidden_layers"]
-        small_steps = sum(1 for step in plan if sum(n for _, n in step) <= 8)
-        assert calls["head"] == calls["tail"] == small_steps * layers
-        ref, fused = results
-        assert (fused - ref).abs().max() <= 2e-2 * max(1.0, float(ref.abs().max()))
+            counted.append(dict(calls))
+        default, toy = counted
+        assert default["fused"] > 0 and default["tcgen05"] > 0 and default["mma"] == 0
+        assert toy["fused"] == 0 and toy["tcgen05"] == 0 and toy["mma"] > 0
+        ref, other = results
+        assert (other - ref).abs().max() <= 2e-2 * max(1.0, float(ref.abs().max()))
     finally:
-        unregister_architecture("ToyFusedForCausalLM")
+        unregister_architecture("ToyOptionsForCausalLM")
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
