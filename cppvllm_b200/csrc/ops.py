@@ -7,6 +7,7 @@ tensor that is not on a CUDA device, or a missing compiler, raises.
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import c_int, c_int64, c_float, c_void_p
 from typing import Dict, Optional
 
@@ -558,17 +559,78 @@ def gemv_splitk_bf16(out: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, r
     return out
 
 
+_project_choice: Dict[tuple, str] = {}
+_flush_buffers: Dict[int, torch.Tensor] = {}
+
+
+def _project_candidates(x: torch.Tensor, weight: torch.Tensor, rows: int):
+    names = []
+    if gemv_supported(x.dtype, weight, rows):
+        names.append("gemv")
+    if (x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and 0 < rows <= SPLITK_MAX_ROWS and weight.dim() == 2
+            and weight.shape[1] % 8 == 0 and weight.numel() * 2 >= (1 << 20)):
+        names.append("splitk")
+    names.append("library")
+    return names
+
+
+def _project_with(name: str, x, weight, out, rows):
+    if name == "gemv":
+        return gemv_bf16(out, x, weight, rows)
+    if name == "splitk":
+        return gemv_splitk_bf16(out, x, weight, rows)
+    return linear(x, weight, out=out)
+
+
+def _measure_projection(name: str, x, weight, out, rows) -> float:
+    """Microseconds of one call with the weight out of the L2 (a buffer larger than the L2 is written in between)."""
+    idx = x.device.index if x.device.index is not None else torch.cuda.current_device()
+    flush = _flush_buffers.get(idx)
+    if flush is None:
+        flush = torch.empty(256 << 20, dtype=torch.int8, device=x.device)
+        _flush_buffers[idx] = flush
+    _project_with(name, x, weight, out, rows)                 # sizes its scratch, loads its code
+    best = float("inf")
+    for _ in range(3):
+        flush.zero_()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        _project_with(name, x, weight, out, rows)
+        e1.record()
+        torch.cuda.synchronize()
+        best = min(best, e0.elapsed_time(e1) * 1e3)
+    return best
+
+
 def project_rows(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, rows: int, dependent: bool = True) -> torch.Tensor:
-    """out = x @ weight^T by the kernel that suits the step: the weight-streaming kernels for a few bf16 rows (split over
-    the inner dimension when the weight is large), the library product otherwise.  `dependent=False` keeps a kernel that
-    would otherwise start ahead of its predecessor's end (and fetch its weights meanwhile) behind it."""
+    """out = x @ weight^T by the kernel that suits the step.  A weight whose share per SM fits into shared memory goes
+    through the product made for chains of dependent launches (`dependent=False` keeps that kernel behind its
+    predecessor's end instead of letting it start early and fetch its weights meanwhile).  Otherwise the candidates for a
+    few bf16 rows (the weight-streaming product, its split-K form, the library's product) are timed once per shape, with
+    the weight out of the L2, the first time the shape is seen outside a graph capture, and the fastest is kept; during
+    a capture an unseen shape takes the split-K form for large weights, the weight-streaming product for small ones.
+    CVB_PROJECT=gemv|splitk|library in the environment fixes the choice."""
     if gemv_stream_supported(x.dtype, weight, rows):
         return gemv_stream_bf16(out, x, weight, rows, dependent=dependent)
-    if gemv_splitk_preferred(x.dtype, weight, rows):
-        return gemv_splitk_bf16(out, x, weight, rows)
-    if gemv_supported(x.dtype, weight, rows):
-        return gemv_bf16(out, x, weight, rows)
-    return linear(x, weight, out=out)
+    if rows > GEMV_MAX_ROWS or x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16:
+        return linear(x, weight, out=out)
+    key = (weight.shape[0], weight.shape[1], rows if rows <= 2 else (8 if rows <= 8 else 16))
+    choice = _project_choice.get(key)
+    if choice is None:
+        names = _project_candidates(x, weight, rows)
+        forced = os.environ.get("CVB_PROJECT")
+        if forced in names:
+            choice = forced
+        elif len(names) == 1:
+            choice = names[0]
+        elif torch.cuda.is_current_stream_capturing():
+            fallback = "splitk" if gemv_splitk_preferred(x.dtype, weight, rows) else ("gemv" if "gemv" in names else "library")
+            return _project_with(fallback, x, weight, out, rows)
+        else:
+            timed = {n: _measure_projection(n, x, weight, out, rows) for n in names}
+            choice = min(timed, key=timed.get)
+        _project_choice[key] = choice
+    return _project_with(choice, x, weight, out, rows)
 
 
 _gemm = None

@@ -4,6 +4,7 @@ of the kernel's own roofline (bytes it must read / time, or flops / time).
     python -m cppvllm_b200.kernel_bench attn_decode  --batch 8 --context 4096
     python -m cppvllm_b200.kernel_bench attn_prefill --tokens 2048
     python -m cppvllm_b200.kernel_bench gemv --batch 8 --rows 4096 --cols 1024
+    python -m cppvllm_b200.kernel_bench gemv_fused --form stream_norm --batch 8 --rows 4096 --cols 1024
 
 Inputs are larger than the 126 MB L2 where the shape allows, or the buffers are rotated between iterations so
 that no iteration finds its operands in L2.  This is also the small case that profiler captures run on.
@@ -131,12 +132,19 @@ def gemv_fused(a) -> dict:
     delta = torch.randn(a.batch, a.cols, device=d).to(torch.bfloat16)
     h2 = torch.empty_like(x)
     nw = torch.ones(a.cols, device=d)
-    n_out = a.rows // 2 if a.form == "swiglu" else a.rows
+    n_out = a.rows // 2 if a.form.endswith("swiglu") else a.rows
     out = torch.empty(a.batch, n_out, device=d, dtype=torch.bfloat16)
 
     def run(i):
         if a.form == "splitk":
             ops.gemv_splitk_bf16(out, x, ws[i % copies], a.batch)
+        elif a.form.startswith("stream"):
+            kind = a.form[len("stream"):].lstrip("_")
+            if kind == "":
+                ops.gemv_stream_bf16(out, x, ws[i % copies], a.batch)
+            else:
+                ops.gemv_stream_bf16(out, x, ws[i % copies], a.batch, norm_weight=nw, eps=1e-6, delta=delta, resid_out=h2,
+                                     swiglu=kind == "swiglu")
         elif a.form == "plain":
             ops.gemv_bf16(out, x, ws[i % copies], a.batch)
         else:
@@ -211,7 +219,7 @@ def main(argv=None) -> int:
     p.add_argument("kernel", choices=["attn_decode", "attn_prefill", "gemv", "gemv_fused", "gemm", "elementwise"])
     p.add_argument("--tile-n", type=int, default=0)
     p.add_argument("--impl", default="tcgen05", choices=["tcgen05", "mma"])
-    p.add_argument("--form", default="plain", choices=["plain", "norm", "swiglu", "splitk"])
+    p.add_argument("--form", default="plain", choices=["plain", "norm", "swiglu", "splitk", "stream", "stream_norm", "stream_swiglu"])
     p.add_argument("--batch", type=int, default=8)
     p.add_argument("--context", type=int, default=4096)
     p.add_argument("--tokens", type=int, default=2048)
@@ -228,7 +236,7 @@ def main(argv=None) -> int:
     a = p.parse_args(argv)
     if a.kernel == "attn_prefill" and a.batch == 8 and "--batch" not in (argv or sys.argv):
         a.batch = 1
-    res = {"attn_decode": attn_decode, "attn_prefill": attn_prefill, "gemv": gemv, "gemv_fused": gemv_fused, "gemm": gemm, "decode_block": decode_block,
+    res = {"attn_decode": attn_decode, "attn_prefill": attn_prefill, "gemv": gemv, "gemv_fused": gemv_fused, "gemm": gemm,
            "elementwise": elementwise}[a.kernel](a)
     print(json.dumps(res))
     return 0
