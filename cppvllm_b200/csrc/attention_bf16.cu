@@ -572,46 +572,54 @@ attn_decode_bf16_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnPa
     // The kernel behind this one may start now: its blocks arrive when most of this kernel's blocks have left their SMs, so
     // they spread evenly, and what they fetch ahead of their own wait overlaps the merge below.
     pdl_trigger();
-    // combine the four warps through shared memory (the tiles are no longer needed)
+    // combine the four warps through shared memory (the tiles are no longer needed); only the rows that hold a query
     __syncthreads();
     float* red_o = reinterpret_cast<float*>(sm.stages);                    // [4][16][HD]
     float* red_ml = red_o + 4 * 16 * HD;                                   // [4][16][2]
-    float* comb_o = red_ml + 4 * 16 * 2;                                   // [16][HD]  this block's part, for its cluster
-    float* comb_ml = comb_o + 16 * HD;                                     // [16][2]
+    // What the other blocks of the cluster send lies behind the new key and value, outside the tiles: a block that is
+    // done may send while this one still computes.  recv_o [splits][share], recv_ml [splits][16][2], weight [16][16], sum [16].
+    const int items = g * HD, share = (items + p.splits - 1) / p.splits;
+    float* recv_o = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(sm.bars) + 64 + 2 * HD * sizeof(__nv_bfloat16));
+    float* recv_ml = recv_o + p.splits * share;
+    float* weight = recv_ml + p.splits * 32;
+    float* row_sum = weight + 256;
 #pragma unroll
     for (int half = 0; half < 2; ++half) {
-        if (warp >= kConsumers / 32) break;                                // the producer warp holds no results
         const int r = (lane >> 2) + half * 8;
+        if (warp >= kConsumers / 32 || r >= g) continue;                   // the producer warp holds no results
 #pragma unroll
-        for (int dt = 0; dt < HD / 8; ++dt) {
-            const int d = dt * 8 + ((lane & 3) << 1);
-            red_o[(warp * 16 + r) * HD + d] = o[dt][half * 2];
-            red_o[(warp * 16 + r) * HD + d + 1] = o[dt][half * 2 + 1];
-        }
-        if ((lane & 3) == 0) {
-            red_ml[(warp * 16 + r) * 2] = m[half];
-            red_ml[(warp * 16 + r) * 2 + 1] = l[half];
-        }
+        for (int dt = 0; dt < HD / 8; ++dt)
+            *reinterpret_cast<float2*>(red_o + (warp * 16 + r) * HD + dt * 8 + ((lane & 3) << 1)) = make_float2(o[dt][half * 2], o[dt][half * 2 + 1]);
+        if ((lane & 3) == 0) *reinterpret_cast<float2*>(red_ml + (warp * 16 + r) * 2) = make_float2(m[half], l[half]);
     }
     __syncthreads();
-    for (int i = threadIdx.x; i < g * HD; i += kThreads) {
+    for (int i = threadIdx.x; i < items; i += kThreads) {
         const int r = i / HD, d = i % HD;
-        float mm = -INFINITY;
+        float mw[4], mm = -INFINITY;
 #pragma unroll
-        for (int w = 0; w < 4; ++w) mm = fmaxf(mm, red_ml[(w * 16 + r) * 2]);
+        for (int w = 0; w < 4; ++w) { mw[w] = red_ml[(w * 16 + r) * 2]; mm = fmaxf(mm, mw[w]); }
         float acc = 0.f, ll = 0.f;
 #pragma unroll
         for (int w = 0; w < 4; ++w) {
-            const float mw = red_ml[(w * 16 + r) * 2];
-            const float f = mw == -INFINITY ? 0.f : exp2f(mw - mm);
+            const float f = mw[w] == -INFINITY ? 0.f : exp2f(mw[w] - mm);
             acc += red_o[(w * 16 + r) * HD + d] * f;
             ll += red_ml[(w * 16 + r) * 2 + 1] * f;
         }
         if (p.splits == 1) {
             p.out[(static_cast<int64_t>(cu0) * p.H + kvh * g + r) * HD + d] = __float2bfloat16_rn(ll > 0.f ? acc / ll : 0.f);
         } else if (p.cluster) {
-            comb_o[r * HD + d] = acc;
-            if (d == 0) { comb_ml[r * 2] = mm; comb_ml[r * 2 + 1] = ll; }
+            // The splits of this (request, kv head) are the blocks of one cluster.  Output element i is merged by block
+            // i / share: this block's part of it goes straight into that block's shared memory, and its (maximum, sum)
+            // of every row to all blocks.  Remote stores do not wait for anything; the cluster's barrier below makes
+            // them visible.
+            const int owner = i / share;
+            st_cluster(recv_o + split * share + (i - owner * share), owner, acc);
+            if (d == 0) {
+                for (int k = 0; k < p.splits; ++k) {
+                    st_cluster(recv_ml + (split * 16 + r) * 2, k, mm);
+                    st_cluster(recv_ml + (split * 16 + r) * 2 + 1, k, ll);
+                }
+            }
         } else {
             const int64_t base = ((static_cast<int64_t>(seq) * p.KV + kvh) * p.splits + split) * 16 + r;
             p.part_o[base * HD + d] = acc;
@@ -619,25 +627,39 @@ attn_decode_bf16_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnPa
         }
     }
     if (p.splits == 1 || !p.cluster) return;
-    // The splits of this (request, kv head) are the blocks of one cluster: each has left its part in its own shared
-    // memory, and after the cluster's barrier each merges a share of the output elements, reading the others' parts
-    // through distributed shared memory.  The second barrier keeps every block's shared memory alive until all have read.
     cluster_sync();
-    const int items = g * HD, share = (items + p.splits - 1) / p.splits;
-    for (int i = split * share + threadIdx.x; i < min(items, (split + 1) * share); i += kThreads) {
-        const int r = i / HD, d = i % HD;
-        float mm = -INFINITY;
-        for (int c = 0; c < p.splits; ++c) mm = fmaxf(mm, ld_cluster(comb_ml + r * 2, c));
-        float acc = 0.f, ll = 0.f;
-        for (int c = 0; c < p.splits; ++c) {
-            const float mc = ld_cluster(comb_ml + r * 2, c);
-            const float f = mc == -INFINITY ? 0.f : exp2f(mc - mm);
-            acc += ld_cluster(comb_o + r * HD + d, c) * f;
-            ll += ld_cluster(comb_ml + r * 2 + 1, c) * f;
+    // From here on every block reads its own shared memory only, so no second barrier is needed: nobody writes into a
+    // block after the barrier, and nobody reads from it.
+    // Row r's weights: sixteen neighbouring lanes hold the sixteen possible splits of the row, find the row's maximum
+    // and the sum of the weighted sums by shuffles (a fixed tree: the same result in every block).
+    // (whole warps walk the rows two at a time, so that every lane of a warp takes part in its shuffles)
+    for (int r0 = warp * 2; r0 < g; r0 += (kThreads >> 5) * 2) {
+        const int r = r0 + (lane >> 4), c = lane & 15;
+        const bool has = r < g && c < p.splits;
+        const float mc = has ? recv_ml[(c * 16 + r) * 2] : -INFINITY;
+        const float lc = has ? recv_ml[(c * 16 + r) * 2 + 1] : 0.f;
+        float mm = mc;
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) mm = fmaxf(mm, __shfl_xor_sync(0xffffffffu, mm, o));
+        const float f = mc == -INFINITY ? 0.f : exp2f(mc - mm);
+        float ll = lc * f;
+#pragma unroll
+        for (int o = 8; o > 0; o >>= 1) ll += __shfl_xor_sync(0xffffffffu, ll, o);
+        if (r < g) {
+            weight[r * 16 + c] = f;
+            if (c == 0) row_sum[r] = ll;
         }
+    }
+    __syncthreads();
+    for (int j = threadIdx.x; j < share; j += kThreads) {
+        const int i = split * share + j;
+        if (i >= items) break;
+        const int r = i / HD, d = i % HD;
+        float acc = 0.f;
+        for (int c = 0; c < p.splits; ++c) acc += recv_o[c * share + j] * weight[r * 16 + c];
+        const float ll = row_sum[r];
         p.out[(static_cast<int64_t>(cu0) * p.H + kvh * g + r) * HD + d] = __float2bfloat16_rn(ll > 0.f ? acc / ll : 0.f);
     }
-    cluster_sync();
 }
 
 template <int HD>
@@ -672,9 +694,13 @@ static int kv_tensor_map(CUtensorMap* out, const void* cache, int64_t rows, int 
 }
 
 template <int HD> constexpr size_t prefill_smem() { return SmemPlan<HD, kPreStages, 64>::kBytes; }
-template <int HD> constexpr size_t decode_smem() {
-    const size_t red = 1024 + static_cast<size_t>(5 * 16) * (HD + 2) * sizeof(float);
-    const size_t plan = SmemPlan<HD, kDecStages, 16>::kBytes + 64 + 2 * HD * sizeof(__nv_bfloat16);   // + the new key and value
+// Shared memory of the decode kernel for `g` query heads per kv head: the tiles (re-used for the four warps' results),
+// the queries, the barriers, the new key and value, and what the cluster's blocks send one another (g * HD + 16 floats
+// of output parts, then [16][16][2] maxima and sums, [16][16] weights, [16] row sums).
+template <int HD> constexpr size_t decode_smem(int g = 16) {
+    const size_t red = 1024 + static_cast<size_t>(4 * 16) * (HD + 2) * sizeof(float);
+    const size_t plan = SmemPlan<HD, kDecStages, 16>::kBytes + 64 + 2 * HD * sizeof(__nv_bfloat16) +
+                        (static_cast<size_t>(g) * HD + 16 + 512 + 256 + 16) * sizeof(float);
     return plan > red ? plan : red;
 }
 
@@ -695,7 +721,7 @@ static int launch_decode(const CUtensorMap& map, AttnParams p, dim3 grid, dim3 m
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = grid;
         cfg.blockDim = dim3(kThreads);
-        cfg.dynamicSmemBytes = decode_smem<HD>();
+        cfg.dynamicSmemBytes = decode_smem<HD>(p.H / p.KV);
         cfg.stream = stream;
         cudaLaunchAttribute attr[2];
         attr[0].id = cudaLaunchAttributeClusterDimension;
@@ -727,7 +753,7 @@ static int launch_decode(const CUtensorMap& map, AttnParams p, dim3 grid, dim3 m
 apart:
     p.cluster = 0;
     if (p.splits > 1 && p.part_o == nullptr) return CVB_E_SCRATCH;
-    launch_kernel(attn_decode_bf16_kernel<HD>, dim3(grid), dim3(kThreads), decode_smem<HD>(), stream, map, p);
+    launch_kernel(attn_decode_bf16_kernel<HD>, dim3(grid), dim3(kThreads), decode_smem<HD>(p.H / p.KV), stream, map, p);
     if (p.splits > 1) launch_kernel(attn_decode_merge_kernel<HD>, dim3(mgrid), dim3(HD), 0, stream, p);
     return launch_status();
 }
@@ -935,10 +961,10 @@ extern "C" int cvb_attn_decode_bf16_static(void* out, const void* q, const void*
     dim3 grid(static_cast<unsigned>(S), static_cast<unsigned>(KV), static_cast<unsigned>(splits));
     dim3 mgrid(static_cast<unsigned>(S), static_cast<unsigned>(H));
     if (hd == 128) {
-        launch_kernel(attn_decode_bf16_kernel<128>, dim3(grid), dim3(kThreads), decode_smem<128>(), stream, map, p);
+        launch_kernel(attn_decode_bf16_kernel<128>, dim3(grid), dim3(kThreads), decode_smem<128>(H / KV), stream, map, p);
         if (splits > 1) launch_kernel(attn_decode_merge_kernel<128>, dim3(mgrid), dim3(128), 0, stream, p);
     } else {
-        launch_kernel(attn_decode_bf16_kernel<64>, dim3(grid), dim3(kThreads), decode_smem<64>(), stream, map, p);
+        launch_kernel(attn_decode_bf16_kernel<64>, dim3(grid), dim3(kThreads), decode_smem<64>(H / KV), stream, map, p);
         if (splits > 1) launch_kernel(attn_decode_merge_kernel<64>, dim3(mgrid), dim3(64), 0, stream, p);
     }
     return launch_status();

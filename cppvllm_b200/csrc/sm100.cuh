@@ -133,6 +133,13 @@ __device__ __forceinline__ float ld_cluster(const float* local, int rank) {
     return v;
 }
 
+// a float into the same shared-memory address of block `rank` of the cluster; visible there after the cluster's barrier
+__device__ __forceinline__ void st_cluster(float* local, int rank, float v) {
+    uint32_t remote;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;\n" : "=r"(remote) : "r"(smem_u32(local)), "r"(rank));
+    asm volatile("st.shared::cluster.f32 [%0], %1;\n" ::"r"(remote), "f"(v) : "memory");
+}
+
 // ---- arithmetic ----------------------------------------------------------------------------------------------
 __device__ __forceinline__ float ex2(float x) {
     float y;
