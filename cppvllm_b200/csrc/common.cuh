@@ -69,13 +69,17 @@ __device__ __forceinline__ float block_max(float v, float* scratch) {
     return r;
 }
 
-// Programmatic dependent launch.  Every kernel of the package starts with pdl_trigger() (the next kernel in the
-// stream may be scheduled as soon as all blocks of this one have started) and pdl_wait() (blocks until the kernels
-// before this one have completed and their writes are visible).  Nothing that depends on an earlier kernel's output is
-// read, and nothing is written, before pdl_wait(); a kernel may fetch weights before it.  This hides launch gaps between
-// the short kernels of eagerly launched steps (prompt portions).  Launches that are being captured into a CUDA graph do
-// not take the attribute: measured on a B200, a decode step replayed from a graph with programmatic edges ran 8 % slower
-// (edges into the weight-streaming products only) to 20 % slower (all edges) than with plain edges.  Both instructions do nothing in a kernel that was launched without the attribute.
+// Programmatic dependent launch.  Most kernels of the package start with pdl_trigger() (the next kernel in the stream
+// may be scheduled as soon as all blocks of this one have started) and pdl_wait() (blocks until the kernels before this
+// one have completed and their writes are visible).  Nothing that depends on an earlier kernel's output is read, and
+// nothing is written, before pdl_wait(); a kernel may fetch weights before it.  This hides launch gaps between the short
+// kernels of eagerly launched steps (prompt portions).  Launched through launch_kernel, a kernel does not take the
+// attribute while a CUDA graph is being captured: measured on a B200, a decode step replayed from a graph in which every
+// kernel had a programmatic edge ran 8 % slower than with plain edges, because blocks that arrive early land unevenly
+// on SMs that the kernel in front still occupies.  The kernels of the decode chain (gemv_bf16.cu: gemv_stream_kernel;
+// attention_bf16.cu: the fused decode attention) are written for such edges and take them inside graphs too, through
+// launch_kernel_dependent: one block per SM, at most half an SM's shared memory, the trigger placed where the successor's
+// early work does not get in the way.  Both instructions do nothing in a kernel that was launched without the attribute.
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 
@@ -98,8 +102,7 @@ inline void launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_
     cfg.numAttrs = 0;
     if (pdl_enabled()) {
         cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
-        static const bool in_graph = [] { const char* e = getenv("CVB_PDL_GRAPH"); return e && e[0] == '1'; }();
-        if (in_graph || (cudaStreamIsCapturing(stream, &cap) == cudaSuccess && cap == cudaStreamCaptureStatusNone)) cfg.numAttrs = 1;
+        if (cudaStreamIsCapturing(stream, &cap) == cudaSuccess && cap == cudaStreamCaptureStatusNone) cfg.numAttrs = 1;
     }
     cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
