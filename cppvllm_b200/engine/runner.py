@@ -103,13 +103,13 @@ class ModelRunner:
                 self.unit_location[uid] = (len(self.group_specs), 0)
                 self.group_specs.append((cs, [uid]))
         elem = torch.empty((), dtype=dtype).element_size()
-        self.page_bytes = [len(m) * 2 * cs.num_kv_heads * page_size * cs.head_dim * elem for cs, m in self.group_specs]
+        self.page_bytes = [len(m) * cs.elements_per_token() * page_size * elem for cs, m in self.group_specs]
         self.table_width = (self.max_model_len + page_size - 1) // page_size
         if num_pages is None:
             num_pages = self._pages_from_free_memory(gpu_memory_utilization)
         self.num_pages = int(num_pages)
-        self.storage = [torch.zeros((len(m), self.num_pages + 1, 2, cs.num_kv_heads, page_size, cs.head_dim),
-                                    dtype=dtype, device=self.device) for cs, m in self.group_specs]
+        self.storage = [torch.zeros((len(m), self.num_pages + 1) + cs.page_shape(page_size), dtype=dtype, device=self.device)
+                        for cs, m in self.group_specs]
         self.scratch_page = self.num_pages                    # the extra page: padding rows of captured graphs
         n_slots = int(num_state_slots if num_state_slots is not None else max_seqs)
         self.state_specs = self.model.state_specs()

@@ -47,7 +47,7 @@ class PagedAttention(Mixer):
 
     # ---- declarations ----
     def cache_spec(self) -> CacheSpec:
-        return CacheSpec(self.num_kv_heads, self.head_dim, self.window)
+        return CacheSpec.keys_and_values(self.num_kv_heads, self.head_dim, self.window)
 
     def weight_specs(self) -> Dict[str, WeightSpec]:
         D, H, KV, hd = self.hidden_size, self.num_heads, self.num_kv_heads, self.head_dim
@@ -96,15 +96,13 @@ class PagedAttention(Mixer):
                 and not ops.gemv_splitk_preferred(self.rt.dtype, self.w_qkv, ctx.num_tokens)
                 and ops.gemv_supported(self.rt.dtype, self.w_o, ctx.num_tokens))
 
-    def forward_fused(self, h, pending, norm, ctx, cache, state):
-        """h: residual stream, pending: delta not yet added (or None).  Returns (output, residual stream)."""
+    def forward_fused(self, h, pending, norm, ctx, cache, state, h_out):
+        """h: residual stream, pending: delta not yet added (or None), h_out: where rnd(h + pending) goes (a buffer
+        other than h; None without pending).  Returns (output, residual stream)."""
         T = ctx.num_tokens
         H, KV, hd = self.num_heads, self.num_kv_heads, self.head_dim
         ws = self.rt.workspace
-        h_new = h
-        if pending is not None:
-            h_new = ws.rows("residual_alt" if h.data_ptr() == ws.rows("residual", T, h.shape[1], h.dtype).data_ptr()
-                            else "residual", T, h.shape[1], h.dtype)
+        h_new = h_out if pending is not None else h
         product = ops.gemv_stream_bf16 if ops.gemv_stream_supported(h.dtype, self.w_qkv, T) else ops.gemv_bf16
         # the O product starts behind the attention kernel; its weights are asked into the L2 from here, ahead of it
         extra = {"prefetch": self.w_o} if product is ops.gemv_stream_bf16 and self.w_o.dtype == torch.bfloat16 else {}

@@ -70,10 +70,28 @@ class WeightSpec:
 
 @dataclass(frozen=True)
 class CacheSpec:
-    """Keys and values that grow by one entry per token.  Units with equal specs form one group of pages."""
-    num_kv_heads: int
-    head_dim: int
-    window: int = 0           # 0 = all keys; w > 0 = only the last w positions are ever read
+    """What a mixer keeps per token in the paged cache.  A page is one tensor of shape
+    `entry_shape[:token_axis] + (page_size,) + entry_shape[token_axis:]` in the engine's element type: the token's entry
+    with the page's positions inserted at `token_axis`.  Units with equal specs form one group of pages; the cache
+    manager hands out pages and block tables and never looks inside a page.
+      attention:   CacheSpec.keys_and_values(kv_heads, head_dim)   pages [2, kv_heads, page, head_dim]
+      a latent:    CacheSpec((width,), token_axis=0)                pages [page, width]"""
+    entry_shape: Tuple[int, ...]
+    token_axis: int = 0
+    window: int = 0           # 0 = all positions; w > 0 = only the last w positions are ever read (older pages go back)
+
+    @staticmethod
+    def keys_and_values(num_kv_heads: int, head_dim: int, window: int = 0) -> "CacheSpec":
+        return CacheSpec((2, int(num_kv_heads), int(head_dim)), token_axis=2, window=int(window))
+
+    def page_shape(self, page_size: int) -> Tuple[int, ...]:
+        return tuple(self.entry_shape[:self.token_axis]) + (page_size,) + tuple(self.entry_shape[self.token_axis:])
+
+    def elements_per_token(self) -> int:
+        n = 1
+        for d in self.entry_shape:
+            n *= int(d)
+        return n
 
 
 @dataclass(frozen=True)
@@ -113,6 +131,12 @@ class Workspace:
                 self._views.clear()
             self._views[(name, n_rows, width, dtype)] = view
         return view
+
+    def other_of_pair(self, name: str, current: torch.Tensor, n_rows: int, width, dtype: torch.dtype) -> torch.Tensor:
+        """Two buffers `name` and `name + "_alt"` take turns (a kernel that reads the residual stream in all of its blocks
+        while one block writes the new one needs the new one elsewhere): returns the one that `current` does not lie in."""
+        first = self.rows(name, n_rows, width, dtype)
+        return self.rows(name + "_alt", n_rows, width, dtype) if current.data_ptr() == first.data_ptr() else first
 
     def flat(self, name: str, numel: int, dtype: torch.dtype, zero: bool = False) -> torch.Tensor:
         """A named scratch buffer of a fixed number of elements (allocated once, at its first use; `zero`: zero-filled)."""

@@ -25,15 +25,20 @@ class PreNormBlock(Block):
     def forward(self, h, pending, ctx, cache, state):
         # A part may offer to take the norm in front of it (and the residual add in front of that) into its own
         # first kernel; it says so with can_fuse_norm(norm, ctx) and then runs forward_fused.
+        # forward_fused(h, pending, norm, ..., h_out): if `pending` is not None the part writes rnd(h + pending) to h_out
+        # (a buffer other than h, which the block chooses) and returns it as the residual stream beside its output.
+        ws = self.rt.workspace
+        T, D = ctx.num_tokens, h.shape[1]
         fuse = getattr(self.mixer, "can_fuse_norm", None)
         if fuse is not None and fuse(self.mixer_norm, ctx):
-            a, h = self.mixer.forward_fused(h, pending, self.mixer_norm, ctx, cache, state)
+            h_out = ws.other_of_pair("residual", h, T, D, h.dtype) if pending is not None else None
+            a, h = self.mixer.forward_fused(h, pending, self.mixer_norm, ctx, cache, state, h_out)
         else:
             x = self.mixer_norm.forward(h) if pending is None else self.mixer_norm.add_forward(h, pending)
             a = self.mixer.forward(x, ctx, cache, state)
         fuse = getattr(self.ffn, "can_fuse_norm", None)
         if fuse is not None and fuse(self.ffn_norm, ctx):
-            m, h = self.ffn.forward_fused(h, a, self.ffn_norm, ctx)
+            m, h = self.ffn.forward_fused(h, a, self.ffn_norm, ctx, ws.other_of_pair("residual", h, T, D, h.dtype))
         else:
             x = self.ffn_norm.add_forward(h, a)
             m = self.ffn.forward(x, ctx)

@@ -25,7 +25,8 @@ class GroupStepView:
 
 @dataclass
 class CacheUnitView:
-    """The keys and values of one cache unit: pages[page, 0 = K | 1 = V, kv_head, slot in page, :]."""
+    """One cache unit's pages: pages[page, *spec.page_shape(page_size)]; for attention's keys and values that is
+    pages[page, 0 = K | 1 = V, kv_head, slot in page, :]."""
     pages: torch.Tensor
     group: int
     spec: CacheSpec

@@ -55,15 +55,12 @@ class SwiGLUMLP(FeedForward):
                 and not ops.gemv_splitk_preferred(self.rt.dtype, self.w_gate_up, ctx.num_tokens)
                 and ops.gemv_supported(self.rt.dtype, self.w_down, ctx.num_tokens))
 
-    def forward_fused(self, h, pending, norm, ctx):
-        """Residual add, RMSNorm, gate/up product and SwiGLU in one kernel, then the down product.
-        Returns (output, residual stream)."""
+    def forward_fused(self, h, pending, norm, ctx, h_out):
+        """Residual add, RMSNorm, gate/up product and SwiGLU in one kernel, then the down product.  h_out: where
+        rnd(h + pending) goes (a buffer other than h).  Returns (output, residual stream)."""
         T = ctx.num_tokens
         ws = self.rt.workspace
-        h_new = h
-        if pending is not None:
-            h_new = ws.rows("residual_alt" if h.data_ptr() == ws.rows("residual", T, h.shape[1], h.dtype).data_ptr()
-                            else "residual", T, h.shape[1], h.dtype)
+        h_new = h_out if pending is not None else h
         product = ops.gemv_stream_bf16 if ops.gemv_stream_supported(h.dtype, self.w_gate_up, T, swiglu=True) else ops.gemv_bf16
         act = product(ws.rows("ffn_act", T, self.intermediate_size, h.dtype), h, self.w_gate_up, T,
                       norm_weight=norm.weight, eps=norm.eps, delta=pending,

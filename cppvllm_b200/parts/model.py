@@ -70,8 +70,8 @@ class CausalLM:
             if cs is None or e.writes_cache:
                 continue
             w = units.get(e.cache)
-            if w is None or (w.num_kv_heads, w.head_dim) != (cs.num_kv_heads, cs.head_dim):
-                raise ValueError(f"layer {e.layer} reads cache unit {e.cache}, whose keys have another shape")
+            if w is None or (w.entry_shape, w.token_axis) != (cs.entry_shape, cs.token_axis):
+                raise ValueError(f"layer {e.layer} reads cache unit {e.cache}, whose entries have another shape")
 
     # ---- weights -------------------------------------------------------------------------------------
     def all_parts(self):

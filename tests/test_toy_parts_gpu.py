@@ -194,3 +194,128 @@ def test_a_toy_position_encoding_can_be_registered_and_used(model_dirs, dtype, m
     finally:
         unregister_part("position", "scaled_rotary_toy")
         unregister_architecture("ToyScaledRopeForCausalLM")
+
+
+def test_a_toy_mixer_with_a_latent_cache_can_be_registered_built_and_stepped(tmp_path):
+    """A mixer that keeps ONE vector per token instead of keys and values: the token's latent z = x Wdown^T goes into
+    pages of shape [page, width] (CacheSpec((width,), token_axis=0)), and the output is softmax attention of a query
+    over the latents of the positions so far, projected back up.  Layer 0 has this mixer, layer 1 the framework's own
+    attention: two groups of pages with different entries side by side, each with its own block tables.  Steps that
+    cut the sequences anywhere, put two requests beside one another and reuse the pages of a finished request must give
+    what a plain whole-sequence computation gives."""
+    from cppvllm_b200.config.registry import register_architecture, unregister_architecture
+    from cppvllm_b200.engine.runner import ModelRunner, StepEntry
+    from cppvllm_b200.parts.base import CacheSpec, Mixer, WeightSpec, register_part, unregister_part
+    from cppvllm_b200.parts.spec import LayerSpec, ModelSpec, PartSpec
+    from cppvllm_b200.weights.random_init import write_random_model
+    from cppvllm_b200.weights.safetensors_io import SafetensorsFile
+
+    class LatentMixer(Mixer):
+        capturable = False                                   # reads the step's positions on the host
+
+        def __init__(self, runtime, prefix="", names=None, *, hidden_size, width):
+            super().__init__(runtime, prefix, names)
+            self.D, self.C = hidden_size, width
+
+        def cache_spec(self):
+            return CacheSpec((self.C,), token_axis=0)
+
+        def weight_specs(self):
+            return {self.full_name("down.weight"): WeightSpec((self.C, self.D)), self.full_name("query.weight"): WeightSpec((self.C, self.D)),
+                    self.full_name("up.weight"): WeightSpec((self.D, self.C))}
+
+        def bind(self, tensors):
+            self.down, self.query, self.up = (tensors[self.full_name(n + ".weight")].float() for n in ("down", "query", "up"))
+
+        def forward(self, x, ctx, cache, state):
+            g = ctx.groups[cache.group]
+            xf = x.float()
+            z, q = xf @ self.down.t(), xf @ self.query.t()
+            flat = cache.pages.view(-1, self.C)              # [pages * page_size, width]: slot = page * page_size + offset
+            flat[g.slot_mapping[:x.shape[0]].long()] = z.to(flat.dtype)
+            pos, seq = ctx.positions[:x.shape[0]].tolist(), ctx.seq_of_token[:x.shape[0]].tolist()
+            out = torch.empty_like(z)
+            for t in range(x.shape[0]):
+                idx = torch.arange(pos[t] + 1, device=x.device)
+                slots = g.block_tables[seq[t], idx // g.page_size].long() * g.page_size + idx % g.page_size
+                lat = flat[slots].float()
+                out[t] = torch.softmax(lat @ q[t] / self.C ** 0.5, 0) @ lat
+            return (out @ self.up.t()).to(x.dtype)
+
+    def build(cfg):
+        D, V, C = cfg["hidden_size"], cfg["vocab_size"], cfg["latent_width"]
+        norms = lambda i: dict(mixer_norm=PartSpec("rmsnorm", dict(size=D, eps=1e-6), prefix=f"toy.layers.{i}.norm1."),
+                               ffn_norm=PartSpec("rmsnorm", dict(size=D, eps=1e-6), prefix=f"toy.layers.{i}.norm2."),
+                               ffn=PartSpec("swiglu", dict(hidden_size=D, intermediate_size=cfg["inter"]), prefix=f"toy.layers.{i}.mlp."))
+        layers = [LayerSpec(mixer=PartSpec("latent_toy", dict(hidden_size=D, width=C), prefix="toy.layers.0.latent."), **norms(0)),
+                  LayerSpec(mixer=PartSpec("paged_attention", dict(hidden_size=D, num_heads=4, num_kv_heads=2, head_dim=16, qk_norm=True,
+                                                                   qk_norm_eps=1e-6, position="rope"), prefix="toy.layers.1.attn."), **norms(1))]
+        return ModelSpec("ToyLatentForCausalLM", D, V,
+                         embedding=PartSpec("token_embedding", dict(vocab_size=V, hidden_size=D), prefix="toy.embed."),
+                         layers=layers, final_norm=PartSpec("rmsnorm", dict(size=D, eps=1e-6, buffer="head_normed"), prefix="toy.norm."),
+                         lm_head=PartSpec("lm_head", dict(vocab_size=V, hidden_size=D), prefix="toy.head."),
+                         positions={"rope": PartSpec("rotary", dict(rotary_dim=16, theta=10000.0, max_positions=256, pairing="half"))},
+                         max_positions=256)
+
+    register_part("mixer", "latent_toy", LatentMixer)
+    register_architecture("ToyLatentForCausalLM", dict, build)
+    try:
+        cfg = dict(architectures=["ToyLatentForCausalLM"], hidden_size=48, vocab_size=90, latent_width=24, inter=64)
+        d = write_random_model(str(tmp_path / "toy"), cfg, seed=9, std=0.3, store_dtype=torch.float32)
+        assert "toy.layers.0.latent.down.weight" in SafetensorsFile(os.path.join(d, "model.safetensors")).names()
+
+        def runner(pages):
+            return ModelRunner(d, dtype=torch.float32, page_size=16, num_pages=pages, max_step_tokens=64, max_seqs=4, max_model_len=128)
+
+        r = runner(8)
+        shapes = sorted(tuple(s.shape[2:]) for s in r.storage)
+        assert shapes == [(2, 2, 16, 16), (16, 24)]          # attention's keys and values; the latents
+        toks = {"a": tiny_models.random_tokens(90, 50, 1), "b": tiny_models.random_tokens(90, 21, 2), "c": tiny_models.random_tokens(90, 40, 3)}
+
+        def whole(rid):
+            rr = runner(8)
+            rr.cache.admit(rid)
+            rr.cache.reserve(rid, len(toks[rid]))
+            return rr.step([StepEntry(rid, toks[rid], 0, list(range(len(toks[rid]))))]).cpu().clone()
+
+        ref = {k: whole(k) for k in toks}
+        # the latent layer alone against a plain loop on the CPU
+        mix = r.model.blocks[0].mixer
+        got, fed = {k: [] for k in toks}, {k: 0 for k in toks}
+        # 8 pages of 16 tokens: "a" (50) and "b" (21) take 6; "c" (40) fits only once "a" has ended and given back its pages
+        plan = ([("a", 9), ("b", 2)], [("a", 1), ("b", 13)], [("a", 30)], [("b", 6), ("a", 2)], [("a", 8)], "end a",
+                [("c", 17)], [("c", 2)], [("c", 21)])
+        for step in plan:
+            if step == "end a":
+                r.cache.release("a")
+                continue
+            entries = []
+            for rid, n in step:
+                if rid not in r.cache.leases:
+                    r.cache.admit(rid)
+                r.cache.reserve(rid, fed[rid] + n)
+                entries.append(StepEntry(rid, toks[rid][fed[rid]:fed[rid] + n], fed[rid], list(range(n))))
+            out = r.step(entries).cpu()
+            o = 0
+            for rid, n in step:
+                got[rid].append(out[o:o + n].clone())
+                o += n
+                fed[rid] += n
+        r.check_errors()
+        for k in toks:
+            g_ = torch.cat(got[k])
+            assert g_.shape == ref[k].shape
+            assert (g_ - ref[k]).abs().max() < 1e-4 * max(1.0, ref[k].abs().max())
+        # the mixer's arithmetic itself: whole sequence "b" through the plain formula
+        x = torch.randn(21, 48)
+        z, q = x @ mix.down.cpu().t(), x @ mix.query.cpu().t()
+        want = torch.stack([torch.softmax(z[:t + 1] @ q[t] / 24 ** 0.5, 0) @ z[:t + 1] for t in range(21)]) @ mix.up.cpu().t()
+        rr = runner(8)
+        import test_parts_gpu
+        ctx = test_parts_gpu.one_sequence_context(rr, list(range(21)), rid="y")
+        view = next(v for v in rr.cache_views.values() if v.spec.entry_shape == (24,))
+        y = rr.model.blocks[0].mixer.forward(x.to(rr.device), ctx, view, None).cpu()
+        assert (y - want).abs().max() < 1e-4 * max(1.0, float(want.abs().max()))
+    finally:
+        unregister_part("mixer", "latent_toy")
+        unregister_architecture("ToyLatentForCausalLM")
