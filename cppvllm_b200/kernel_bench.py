@@ -66,10 +66,16 @@ def attn_decode(a) -> dict:
     from .csrc import ops
     H, KV, hd, page = a.heads, a.kv_heads, a.head_dim, a.page_size
     kv_bytes = a.batch * a.context * 2 * KV * hd * 2
-    copies = max(1, min(8, int(300e6 // kv_bytes) + 1))
+    copies = 1 if a.warm else max(1, min(8, int(300e6 // kv_bytes) + 1))
     caches, tables, q, cu, pos = _paged_inputs(a.batch, a.context, 1, H, KV, hd, page, copies)
     out = torch.empty_like(q)
-    splits = a.splits or max(1, min(32, 296 // (a.batch * KV), (a.context + 63) // 64))
+    splits = a.splits
+    if not splits:                                       # the engine's choice (parts/attention.py: decode_splits)
+        splits = 1
+        while splits * 2 <= min(16, (a.context + 63) // 64) and a.batch * KV * splits * 2 <= 296:
+            splits *= 2
+        if splits == 16 and a.batch * KV * 16 > 128:
+            splits = 8
     n = ops.attn_decode_scratch_floats(a.batch, KV, hd, splits)
     scratch = torch.empty(max(1, n), dtype=torch.float32, device=q.device)
     scale = 1 / math.sqrt(hd)
@@ -232,7 +238,7 @@ def main(argv=None) -> int:
     p.add_argument("--rows", type=int, default=4096)
     p.add_argument("--cols", type=int, default=1024)
     p.add_argument("--iters", type=int, default=20)
-    p.add_argument("--warm", action="store_true", help="gemv: one weight buffer, so that it stays in L2")
+    p.add_argument("--warm", action="store_true", help="one weight buffer (gemv) or one cache (attn_decode), so that it stays in L2 where it fits")
     a = p.parse_args(argv)
     if a.kernel == "attn_prefill" and a.batch == 8 and "--batch" not in (argv or sys.argv):
         a.batch = 1

@@ -152,14 +152,23 @@ class PagedAttention(Mixer):
                 and ops.fast_attention_supported(self.rt.dtype, self.num_heads, self.num_kv_heads, self.head_dim, g.page_size)
                 and (pos is None or (pos.rotary_dim == self.head_dim and not pos.interleaved)))
 
-    # target number of blocks for the split-KV decode kernel: two per SM of a B200
+    # The split-KV decode kernel wants about two blocks per SM of a B200 and a power of two of splits: the splits of a
+    # (request, kv head) are one thread-block cluster, and clusters of 5, 6, 7, 9 or 12 blocks pack badly into a GPC's SMs
+    # (measured at 4,096 keys: batch 4 takes 24.5 us with 9 splits and 15.7 us with 8; batch 6 31.6 us with 6, 21.2 us with
+    # 4).  Clusters of 16 blocks fit one to a GPC, so they are taken only while all of them are resident at once.
     DECODE_TARGET_BLOCKS = 296
-    MAX_SPLITS = 16      # measured at one request and 4,096 keys: 16 chunks take 11.0 us, 32 take 12.6 us
+    MAX_SPLITS = 16
+    WIDE_CLUSTER_BLOCKS = 128
 
     def decode_splits(self, num_seqs: int, max_kv_len: int) -> int:
-        per_seq = self.DECODE_TARGET_BLOCKS // max(1, num_seqs * self.num_kv_heads)
+        pairs = max(1, num_seqs * self.num_kv_heads)
         tiles = (max_kv_len + 63) // 64
-        return max(1, min(self.MAX_SPLITS, per_seq, tiles))
+        splits = 1
+        while splits * 2 <= min(self.MAX_SPLITS, tiles) and pairs * splits * 2 <= self.DECODE_TARGET_BLOCKS:
+            splits *= 2
+        if splits == 16 and pairs * 16 > self.WIDE_CLUSTER_BLOCKS:
+            splits = 8
+        return splits
 
     def attend(self, att, q, ctx, cache, g):
         H, KV, hd = self.num_heads, self.num_kv_heads, self.head_dim
