@@ -729,6 +729,147 @@ static bool stream_plan(int N, int K, bool swiglu, StreamPlan* plan) {
     return true;
 }
 
+
+// ---- large weights: one block per SM, the block's rows streamed through a ring of bulk copies ------------------------
+// A weight of tens or hundreds of megabytes is a stream that must keep every SM's memory pipe full from the first
+// microsecond to the last.  Block b owns the rows [b N / G, (b + 1) N / G) of W (whole rows, so no partial sums cross
+// blocks, and the split is even to a row) and walks them in tiles of 16 rows times chunks of kRingK columns.  Two
+// producer warps bring a tile's chunk (one bulk copy per row piece, 2 KB) and the same chunk of the activations (from
+// the L2) into one of kRingStages stages; eight consumer warps each multiply an eighth of the chunk's columns (the same
+// fragments as above) and keep their partial sums in registers across the chunks of a tile; at the tile's end the eight
+// parts are added through shared memory.  The first stages' weights are asked for ahead of griddepcontrol.wait.
+constexpr int kRingK = 1024;                 // columns per chunk
+constexpr int kRingStages = 4;
+constexpr int kRingConsumers = 8;            // warps
+constexpr int kRingProducers = 2;            // warps
+constexpr int kRingThreads = (kRingConsumers + kRingProducers) * 32;
+constexpr int kRingRowBytes = kRingK * 2 + 64;                       // a row piece in shared memory, padded
+constexpr int kRingStageBytes = (16 + kBatch) * kRingRowBytes;       // 16 rows of W, then 8 rows of x
+constexpr size_t kRingSmem = 128 + static_cast<size_t>(kRingStages) * kRingStageBytes + kRingConsumers * 16 * kBatch * sizeof(float);
+
+struct RingParams {
+    __nv_bfloat16* out;            // [M, N]
+    const __nv_bfloat16* x;        // [M, K]
+    const __nv_bfloat16* W;        // [N, K]
+    int* err;
+    int M, N, K;
+};
+
+__global__ void __launch_bounds__(kRingThreads, 1)
+gemv_ring_kernel(const RingParams p) {
+    extern __shared__ __align__(16) unsigned char smem_raw[];
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem_raw);                 // [stages]: the copies of a stage have landed
+    uint64_t* empty = full + kRingStages;                                    // [stages]: the eight consumer warps are done with it
+    unsigned char* stages = smem_raw + 128;
+    float* red = reinterpret_cast<float*>(stages + static_cast<size_t>(kRingStages) * kRingStageBytes);   // [8][16][8]
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int K = p.K;
+    const int row0 = static_cast<int>(static_cast<long long>(blockIdx.x) * p.N / gridDim.x);
+    const int row1 = static_cast<int>(static_cast<long long>(blockIdx.x + 1) * p.N / gridDim.x);
+    const int n_tiles = (row1 - row0 + 15) >> 4;
+    const int n_chunks = (K + kRingK - 1) / kRingK;
+    const int total = n_tiles * n_chunks;                                    // stages' worth of work, tile-major
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < kRingStages; ++i) { mbar_init(full + i, kRingProducers); mbar_init(empty + i, kRingConsumers); }
+        mbar_fence_init();
+    }
+    __syncthreads();
+    if (warp >= kRingConsumers) {
+        // ---- producers: warp 0 of them brings the rows 0..7 of a tile and the activation rows 0..3, warp 1 the others ----
+        const int pw = warp - kRingConsumers;
+        const int w_row = pw * 8 + lane;                                     // lanes 0..7: a row of W; lanes 8..11: a row of x
+        const int x_row = pw * 4 + (lane - 8);
+        auto bytes_of = [&](int it) {                                        // what this warp brings for item `it`
+            const int tile = it / n_chunks, chunk = it - tile * n_chunks;
+            const uint32_t piece = static_cast<uint32_t>(min(kRingK, K - chunk * kRingK)) * 2u;
+            const int rows_here = max(0, min(8, row1 - row0 - tile * 16 - pw * 8));
+            const int x_here = max(0, min(4, p.M - pw * 4));
+            return piece * static_cast<uint32_t>(rows_here + x_here);
+        };
+        auto issue = [&](int it, bool weights, bool acts) {
+            const int tile = it / n_chunks, chunk = it - tile * n_chunks;
+            const int st = it % kRingStages;
+            const uint32_t piece = static_cast<uint32_t>(min(kRingK, K - chunk * kRingK)) * 2u;
+            unsigned char* base = stages + static_cast<size_t>(st) * kRingStageBytes;
+            if (weights && lane < 8) {
+                const int row = row0 + tile * 16 + w_row;
+                if (row < row1)
+                    bulk_row_to_smem(base + w_row * kRingRowBytes, p.W + static_cast<int64_t>(row) * K + chunk * kRingK, piece, full + st);
+            }
+            if (acts && lane >= 8 && lane < 12 && x_row < p.M)
+                bulk_row_to_smem(base + (16 + x_row) * kRingRowBytes, p.x + static_cast<int64_t>(x_row) * K + chunk * kRingK, piece, full + st);
+        };
+        const int ahead = min(kRingStages, total);
+        for (int it = 0; it < ahead; ++it) {                                 // weights depend on no kernel: before the wait
+            if (lane == 0) mbar_expect_tx(full + it, bytes_of(it));
+            __syncwarp();
+            issue(it, true, false);
+        }
+        pdl_wait();
+        for (int it = 0; it < ahead; ++it) issue(it, false, true);           // the activations: behind it
+        for (int it = ahead; it < total; ++it) {
+            const int st = it % kRingStages;
+            if (lane == 0) {
+                mbar_wait(empty + st, ((it / kRingStages) - 1) & 1, p.err);
+                mbar_expect_tx(full + st, bytes_of(it));
+            }
+            __syncwarp();
+            issue(it, true, true);
+        }
+        pdl_trigger();
+        return;
+    }
+    // ---- consumers ----
+    pdl_wait();
+    const int r = lane >> 2, q = lane & 3;
+    const uint4 zero = make_uint4(0, 0, 0, 0);
+    int it = 0;
+    for (int tile = 0; tile < n_tiles; ++tile) {
+        float acc[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+        const int rows_here = min(16, row1 - row0 - tile * 16);
+        for (int chunk = 0; chunk < n_chunks; ++chunk, ++it) {
+            const int st = it % kRingStages;
+            mbar_wait(full + st, (it / kRingStages) & 1, p.err);
+            const unsigned char* base = stages + static_cast<size_t>(st) * kRingStageBytes;
+            // rows past the block's last row were not copied: their lanes read the tile's last row, and are not stored
+            const uint4* w_hi = reinterpret_cast<const uint4*>(base + min(r, rows_here - 1) * kRingRowBytes);
+            const uint4* w_lo = reinterpret_cast<const uint4*>(base + min(r + 8, rows_here - 1) * kRingRowBytes);
+            const uint4* xs = reinterpret_cast<const uint4*>(base + (16 + min(r, p.M - 1)) * kRingRowBytes);
+            const int n16 = min(kRingK, K - chunk * kRingK) >> 3;            // 16-byte pieces in this chunk's rows
+#pragma unroll
+            for (int j = 0; j < kRingK / 32 / kRingConsumers; j += 2) {      // this warp's slabs of 32 columns, two at a time
+                const int c0 = (warp * (kRingK / 32 / kRingConsumers) + j) * 4 + q, c1 = c0 + 4;
+                const bool ok0 = c0 < n16, ok1 = c1 < n16;
+                const uint4 wh0 = ok0 ? w_hi[c0] : zero, wl0 = ok0 ? w_lo[c0] : zero, xv0 = ok0 ? xs[c0] : zero;
+                const uint4 wh1 = ok1 ? w_hi[c1] : zero, wl1 = ok1 ? w_lo[c1] : zero, xv1 = ok1 ? xs[c1] : zero;
+                mma_16816(acc[0], wh0.x, wl0.x, wh0.y, wl0.y, xv0.x, xv0.y);
+                mma_16816(acc[1], wh0.z, wl0.z, wh0.w, wl0.w, xv0.z, xv0.w);
+                mma_16816(acc[0], wh1.x, wl1.x, wh1.y, wl1.y, xv1.x, xv1.y);
+                mma_16816(acc[1], wh1.z, wl1.z, wh1.w, wl1.w, xv1.z, xv1.w);
+            }
+            __syncwarp();
+            if (lane == 0) mbar_arrive(empty + st);
+        }
+        // the tile is complete: add the eight warps' parts (acc[.][0], [1]: row r, batch 2q, 2q + 1; [2], [3]: row r + 8)
+        float* mine = red + warp * 128;
+        mine[r * 8 + 2 * q] = acc[0][0] + acc[1][0];
+        mine[r * 8 + 2 * q + 1] = acc[0][1] + acc[1][1];
+        mine[(r + 8) * 8 + 2 * q] = acc[0][2] + acc[1][2];
+        mine[(r + 8) * 8 + 2 * q + 1] = acc[0][3] + acc[1][3];
+        asm volatile("bar.sync 1, %0;\n" ::"n"(kRingConsumers * 32) : "memory");
+        if (threadIdx.x < 128) {
+            const int m = threadIdx.x >> 4, row = threadIdx.x & 15;          // consecutive threads, consecutive outputs
+            if (m < p.M && row < rows_here) {
+                float sum = 0.f;
+#pragma unroll
+                for (int w = 0; w < kRingConsumers; ++w) sum += red[w * 128 + row * 8 + m];
+                p.out[static_cast<int64_t>(m) * p.N + row0 + tile * 16 + row] = __float2bfloat16_rn(sum);
+            }
+        }
+        asm volatile("bar.sync 1, %0;\n" ::"n"(kRingConsumers * 32) : "memory");      // `red` is free again
+    }
+}
+
 }  // namespace cvb
 
 using namespace cvb;
@@ -825,5 +966,35 @@ extern "C" int cvb_gemv_splitk_bf16(void* out, const void* x, const void* W, int
     if (p.splits > 65535) return CVB_E_SIZE;
     dim3 grid(static_cast<unsigned>(cvb_gemv_splitk_counters(N)), static_cast<unsigned>(p.splits));
     launch_kernel(gemv_splitk_kernel, grid, dim3(kSkThreads), 0, stream, p);
+    return launch_status();
+}
+
+// out[:M] = x[:M] W^T for up to 8 rows and a weight of any size, streamed through a ring of shared-memory stages by one
+// block per SM (see gemv_ring_kernel).  `dependent`: launch with the programmatic-dependent-launch attribute.
+extern "C" int cvb_gemv_ring_bf16(void* out, const void* x, const void* W, int M, int N, int K, int dependent, int* err,
+                                  cudaStream_t stream) {
+    if (M == 0) return CVB_OK;
+    if (M < 0 || M > kBatch || N <= 0 || K <= 0) return CVB_E_SIZE;
+    if (K % 8) return CVB_E_ALIGN;
+    auto al = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
+    if (!al(out) || !al(x) || !al(W)) return CVB_E_ALIGN;
+    if (err == nullptr) return CVB_E_SHAPE;
+    static int sms = 0;
+    static bool set = false;
+    if (!set) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (cudaFuncSetAttribute(gemv_ring_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kRingSmem)) != cudaSuccess) {
+            cudaGetLastError();
+            return CVB_E_SIZE;
+        }
+        set = true;
+    }
+    RingParams p{};
+    p.out = (__nv_bfloat16*)out; p.x = (const __nv_bfloat16*)x; p.W = (const __nv_bfloat16*)W; p.err = err;
+    p.M = M; p.N = N; p.K = K;
+    const int blocks = min(sms > 0 ? sms : 148, N);
+    launch_kernel_dependent(gemv_ring_kernel, dim3(blocks), dim3(kRingThreads), kRingSmem, stream, dependent != 0, p);
     return launch_status();
 }

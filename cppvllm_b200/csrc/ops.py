@@ -466,7 +466,7 @@ def _gemv_lib():
     if _gemv is None:
         lib = load_library("gemv_bf16")
         for name in ("cvb_gemv_bf16", "cvb_gemv_splitk_bf16", "cvb_gemv_splitk_counters", "cvb_gemv_stream_bf16",
-                     "cvb_gemv_stream_supported"):
+                     "cvb_gemv_stream_supported", "cvb_gemv_ring_bf16"):
             getattr(lib, name).restype = c_int
         lib.cvb_gemv_splitk_scratch_floats.restype = c_int64
         _gemv = lib
@@ -559,6 +559,32 @@ def gemv_splitk_bf16(out: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, r
     return out
 
 
+RING_MAX_ROWS = 8
+
+
+def gemv_ring_supported(x_dtype: torch.dtype, weight: torch.Tensor, rows: int) -> bool:
+    """The ring-buffered streaming product covers bf16 operands, up to 8 rows, any weight whose rows are multiples of 16
+    bytes; it is meant for weights too large for the decode chain's product."""
+    return (x_dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and weight.dim() == 2 and 0 < rows <= RING_MAX_ROWS
+            and weight.shape[1] % 8 == 0)
+
+
+def gemv_ring_bf16(out: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, rows: int, dependent: bool = False) -> torch.Tensor:
+    """out[:rows] = x[:rows] @ weight^T for up to 8 rows: one block per SM streams its share of the weight's rows through a
+    ring of shared-memory stages filled by bulk copies."""
+    lib = _gemv_lib()
+    _cuda(out, x, weight)
+    _contig(out, x, weight)
+    N, K = weight.shape
+    if x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or x.shape[1] != K:
+        raise KernelError("gemv_ring_bf16: x [M, K], weight [N, K] and out must be bf16")
+    if out.shape[1] != N or out.shape[0] < rows or x.shape[0] < rows:
+        raise KernelError("gemv_ring_bf16: out must be [M, N]")
+    _check(lib.cvb_gemv_ring_bf16(_ptr(out), _ptr(x), _ptr(weight), c_int(rows), c_int(N), c_int(K), c_int(1 if dependent else 0),
+                                  _ptr(error_flag(x.device)), _stream()), "gemv_ring_bf16")
+    return out
+
+
 _project_choice: Dict[tuple, str] = {}
 _flush_buffers: Dict[int, torch.Tensor] = {}
 
@@ -570,15 +596,19 @@ def _project_candidates(x: torch.Tensor, weight: torch.Tensor, rows: int):
     if (x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and 0 < rows <= SPLITK_MAX_ROWS and weight.dim() == 2
             and weight.shape[1] % 8 == 0 and weight.numel() * 2 >= (1 << 20)):
         names.append("splitk")
+    if gemv_ring_supported(x.dtype, weight, rows) and weight.numel() * 2 >= (1 << 20):
+        names.append("ring")
     names.append("library")
     return names
 
 
-def _project_with(name: str, x, weight, out, rows):
+def _project_with(name: str, x, weight, out, rows, dependent: bool = False):
     if name == "gemv":
         return gemv_bf16(out, x, weight, rows)
     if name == "splitk":
         return gemv_splitk_bf16(out, x, weight, rows)
+    if name == "ring":
+        return gemv_ring_bf16(out, x, weight, rows, dependent=dependent)
     return linear(x, weight, out=out)
 
 
@@ -606,10 +636,10 @@ def project_rows(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, rows:
     """out = x @ weight^T by the kernel that suits the step.  A weight whose share per SM fits into shared memory goes
     through the product made for chains of dependent launches (`dependent=False` keeps that kernel behind its
     predecessor's end instead of letting it start early and fetch its weights meanwhile).  Otherwise the candidates for a
-    few bf16 rows (the weight-streaming product, its split-K form, the library's product) are timed once per shape, with
+    few bf16 rows (the weight-streaming product, its split-K form, the ring-buffered product, the library's product) are timed once per shape, with
     the weight out of the L2, the first time the shape is seen outside a graph capture, and the fastest is kept; during
     a capture an unseen shape takes the split-K form for large weights, the weight-streaming product for small ones.
-    CVB_PROJECT=gemv|splitk|library in the environment fixes the choice."""
+    CVB_PROJECT=gemv|splitk|ring|library in the environment fixes the choice."""
     if gemv_stream_supported(x.dtype, weight, rows):
         return gemv_stream_bf16(out, x, weight, rows, dependent=dependent)
     if rows > GEMV_MAX_ROWS or x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16:
@@ -630,7 +660,7 @@ def project_rows(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, rows:
             timed = {n: _measure_projection(n, x, weight, out, rows) for n in names}
             choice = min(timed, key=timed.get)
         _project_choice[key] = choice
-    return _project_with(choice, x, weight, out, rows)
+    return _project_with(choice, x, weight, out, rows, dependent)
 
 
 _gemm = None

@@ -144,6 +144,8 @@ def gemv_fused(a) -> dict:
     def run(i):
         if a.form == "splitk":
             ops.gemv_splitk_bf16(out, x, ws[i % copies], a.batch)
+        elif a.form == "ring":
+            ops.gemv_ring_bf16(out, x, ws[i % copies], a.batch)
         elif a.form.startswith("stream"):
             kind = a.form[len("stream"):].lstrip("_")
             if kind == "":
@@ -225,7 +227,7 @@ def main(argv=None) -> int:
     p.add_argument("kernel", choices=["attn_decode", "attn_prefill", "gemv", "gemv_fused", "gemm", "elementwise"])
     p.add_argument("--tile-n", type=int, default=0)
     p.add_argument("--impl", default="tcgen05", choices=["tcgen05", "mma"])
-    p.add_argument("--form", default="plain", choices=["plain", "norm", "swiglu", "splitk", "stream", "stream_norm", "stream_swiglu"])
+    p.add_argument("--form", default="plain", choices=["plain", "norm", "swiglu", "splitk", "ring", "stream", "stream_norm", "stream_swiglu"])
     p.add_argument("--batch", type=int, default=8)
     p.add_argument("--context", type=int, default=4096)
     p.add_argument("--tokens", type=int, default=2048)

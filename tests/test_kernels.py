@@ -618,6 +618,23 @@ def test_tcgen05_gemm_with_swiglu_epilogue(ops, M, I, K):
     torch.testing.assert_close(out.float(), rnd(rnd(gate / (1 + torch.exp(-gate)), dt) * up, dt), atol=3e-2, rtol=3e-2)
 
 
+@pytest.mark.parametrize("M,N,K", [(1, 200, 1000), (5, 128, 512), (8, 1031, 2056), (3, 4096, 4096), (8, 6144, 4096), (2, 300, 12288),
+                                   (7, 16, 8), (4, 149, 1024), (8, 2368, 1032)])
+def test_ring_buffered_streaming_product(ops, M, N, K):
+    """The product for large weights (one block per SM, its rows through a ring of bulk copies): row counts that do not
+    divide among the SMs, inner sizes that are no multiple of a chunk, fewer rows than SMs; twice in a row; against float32."""
+    g = torch.Generator().manual_seed(M * 1000 + N + K)
+    W = (torch.randn(N, K, generator=g) * 0.05).to(torch.bfloat16).to(dev())
+    assert ops.gemv_ring_supported(torch.bfloat16, W, M) and not ops.gemv_ring_supported(torch.bfloat16, W, 9)
+    for rep in range(2):
+        x = torch.randn(M, K, generator=g).to(torch.bfloat16).to(dev())
+        out = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device=dev())
+        ops.gemv_ring_bf16(out, x, W, M, dependent=bool(rep))
+        ref = x.float() @ W.float().t()
+        torch.testing.assert_close(out.float(), rnd(ref, torch.bfloat16), atol=2e-2, rtol=2e-2)
+    ops.check_device_errors(dev())
+
+
 # ---- a bounded wait that runs out ------------------------------------------------------------------------------------
 
 def test_a_wait_that_runs_out_is_reported_and_the_kernel_ends(ops):
