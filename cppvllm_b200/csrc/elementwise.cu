@@ -10,6 +10,20 @@
 
 namespace cvb {
 
+// One row from `src` to `dst` by the block's threads: 16 bytes at a time where the row's length and both addresses
+// allow it (a thread then has several copies in flight), element by element otherwise.
+template <typename T>
+__device__ __forceinline__ void copy_row(T* __restrict__ dst, const T* __restrict__ src, int D) {
+    constexpr int N = 16 / sizeof(T);
+    if (D % N == 0 && ((reinterpret_cast<uintptr_t>(dst) | reinterpret_cast<uintptr_t>(src)) & 15) == 0) {
+        const uint4* s4 = reinterpret_cast<const uint4*>(src);
+        uint4* d4 = reinterpret_cast<uint4*>(dst);
+        for (int i = threadIdx.x; i < D / N; i += blockDim.x) d4[i] = s4[i];
+    } else {
+        for (int i = threadIdx.x; i < D; i += blockDim.x) dst[i] = src[i];
+    }
+}
+
 template <typename T>
 __global__ void embed_kernel(T* __restrict__ out, const T* __restrict__ table, const int* __restrict__ tokens,
                              int D, int V, int* __restrict__ err) {
@@ -21,9 +35,7 @@ __global__ void embed_kernel(T* __restrict__ out, const T* __restrict__ table, c
         if (threadIdx.x == 0) atomicExch(err, 1);
         tok = tok < 0 ? 0 : V - 1;
     }
-    const T* src = table + static_cast<int64_t>(tok) * D;
-    T* dst = out + t * D;
-    for (int i = threadIdx.x; i < D; i += blockDim.x) dst[i] = src[i];
+    copy_row(out + t * D, table + static_cast<int64_t>(tok) * D, D);
 }
 
 // Rows of any length and alignment (the forms further down need 16-byte rows): a warp owns a row and its lanes walk
@@ -72,7 +84,7 @@ __global__ void gather_rows_kernel(T* __restrict__ out, const T* __restrict__ in
     int src = rows[r];
     if (src < 0) src = 0;
     if (src >= n_in) src = n_in - 1;
-    for (int i = threadIdx.x; i < D; i += blockDim.x) out[r * D + i] = in[static_cast<int64_t>(src) * D + i];
+    copy_row(out + r * D, in + static_cast<int64_t>(src) * D, D);
 }
 
 
@@ -220,6 +232,9 @@ template <typename T, bool ADD>
 __host__ bool launch_warp_norm(T* out, T* resid, const T* x, const float* w, int T_rows, int D, float eps, cudaStream_t stream) {
     const int per_lane = (D / Vec16<T>::N + 31) / 32;
     if (per_lane > kWarpNormChunks || (reinterpret_cast<uintptr_t>(w) & 15) != 0) return false;
+    // A few long rows (a decode step of a wide model) are a chain of latencies for one warp per row (23 us for one row of
+    // 4,096 elements): the form with a block per row spreads a row over 128 threads.
+    if (per_lane > 4 && T_rows < 256 && D <= kNormThreads * kNormMaxChunks * Vec16<T>::N) return false;
     const dim3 grid((T_rows + kWarpNormWarps - 1) / kWarpNormWarps), block(kWarpNormWarps * 32);
     if (per_lane <= 1) launch_kernel(rmsnorm_warp_kernel<T, ADD, 1>, grid, block, 0, stream, out, resid, x, w, T_rows, D, eps);
     else if (per_lane <= 2) launch_kernel(rmsnorm_warp_kernel<T, ADD, 2>, grid, block, 0, stream, out, resid, x, w, T_rows, D, eps);
