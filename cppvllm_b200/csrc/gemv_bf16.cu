@@ -733,7 +733,7 @@ static bool stream_plan(int N, int K, bool swiglu, StreamPlan* plan) {
 // ---- large weights: one block per SM, the block's rows streamed through a ring of bulk copies ------------------------
 // A weight of tens or hundreds of megabytes is a stream that must keep every SM's memory pipe full from the first
 // microsecond to the last.  Block b owns the rows [b N / G, (b + 1) N / G) of W (whole rows, so no partial sums cross
-// blocks, and the split is even to a row) and walks them in tiles of 16 rows times chunks of kRingK columns.  Two
+// blocks, and the split is even to a row) and walks them in tiles of 16 rows times chunks of kRingK columns.  Four
 // producer warps bring a tile's chunk (one bulk copy per row piece, 2 KB) and the same chunk of the activations (from
 // the L2) into one of kRingStages stages; eight consumer warps each multiply an eighth of the chunk's columns (the same
 // fragments as above) and keep their partial sums in registers across the chunks of a tile; at the tile's end the eight
@@ -741,7 +741,7 @@ static bool stream_plan(int N, int K, bool swiglu, StreamPlan* plan) {
 constexpr int kRingK = 1024;                 // columns per chunk
 constexpr int kRingStages = 4;
 constexpr int kRingConsumers = 8;            // warps
-constexpr int kRingProducers = 2;            // warps
+constexpr int kRingProducers = 4;            // warps (a warp issues its lanes' copies one after the other)
 constexpr int kRingThreads = (kRingConsumers + kRingProducers) * 32;
 constexpr int kRingRowBytes = kRingK * 2 + 64;                       // a row piece in shared memory, padded
 constexpr int kRingStageBytes = (16 + kBatch) * kRingRowBytes;       // 16 rows of W, then 8 rows of x
@@ -775,15 +775,16 @@ gemv_ring_kernel(const RingParams p) {
     }
     __syncthreads();
     if (warp >= kRingConsumers) {
-        // ---- producers: warp 0 of them brings the rows 0..7 of a tile and the activation rows 0..3, warp 1 the others ----
+        // ---- producers: each of the four warps brings four rows of a tile (lanes 0..3) and two activation rows (lanes 4, 5) ----
+        constexpr int kWRows = 16 / kRingProducers, kXRows = kBatch / kRingProducers;
         const int pw = warp - kRingConsumers;
-        const int w_row = pw * 8 + lane;                                     // lanes 0..7: a row of W; lanes 8..11: a row of x
-        const int x_row = pw * 4 + (lane - 8);
+        const int w_row = pw * kWRows + lane;
+        const int x_row = pw * kXRows + (lane - kWRows);
         auto bytes_of = [&](int it) {                                        // what this warp brings for item `it`
             const int tile = it / n_chunks, chunk = it - tile * n_chunks;
             const uint32_t piece = static_cast<uint32_t>(min(kRingK, K - chunk * kRingK)) * 2u;
-            const int rows_here = max(0, min(8, row1 - row0 - tile * 16 - pw * 8));
-            const int x_here = max(0, min(4, p.M - pw * 4));
+            const int rows_here = max(0, min(kWRows, row1 - row0 - tile * 16 - pw * kWRows));
+            const int x_here = max(0, min(kXRows, p.M - pw * kXRows));
             return piece * static_cast<uint32_t>(rows_here + x_here);
         };
         auto issue = [&](int it, bool weights, bool acts) {
@@ -791,12 +792,12 @@ gemv_ring_kernel(const RingParams p) {
             const int st = it % kRingStages;
             const uint32_t piece = static_cast<uint32_t>(min(kRingK, K - chunk * kRingK)) * 2u;
             unsigned char* base = stages + static_cast<size_t>(st) * kRingStageBytes;
-            if (weights && lane < 8) {
+            if (weights && lane < kWRows) {
                 const int row = row0 + tile * 16 + w_row;
                 if (row < row1)
                     bulk_row_to_smem(base + w_row * kRingRowBytes, p.W + static_cast<int64_t>(row) * K + chunk * kRingK, piece, full + st);
             }
-            if (acts && lane >= 8 && lane < 12 && x_row < p.M)
+            if (acts && lane >= kWRows && lane < kWRows + kXRows && x_row < p.M)
                 bulk_row_to_smem(base + (16 + x_row) * kRingRowBytes, p.x + static_cast<int64_t>(x_row) * K + chunk * kRingK, piece, full + st);
         };
         const int ahead = min(kRingStages, total);

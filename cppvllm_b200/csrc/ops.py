@@ -8,6 +8,7 @@ from __future__ import annotations
 
 import ctypes
 import os
+import sys
 from ctypes import c_int, c_int64, c_float, c_void_p
 from typing import Dict, Optional
 
@@ -613,19 +614,27 @@ def _project_with(name: str, x, weight, out, rows, dependent: bool = False):
 
 
 def _measure_projection(name: str, x, weight, out, rows) -> float:
-    """Microseconds of one call with the weight out of the L2 (a buffer larger than the L2 is written in between)."""
+    """Microseconds of four calls, each with the weight out of the L2 (a buffer larger than the L2 is written before every
+    call), replayed from a captured graph so that the host's launch cost does not blur the comparison.  The writes of
+    the buffer take the same time for every candidate."""
     idx = x.device.index if x.device.index is not None else torch.cuda.current_device()
     flush = _flush_buffers.get(idx)
     if flush is None:
         flush = torch.empty(256 << 20, dtype=torch.int8, device=x.device)
         _flush_buffers[idx] = flush
     _project_with(name, x, weight, out, rows)                 # sizes its scratch, loads its code
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for _ in range(4):
+            flush.zero_()
+            _project_with(name, x, weight, out, rows)
+    graph.replay()
     best = float("inf")
     for _ in range(3):
-        flush.zero_()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
-        _project_with(name, x, weight, out, rows)
+        graph.replay()
         e1.record()
         torch.cuda.synchronize()
         best = min(best, e0.elapsed_time(e1) * 1e3)
@@ -659,6 +668,9 @@ def project_rows(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, rows:
         else:
             timed = {n: _measure_projection(n, x, weight, out, rows) for n in names}
             choice = min(timed, key=timed.get)
+            if os.environ.get("CVB_PROJECT_VERBOSE"):
+                print(f"[cppvllm_b200] projection {key}: " + ", ".join(f"{n} {t:.1f} us" for n, t in timed.items()) + f" -> {choice}",
+                      file=sys.stderr, flush=True)
         _project_choice[key] = choice
     return _project_with(choice, x, weight, out, rows, dependent)
 
