@@ -444,6 +444,7 @@ struct StreamParams {
     __nv_bfloat16* resid_out;      // NORM with delta: receives rnd(x + delta)
     const float* norm_w;           // NORM: [K]
     const __nv_bfloat16* W;        // [N, K]
+    const __nv_bfloat16* add_to;   // plain form: out = rnd(add_to + rnd(x W^T)) (the residual stream; may be `out` itself), or nullptr
     const unsigned char* prefetch; // bytes that a later kernel will stream: asked into the L2 by this one (or nullptr)
     long long prefetch_bytes;
     int* err;
@@ -549,6 +550,10 @@ gemv_stream_kernel(const StreamParams p) {
     int e_m = threadIdx.x / n_mine, e_o = threadIdx.x - e_m * n_mine;
     const float inv_k = 1.f / static_cast<float>(K);
     pdl_wait();
+    // the residual element that this thread's first output is added to: asked for now, used at the very end
+    float res_first = 0.f;
+    if (p.add_to != nullptr && threadIdx.x < p.M * n_mine)
+        res_first = __bfloat162float(__ldcg(p.add_to + static_cast<int64_t>(e_m) * n_out + o0 + e_o));
 
     // ---- activations into shared memory (read past the L1: another kernel wrote them while this block was resident) ----
     if constexpr (NORM) {
@@ -566,24 +571,22 @@ gemv_stream_kernel(const StreamParams p) {
 #pragma unroll
                 for (int u = 0; u < kStage; ++u) {
                     const int c = c0 + u * 32;
-                    float v[8];
-                    unpack8(xv[u], v);
+                    // rnd(x + delta) two at a time: the packed addition rounds the exact sum once, as the float one does
+                    uint4 packed = xv[u];
                     if (dg != nullptr) {
-                        float d[8];
-                        unpack8(dv[u], d);
+                        __nv_bfloat162* a2 = reinterpret_cast<__nv_bfloat162*>(&packed);
+                        const __nv_bfloat162* d2 = reinterpret_cast<const __nv_bfloat162*>(&dv[u]);
 #pragma unroll
-                        for (int i = 0; i < 8; ++i) v[i] = rnd<__nv_bfloat16>(v[i] + d[i]);
+                        for (int i = 0; i < 4; ++i) a2[i] = __hadd2(a2[i], d2[i]);
                     }
-                    uint4 packed;
-                    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&packed);
-#pragma unroll
-                    for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
                     if (c0 == c_begin + lane) keep[u] = packed;
                     else if (c < c_end) xs_row[c] = packed;              // later passes wait in shared memory
                     if (dg != nullptr && blockIdx.x == 0 && c < c_end)
                         *reinterpret_cast<uint4*>(p.resid_out + static_cast<int64_t>(my_row) * K + c * 8) = packed;
+                    float v[8];
+                    unpack8(packed, v);
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) ss += v[i] * v[i];       // chunks past the end are zero
+                    for (int i = 0; i < 8; ++i) ss = fmaf(v[i], v[i], ss);   // chunks past the end are zero
                 }
             }
             ss = warp_sum(ss);
@@ -591,12 +594,8 @@ gemv_stream_kernel(const StreamParams p) {
         }
         __syncthreads();
         if (has_row) {
-            float part[kStWarps];
-#pragma unroll
-            for (int i = 0; i < kStWarps; ++i) part[i] = i < wpr ? row_ss[my_row * kStWarps + i] : 0.f;
-            float total = 0.f;
-#pragma unroll
-            for (int i = 0; i < kStWarps; ++i) total += part[i];         // in part order, whichever warp adds
+            // the row's parts, one per lane, added by the same tree in every warp and block
+            float total = warp_sum(lane < wpr ? row_ss[my_row * kStWarps + lane] : 0.f);
             const float inv = rsqrtf(total * inv_k + p.eps);
             for (int c0 = c_begin + lane; c0 < c_end; c0 += 32 * kStage) {
                 const bool first = c0 == c_begin + lane;
@@ -698,6 +697,11 @@ gemv_stream_kernel(const StreamParams p) {
         if constexpr (SWIGLU) {
             const float g = rnd<__nv_bfloat16>(s0), u = rnd<__nv_bfloat16>(s1);
             y = rnd<__nv_bfloat16>(g / (1.f + expf(-g))) * u;
+        }
+        if (p.add_to != nullptr) {                                   // the residual sum, rounded where the separate kernels round
+            const float res = i == static_cast<int>(threadIdx.x) ? res_first
+                                                                 : __bfloat162float(__ldcg(p.add_to + static_cast<int64_t>(e_m) * n_out + o0 + e_o));
+            y = res + rnd<__nv_bfloat16>(y);
         }
         p.out[static_cast<int64_t>(e_m) * n_out + o0 + e_o] = __float2bfloat16_rn(y);
     }
@@ -882,11 +886,12 @@ extern "C" int cvb_gemv_stream_supported(int N, int K, int mode) {
 }
 
 // out[:M] = x[:M] W^T for up to 8 rows and a weight whose per-SM share fits into shared memory; modes as cvb_gemv_bf16.
+// `add_to` (plain mode; or null): out = rnd(add_to + rnd(x W^T)), the residual sum folded into the store (add_to may be out).
 // `prefetch` (or null) names bytes that a later kernel will stream; this one asks them into the L2.  With `late_trigger`
 // the kernel behind this one starts when this one's products are done rather than as early as possible.  The launch
 // always carries the programmatic-dependent-launch attribute unless `pdl` is 0.
 extern "C" int cvb_gemv_stream_bf16(void* out, const void* x, const void* delta, void* resid_out, const float* norm_w,
-                                    const void* W, int M, int N, int K, float eps, int mode, const void* prefetch,
+                                    const void* W, int M, int N, int K, float eps, int mode, const void* add_to, const void* prefetch,
                                     long long prefetch_bytes, int late_trigger, int pdl, int* err, cudaStream_t stream) {
     if (M == 0) return CVB_OK;
     if (M < 0 || M > kBatch || N <= 0 || K <= 0) return CVB_E_SIZE;
@@ -896,11 +901,13 @@ extern "C" int cvb_gemv_stream_bf16(void* out, const void* x, const void* delta,
     if (mode != 0 && norm_w == nullptr) return CVB_E_SHAPE;
     if (mode < 0 || mode > 2 || err == nullptr) return CVB_E_SHAPE;
     if (delta != nullptr && (resid_out == nullptr || resid_out == x)) return CVB_E_SHAPE;
+    if (add_to != nullptr && (mode != 0 || (reinterpret_cast<uintptr_t>(add_to) & 1))) return CVB_E_SHAPE;
     StreamPlan plan;
     if (!stream_plan(N, K, mode == 2, &plan)) return CVB_E_UNSUPPORTED;
     StreamParams p{};
     p.out = (__nv_bfloat16*)out; p.x = (const __nv_bfloat16*)x; p.delta = (const __nv_bfloat16*)delta;
     p.resid_out = (__nv_bfloat16*)resid_out; p.norm_w = norm_w; p.W = (const __nv_bfloat16*)W;
+    p.add_to = (const __nv_bfloat16*)add_to;
     p.prefetch = (const unsigned char*)prefetch; p.prefetch_bytes = prefetch != nullptr ? prefetch_bytes : 0; p.err = err;
     p.M = M; p.N = N; p.K = K; p.opb = plan.opb; p.n_tiles = plan.n_tiles; p.warps_k = plan.warps_k;
     p.late_trigger = late_trigger ? 1 : 0; p.eps = eps;

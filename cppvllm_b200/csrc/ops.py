@@ -495,14 +495,17 @@ def gemv_stream_supported(x_dtype: torch.dtype, weight: torch.Tensor, rows: int,
 def gemv_stream_bf16(out: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, rows: int, norm_weight: Optional[torch.Tensor] = None,
                      eps: float = 0.0, delta: Optional[torch.Tensor] = None, resid_out: Optional[torch.Tensor] = None,
                      swiglu: bool = False, prefetch: Optional[torch.Tensor] = None, late_trigger: bool = False,
-                     dependent: bool = True) -> torch.Tensor:
+                     dependent: bool = True, add_to: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Same contract as gemv_bf16 for shapes that gemv_stream_supported accepts.  `prefetch`: a tensor that a later kernel
     will stream (asked into the L2 by this kernel).  `late_trigger`: the next kernel on the stream may start only when
     this one's products are done (for successors whose blocks should find the SMs free).  `dependent=False` launches
-    without the programmatic-dependent-launch attribute."""
+    without the programmatic-dependent-launch attribute.  `add_to` (plain form only): out = rnd(add_to + rnd(x @ weight^T)),
+    the residual sum folded into the product's store; `add_to` may be `out` itself."""
     lib = _gemv_lib()
-    _cuda(out, x, weight, norm_weight, delta, resid_out, prefetch)
-    _contig(out, x, weight, norm_weight, delta, resid_out, prefetch)
+    _cuda(out, x, weight, norm_weight, delta, resid_out, prefetch, add_to)
+    _contig(out, x, weight, norm_weight, delta, resid_out, prefetch, add_to)
+    if add_to is not None and (norm_weight is not None or add_to.dtype != torch.bfloat16 or add_to.shape != out.shape):
+        raise KernelError("gemv_stream_bf16: add_to goes with the plain form and must be bf16, shaped like out")
     N, K = weight.shape
     if x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or x.shape[1] != K:
         raise KernelError("gemv_stream_bf16: x [M, K], weight [N, K] and out must be bf16")
@@ -517,7 +520,7 @@ def gemv_stream_bf16(out: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, r
         raise KernelError("gemv_stream_bf16: delta needs the norm prologue and a resid_out buffer other than x")
     mode = 0 if norm_weight is None else (2 if swiglu else 1)
     _check(lib.cvb_gemv_stream_bf16(_ptr(out), _ptr(x), _ptr(delta), _ptr(resid_out), _ptr(norm_weight), _ptr(weight), c_int(rows),
-                                    c_int(N), c_int(K), c_float(eps), c_int(mode), _ptr(prefetch),
+                                    c_int(N), c_int(K), c_float(eps), c_int(mode), _ptr(add_to), _ptr(prefetch),
                                     ctypes.c_longlong(prefetch.numel() * prefetch.element_size() if prefetch is not None else 0),
                                     c_int(1 if late_trigger else 0), c_int(1 if dependent else 0),
                                     _ptr(error_flag(x.device)), _stream()), "gemv_stream_bf16")

@@ -98,7 +98,8 @@ class PagedAttention(Mixer):
 
     def forward_fused(self, h, pending, norm, ctx, cache, state, h_out):
         """h: residual stream, pending: delta not yet added (or None), h_out: where rnd(h + pending) goes (a buffer
-        other than h; None without pending).  Returns (output, residual stream)."""
+        other than h; None without pending).  Returns (output, residual stream); the output is None when the part has
+        added it to the residual stream itself (the O product's store does, where that product is the decode chain's)."""
         T = ctx.num_tokens
         H, KV, hd = self.num_heads, self.num_kv_heads, self.head_dim
         ws = self.rt.workspace
@@ -108,9 +109,9 @@ class PagedAttention(Mixer):
         extra = {"prefetch": self.w_o} if product is ops.gemv_stream_bf16 and self.w_o.dtype == torch.bfloat16 else {}
         qkv = product(ws.rows("attn_qkv", T, (H + 2 * KV) * hd, h.dtype), h, self.w_qkv, T, norm_weight=norm.weight,
                       eps=norm.eps, delta=pending, resid_out=h_new if pending is not None else None, **extra)
-        return self._after_projection(qkv, ctx, cache), h_new
+        return self._after_projection(qkv, ctx, cache, add_to=h_new), h_new
 
-    def _after_projection(self, qkv, ctx, cache):
+    def _after_projection(self, qkv, ctx, cache, add_to=None):
         T = qkv.shape[0]
         x = qkv
         H, KV, hd = self.num_heads, self.num_kv_heads, self.head_dim
@@ -141,6 +142,9 @@ class PagedAttention(Mixer):
             self.attend(att, q, ctx, cache, g)
         # Behind the attention kernel the product starts only when that kernel has ended: measured, blocks of the product
         # that arrive among the attention kernel's last blocks cost more (4 us a layer) than their early weights save.
+        if add_to is not None and not self.rt.plain_kernels and ops.gemv_stream_supported(x.dtype, self.w_o, T):
+            ops.gemv_stream_bf16(add_to, att, self.w_o, T, dependent=False, add_to=add_to)    # h <- rnd(h + rnd(att Wo^T)), in place
+            return None
         return self._project(att, self.w_o, ws.rows("attn_proj", T, self.hidden_size, x.dtype), T, dependent=False)
 
     def _project(self, x, w, out, rows, dependent=True):

@@ -26,7 +26,8 @@ class PreNormBlock(Block):
         # A part may offer to take the norm in front of it (and the residual add in front of that) into its own
         # first kernel; it says so with can_fuse_norm(norm, ctx) and then runs forward_fused.
         # forward_fused(h, pending, norm, ..., h_out): if `pending` is not None the part writes rnd(h + pending) to h_out
-        # (a buffer other than h, which the block chooses) and returns it as the residual stream beside its output.
+        # (a buffer other than h, which the block chooses) and returns it as the residual stream beside its output.  A
+        # part may return None as its output: it has then added the output to the residual stream itself.
         ws = self.rt.workspace
         T, D = ctx.num_tokens, h.shape[1]
         fuse = getattr(self.mixer, "can_fuse_norm", None)
@@ -38,8 +39,8 @@ class PreNormBlock(Block):
             a = self.mixer.forward(x, ctx, cache, state)
         fuse = getattr(self.ffn, "can_fuse_norm", None)
         if fuse is not None and fuse(self.ffn_norm, ctx):
-            m, h = self.ffn.forward_fused(h, a, self.ffn_norm, ctx, ws.other_of_pair("residual", h, T, D, h.dtype))
+            m, h = self.ffn.forward_fused(h, a, self.ffn_norm, ctx, ws.other_of_pair("residual", h, T, D, h.dtype) if a is not None else None)
         else:
-            x = self.ffn_norm.add_forward(h, a)
+            x = self.ffn_norm.add_forward(h, a) if a is not None else self.ffn_norm.forward(h)
             m = self.ffn.forward(x, ctx)
         return h, m

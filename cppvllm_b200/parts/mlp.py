@@ -57,7 +57,9 @@ class SwiGLUMLP(FeedForward):
 
     def forward_fused(self, h, pending, norm, ctx, h_out):
         """Residual add, RMSNorm, gate/up product and SwiGLU in one kernel, then the down product.  h_out: where
-        rnd(h + pending) goes (a buffer other than h).  Returns (output, residual stream)."""
+        rnd(h + pending) goes (a buffer other than h; unused when pending is None: the part before has added its output
+        already).  Returns (output, residual stream); the output is None when the down product's store has added it to the
+        residual stream itself."""
         T = ctx.num_tokens
         ws = self.rt.workspace
         h_new = h_out if pending is not None else h
@@ -65,4 +67,7 @@ class SwiGLUMLP(FeedForward):
         act = product(ws.rows("ffn_act", T, self.intermediate_size, h.dtype), h, self.w_gate_up, T,
                       norm_weight=norm.weight, eps=norm.eps, delta=pending,
                       resid_out=h_new if pending is not None else None, swiglu=True)
+        if ops.gemv_stream_supported(act.dtype, self.w_down, T):
+            ops.gemv_stream_bf16(h_new, act, self.w_down, T, add_to=h_new)              # h <- rnd(h + rnd(act Wdown^T)), in place
+            return None, h_new
         return self._down(act, T), h_new

@@ -552,6 +552,11 @@ def test_gemv_stream_forms(ops, M, N, K, dependent):
         out = torch.full((M, N), float("nan"), dtype=dt, device=d)
         ops.gemv_stream_bf16(out, x, W, M, dependent=dependent, prefetch=W if rep else None, late_trigger=bool(rep))
         torch.testing.assert_close(out.float(), rnd(x.float() @ W.float().t(), dt), atol=2e-2, rtol=2e-2)
+        # the residual sum folded into the store, in place: exactly rnd(h + y) for the y the kernel has just produced
+        h = torch.randn(M, N, generator=g).to(dt).to(d)
+        want = rnd(h.float() + out.float(), dt)
+        ops.gemv_stream_bf16(h, x, W, M, dependent=dependent, add_to=h)
+        assert torch.equal(h.float(), want)
         delta = (torch.randn(M, K, generator=g) * 0.3).to(dt).to(d)
         nw = (1 + 0.2 * torch.randn(K, generator=g)).to(d)
         eps = 1e-5
