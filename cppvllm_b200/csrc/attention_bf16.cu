@@ -614,11 +614,9 @@ attn_decode_bf16_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnPa
             // them visible.
             const int owner = i / share;
             st_cluster(recv_o + split * share + (i - owner * share), owner, acc);
-            if (d == 0) {
-                for (int k = 0; k < p.splits; ++k) {
-                    st_cluster(recv_ml + (split * 16 + r) * 2, k, mm);
-                    st_cluster(recv_ml + (split * 16 + r) * 2 + 1, k, ll);
-                }
+            if (d < p.splits) {                                            // the row's first threads: one block each
+                st_cluster(recv_ml + (split * 16 + r) * 2, d, mm);
+                st_cluster(recv_ml + (split * 16 + r) * 2 + 1, d, ll);
             }
         } else {
             const int64_t base = ((static_cast<int64_t>(seq) * p.KV + kvh) * p.splits + split) * 16 + r;

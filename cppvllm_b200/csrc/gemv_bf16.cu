@@ -911,7 +911,10 @@ extern "C" int cvb_gemv_stream_bf16(void* out, const void* x, const void* delta,
     p.prefetch = (const unsigned char*)prefetch; p.prefetch_bytes = prefetch != nullptr ? prefetch_bytes : 0; p.err = err;
     p.M = M; p.N = N; p.K = K; p.opb = plan.opb; p.n_tiles = plan.n_tiles; p.warps_k = plan.warps_k;
     p.late_trigger = late_trigger ? 1 : 0; p.eps = eps;
+    // warps that share an activation row in the norm prologue: 16 / rows, but no more than give every lane a chunk (warps
+    // without work go straight to the barrier and leave the issue slots to those that have some)
     p.warps_per_row = M <= 1 ? 16 : (M <= 2 ? 8 : (M <= 4 ? 4 : 2));
+    while (p.warps_per_row > 1 && (K / 8 + 31) / 32 < p.warps_per_row) p.warps_per_row >>= 1;
     static bool set[3] = {false, false, false};                       // the three kernels share one pointer type: one flag per mode
     auto go = [&](void (*kernel)(StreamParams)) {
         if (!set[mode]) {
