@@ -107,6 +107,12 @@ template <> struct Chunk<float> {
     static __device__ __forceinline__ void round_all(float (&)[4]) {}
     static __device__ __forceinline__ void load(float (&v)[4], const float* p) { const float4 t = *reinterpret_cast<const float4*>(p); v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w; }
     static __device__ __forceinline__ void store(float* p, const float (&v)[4]) { *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]); }
+    static __device__ __forceinline__ void store_raw(float* p, const Raw& t) { *reinterpret_cast<float4*>(p) = t; }
+    // the partner lane's values (lane ^ delta)
+    static __device__ __forceinline__ void exchange(float (&other)[4], const float (&v)[4], int delta) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) other[i] = __shfl_xor_sync(0xffffffffu, v[i], delta);
+    }
 };
 template <> struct Chunk<__nv_bfloat16> {
     static constexpr int N = 8;
@@ -139,6 +145,17 @@ template <> struct Chunk<__nv_bfloat16> {
 #pragma unroll
         for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
         *reinterpret_cast<uint4*>(p) = t;
+    }
+    static __device__ __forceinline__ void store_raw(__nv_bfloat16* p, const Raw& t) { *reinterpret_cast<uint4*>(p) = t; }
+    // the partner lane's values (lane ^ delta); the values are exact in bf16 here, so they travel two to a word
+    static __device__ __forceinline__ void exchange(float (&other)[8], const float (&v)[8], int delta) {
+#pragma unroll
+        for (int i = 0; i < 8; i += 2) {
+            const uint32_t mine = (__float_as_uint(v[i]) >> 16) | (__float_as_uint(v[i + 1]) & 0xffff0000u);
+            const uint32_t theirs = __shfl_xor_sync(0xffffffffu, mine, delta);
+            other[i] = __uint_as_float(theirs << 16);
+            other[i + 1] = __uint_as_float(theirs & 0xffff0000u);
+        }
     }
 };
 
@@ -221,6 +238,14 @@ qk_norm_rope_kv_vec_kernel(T* __restrict__ q_out, const T* __restrict__ qkv, con
             const bool active = task_raw < n_tasks;
             const int task = active ? task_raw : n_tasks - 1;       // idle lanes hold a valid vector and store nothing
             const bool is_q = task < H, is_v = task >= H + KV;
+            if (round * per_round >= H + KV) {
+                // the whole round holds value heads (uniform over the block): they are copied as they are
+                if (active && k_row >= 0)
+                    Chunk<T>::store_raw(cache + (k_row + static_cast<int64_t>(task - H) * page_size) * hd + c * N, raw[k]);
+                if (round + kBatch < rounds)
+                    raw[k] = Chunk<T>::load_raw(src_row + min((round + kBatch) * per_round + sub, n_tasks - 1) * hd);
+                continue;
+            }
             float x[N];
             Chunk<T>::unpack(x, raw[k]);
             if (round + kBatch < rounds)                          // the same slot of the next batch
@@ -251,8 +276,12 @@ qk_norm_rope_kv_vec_kernel(T* __restrict__ q_out, const T* __restrict__ qkv, con
                 Chunk<T>::round_all(x);
             }
             float other[N];
+            if (q_w != nullptr) {
+                Chunk<T>::exchange(other, x, CH >> 1);            // normed values are exact in the activation type
+            } else {
 #pragma unroll
-            for (int i = 0; i < N; ++i) other[i] = __shfl_xor_sync(0xffffffffu, x[i], CH >> 1);
+                for (int i = 0; i < N; ++i) other[i] = __shfl_xor_sync(0xffffffffu, x[i], CH >> 1);
+            }
             if (is_v || dst == nullptr) continue;
             if (cos_t != nullptr) {
                 float out[N];
