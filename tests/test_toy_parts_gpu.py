@@ -319,3 +319,139 @@ def test_a_toy_mixer_with_a_latent_cache_can_be_registered_built_and_stepped(tmp
     finally:
         unregister_part("mixer", "latent_toy")
         unregister_architecture("ToyLatentForCausalLM")
+
+
+def test_a_toy_norm_and_a_toy_arrangement_can_be_registered_built_and_stepped(tmp_path):
+    """Another norm (it subtracts the mean, divides by the standard deviation, scales and shifts: two tensors) and another
+    arrangement of a layer (mixer and feed-forward both read the same normed input and are added to the stream together),
+    defined here and named in a model specification.  The mixer and the feed-forward are the framework's own.  The
+    engine in steps that cut two requests anywhere against one whole step each, and the whole step against a plain
+    computation of the same formulas on the CPU."""
+    from cppvllm_b200.config.registry import register_architecture, unregister_architecture
+    from cppvllm_b200.engine.runner import ModelRunner, StepEntry
+    from cppvllm_b200.parts.base import Block, Norm, WeightSpec, register_part, unregister_part
+    from cppvllm_b200.parts.spec import LayerSpec, ModelSpec, PartSpec
+    from cppvllm_b200.weights.random_init import write_random_model
+
+    class CentredNorm(Norm):
+        def __init__(self, runtime, prefix="", names=None, *, size, eps):
+            super().__init__(runtime, prefix, names)
+            self.size, self.eps = size, eps
+
+        def weight_specs(self):
+            return {self.full_name("scale"): WeightSpec((self.size,), role="vector", init="norm"),
+                    self.full_name("shift"): WeightSpec((self.size,), role="vector")}
+
+        def bind(self, tensors):
+            self.scale, self.shift = tensors[self.full_name("scale")], tensors[self.full_name("shift")]
+
+        def forward(self, x, out=None):
+            xf = x.float()
+            y = (xf - xf.mean(-1, keepdim=True)) * torch.rsqrt(xf.var(-1, unbiased=False, keepdim=True) + self.eps) * self.scale + self.shift
+            if out is not None:
+                out.copy_(y)
+                return out
+            return y.to(x.dtype)
+
+        def add_forward(self, residual, delta, out=None):
+            residual.add_(delta)
+            return self.forward(residual, out)
+
+    class ParallelBlock(Block):
+        """h <- h + mixer(norm(h)) + ffn(norm(h)): one norm, both branches read it."""
+        def __init__(self, runtime, prefix="", names=None, *, mixer, ffn, mixer_norm, ffn_norm):
+            super().__init__(runtime, prefix, names)
+            self.mixer, self.ffn, self.norm = mixer, ffn, mixer_norm
+
+        def parts(self):
+            return (self.norm, self.mixer, self.ffn)
+
+        def forward(self, h, pending, ctx, cache, state):
+            x = self.norm.forward(h) if pending is None else self.norm.add_forward(h, pending)
+            a = self.mixer.forward(x, ctx, cache, state)
+            m = self.ffn.forward(x, ctx)
+            return h, a + m
+
+    D, V, H, KV, hd, I = 48, 90, 4, 2, 16, 64
+
+    def build(cfg):
+        layers = [LayerSpec(
+            mixer=PartSpec("paged_attention", dict(hidden_size=D, num_heads=H, num_kv_heads=KV, head_dim=hd, qk_norm=False, position="rope"),
+                           prefix=f"toy.layers.{i}.attn."),
+            ffn=PartSpec("swiglu", dict(hidden_size=D, intermediate_size=I), prefix=f"toy.layers.{i}.mlp."),
+            mixer_norm=PartSpec("centred_toy", dict(size=D, eps=1e-5), prefix=f"toy.layers.{i}.norm."),
+            ffn_norm=PartSpec("centred_toy", dict(size=D, eps=1e-5), prefix=f"toy.layers.{i}.unused_norm."),
+            block="parallel_toy") for i in range(2)]
+        return ModelSpec("ToyParallelForCausalLM", D, V,
+                         embedding=PartSpec("token_embedding", dict(vocab_size=V, hidden_size=D), prefix="toy.embed."),
+                         layers=layers, final_norm=PartSpec("centred_toy", dict(size=D, eps=1e-5), prefix="toy.norm."),
+                         lm_head=PartSpec("lm_head", dict(vocab_size=V, hidden_size=D), prefix="toy.head."),
+                         positions={"rope": PartSpec("rotary", dict(rotary_dim=hd, theta=10000.0, max_positions=256, pairing="half"))},
+                         max_positions=256)
+
+    register_part("norm", "centred_toy", CentredNorm)
+    register_part("block", "parallel_toy", ParallelBlock)
+    register_architecture("ToyParallelForCausalLM", dict, build)
+    try:
+        d = write_random_model(str(tmp_path / "toy"), dict(architectures=["ToyParallelForCausalLM"]), seed=4, std=0.3,
+                               store_dtype=torch.float32)
+
+        def runner():
+            return ModelRunner(d, dtype=torch.float32, page_size=16, num_pages=12, max_step_tokens=64, max_seqs=4, max_model_len=128)
+
+        toks = {"a": tiny_models.random_tokens(V, 50, 1), "b": tiny_models.random_tokens(V, 21, 2)}
+
+        def whole(rid):
+            rr = runner()
+            rr.cache.admit(rid)
+            rr.cache.reserve(rid, len(toks[rid]))
+            return rr.step([StepEntry(rid, toks[rid], 0, list(range(len(toks[rid]))))]).cpu().clone()
+
+        ref = {k: whole(k) for k in toks}
+        r = runner()
+        got, fed = {k: [] for k in toks}, {k: 0 for k in toks}
+        for step in ([("a", 9), ("b", 2)], [("a", 1), ("b", 13)], [("a", 30)], [("b", 6), ("a", 2)], [("a", 8)]):
+            entries = []
+            for rid, n in step:
+                if rid not in r.cache.leases:
+                    r.cache.admit(rid)
+                r.cache.reserve(rid, fed[rid] + n)
+                entries.append(StepEntry(rid, toks[rid][fed[rid]:fed[rid] + n], fed[rid], list(range(n))))
+            out = r.step(entries).cpu()
+            o = 0
+            for rid, n in step:
+                got[rid].append(out[o:o + n].clone())
+                o += n
+                fed[rid] += n
+        r.check_errors()
+        for k in toks:
+            assert (torch.cat(got[k]) - ref[k]).abs().max() < 1e-4 * max(1.0, ref[k].abs().max())
+
+        # the whole step against the same formulas on the CPU
+        from cppvllm_b200.weights.safetensors_io import SafetensorsFile
+        f = SafetensorsFile(os.path.join(d, "model.safetensors"))
+        w = {n: f.tensor(n).float() for n in f.names()}
+
+        def cnorm(x, p):
+            return (x - x.mean(-1, keepdim=True)) * torch.rsqrt(x.var(-1, unbiased=False, keepdim=True) + 1e-5) * w[p + "scale"] + w[p + "shift"]
+
+        t = torch.tensor(toks["b"])
+        T = len(t)
+        cos, sin = plain.rope_tables(hd, 10000.0, 256)
+        pos = torch.arange(T)
+        h = w["toy.embed.weight"][t]
+        for i in range(2):
+            p = f"toy.layers.{i}."
+            x = cnorm(h, p + "norm.")
+            q = plain.apply_rope((x @ w[p + "attn.q_proj.weight"].t()).view(T, H, hd), cos, sin, pos, "float32")
+            kk = plain.apply_rope((x @ w[p + "attn.k_proj.weight"].t()).view(T, KV, hd), cos, sin, pos, "float32")
+            v = (x @ w[p + "attn.v_proj.weight"].t()).view(T, KV, hd)
+            a = plain.attention(q, kk, v, "float32").reshape(T, -1) @ w[p + "attn.o_proj.weight"].t()
+            m = plain.swiglu(x @ w[p + "mlp.gate_proj.weight"].t(), x @ w[p + "mlp.up_proj.weight"].t(), "float32") @ w[p + "mlp.down_proj.weight"].t()
+            h = h + a + m
+        want = cnorm(h, "toy.norm.") @ w["toy.head.weight"].t()
+        assert (ref["b"] - want).abs().max() < 1e-4 * max(1.0, float(want.abs().max()))
+    finally:
+        unregister_part("norm", "centred_toy")
+        unregister_part("block", "parallel_toy")
+        unregister_architecture("ToyParallelForCausalLM")
