@@ -22,6 +22,9 @@
 //              multiplied, written back by the row's thread) only when the running maximum of some row of the warp has
 //              grown by more than 2^8 since the reference was set, which happens in the first tiles and then hardly
 //              ever.  The result is exact: the same reference scales P and the row sum.
+// A grid of few query blocks with many key tiles each (a portion behind a long context) leaves SMs idle, so the launcher
+// may allow a query block's key tiles to be shared out among up to eight blocks ("pieces"); each leaves its unnormalised
+// rows, reference maxima and sums in global memory, and attn_prefill_merge_kernel adds them up in the order of the pieces.
 // Tensor memory columns: S(A) 0..127, S(B) 128..255, O(A) 256.., O(B) 256 + head size...
 // Buffers are handed over with mbarriers: TMA transaction counts, tcgen05.commit arrivals from the tensor core, and
 // plain arrivals from the softmax threads.  Every wait is bounded by a cycle count; a wait that runs out records
@@ -48,6 +51,11 @@ struct TcAttnParams {
     int table_width, S, H, KV, page_size, window, num_pages, box_rows;
     float scale_log2;
     int* err;
+    // A query block's key tiles may be shared out among up to `pieces` blocks (see the kernel's comment).
+    int pieces, min_rounds;
+    float* part_o;            // [query block * kv head * pieces][2 query tiles][HD][128 rows]
+    float* part_ml;           // [query block * kv head * pieces][2 query tiles][maximum | sum][128 rows]
+    int* piece_counts;        // [query block * kv head]: into how many pieces the block was cut (written by piece 0)
 };
 
 constexpr int kTcThreads = 128 + 256;         // one warpgroup of helpers (two warps idle), one warpgroup per query tile
@@ -85,12 +93,16 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, const Tc
     const int g = p.H / p.KV;
     const int tok_per_tile = kTM / g;
     const int tok_per_block = 2 * tok_per_tile;
-    const int kvh = blockIdx.y;
+    const int kvh = blockIdx.x;
     constexpr int CPR = HD / 8;
 
     int seq = -1, q0 = 0, q_len = 0, cu0 = 0;
+    // Blocks are handed out with the kv head running fastest, then the query block, long ones (late in their request)
+    // first, then the piece: all first pieces start before any second piece, and the blocks that find nothing to do
+    // (a piece beyond the number its query block is cut into) come last within their piece.
+    const int block_id = gridDim.y - 1 - blockIdx.y, piece = blockIdx.z;
     {
-        int tile = gridDim.x - 1 - blockIdx.x;                      // long blocks (late in the request) come first
+        int tile = block_id;
         for (int s = 0; s < p.S; ++s) {
             const int a = p.cu_seqlens[s], n = p.cu_seqlens[s + 1] - a;
             if (skip_single && n == 1) continue;
@@ -100,7 +112,6 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, const Tc
         }
     }
     if (seq < 0) return;
-    pdl_wait();
     const int* table = p.block_tables + static_cast<int64_t>(seq) * p.table_width;
     int n_tok[2];
 #pragma unroll
@@ -108,6 +119,49 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, const Tc
     // r / g for r < 256 without a division (g <= 16): exact with this multiplier
     const uint32_t g_mul = ((1u << 20) + g - 1) / g;
     auto row_tok = [&](int r) { return static_cast<int>((static_cast<uint32_t>(r) * g_mul) >> 20); };
+    // per query tile: the range of key tiles it needs, t_lo <= j < t_hi (none if t_lo >= t_hi)
+    int t_lo[2], t_hi[2], key_hi = 0, key_lo = 0x3fffffff;
+#pragma unroll
+    for (int x = 0; x < 2; ++x) {
+        if (n_tok[x] > 0) {
+            const int first = p.positions[cu0 + q0 + x * tok_per_tile];
+            const int last = p.positions[cu0 + q0 + x * tok_per_tile + n_tok[x] - 1];
+            const int first_key = p.window > 0 ? max(0, first - p.window + 1) : 0;   // the oldest key any of its tokens sees
+            t_lo[x] = first_key / kTN;
+            t_hi[x] = last / kTN + 1;
+            key_lo = min(key_lo, first_key);
+            key_hi = last;                                          // the block's last token
+        } else {
+            t_lo[x] = 0x3fffffff;
+            t_hi[x] = 0;
+        }
+    }
+    int j_lo = min(t_lo[0], t_lo[1]), j_hi = max(t_hi[0], t_hi[1]);
+    // A block with many key tiles shares them with up to pieces - 1 other blocks, each at least min_rounds tiles long:
+    // piece k of n walks the tiles j_lo + R k / n .. j_lo + R (k + 1) / n of the block's R.  Every piece leaves its
+    // unnormalised output, maxima and sums in global memory, and attn_prefill_merge_kernel adds them up and stores the
+    // rows.  Blocks beyond n have nothing to do.
+    int n_pieces = 1;
+    if (p.pieces > 1) {
+        const int rounds = j_hi - j_lo;
+        n_pieces = min(p.pieces, max(1, rounds / p.min_rounds));
+        if (piece >= n_pieces) return;
+        if (n_pieces > 1) {
+            const int lo = j_lo + (rounds * piece) / n_pieces, hi = j_lo + (rounds * (piece + 1)) / n_pieces;
+#pragma unroll
+            for (int x = 0; x < 2; ++x) {
+                t_lo[x] = max(t_lo[x], lo);
+                t_hi[x] = min(t_hi[x], hi);
+                if (t_lo[x] >= t_hi[x]) { t_lo[x] = 0x3fffffff; t_hi[x] = 0; }
+            }
+            j_lo = min(t_lo[0], t_lo[1]);
+            j_hi = max(t_hi[0], t_hi[1]);
+        }
+    }
+    const int part_slot = (block_id * p.KV + kvh) * p.pieces + piece;
+    if (p.pieces > 1 && piece == 0 && threadIdx.x == 0) p.piece_counts[block_id * p.KV + kvh] = n_pieces;
+    // Everything read so far is a step input, in place before the first kernel of the step started.
+    pdl_wait();
     // query rows: row r of tile x = (token x * tok_per_tile + r / g, head kvh * g + r % g); rows past the portion are zero.
     // Warp 0 takes no part: it starts fetching keys as soon as the barriers exist.  Warp 1 asks for the tensor memory first.
     if (warp > 0) {
@@ -126,24 +180,6 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, const Tc
         }
         asm volatile("cp.async.commit_group;\n" ::: "memory");
     }
-    // per query tile: the range of key tiles it needs, t_lo <= j < t_hi (none if t_lo >= t_hi)
-    int t_lo[2], t_hi[2], key_hi = 0, key_lo = 0x3fffffff;
-#pragma unroll
-    for (int x = 0; x < 2; ++x) {
-        if (n_tok[x] > 0) {
-            const int first = p.positions[cu0 + q0 + x * tok_per_tile];
-            const int last = p.positions[cu0 + q0 + x * tok_per_tile + n_tok[x] - 1];
-            const int first_key = p.window > 0 ? max(0, first - p.window + 1) : 0;   // the oldest key any of its tokens sees
-            t_lo[x] = first_key / kTN;
-            t_hi[x] = last / kTN + 1;
-            key_lo = min(key_lo, first_key);
-            key_hi = last;                                          // the block's last token
-        } else {
-            t_lo[x] = 0x3fffffff;
-            t_hi[x] = 0;
-        }
-    }
-    const int j_lo = min(t_lo[0], t_lo[1]), j_hi = max(t_hi[0], t_hi[1]);
     // Loads are clamped to [key_lo, key_hi], the keys that the block's tokens see: a page below the window may have been
     // given back by its request already (its table entry is -1) and is never looked up; rounding a key down to its box
     // stays inside the page that holds it.
@@ -250,13 +286,14 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, const Tc
         const int quarter = warp & 3;                // the 32 lanes of tensor memory this warp may touch
         const int r = quarter * 32 + lane;           // row within the tile
         const uint32_t lane_base = static_cast<uint32_t>(quarter * 32) << 16;
-        if (t_lo[x] < t_hi[x]) {
+        const bool has_keys = t_lo[x] < t_hi[x];
+        float m_ref = -INFINITY, l = 0.f;
+        if (has_keys) {
             const int r_tok = row_tok(r);
             const int tok_in_tile = min(r_tok, n_tok[x] - 1);
             const int tok = x * tok_per_tile + tok_in_tile;
             const int row_pos = p.positions[cu0 + q0 + tok];
             const int row_lo = p.window > 0 ? max(0, row_pos - p.window + 1) : 0;
-            float m_ref = -INFINITY, l = 0.f;
             for (int j = t_lo[x]; j < t_hi[x]; ++j) {
                 const int i = j - t_lo[x];
                 const int key0 = j * kTN;
@@ -326,24 +363,51 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, const Tc
             }
             mbar_wait(o_done + x, 0, p.err);
             tc_after();
-            // The rows go through shared memory (over the query tile, which no product reads any more, in its swizzled
-            // layout) so that the stores to global memory are whole rows side by side: a thread that stored its own row
-            // would touch 32 lines with every instruction.
-            const float inv = l > 0.f ? 1.f / l : 0.f;
-            __nv_bfloat16* stage = reinterpret_cast<__nv_bfloat16*>(sQ + x * L::kTile);
-            uint32_t o[HD];
+        }
+        // The rows go through shared memory (over the query tile, which no product reads any more, in its swizzled
+        // layout) so that the stores to global memory are whole rows side by side: a thread that stored its own row
+        // would touch 32 lines with every instruction.
+        __nv_bfloat16* stage = reinterpret_cast<__nv_bfloat16*>(sQ + x * L::kTile);
+        auto stage_chunk = [&](int c0, const uint32_t (&o)[32], float inv) {   // 32 columns of the thread's row
 #pragma unroll
-            for (int c = 0; c < HD; c += 32) tm_load32(tO[x] + lane_base + c, *reinterpret_cast<uint32_t(*)[32]>(&o[c]));
-            tm_wait_ld();
-#pragma unroll
-            for (int k = 0; k < HD; k += 8) {
+            for (int k = 0; k < 32; k += 8) {
                 uint4 t;
                 __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&t);
 #pragma unroll
                 for (int e = 0; e < 4; ++e)
                     h[e] = __floats2bfloat162_rn(__uint_as_float(o[k + 2 * e]) * inv, __uint_as_float(o[k + 2 * e + 1]) * inv);
-                *reinterpret_cast<uint4*>(stage + tile_off(r, k >> 3)) = t;
+                *reinterpret_cast<uint4*>(stage + tile_off(r, (c0 + k) >> 3)) = t;
             }
+        };
+        const bool store = has_keys && n_pieces == 1;
+        if (store) {
+            const float inv = l > 0.f ? 1.f / l : 0.f;
+#pragma unroll
+            for (int c0 = 0; c0 < HD; c0 += 32) {
+                uint32_t o[32];
+                tm_load32(tO[x] + lane_base + c0, o);
+                tm_wait_ld();
+                stage_chunk(c0, o, inv);
+            }
+        } else if (n_pieces > 1) {
+            // ---- one of several pieces: leave its share (unnormalised rows, reference maxima, sums) for
+            // attn_prefill_merge_kernel; rows lie side by side so that the threads of a warp write whole lines ----
+            float* mine = p.part_o + (static_cast<int64_t>(part_slot) * 2 + x) * (HD * 128) + r;
+            float* mine_ml = p.part_ml + (static_cast<int64_t>(part_slot) * 2 + x) * 256 + r;
+            if (has_keys) {
+#pragma unroll
+                for (int c0 = 0; c0 < HD; c0 += 32) {
+                    uint32_t o[32];
+                    tm_load32(tO[x] + lane_base + c0, o);
+                    tm_wait_ld();
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) __stcg(mine + (c0 + c) * 128, __uint_as_float(o[c]));
+                }
+            }
+            __stcg(mine_ml, has_keys ? m_ref : -INFINITY);
+            __stcg(mine_ml + 128, has_keys ? l : 0.f);          // no sum: the piece had no key for this row
+        }
+        if (store) {
             asm volatile("bar.sync %0, 128;\n" ::"r"(2 + x) : "memory");       // the 128 threads of this query tile
             __nv_bfloat16* out_base = p.out + ((static_cast<int64_t>(cu0 + q0) + x * tok_per_tile) * p.H + kvh * g) * HD;
             // thread r takes chunk r % CPR of the rows r / CPR + k * (128 / CPR): a row's chunks lie in neighbouring lanes
@@ -368,6 +432,88 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, const Tc
     }
 }
 
+// Adds up the shares of query blocks that attn_prefill_tcgen05_kernel cut into pieces and stores their rows.  Grid:
+// (query block * kv head, query tile, 32 columns of the head); thread r owns row r of the query tile.  Piece k weighs
+// 2^(its reference maximum - the largest of them); shares are added in the order of the pieces.
+__global__ void __launch_bounds__(128)
+attn_prefill_merge_kernel(const TcAttnParams p, const int skip_single, const int hd) {
+    constexpr int kMaxPieces = 8;
+    constexpr int kRowBytes = 64 + 16;                              // 32 bf16 of a row, padded against bank conflicts
+    __shared__ __align__(16) unsigned char stage[128 * kRowBytes];
+    pdl_trigger();
+    const int g = p.H / p.KV;
+    const int tok_per_tile = kTM / g, tok_per_block = 2 * tok_per_tile;
+    const int block_id = blockIdx.x / p.KV, kvh = blockIdx.x - block_id * p.KV;
+    const int x = blockIdx.y, c0 = blockIdx.z * 32, r = threadIdx.x;
+    int seq = -1, q0 = 0, q_len = 0, cu0 = 0;
+    {
+        int tile = block_id;
+        for (int s = 0; s < p.S; ++s) {
+            const int a = p.cu_seqlens[s], n = p.cu_seqlens[s + 1] - a;
+            if (skip_single && n == 1) continue;
+            const int tiles = (n + tok_per_block - 1) / tok_per_block;
+            if (tile < tiles) { seq = s; q0 = tile * tok_per_block; q_len = n; cu0 = a; break; }
+            tile -= tiles;
+        }
+    }
+    if (seq < 0) return;
+    const int n_tok = max(0, min(tok_per_tile, q_len - q0 - x * tok_per_tile));
+    if (n_tok == 0) return;
+    pdl_wait();
+    const int n_pieces = min(p.piece_counts[blockIdx.x], kMaxPieces);
+    if (n_pieces <= 1) return;                                      // the block stored its rows itself
+    const int64_t first = static_cast<int64_t>(blockIdx.x) * p.pieces;
+    float w[kMaxPieces], sum[kMaxPieces];
+#pragma unroll
+    for (int k = 0; k < kMaxPieces; ++k) {
+        const float* ml = p.part_ml + ((first + k) * 2 + x) * 256 + r;
+        w[k] = k < n_pieces ? __ldcg(ml) : -INFINITY;
+        sum[k] = k < n_pieces ? __ldcg(ml + 128) : 0.f;
+    }
+    float m_all = -INFINITY, l = 0.f;
+#pragma unroll
+    for (int k = 0; k < kMaxPieces; ++k) {
+        if (!(sum[k] > 0.f)) w[k] = -INFINITY;                      // a piece without a key for this row
+        m_all = fmaxf(m_all, w[k]);
+    }
+#pragma unroll
+    for (int k = 0; k < kMaxPieces; ++k) {
+        w[k] = w[k] == -INFINITY ? 0.f : ex2(w[k] - m_all);
+        l = __fadd_rn(l, __fmul_rn(sum[k], w[k]));
+    }
+    float acc[32];
+#pragma unroll
+    for (int c = 0; c < 32; ++c) acc[c] = 0.f;
+#pragma unroll
+    for (int k = 0; k < kMaxPieces; ++k) {
+        if (k >= n_pieces || w[k] == 0.f) continue;
+        const float* share = p.part_o + ((first + k) * 2 + x) * (static_cast<int64_t>(hd) * 128) + static_cast<int64_t>(c0) * 128 + r;
+#pragma unroll
+        for (int c = 0; c < 32; ++c) acc[c] = __fadd_rn(acc[c], __fmul_rn(__ldcg(share + c * 128), w[k]));
+    }
+    const float inv = l > 0.f ? 1.f / l : 0.f;
+#pragma unroll
+    for (int k = 0; k < 32; k += 8) {
+        uint4 t;
+        __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&t);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) h[e] = __floats2bfloat162_rn(acc[k + 2 * e] * inv, acc[k + 2 * e + 1] * inv);
+        *reinterpret_cast<uint4*>(stage + r * kRowBytes + k * 2) = t;
+    }
+    __syncthreads();
+    // four threads store the 64 bytes of a row
+    __nv_bfloat16* out_base = p.out + ((static_cast<int64_t>(cu0 + q0) + x * tok_per_tile) * p.H + kvh * g) * hd + c0;
+    const int chunk = r & 3;
+#pragma unroll
+    for (int pass = 0; pass < 4; ++pass) {
+        const int row = pass * 32 + (r >> 2);
+        const int t = row / g, h = row - t * g;
+        if (t < n_tok)
+            *reinterpret_cast<uint4*>(out_base + (static_cast<int64_t>(t) * p.H + h) * hd + chunk * 8) =
+                *reinterpret_cast<const uint4*>(stage + row * kRowBytes + chunk * 16);
+    }
+}
+
 // ---- host side ------------------------------------------------------------------------------------------------
 
 static int kv_map_for(CUtensorMap* out, const void* cache, int64_t rows, int hd, int box_rows) {
@@ -378,29 +524,47 @@ static int kv_map_for(CUtensorMap* out, const void* cache, int64_t rows, int hd,
 
 using namespace cvb;
 
-// Blocks the grid needs: per request with more than one token, ceil(tokens / (256 / group)).
+// Floats of scratch that `pieces` > 1 needs for num_tiles query blocks: outputs, maxima and sums of every piece.
+extern "C" int64_t cvb_attn_prefill_tcgen05_scratch_floats(int num_tiles, int KV, int hd, int pieces) {
+    return static_cast<int64_t>(num_tiles) * KV * pieces * 2 * (hd + 2) * 128;
+}
+
+// Blocks the grid needs: per request with more than one token, ceil(tokens / (256 / group)) query blocks, times
+// `pieces`.  With pieces > 1 a query block whose tokens see at least 2 * min_rounds key tiles of 128 is worked on by up
+// to `pieces` blocks of the grid, each with at least min_rounds tiles; `scratch` then holds
+// cvb_attn_prefill_tcgen05_scratch_floats floats and `piece_counts` num_tiles * KV ints (both are written before they
+// are read), and a second kernel adds the pieces' shares up.
 extern "C" int cvb_attn_prefill_tcgen05(void* out, const void* q, const void* cache, const int* block_tables,
                                            int table_width, const int* cu_seqlens, const int* positions, int S,
                                            int num_tiles, int H, int KV, int hd, int page_size, int window, float scale,
-                                           int num_pages, int skip_single, int* err_flag, cudaStream_t stream) {
+                                           int num_pages, int skip_single, int pieces, int min_rounds, float* scratch,
+                                           int64_t scratch_floats, int* piece_counts, int* err_flag, cudaStream_t stream) {
     if (num_tiles == 0) return CVB_OK;
     if (num_tiles < 0 || S <= 0 || H <= 0 || KV <= 0 || page_size <= 0 || table_width <= 0 || num_pages <= 0) return CVB_E_SIZE;
     if (H % KV) return CVB_E_SHAPE;
     if (hd != 64 && hd != 128) return CVB_E_UNSUPPORTED;
     const int g = H / KV;
-    if (g > 16 || KV > 65535) return CVB_E_UNSUPPORTED;
+    if (g > 16) return CVB_E_UNSUPPORTED;
     if (page_size < 16 || (page_size & (page_size - 1)) != 0) return CVB_E_UNSUPPORTED;
     if (static_cast<int64_t>(num_pages) * 2 * KV * page_size > 2147483647LL) return CVB_E_SIZE;
+    if (pieces < 1 || pieces > 8 || min_rounds < 1) return CVB_E_SIZE;     // the kernel adds up at most eight shares
+    if (static_cast<int64_t>(num_tiles) * pieces > 2147483647LL) return CVB_E_SIZE;
+    if (pieces > 1 && (!scratch || !piece_counts || scratch_floats < cvb_attn_prefill_tcgen05_scratch_floats(num_tiles, KV, hd, pieces)))
+        return CVB_E_SCRATCH;
     TcAttnParams p{};
     p.out = (__nv_bfloat16*)out; p.q = (const __nv_bfloat16*)q;
     p.block_tables = block_tables; p.cu_seqlens = cu_seqlens; p.positions = positions;
     p.table_width = table_width; p.S = S; p.H = H; p.KV = KV; p.page_size = page_size; p.window = window;
     p.num_pages = num_pages; p.scale_log2 = scale * kLog2eF; p.err = err_flag;
     p.box_rows = page_size < 64 ? page_size : 64;
+    p.pieces = pieces; p.min_rounds = min_rounds; p.piece_counts = piece_counts;
+    p.part_o = scratch;
+    p.part_ml = scratch ? scratch + static_cast<int64_t>(num_tiles) * KV * pieces * 2 * hd * 128 : nullptr;
     CUtensorMap map;
     const int rc = kv_map_for(&map, cache, static_cast<int64_t>(num_pages) * 2 * KV * page_size, hd, p.box_rows);
     if (rc != CVB_OK) return rc;
-    dim3 grid(static_cast<unsigned>(num_tiles), static_cast<unsigned>(KV));
+    if (num_tiles > 65535) return CVB_E_SIZE;
+    dim3 grid(static_cast<unsigned>(KV), static_cast<unsigned>(num_tiles), static_cast<unsigned>(pieces));
     if (hd == 128) {
         static bool set = false;
         if (!set) { cudaFuncSetAttribute(attn_prefill_tcgen05_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TcSmem<128>::kBytes); set = true; }
@@ -410,5 +574,10 @@ extern "C" int cvb_attn_prefill_tcgen05(void* out, const void* q, const void* ca
         if (!set) { cudaFuncSetAttribute(attn_prefill_tcgen05_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)TcSmem<64>::kBytes); set = true; }
         launch_kernel(attn_prefill_tcgen05_kernel<64>, grid, dim3(kTcThreads), TcSmem<64>::kBytes, stream, map, p, skip_single);
     }
+    const int launched = launch_status();
+    if (launched != CVB_OK || pieces == 1) return launched;
+    if (static_cast<int64_t>(num_tiles) * KV > 2147483647LL) return CVB_E_SIZE;
+    launch_kernel(attn_prefill_merge_kernel, dim3(static_cast<unsigned>(num_tiles * KV), 2, static_cast<unsigned>(hd / 32)), dim3(128), 0,
+                  stream, p, skip_single, hd);
     return launch_status();
 }

@@ -332,22 +332,63 @@ def prefill_tiles_tcgen05(q_lens, num_heads: int, num_kv_heads: int, skip_single
     return sum((n + tpt - 1) // tpt for n in q_lens if not (skip_single and n == 1))
 
 
-def attn_prefill_tcgen05(out, q, cache, block_tables, cu_seqlens, positions, num_seqs: int, num_tiles: int,
-                         num_heads: int, num_kv_heads: int, head_dim: int, page_size: int, scale: float,
-                         window: int = 0, skip_single: bool = True):
-    """Flash attention of prompt portions on the tcgen05 tensor cores (same contract as attn_prefill_bf16)."""
+def _attn_tc_lib():
     global _attn_tc
     if _attn_tc is None:
         lib = load_library("attn_tcgen05")
         lib.cvb_attn_prefill_tcgen05.restype = c_int
+        lib.cvb_attn_prefill_tcgen05_scratch_floats.restype = c_int64
         _attn_tc = lib
+    return _attn_tc
+
+
+# The tcgen05 prefill kernel shares the key tiles of a long query block out among several blocks when its grid leaves
+# most SMs idle: a portion of 512 tokens behind 8,192 cached ones is 32 blocks (8 kv heads) of 68 key tiles each, 128 us
+# as they are and 52 us in four pieces.  Pieces are taken only while all blocks can run at once (a second wave costs
+# what the cut saves), and a piece has at least PREFILL_MIN_ROUNDS tiles: what a block costs outside its tiles, and
+# adding the shares up, is worth about six tiles.
+PREFILL_SMS = 148
+PREFILL_MAX_PIECES = 8
+PREFILL_MIN_ROUNDS = 8
+
+
+def prefill_pieces_tcgen05(num_tiles: int, num_kv_heads: int, max_kv_len: int = 1 << 30) -> int:
+    """Into how many pieces the kernel may cut a query block's keys; 1 if no request of the step is long enough for two
+    pieces (the kernel that adds the shares up is then not launched)."""
+    if max_kv_len < 2 * PREFILL_MIN_ROUNDS * 128:
+        return 1
+    blocks = max(1, num_tiles * num_kv_heads)
+    return max(1, min(PREFILL_MAX_PIECES, PREFILL_SMS // blocks))
+
+
+def attn_prefill_tcgen05_scratch_floats(num_tiles: int, num_kv_heads: int, head_dim: int, pieces: int) -> int:
+    return int(_attn_tc_lib().cvb_attn_prefill_tcgen05_scratch_floats(c_int(num_tiles), c_int(num_kv_heads), c_int(head_dim),
+                                                                      c_int(pieces)))
+
+
+def attn_prefill_tcgen05(out, q, cache, block_tables, cu_seqlens, positions, num_seqs: int, num_tiles: int,
+                         num_heads: int, num_kv_heads: int, head_dim: int, page_size: int, scale: float,
+                         window: int = 0, skip_single: bool = True, pieces: int = 1, min_rounds: int = PREFILL_MIN_ROUNDS,
+                         scratch=None, piece_counts=None):
+    """Flash attention of prompt portions on the tcgen05 tensor cores (same contract as attn_prefill_bf16).
+    ``pieces`` > 1: a query block with at least 2 * min_rounds key tiles is worked on by up to ``pieces`` blocks;
+    ``scratch`` (float32, attn_prefill_tcgen05_scratch_floats elements) and ``piece_counts`` (int32, num_tiles * kv heads)
+    are then required, and a second kernel adds the pieces' shares up."""
+    lib = _attn_tc_lib()
     _attn_common_checks(out, q, cache, block_tables, cu_seqlens, positions)
     num_pages = cache.numel() // (2 * num_kv_heads * page_size * head_dim)
-    _check(_attn_tc.cvb_attn_prefill_tcgen05(
+    if pieces > 1:
+        if scratch is None or piece_counts is None:
+            raise ValueError("attn_prefill_tcgen05 with pieces > 1 needs scratch and piece_counts")
+        if scratch.dtype != torch.float32 or piece_counts.dtype != torch.int32 or piece_counts.numel() < num_tiles * num_kv_heads:
+            raise ValueError("attn_prefill_tcgen05: scratch must be float32 and piece_counts int32 with one entry per "
+                             "(query block, kv head)")
+    _check(lib.cvb_attn_prefill_tcgen05(
         _ptr(out), _ptr(q), _ptr(cache), _ptr(block_tables), c_int(block_tables.shape[1]), _ptr(cu_seqlens),
         _ptr(positions), c_int(num_seqs), c_int(num_tiles), c_int(num_heads), c_int(num_kv_heads), c_int(head_dim),
         c_int(page_size), c_int(window), c_float(scale), c_int(num_pages), c_int(1 if skip_single else 0),
-        _ptr(error_flag(q.device)), _stream()), "attn_prefill_tcgen05")
+        c_int(pieces), c_int(min_rounds), _ptr(scratch), c_int64(scratch.numel() if scratch is not None else 0), _ptr(piece_counts),
+        _ptr(error_flag(q.device)), _stream()), "attn_prefill_tcgen05", kernels=2 if pieces > 1 else 1)
     return out
 
 

@@ -98,8 +98,15 @@ def attn_prefill(a) -> dict:
     if a.impl == "tcgen05":
         tiles = ops.prefill_tiles_tcgen05([a.tokens] * a.batch, H, KV)
 
+        pieces = a.pieces if a.pieces else ops.prefill_pieces_tcgen05(tiles, KV)        # 0: the engine's choice
+        scratch = counters = None
+        if pieces > 1:
+            scratch = torch.empty(ops.attn_prefill_tcgen05_scratch_floats(tiles, KV, hd, pieces), dtype=torch.float32, device=q.device)
+            counters = torch.zeros(tiles * KV, dtype=torch.int32, device=q.device)
+
         def run(i):
-            ops.attn_prefill_tcgen05(out, q, caches[0], tables, cu, pos, a.batch, tiles, H, KV, hd, page, scale)
+            ops.attn_prefill_tcgen05(out, q, caches[0], tables, cu, pos, a.batch, tiles, H, KV, hd, page, scale,
+                                     pieces=pieces, min_rounds=a.min_rounds, scratch=scratch, piece_counts=counters)
     else:
         tiles = ops.prefill_tiles([a.tokens] * a.batch, H, KV)
 
@@ -108,8 +115,8 @@ def attn_prefill(a) -> dict:
     us = _time(run, a.iters)
     ops.check_device_errors(q.device)
     flops = a.batch * 4 * H * hd * (a.tokens * (a.tokens + 1) // 2 + a.tokens * a.cached)
-    return {"kernel": f"attn_prefill ({a.impl})", "batch": a.batch, "tokens": a.tokens, "cached": a.cached, "us": round(us, 2),
-            "TFLOPs": round(flops / us / 1e6, 1), "flops": flops}
+    return {"kernel": f"attn_prefill ({a.impl})", "batch": a.batch, "tokens": a.tokens, "cached": a.cached, "pieces": pieces if a.impl == "tcgen05" else 1,
+            "us": round(us, 2), "TFLOPs": round(flops / us / 1e6, 1), "flops": flops}
 
 
 def gemv(a) -> dict:
@@ -237,6 +244,8 @@ def main(argv=None) -> int:
     p.add_argument("--head-dim", type=int, default=128)
     p.add_argument("--page-size", type=int, default=32)
     p.add_argument("--splits", type=int, default=0)
+    p.add_argument("--pieces", type=int, default=0, help="attn_prefill: blocks per long query block (0: the engine's choice)")
+    p.add_argument("--min-rounds", type=int, default=8, help="attn_prefill: the fewest key tiles of a piece")
     p.add_argument("--rows", type=int, default=4096)
     p.add_argument("--cols", type=int, default=1024)
     p.add_argument("--iters", type=int, default=20)

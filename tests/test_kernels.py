@@ -408,6 +408,65 @@ def test_tensor_core_attention_mixed_portions_and_single_tokens(ops, H, KV, hd, 
     torch.testing.assert_close(results[(3, True)], gen.float().cpu().view(T, H, hd), atol=2e-2, rtol=2e-2)
 
 
+@pytest.mark.parametrize("H,KV,hd,page,window", [(4, 2, 128, 16, 0), (6, 1, 64, 32, 0), (6, 2, 128, 16, 300), (16, 8, 128, 32, 0)])
+@pytest.mark.parametrize("pieces,min_rounds", [(2, 1), (3, 2), (8, 1), (5, 4)])
+def test_tcgen05_prefill_shares_the_keys_of_long_query_blocks_among_blocks(ops, H, KV, hd, page, window, pieces, min_rounds):
+    """Query blocks with many key tiles are worked on by several blocks, each with a range of the tiles, and a second
+    kernel adds their shares up: the same rows as one block per query block gives, at contexts where the pieces' edges
+    fall before, inside and after a query tile's own keys.  One early key of the longest request is made to stand out
+    (its query and key are scaled), so a piece whose share went missing would show in every row that sees it."""
+    dt = torch.bfloat16
+    g = torch.Generator().manual_seed(H + 3 * hd + pieces)
+    reqs = [(1000, 300), (0, 700), (2000, 40), (0, 3), (130, 1), (384, 129)]
+    seqs_k = [torch.randn(c + n, KV, hd, generator=g).to(dt) for c, n in reqs]
+    seqs_v = [torch.randn(c + n, KV, hd, generator=g).to(dt) for c, n in reqs]
+    cu, positions, seq_of = [0], [], []
+    for s, (c, n) in enumerate(reqs):
+        cu.append(cu[-1] + n)
+        positions += list(range(c, c + n))
+        seq_of += [s] * n
+    T = cu[-1]
+    q = (torch.randn(T, H, hd, generator=g) * 1.5).to(dt)
+    unit = torch.zeros(hd)
+    unit[3] = 1.0
+    seqs_k[1][37] = (unit * 12).to(dt)                    # key 37 of the request with 700 tokens ...
+    q[cu[1] + 200:cu[1] + 700] += (unit * 12).to(dt)      # ... draws most of the weight of its later tokens
+    total_pages = sum((c + n + page - 1) // page for c, n in reqs) + 3
+    cache, tables = build_paged(seqs_k, seqs_v, page, total_pages, KV, hd, dt, g)
+    if window > 0:
+        for s, (c, n) in enumerate(reqs):
+            for slot in range(max(0, c - window + 1) // page):
+                cache[tables[s, slot]] = float("nan")
+                tables[s, slot] = -1
+    scale = 1 / math.sqrt(hd)
+    d = dev()
+    q_lens = [n for _, n in reqs]
+    cu_t = torch.tensor(cu, dtype=torch.int32, device=d)
+    pos_t = torch.tensor(positions, dtype=torch.int32, device=d)
+    tiles = ops.prefill_tiles_tcgen05(q_lens, H, KV)
+    args = (q.view(T, -1).to(d), cache.to(d), tables.to(d), cu_t, pos_t, len(reqs), tiles, H, KV, hd, page, scale)
+    whole = ops.attn_prefill_tcgen05(torch.zeros(T, H * hd, dtype=dt, device=d), *args, window=window)
+    scratch = torch.full((ops.attn_prefill_tcgen05_scratch_floats(tiles, KV, hd, pieces),), float("nan"), device=d)
+    counters = torch.full((tiles * KV,), -7, dtype=torch.int32, device=d)
+    outs = []
+    for _ in range(2):
+        out = torch.full((T, H * hd), float("nan"), dtype=dt, device=d)
+        ops.attn_prefill_tcgen05(out, *args, window=window, pieces=pieces, min_rounds=min_rounds, scratch=scratch, piece_counts=counters)
+        outs.append(out)
+    ops.check_device_errors(d)
+    keep = torch.tensor([n > 1 for s, (c, n) in enumerate(reqs) for _ in range(n)])      # single tokens are the decode kernel's
+    assert torch.equal(outs[0][keep.to(d)], outs[1][keep.to(d)])
+    got = outs[0].float().cpu().view(T, H, hd)[keep]
+    ref = attention_ref(q, [seqs_k[s] for s in seq_of], [seqs_v[s] for s in seq_of], None, positions, H, KV, hd, scale, window)[keep]
+    torch.testing.assert_close(got, rnd(ref, dt), atol=2e-2, rtol=2e-2)
+    torch.testing.assert_close(got, whole.float().cpu().view(T, H, hd)[keep], atol=1e-2, rtol=1e-2)
+    if window == 0:
+        rows = slice(cu[1] + 300, cu[1] + 700)
+        weight = torch.softmax((seqs_k[1][:, 0].float() @ q[cu[1] + 650, 0].float()) * scale, 0)[37]
+        assert weight > 0.5, "the planted key does not stand out"
+        assert torch.isfinite(got).all() and (got[rows] - rnd(ref, dt)[rows]).abs().max() < 2e-2
+
+
 @pytest.mark.parametrize("H,KV,hd,page,window,norm,rope", [(16, 8, 128, 32, 0, True, True), (6, 2, 64, 16, 0, True, True),
                                                           (16, 1, 128, 16, 0, False, True), (4, 4, 64, 64, 70, True, False)])
 def test_decode_attention_from_the_projection(ops, H, KV, hd, page, window, norm, rope):

@@ -137,6 +137,41 @@ def test_four_cuttings_at_the_0p6b_layer_sizes(model_4l, dtype):
     r.cache.check_invariants()
 
 
+def test_a_late_portion_attended_in_pieces_matches_the_whole_prompt(model_4l):
+    """A portion of a few hundred tokens behind two thousand cached ones is few query blocks with many key tiles each: the
+    tensor-core attention shares each block's tiles out among several blocks and adds their shares up.  The same prompt
+    in one step is many blocks and no pieces.  Both against the plain implementation, and against each other."""
+    from cppvllm_b200.csrc import ops
+    from cppvllm_b200.engine.runner import ModelRunner, StepEntry
+    toks = tiny_models.random_tokens(10000, 2600, 77)
+    rows = [2048, 2049, 2175, 2176, 2300, 2598, 2599]
+    outs, used = [], []
+    for cuts in ((2600,), (2048, 552)):
+        r = ModelRunner(model_4l, dtype=torch.bfloat16, page_size=32, num_pages=96, max_step_tokens=4096, max_seqs=4,
+                        max_model_len=4096)
+        r.cache.admit("a")
+        r.cache.reserve("a", len(toks))
+        got, pos = {}, 0
+        for n in cuts:
+            want = [p_ - pos for p_ in rows if pos <= p_ < pos + n]
+            out = r.step([StepEntry("a", toks[pos:pos + n], pos, want)]).float().cpu()
+            got.update({pos + w: out[i] for i, w in enumerate(want)})
+            pos += n
+        r.check_errors()
+        outs.append(torch.stack([got[p_] for p_ in rows]))
+        used.append(any(k.startswith("attn_prefill_pieces") for k in r.workspace._buffers))
+    assert used == [False, True], "the second cutting's last portion should have been attended in pieces"
+    assert ops.prefill_pieces_tcgen05(ops.prefill_tiles_tcgen05([552], 16, 8), 8) >= 2
+    c, w = plain.read_config(model_4l), plain.read_weights(model_4l)
+    ref16 = plain.forward(model_4l, toks, "bfloat16", weights=w, cfg=c, rows=rows)
+    ref32 = plain.forward(model_4l, toks, "float32", weights=w, cfg=c, rows=rows)
+    scale = float(ref32.abs().max())
+    limit = max(2e-2, 1.5 * float((ref16 - ref32).abs().max()) / scale)
+    for got in outs:
+        assert float((got - ref16).abs().max()) / scale <= limit
+    assert float((outs[0] - outs[1]).abs().max()) / scale <= limit
+
+
 @pytest.mark.parametrize("batch", [12, 20])
 def test_decode_batches_beyond_eight_rows_at_the_0p6b_layer_sizes(model_4l, batch):
     """12 rows: the weight-streaming products in their 16-row form; 20 rows: the library's products; both through the
