@@ -7,6 +7,7 @@ tensor that is not on a CUDA device, or a missing compiler, raises.
 from __future__ import annotations
 
 import ctypes
+import math
 import os
 import sys
 from ctypes import c_int, c_int64, c_float, c_void_p
@@ -730,28 +731,57 @@ def gemm_tcgen05_supported(x_dtype: torch.dtype, weight: torch.Tensor, swiglu: b
             and (not swiglu or weight.shape[0] % 2 == 0))
 
 
-def gemm_bf16_tcgen05(out: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, swiglu: bool = False, tile_n: int = 0) -> torch.Tensor:
+def gemm_bf16_tcgen05(out: torch.Tensor, x: torch.Tensor, weight: torch.Tensor, swiglu: bool = False, tile_n: int = 0,
+                      resid: Optional[torch.Tensor] = None) -> torch.Tensor:
     """out = x @ weight^T on the tcgen05 tensor cores; with `swiglu`, weight holds gate rows over up rows and
-    out = silu(x @ gate^T) * (x @ up^T).  `tile_n` (128 or 256) picks the tile width; 0 chooses by the grid it gives."""
+    out = silu(x @ gate^T) * (x @ up^T); with `resid` (which may be `out`), out = round(x @ weight^T) + resid.
+    `tile_n` (128 or 256) picks the tile width; 0 chooses by the number of tiles it gives."""
     global _gemm
     if _gemm is None:
         lib = load_library("gemm_bf16")
         lib.cvb_gemm_bf16_tcgen05.restype = c_int
         _gemm = lib
-    _cuda(out, x, weight); _contig(out, x, weight)
+    _cuda(out, x, weight, resid); _contig(out, x, weight, resid)
     M, K = x.shape
     N = weight.shape[0]
     n_out = N // 2 if swiglu else N
     if x.dtype != torch.bfloat16 or weight.dtype != torch.bfloat16 or out.dtype != torch.bfloat16 or weight.shape[1] != K \
-            or out.shape != (M, n_out):
-        raise KernelError("gemm_bf16_tcgen05: x [M, K], weight [N, K], out [M, N] (or [M, N / 2] with swiglu), all bf16")
+            or out.shape != (M, n_out) or (swiglu and resid is not None) \
+            or (resid is not None and (resid.dtype != torch.bfloat16 or resid.shape != out.shape)):
+        raise KernelError("gemm_bf16_tcgen05: x [M, K], weight [N, K], out [M, N] (or [M, N / 2] with swiglu), resid like out, "
+                          "all bf16")
     if tile_n == 0:
         # tiles of 256 columns halve the traffic of A; take them when they still fill the SMs
         tiles_256 = ((M + 127) // 128) * ((N + 255) // 256)
         tile_n = 256 if tiles_256 >= 120 else 128
-    _check(_gemm.cvb_gemm_bf16_tcgen05(_ptr(out), _ptr(x), _ptr(weight), c_int(M), c_int(N), c_int(K), c_int(1 if swiglu else 0),
+    mode = 1 if swiglu else (2 if resid is not None else 0)
+    _check(_gemm.cvb_gemm_bf16_tcgen05(_ptr(out), _ptr(x), _ptr(weight), _ptr(resid), c_int(M), c_int(N), c_int(K), c_int(mode),
                                        c_int(tile_n), _ptr(error_flag(x.device)), _stream()), "gemm_bf16_tcgen05")
     return out
+
+
+GATED_MIN_ROWS = 1024
+GATED_SMS = 148
+
+
+def gated_product_fused(x_dtype: torch.dtype, weight: torch.Tensor, rows: int) -> bool:
+    """Whether the gate/up product of `rows` tokens goes through the tcgen05 kernel with the SwiGLU epilogue instead of the
+    library's product followed by the SwiGLU kernel.  The fused kernel wins where its tiles of 128 rows by 128 outputs
+    fill the SMs at least twice over with little left over in the last round (measured on a B200, against the library
+    product plus the SwiGLU kernel: 2,048 x 6,144 x 1,024: 25 us against 30; 4,096 rows: 43 against 57; 2,048 x 24,576 x
+    4,096: 281 against 302; 1,024 rows or fewer: the library wins by 2 to 35 %).  CVB_GATED=fused|library fixes it."""
+    forced = os.environ.get("CVB_GATED", "")
+    ok = (x_dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and weight.dim() == 2 and weight.shape[1] % 8 == 0
+          and weight.shape[0] % 16 == 0)
+    if not ok or forced == "library":
+        return False
+    if forced == "fused":
+        return True
+    if rows < GATED_MIN_ROWS:
+        return False
+    tiles = ((rows + 127) // 128) * ((weight.shape[0] // 2 + 127) // 128)
+    rounds = tiles / GATED_SMS
+    return rounds >= 2 and rounds / math.ceil(rounds) >= 0.8
 
 
 # ---- sampling ----------------------------------------------------------------------------------------------

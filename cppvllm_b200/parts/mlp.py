@@ -39,8 +39,12 @@ class SwiGLUMLP(FeedForward):
     def forward(self, x, ctx):
         T = x.shape[0]
         ws = self.rt.workspace
-        gu = self._project(x, self.w_gate_up, ws.rows("ffn_gate_up", T, 2 * self.intermediate_size, x.dtype), T)
-        act = ops.swiglu(ws.rows("ffn_act", T, self.intermediate_size, x.dtype), gu)
+        act = ws.rows("ffn_act", T, self.intermediate_size, x.dtype)
+        if not self.rt.plain_kernels and ops.gated_product_fused(x.dtype, self.w_gate_up, T):
+            ops.gemm_bf16_tcgen05(act, x, self.w_gate_up, swiglu=True)       # gate and up never travel through memory
+        else:
+            gu = self._project(x, self.w_gate_up, ws.rows("ffn_gate_up", T, 2 * self.intermediate_size, x.dtype), T)
+            ops.swiglu(act, gu)
         return self._down(act, T)
 
     def _down(self, act, T):

@@ -654,8 +654,11 @@ def test_split_k_weight_streaming_product(ops, M, N, K):
 # ---- tcgen05 matrix product -----------------------------------------------------------------------------------
 
 @pytest.mark.parametrize("M,N,K,tile_n", [(128, 128, 64, 128), (2048, 1024, 2048, 128), (300, 520, 200, 128), (1, 8, 8, 128),
-                                          (257, 4096, 1024, 256), (129, 264, 3072, 256)])
+                                          (257, 4096, 1024, 256), (129, 264, 3072, 256), (2048, 6144, 1024, 256),
+                                          (2100, 4104, 136, 128), (5000, 2560, 72, 256)])
 def test_tcgen05_gemm_against_float32(ops, M, N, K, tile_n):
+    """One tile, fewer tiles than SMs, and several tiles per block (the kernel is persistent: a block's tiles alternate
+    between two accumulators and share one ring of stages), with edges in every dimension."""
     g = torch.Generator().manual_seed(M + N + K)
     d = dev()
     x = torch.randn(M, K, generator=g).to(torch.bfloat16).to(d)
@@ -667,7 +670,27 @@ def test_tcgen05_gemm_against_float32(ops, M, N, K, tile_n):
     torch.testing.assert_close(out.float(), rnd(ref, torch.bfloat16), atol=2e-2, rtol=2e-2)
 
 
-@pytest.mark.parametrize("M,I,K", [(128, 128, 64), (2048, 3072, 1024), (77, 200, 136)])
+@pytest.mark.parametrize("M,N,K,tile_n", [(128, 128, 64, 128), (300, 520, 200, 128), (2048, 1024, 3072, 128), (2500, 4096, 264, 256)])
+def test_tcgen05_gemm_with_residual_epilogue(ops, M, N, K, tile_n):
+    """out = round(x W^T) + residual, in place over the residual: what the norm after an attention or feed-forward output
+    product would otherwise add."""
+    dt = torch.bfloat16
+    g = torch.Generator().manual_seed(M + N + K + 1)
+    d = dev()
+    x = torch.randn(M, K, generator=g).to(dt).to(d)
+    w = (torch.randn(N, K, generator=g) * 0.05).to(dt).to(d)
+    resid = torch.randn(M, N, generator=g).to(dt).to(d)
+    ref = rnd(rnd(x.float() @ w.float().t(), dt) + resid.float(), dt)
+    out = resid.clone()
+    ops.gemm_bf16_tcgen05(out, x, w, tile_n=tile_n, resid=out)
+    other = torch.full((M, N), float("nan"), dtype=dt, device=d)
+    ops.gemm_bf16_tcgen05(other, x, w, tile_n=tile_n, resid=resid)
+    ops.check_device_errors(d)
+    assert torch.equal(out, other)
+    torch.testing.assert_close(out.float(), ref, atol=3e-2, rtol=2e-2)
+
+
+@pytest.mark.parametrize("M,I,K", [(128, 128, 64), (2048, 3072, 1024), (77, 200, 136), (3000, 1544, 200)])
 def test_tcgen05_gemm_with_swiglu_epilogue(ops, M, I, K):
     dt = torch.bfloat16
     g = torch.Generator().manual_seed(M + I + K)
