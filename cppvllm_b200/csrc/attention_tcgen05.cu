@@ -102,13 +102,31 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, const Tc
     // (a piece beyond the number its query block is cut into) come last within their piece.
     const int block_id = gridDim.y - 1 - blockIdx.y, piece = blockIdx.z;
     {
-        int tile = block_id;
-        for (int s = 0; s < p.S; ++s) {
-            const int a = p.cu_seqlens[s], n = p.cu_seqlens[s + 1] - a;
-            if (skip_single && n == 1) continue;
-            const int tiles = (n + tok_per_block - 1) / tok_per_block;
-            if (tile < tiles) { seq = s; q0 = tile * tok_per_block; q_len = n; cu0 = a; break; }
-            tile -= tiles;
+        // Which request the query block belongs to: the lanes of a warp take a request each (every warp does the same),
+        // count its query blocks, add them up with shuffles and see whose range holds block_id: one trip to memory
+        // for up to 32 requests instead of one per request.
+        int before = 0;
+        for (int s0 = 0; s0 < p.S && seq < 0; s0 += 32) {
+            const int s = s0 + lane;
+            int a = 0, n = 0;
+            if (s < p.S) { a = p.cu_seqlens[s]; n = p.cu_seqlens[s + 1] - a; }
+            const int tiles = (s < p.S && !(skip_single && n == 1)) ? (n + tok_per_block - 1) / tok_per_block : 0;
+            int upto = tiles;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int v = __shfl_up_sync(0xffffffffu, upto, o);
+                if (lane >= o) upto += v;
+            }
+            const int first = before + upto - tiles;
+            const unsigned hit = __ballot_sync(0xffffffffu, tiles > 0 && block_id >= first && block_id < first + tiles);
+            if (hit) {
+                const int src = __ffs(hit) - 1;
+                seq = s0 + src;
+                q0 = (block_id - __shfl_sync(0xffffffffu, first, src)) * tok_per_block;
+                q_len = __shfl_sync(0xffffffffu, n, src);
+                cu0 = __shfl_sync(0xffffffffu, a, src);
+            }
+            before += __shfl_sync(0xffffffffu, upto, 31);
         }
     }
     if (seq < 0) return;
@@ -119,18 +137,51 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, const Tc
     // r / g for r < 256 without a division (g <= 16): exact with this multiplier
     const uint32_t g_mul = ((1u << 20) + g - 1) / g;
     auto row_tok = [&](int r) { return static_cast<int>((static_cast<uint32_t>(r) * g_mul) >> 20); };
+    // The positions of each query tile's first and last token are asked for here and used further down: they are a step
+    // input, in place before the first kernel of the step started, so they may be read ahead of griddepcontrol.wait.
+    int first_pos[2] = {0, 0}, last_pos[2] = {0, 0};
+#pragma unroll
+    for (int x = 0; x < 2; ++x) {
+        if (n_tok[x] > 0) {
+            first_pos[x] = p.positions[cu0 + q0 + x * tok_per_tile];
+            last_pos[x] = p.positions[cu0 + q0 + x * tok_per_tile + n_tok[x] - 1];
+        }
+    }
+    // query rows: row r of tile x = (token x * tok_per_tile + r / g, head kvh * g + r % g); rows past the portion are zero.
+    // Warp 0 takes no part: it starts fetching keys as soon as the barriers exist.  Warp 1 asks for the tensor memory first.
+    auto start_queries = [&]() {
+        if (warp == 0) return;
+        if (warp == 1) {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(tmem_slot)), "r"(512));
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
+        }
+        const __nv_bfloat16* q_base = p.q + (static_cast<int64_t>(cu0 + q0) * p.H + kvh * g) * HD;
+        for (int i = threadIdx.x - 32; i < 2 * kTM * CPR; i += kTcThreads - 32) {
+            const int row = i / CPR, c = i % CPR;
+            const int x = row >> 7, r = row & 127;
+            const int t = row_tok(r), h = r - t * g;
+            const bool valid = t < n_tok[x];
+            const __nv_bfloat16* src = valid ? q_base + (static_cast<int64_t>(x * tok_per_tile + t) * p.H + h) * HD + c * 8 : p.q;
+            cp_async16(reinterpret_cast<__nv_bfloat16*>(sQ + x * L::kTile) + tile_off(r, c), src, valid);
+        }
+        asm volatile("cp.async.commit_group;\n" ::: "memory");
+    };
+    // Without pieces every block has work: the query rows are on their way while the positions arrive.  With pieces a
+    // block first has to know from the positions whether it has any (it asks for nothing it would have to give back).
+    if (p.pieces == 1) {
+        pdl_wait();
+        start_queries();
+    }
     // per query tile: the range of key tiles it needs, t_lo <= j < t_hi (none if t_lo >= t_hi)
     int t_lo[2], t_hi[2], key_hi = 0, key_lo = 0x3fffffff;
 #pragma unroll
     for (int x = 0; x < 2; ++x) {
         if (n_tok[x] > 0) {
-            const int first = p.positions[cu0 + q0 + x * tok_per_tile];
-            const int last = p.positions[cu0 + q0 + x * tok_per_tile + n_tok[x] - 1];
-            const int first_key = p.window > 0 ? max(0, first - p.window + 1) : 0;   // the oldest key any of its tokens sees
+            const int first_key = p.window > 0 ? max(0, first_pos[x] - p.window + 1) : 0;   // the oldest key any of its tokens sees
             t_lo[x] = first_key / kTN;
-            t_hi[x] = last / kTN + 1;
+            t_hi[x] = last_pos[x] / kTN + 1;
             key_lo = min(key_lo, first_key);
-            key_hi = last;                                          // the block's last token
+            key_hi = last_pos[x];                                   // the block's last token
         } else {
             t_lo[x] = 0x3fffffff;
             t_hi[x] = 0;
@@ -160,25 +211,9 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, const Tc
     }
     const int part_slot = (block_id * p.KV + kvh) * p.pieces + piece;
     if (p.pieces > 1 && piece == 0 && threadIdx.x == 0) p.piece_counts[block_id * p.KV + kvh] = n_pieces;
-    // Everything read so far is a step input, in place before the first kernel of the step started.
-    pdl_wait();
-    // query rows: row r of tile x = (token x * tok_per_tile + r / g, head kvh * g + r % g); rows past the portion are zero.
-    // Warp 0 takes no part: it starts fetching keys as soon as the barriers exist.  Warp 1 asks for the tensor memory first.
-    if (warp > 0) {
-        if (warp == 1) {
-            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;\n" ::"r"(smem_u32(tmem_slot)), "r"(512));
-            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;\n" ::);
-        }
-        const __nv_bfloat16* q_base = p.q + (static_cast<int64_t>(cu0 + q0) * p.H + kvh * g) * HD;
-        for (int i = threadIdx.x - 32; i < 2 * kTM * CPR; i += kTcThreads - 32) {
-            const int row = i / CPR, c = i % CPR;
-            const int x = row >> 7, r = row & 127;
-            const int t = row_tok(r), h = r - t * g;
-            const bool valid = t < n_tok[x];
-            const __nv_bfloat16* src = valid ? q_base + (static_cast<int64_t>(x * tok_per_tile + t) * p.H + h) * HD + c * 8 : p.q;
-            cp_async16(reinterpret_cast<__nv_bfloat16*>(sQ + x * L::kTile) + tile_off(r, c), src, valid);
-        }
-        asm volatile("cp.async.commit_group;\n" ::: "memory");
+    if (p.pieces > 1) {
+        pdl_wait();
+        start_queries();
     }
     // Loads are clamped to [key_lo, key_hi], the keys that the block's tokens see: a page below the window may have been
     // given back by its request already (its table entry is -1) and is never looked up; rounding a key down to its box
@@ -444,16 +479,34 @@ attn_prefill_merge_kernel(const TcAttnParams p, const int skip_single, const int
     const int g = p.H / p.KV;
     const int tok_per_tile = kTM / g, tok_per_block = 2 * tok_per_tile;
     const int block_id = blockIdx.x / p.KV, kvh = blockIdx.x - block_id * p.KV;
-    const int x = blockIdx.y, c0 = blockIdx.z * 32, r = threadIdx.x;
+    const int x = blockIdx.y, c0 = blockIdx.z * 32, r = threadIdx.x, lane = threadIdx.x & 31;
     int seq = -1, q0 = 0, q_len = 0, cu0 = 0;
     {
-        int tile = block_id;
-        for (int s = 0; s < p.S; ++s) {
-            const int a = p.cu_seqlens[s], n = p.cu_seqlens[s + 1] - a;
-            if (skip_single && n == 1) continue;
-            const int tiles = (n + tok_per_block - 1) / tok_per_block;
-            if (tile < tiles) { seq = s; q0 = tile * tok_per_block; q_len = n; cu0 = a; break; }
-            tile -= tiles;
+        // Which request the query block belongs to: the lanes of a warp take a request each (every warp does the same),
+        // count its query blocks, add them up with shuffles and see whose range holds block_id: one trip to memory
+        // for up to 32 requests instead of one per request.
+        int before = 0;
+        for (int s0 = 0; s0 < p.S && seq < 0; s0 += 32) {
+            const int s = s0 + lane;
+            int a = 0, n = 0;
+            if (s < p.S) { a = p.cu_seqlens[s]; n = p.cu_seqlens[s + 1] - a; }
+            const int tiles = (s < p.S && !(skip_single && n == 1)) ? (n + tok_per_block - 1) / tok_per_block : 0;
+            int upto = tiles;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int v = __shfl_up_sync(0xffffffffu, upto, o);
+                if (lane >= o) upto += v;
+            }
+            const int first = before + upto - tiles;
+            const unsigned hit = __ballot_sync(0xffffffffu, tiles > 0 && block_id >= first && block_id < first + tiles);
+            if (hit) {
+                const int src = __ffs(hit) - 1;
+                seq = s0 + src;
+                q0 = (block_id - __shfl_sync(0xffffffffu, first, src)) * tok_per_block;
+                q_len = __shfl_sync(0xffffffffu, n, src);
+                cu0 = __shfl_sync(0xffffffffu, a, src);
+            }
+            before += __shfl_sync(0xffffffffu, upto, 31);
         }
     }
     if (seq < 0) return;

@@ -59,7 +59,7 @@ __device__ __forceinline__ unsigned long long best_of_warp(unsigned long long c)
 struct RowDraw {
     const float* logits;
     float inv_temp;
-    bool greedy;
+    bool greedy, vec4;
     uint32_t key_lo, key_hi, out_pos;
 };
 __device__ __forceinline__ RowDraw row_draw(int r, const float* logits, const int* rows, const float* temps,
@@ -68,7 +68,8 @@ __device__ __forceinline__ RowDraw row_draw(int r, const float* logits, const in
     src = max(0, min(src, n_logit_rows - 1));
     const float temp = temps[r];
     const uint64_t seed = seeds[r];
-    return RowDraw{logits + static_cast<int64_t>(src) * V, 1.0f / fmaxf(temp, 1e-5f), temp <= 0.f,
+    const float* row = logits + static_cast<int64_t>(src) * V;
+    return RowDraw{row, 1.0f / fmaxf(temp, 1e-5f), temp <= 0.f, (reinterpret_cast<uintptr_t>(row) & 15) == 0,
                    static_cast<uint32_t>(seed), static_cast<uint32_t>(seed >> 32), static_cast<uint32_t>(out_positions[r])};
 }
 
@@ -83,8 +84,17 @@ __device__ __forceinline__ unsigned long long best_of_groups(const RowDraw& d, i
             bits[0] = p.x; bits[1] = p.y; bits[2] = p.z; bits[3] = p.w;
         }
         const int first = group << 2, n = min(4, V - first);
-        for (int j = 0; j < n; ++j) {
-            float score = d.logits[first + j];
+        float v[4] = {0.f, 0.f, 0.f, 0.f};
+        if (d.vec4 && n == 4) {                               // the row starts on a 16-byte boundary: one load a group
+            const float4 q = __ldcs(reinterpret_cast<const float4*>(d.logits + first));
+            v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w;
+        } else {
+            for (int j = 0; j < n; ++j) v[j] = d.logits[first + j];
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            if (j >= n) break;
+            float score = v[j];
             if (!d.greedy) score = score * d.inv_temp - logf(fmaxf(-logf(uniform01(bits[j])), 1e-10f));   // Gumbel-max
             const unsigned long long c = candidate(score, first + j);
             best = c > best ? c : best;
