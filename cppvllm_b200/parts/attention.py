@@ -183,12 +183,12 @@ class PagedAttention(Mixer):
                 tiles = ops.prefill_tiles_tcgen05(q_lens, H, KV)
                 if tiles:
                     pieces = ops.prefill_pieces_tcgen05(tiles, KV, ctx.max_kv_len)
-                    scratch = counters = None
-                    if pieces > 1:
-                        # a grid that is cut into pieces has at most one block per SM after the cut
-                        ws = self.rt.workspace
-                        scratch = ws.flat("attn_prefill_pieces", ops.PREFILL_SMS * 2 * (hd + 2) * 128, torch.float32)
-                        counters = ws.flat("attn_prefill_piece_counts", ops.PREFILL_SMS, torch.int32)
+                    # Scratch for the pieces of long query blocks: a grid that is cut has at most one block per SM after
+                    # the cut.  Made at the first prompt portion, whether that one is cut or not, so that a later
+                    # capture of a graph finds it.
+                    ws = self.rt.workspace
+                    scratch = ws.flat("attn_prefill_pieces", ops.PREFILL_SMS * 2 * (hd + 2) * 128, torch.float32)
+                    counters = ws.flat("attn_prefill_piece_counts", ops.PREFILL_SMS, torch.int32)
                     ops.attn_prefill_tcgen05(att, q, cache.pages, g.block_tables, ctx.cu_seqlens, ctx.positions, S, tiles,
                                              H, KV, hd, g.page_size, self.scale, window=self.window, skip_single=True,
                                              pieces=pieces, scratch=scratch, piece_counts=counters)

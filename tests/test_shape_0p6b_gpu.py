@@ -137,7 +137,11 @@ def test_four_cuttings_at_the_0p6b_layer_sizes(model_4l, dtype):
     r.cache.check_invariants()
 
 
-def test_a_late_portion_attended_in_pieces_matches_the_whole_prompt(model_4l):
+def scale_of(t):
+    return max(1.0, float(t.abs().max()))
+
+
+def test_a_late_portion_attended_in_pieces_matches_the_whole_prompt(model_4l, monkeypatch):
     """A portion of a few hundred tokens behind two thousand cached ones is few query blocks with many key tiles each: the
     tensor-core attention shares each block's tiles out among several blocks and adds their shares up.  The same prompt
     in one step is many blocks and no pieces.  Both against the plain implementation, and against each other."""
@@ -145,9 +149,16 @@ def test_a_late_portion_attended_in_pieces_matches_the_whole_prompt(model_4l):
     from cppvllm_b200.engine.runner import ModelRunner, StepEntry
     toks = tiny_models.random_tokens(10000, 2600, 77)
     rows = [2048, 2049, 2175, 2176, 2300, 2598, 2599]
-    outs, used = [], []
+    outs, used, seen = [], [], []
+    real = ops.attn_prefill_tcgen05
+
+    def recording(*a, **kw):
+        seen.append(kw.get("pieces", 1))
+        return real(*a, **kw)
+    monkeypatch.setattr(ops, "attn_prefill_tcgen05", recording)
     for cuts in ((2600,), (2048, 552)):
-        r = ModelRunner(model_4l, dtype=torch.bfloat16, page_size=32, num_pages=96, max_step_tokens=4096, max_seqs=4,
+        seen.clear()
+        r = ModelRunner(model_4l, dtype=torch.bfloat16, page_size=32, num_pages=96, max_step_tokens=4096, max_seqs=8,
                         max_model_len=4096)
         r.cache.admit("a")
         r.cache.reserve("a", len(toks))
@@ -159,8 +170,22 @@ def test_a_late_portion_attended_in_pieces_matches_the_whole_prompt(model_4l):
             pos += n
         r.check_errors()
         outs.append(torch.stack([got[p_] for p_ in rows]))
-        used.append(any(k.startswith("attn_prefill_pieces") for k in r.workspace._buffers))
-    assert used == [False, True], "the second cutting's last portion should have been attended in pieces"
+        used.append(max(seen))
+    assert used[0] == 1 and used[1] >= 2, "the second cutting's last portion should have been attended in pieces"
+    # the same cutting again, for other requests on the same runner: from the second time on a shape replays a captured
+    # graph, in which the pieces are allowed for the longest context the model takes
+    r.cache.release("a")
+    before = r.stats["graph_steps"]
+    for rid in ("b", "c"):
+        r.cache.admit(rid)
+        r.cache.reserve(rid, len(toks))
+        r.step([StepEntry(rid, toks[:2048], 0, [0])])
+        want = [p_ - 2048 for p_ in rows]
+        again = r.step([StepEntry(rid, toks[2048:], 2048, want)]).float().cpu()
+        r.check_errors()
+        assert float((again - outs[1]).abs().max()) / scale_of(outs[1]) < 1e-3
+        r.cache.release(rid)
+    assert r.stats["graph_steps"] >= before + 2
     assert ops.prefill_pieces_tcgen05(ops.prefill_tiles_tcgen05([552], 16, 8), 8) >= 2
     c, w = plain.read_config(model_4l), plain.read_weights(model_4l)
     ref16 = plain.forward(model_4l, toks, "bfloat16", weights=w, cfg=c, rows=rows)
