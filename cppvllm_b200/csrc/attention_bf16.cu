@@ -161,6 +161,20 @@ __device__ __forceinline__ void pv_product(float (&o)[HD / 8][4], const float (&
     }
 }
 
+// Rows first_row .. last_row of a value tile in shared memory become zero (the lanes of one warp share the work).  Keys
+// behind a request's last one lie in the same page of the cache as its last keys and come along with them; their
+// probability is 0, but what a former holder of the page left there (an Inf, a NaN) times 0 would be NaN, so they must
+// not meet the product as they are.  A warp clears the rows that it reads itself; warps that clear the same rows write
+// the same zeros.
+template <int HD>
+__device__ __forceinline__ void clear_value_rows(__nv_bfloat16* sV, int first_row, int last_row, int lane) {
+    constexpr int CPR = HD / 8;
+    for (int i = lane; i < (last_row - first_row + 1) * CPR; i += 32)
+        *reinterpret_cast<uint4*>(sV + kv_off(first_row + i / CPR, i % CPR)) = make_uint4(0u, 0u, 0u, 0u);
+    fence_async_smem();                                  // the next filling of the stage comes through the async proxy
+    __syncwarp();
+}
+
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -272,6 +286,7 @@ attn_prefill_bf16_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnP
     const int pos_last = p.positions[cu0 + q0 + n_tok - 1];
     const int key_lo = p.window > 0 ? max(0, pos_first - p.window + 1) : 0;
     const int key_hi = pos_last;
+    const int seq_last = p.positions[cu0 + q_len - 1];   // the request's last key in the cache after this step
     const int tile_begin = key_lo / kBN, n_tiles = key_hi / kBN - tile_begin + 1;
 
     uint64_t* full = sm.bars;
@@ -334,7 +349,8 @@ attn_prefill_bf16_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnP
         mbar_wait(full + st, (it / kPreStages) & 1, p.err);
         if (warp_has_rows && key0 <= warp_last_pos) {
             const __nv_bfloat16* sK = sm.stages + st * Plan::kStageElems;
-            const __nv_bfloat16* sV = sK + kBN * HD;
+            __nv_bfloat16* sV = sm.stages + st * Plan::kStageElems + kBN * HD;
+            if (key0 + kBN - 1 > seq_last) clear_value_rows<HD>(sV, max(0, seq_last + 1 - key0), kBN - 1, lane);
             float s[8][4];
             qk_product<HD, 8>(s, qf, sK, 0, lane);
             if (key0 + kBN - 1 <= warp_first_pos && key0 >= warp_max_lo)
@@ -549,7 +565,8 @@ attn_decode_bf16_kernel(const __grid_constant__ CUtensorMap kv_map, const AttnPa
                 }
                 if (key0 <= key_hi && key0 + 15 >= key_lo) {
                     const __nv_bfloat16* sK = sm.stages + st * Plan::kStageElems;
-                    const __nv_bfloat16* sV = sK + kBN * HD;
+                    __nv_bfloat16* sV = sm.stages + st * Plan::kStageElems + kBN * HD;
+                    if (key0 + 15 > key_hi) clear_value_rows<HD>(sV, key_hi + 1 - (tile_begin + it) * kBN, warp * 16 + 15, lane);
                     float s[2][4];
                     qk_product<HD, 2>(s, qf, sK, warp * 16, lane);
                     if (key0 >= key_lo && key0 + 15 <= key_hi)

@@ -140,6 +140,7 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, const Tc
     // The positions of each query tile's first and last token are asked for here and used further down: they are a step
     // input, in place before the first kernel of the step started, so they may be read ahead of griddepcontrol.wait.
     int first_pos[2] = {0, 0}, last_pos[2] = {0, 0};
+    const int seq_last = p.positions[cu0 + q_len - 1];              // the request's last key in the cache after this step
 #pragma unroll
     for (int x = 0; x < 2; ++x) {
         if (n_tok[x] > 0) {
@@ -392,6 +393,20 @@ attn_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap kv_map, const Tc
                     tm_store32(tS[x] + lane_base + h * 32, packed);     // P over the first 64 columns of S
                 }
                 l += (sum2[0].x + sum2[0].y) + (sum2[1].x + sum2[1].y);
+                if (key0 + kTN - 1 > seq_last) {
+                    // Keys behind the request's last one came along with its last page.  Their probability is 0, but
+                    // what a former holder of the page left there (an Inf, a NaN) times 0 would be NaN: thread r clears
+                    // row r of the value tile, which load j - j_lo + 1 brought, before the product P V may start.  (The
+                    // threads of the other query tile may do the same; they write the same zeros.)
+                    const int load = j - j_lo + 1, vst = load % kStages;
+                    mbar_wait(kv_full + vst, (load / kStages) & 1, p.err);
+                    if (key0 + r > seq_last) {
+                        __nv_bfloat16* v_rows = reinterpret_cast<__nv_bfloat16*>(sKV + (2 * vst + 1) * L::kTile);
+#pragma unroll
+                        for (int c = 0; c < CPR; ++c) *reinterpret_cast<uint4*>(v_rows + tile_off(r, c)) = make_uint4(0u, 0u, 0u, 0u);
+                    }
+                    fence_async_smem();                                       // the tensor core reads through the async proxy
+                }
                 tm_wait_st();
                 tc_before();
                 mbar_arrive(p_ready + x);

@@ -361,6 +361,11 @@ def test_tensor_core_attention_mixed_portions_and_single_tokens(ops, H, KV, hd, 
     seqs_v = [torch.randn(c + n, KV, hd, generator=g).to(dt) for c, n in reqs]
     total_pages = sum((c + n + page - 1) // page for c, n in reqs) + 3
     cache, tables = build_paged(seqs_k, seqs_v, page, total_pages, KV, hd, dt, g)
+    # what a former holder left behind a request's last key, in the same page: it has probability 0, and 0 times this
+    # must not reach the output
+    for s, (c, n) in enumerate(reqs):
+        if (c + n) % page:
+            cache[tables[s, (c + n - 1) // page], :, :, (c + n) % page:] = float("nan") if s % 2 else float("inf")
     if window > 0:
         # as in the engine: a request has given back the pages that lie wholly below its window (table entry -1), and
         # someone else may have left anything in them (here NaN): no kernel may look them up or read them
@@ -433,6 +438,9 @@ def test_tcgen05_prefill_shares_the_keys_of_long_query_blocks_among_blocks(ops, 
     q[cu[1] + 200:cu[1] + 700] += (unit * 12).to(dt)      # ... draws most of the weight of its later tokens
     total_pages = sum((c + n + page - 1) // page for c, n in reqs) + 3
     cache, tables = build_paged(seqs_k, seqs_v, page, total_pages, KV, hd, dt, g)
+    for s, (c, n) in enumerate(reqs):                    # behind a request's last key: nothing that may reach the output
+        if (c + n) % page:
+            cache[tables[s, (c + n - 1) // page], :, :, (c + n) % page:] = float("nan")
     if window > 0:
         for s, (c, n) in enumerate(reqs):
             for slot in range(max(0, c - window + 1) // page):
