@@ -473,19 +473,22 @@ __device__ __forceinline__ void bulk_row_to_smem(void* smem, const void* gmem, u
 // What runs after the wait is the chain that every decode step passes through once per product, so it is kept short:
 // everything that can be worked out before the wait (addresses, which rows and outputs a thread owns, quotients) is,
 // and no thread divides by a run-time number behind it.
-template <bool NORM, bool SWIGLU>
-__global__ void __launch_bounds__(kStThreads, 2)
+// NB: groups of eight activation rows (1 or 2).  With two groups a block's shared memory may pass half an SM's, so
+// one block runs per SM and a thread may hold twice the accumulators.
+template <bool NORM, bool SWIGLU, int NB>
+__global__ void __launch_bounds__(kStThreads, NB == 1 ? 2 : 1)
 gemv_stream_kernel(const StreamParams p) {
+    constexpr int kRowsX = kBatch * NB;                                            // activation rows staged
     extern __shared__ __align__(16) unsigned char smem_raw[];
     const int K = p.K, chunks = K >> 3, stride = K + kXPad;
     const int n_out = SWIGLU ? p.N / 2 : p.N;
     const int o0 = blockIdx.x * p.opb, n_mine = min(p.opb, n_out - o0);           // this block's outputs
     const int w_rows = SWIGLU ? 2 * n_mine : n_mine;
     uint64_t* bar = reinterpret_cast<uint64_t*>(smem_raw);
-    float* row_ss = reinterpret_cast<float*>(smem_raw + 16);                       // [8 rows][16 parts]
-    __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(smem_raw + 16 + kBatch * kStWarps * sizeof(float));   // [8][K + pad]
-    __nv_bfloat16* ws = xs + kBatch * stride;                                      // [rows of W][K + pad]
-    float* red = reinterpret_cast<float*>(ws + static_cast<size_t>(SWIGLU ? 2 : 1) * p.opb * stride);   // [item][16][8]
+    float* row_ss = reinterpret_cast<float*>(smem_raw + 16);                       // [rows][16 parts]
+    __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(smem_raw + 16 + kRowsX * kStWarps * sizeof(float));   // [rows][K + pad]
+    __nv_bfloat16* ws = xs + kRowsX * stride;                                      // [rows of W][K + pad]
+    float* red = reinterpret_cast<float*>(ws + static_cast<size_t>(SWIGLU ? 2 : 1) * p.opb * stride);   // [item][16][rows]
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const uint4 zero = make_uint4(0, 0, 0, 0);
 
@@ -531,6 +534,7 @@ gemv_stream_kernel(const StreamParams p) {
     const int items = p.n_tiles * p.warps_k;
     // B operand: column r of a product is activation row r; columns without a token repeat the last row and are not stored
     const uint4* x_row = reinterpret_cast<const uint4*>(xs + min(r, p.M - 1) * stride);
+    const uint4* x_row_b = reinterpret_cast<const uint4*>(xs + min(r + kBatch, p.M - 1) * stride);   // second group (NB == 2)
     auto rows_of = [&](int tile, const uint4*& w_hi, const uint4*& w_lo) {
         int row_hi, row_lo;
         if constexpr (SWIGLU) {
@@ -659,9 +663,12 @@ gemv_stream_kernel(const StreamParams p) {
             wk = item - tile * p.warps_k;
             rows_of(tile, w_hi, w_lo);
         }
-        float acc[4][4];
+        float acc[4][4], acc_b[4][4];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) { acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f; }
+        for (int i = 0; i < 4; ++i) {
+            acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+            acc_b[i][0] = acc_b[i][1] = acc_b[i][2] = acc_b[i][3] = 0.f;
+        }
         const int j_end = min(slabs, (wk + 1) * per_warp);
         int c = wk * per_warp * 4 + q;
         for (int j0 = wk * per_warp; j0 < j_end; j0 += 2, c += 8) {
@@ -672,13 +679,26 @@ gemv_stream_kernel(const StreamParams p) {
             mma_16816(acc[1], wh0.z, wl0.z, wh0.w, wl0.w, xv0.z, xv0.w);
             mma_16816(acc[2], wh1.x, wl1.x, wh1.y, wl1.y, xv1.x, xv1.y);
             mma_16816(acc[3], wh1.z, wl1.z, wh1.w, wl1.w, xv1.z, xv1.w);
+            if constexpr (NB == 2) {                                 // the same weight fragments against rows 8 .. 15
+                const uint4 xb0 = ok0 ? x_row_b[c] : zero, xb1 = ok1 ? x_row_b[c + 4] : zero;
+                mma_16816(acc_b[0], wh0.x, wl0.x, wh0.y, wl0.y, xb0.x, xb0.y);
+                mma_16816(acc_b[1], wh0.z, wl0.z, wh0.w, wl0.w, xb0.z, xb0.w);
+                mma_16816(acc_b[2], wh1.x, wl1.x, wh1.y, wl1.y, xb1.x, xb1.y);
+                mma_16816(acc_b[3], wh1.z, wl1.z, wh1.w, wl1.w, xb1.z, xb1.w);
+            }
         }
         // acc[.][0], [1]: (row r, batch 2q, 2q + 1); acc[.][2], [3]: (row r + 8, same)
-        float* mine = red + item * 128;
-        mine[r * 8 + 2 * q] = (acc[0][0] + acc[1][0]) + (acc[2][0] + acc[3][0]);
-        mine[r * 8 + 2 * q + 1] = (acc[0][1] + acc[1][1]) + (acc[2][1] + acc[3][1]);
-        mine[(r + 8) * 8 + 2 * q] = (acc[0][2] + acc[1][2]) + (acc[2][2] + acc[3][2]);
-        mine[(r + 8) * 8 + 2 * q + 1] = (acc[0][3] + acc[1][3]) + (acc[2][3] + acc[3][3]);
+        float* mine = red + item * (128 * NB);
+        mine[r * kRowsX + 2 * q] = (acc[0][0] + acc[1][0]) + (acc[2][0] + acc[3][0]);
+        mine[r * kRowsX + 2 * q + 1] = (acc[0][1] + acc[1][1]) + (acc[2][1] + acc[3][1]);
+        mine[(r + 8) * kRowsX + 2 * q] = (acc[0][2] + acc[1][2]) + (acc[2][2] + acc[3][2]);
+        mine[(r + 8) * kRowsX + 2 * q + 1] = (acc[0][3] + acc[1][3]) + (acc[2][3] + acc[3][3]);
+        if constexpr (NB == 2) {
+            mine[r * kRowsX + 8 + 2 * q] = (acc_b[0][0] + acc_b[1][0]) + (acc_b[2][0] + acc_b[3][0]);
+            mine[r * kRowsX + 8 + 2 * q + 1] = (acc_b[0][1] + acc_b[1][1]) + (acc_b[2][1] + acc_b[3][1]);
+            mine[(r + 8) * kRowsX + 8 + 2 * q] = (acc_b[0][2] + acc_b[1][2]) + (acc_b[2][2] + acc_b[3][2]);
+            mine[(r + 8) * kRowsX + 8 + 2 * q + 1] = (acc_b[0][3] + acc_b[1][3]) + (acc_b[2][3] + acc_b[3][3]);
+        }
     }
     __syncthreads();
     if (p.late_trigger) pdl_trigger();
@@ -687,11 +707,11 @@ gemv_stream_kernel(const StreamParams p) {
     for (int i = threadIdx.x; i < p.M * n_mine; i += kStThreads) {
         if (i != static_cast<int>(threadIdx.x)) { e_m = i / n_mine; e_o = i - e_m * n_mine; }
         const int t = e_o / OUT_PER_TILE, row = e_o - t * OUT_PER_TILE;
-        const float* part = red + t * p.warps_k * 128 + row * 8 + e_m;
+        const float* part = red + t * p.warps_k * (128 * NB) + row * kRowsX + e_m;
         float s0 = 0.f, s1 = 0.f;
         for (int w = 0; w < p.warps_k; ++w) {
-            s0 += part[w * 128];
-            if constexpr (SWIGLU) s1 += part[w * 128 + 64];
+            s0 += part[w * (128 * NB)];
+            if constexpr (SWIGLU) s1 += part[w * (128 * NB) + 64 * NB];
         }
         float y = s0;
         if constexpr (SWIGLU) {
@@ -710,7 +730,7 @@ gemv_stream_kernel(const StreamParams p) {
 // The plan of a launch: outputs per block, tiles, warps per tile and shared memory; false if the shape is not for this
 // kernel (the block's rows do not fit into about half an SM's shared memory).
 struct StreamPlan { int blocks, opb, n_tiles, warps_k; size_t smem; };
-static bool stream_plan(int N, int K, bool swiglu, StreamPlan* plan) {
+static bool stream_plan(int N, int K, bool swiglu, int nb, StreamPlan* plan) {
     static int sms = 0;
     if (sms == 0) {
         int dev = 0;
@@ -726,9 +746,12 @@ static bool stream_plan(int N, int K, bool swiglu, StreamPlan* plan) {
     const int slabs = (K + 31) / 32;
     const int warps_k = max(1, min(slabs, kStWarps / n_tiles));
     const size_t row = static_cast<size_t>(K + kXPad) * sizeof(__nv_bfloat16);
-    const size_t smem = 16 + kBatch * kStWarps * sizeof(float) + row * (kBatch + static_cast<size_t>(swiglu ? 2 : 1) * opb) +
-                        static_cast<size_t>(n_tiles) * warps_k * 128 * sizeof(float);
-    if (smem > 113 * 1024 || static_cast<size_t>(swiglu ? 2 : 1) * opb * K * 2 >= (1u << 20)) return false;
+    const size_t smem = 16 + static_cast<size_t>(kBatch) * nb * kStWarps * sizeof(float) +
+                        row * (static_cast<size_t>(kBatch) * nb + static_cast<size_t>(swiglu ? 2 : 1) * opb) +
+                        static_cast<size_t>(n_tiles) * warps_k * 128 * nb * sizeof(float);
+    // up to eight rows: half an SM's shared memory, so that a block of the next kernel fits beside this one; nine to
+    // sixteen rows: whatever an SM has
+    if (smem > (nb == 1 ? 113u : 226u) * 1024 || static_cast<size_t>(swiglu ? 2 : 1) * opb * K * 2 >= (1u << 20)) return false;
     plan->blocks = (n_out + opb - 1) / opb; plan->opb = opb; plan->n_tiles = n_tiles; plan->warps_k = warps_k; plan->smem = smem;
     return true;
 }
@@ -879,13 +902,14 @@ gemv_ring_kernel(const RingParams p) {
 
 using namespace cvb;
 
-// 1 if cvb_gemv_stream_bf16 takes a weight of N rows and K columns in this mode (0 plain, 1 norm, 2 norm + SwiGLU).
-extern "C" int cvb_gemv_stream_supported(int N, int K, int mode) {
+// 1 if cvb_gemv_stream_bf16 takes a weight of N rows and K columns in this mode (0 plain, 1 norm, 2 norm + SwiGLU)
+// for `rows` activation rows.
+extern "C" int cvb_gemv_stream_supported(int N, int K, int mode, int rows) {
     StreamPlan plan;
-    return stream_plan(N, K, mode == 2, &plan) ? 1 : 0;
+    return rows > 0 && rows <= 2 * kBatch && stream_plan(N, K, mode == 2, rows > kBatch ? 2 : 1, &plan) ? 1 : 0;
 }
 
-// out[:M] = x[:M] W^T for up to 8 rows and a weight whose per-SM share fits into shared memory; modes as cvb_gemv_bf16.
+// out[:M] = x[:M] W^T for up to 16 rows and a weight whose per-SM share fits into shared memory; modes as cvb_gemv_bf16.
 // `add_to` (plain mode; or null): out = rnd(add_to + rnd(x W^T)), the residual sum folded into the store (add_to may be out).
 // `prefetch` (or null) names bytes that a later kernel will stream; this one asks them into the L2.  With `late_trigger`
 // the kernel behind this one starts when this one's products are done rather than as early as possible.  The launch
@@ -894,8 +918,9 @@ extern "C" int cvb_gemv_stream_bf16(void* out, const void* x, const void* delta,
                                     const void* W, int M, int N, int K, float eps, int mode, const void* add_to, const void* prefetch,
                                     long long prefetch_bytes, int late_trigger, int pdl, int* err, cudaStream_t stream) {
     if (M == 0) return CVB_OK;
-    if (M < 0 || M > kBatch || N <= 0 || K <= 0) return CVB_E_SIZE;
+    if (M < 0 || M > 2 * kBatch || N <= 0 || K <= 0) return CVB_E_SIZE;
     if (K % 8) return CVB_E_ALIGN;
+    const int nb = M > kBatch ? 2 : 1;
     auto al = [](const void* q) { return q == nullptr || (reinterpret_cast<uintptr_t>(q) & 15) == 0; };
     if (!al(out) || !al(x) || !al(delta) || !al(resid_out) || !al(W) || !al(norm_w) || !al(prefetch)) return CVB_E_ALIGN;
     if (mode != 0 && norm_w == nullptr) return CVB_E_SHAPE;
@@ -903,7 +928,7 @@ extern "C" int cvb_gemv_stream_bf16(void* out, const void* x, const void* delta,
     if (delta != nullptr && (resid_out == nullptr || resid_out == x)) return CVB_E_SHAPE;
     if (add_to != nullptr && (mode != 0 || (reinterpret_cast<uintptr_t>(add_to) & 1))) return CVB_E_SHAPE;
     StreamPlan plan;
-    if (!stream_plan(N, K, mode == 2, &plan)) return CVB_E_UNSUPPORTED;
+    if (!stream_plan(N, K, mode == 2, nb, &plan)) return CVB_E_UNSUPPORTED;
     StreamParams p{};
     p.out = (__nv_bfloat16*)out; p.x = (const __nv_bfloat16*)x; p.delta = (const __nv_bfloat16*)delta;
     p.resid_out = (__nv_bfloat16*)resid_out; p.norm_w = norm_w; p.W = (const __nv_bfloat16*)W;
@@ -913,24 +938,30 @@ extern "C" int cvb_gemv_stream_bf16(void* out, const void* x, const void* delta,
     p.late_trigger = late_trigger ? 1 : 0; p.eps = eps;
     // warps that share an activation row in the norm prologue: 16 / rows, but no more than give every lane a chunk (warps
     // without work go straight to the barrier and leave the issue slots to those that have some)
-    p.warps_per_row = M <= 1 ? 16 : (M <= 2 ? 8 : (M <= 4 ? 4 : 2));
+    p.warps_per_row = M <= 1 ? 16 : (M <= 2 ? 8 : (M <= 4 ? 4 : (M <= 8 ? 2 : 1)));
     while (p.warps_per_row > 1 && (K / 8 + 31) / 32 < p.warps_per_row) p.warps_per_row >>= 1;
-    static bool set[3] = {false, false, false};                       // the three kernels share one pointer type: one flag per mode
+    static bool set[6] = {false, false, false, false, false, false};   // the kernels share one pointer type: one flag per (mode, groups)
     auto go = [&](void (*kernel)(StreamParams)) {
-        if (!set[mode]) {
-            if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 113 * 1024) != cudaSuccess) { cudaGetLastError(); return CVB_E_SIZE; }
+        const int which = mode + 3 * (nb - 1);
+        if (!set[which]) {
+            if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (nb == 1 ? 113 : 226) * 1024) != cudaSuccess) { cudaGetLastError(); return CVB_E_SIZE; }
             // all kernels of the chain ask for the largest shared-memory partition, so that a block of the next kernel
             // can join a running block on its SM without the partition having to change
             cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
             cudaGetLastError();
-            set[mode] = true;
+            set[which] = true;
         }
         launch_kernel_dependent(kernel, dim3(plan.blocks), dim3(kStThreads), plan.smem, stream, pdl != 0, p);
         return launch_status();
     };
-    if (mode == 0) return go(gemv_stream_kernel<false, false>);
-    if (mode == 1) return go(gemv_stream_kernel<true, false>);
-    return go(gemv_stream_kernel<true, true>);
+    if (nb == 1) {
+        if (mode == 0) return go(gemv_stream_kernel<false, false, 1>);
+        if (mode == 1) return go(gemv_stream_kernel<true, false, 1>);
+        return go(gemv_stream_kernel<true, true, 1>);
+    }
+    if (mode == 0) return go(gemv_stream_kernel<false, false, 2>);
+    if (mode == 1) return go(gemv_stream_kernel<true, false, 2>);
+    return go(gemv_stream_kernel<true, true, 2>);
 }
 
 

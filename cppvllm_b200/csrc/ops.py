@@ -516,20 +516,20 @@ def _gemv_lib():
     return _gemv
 
 
-STREAM_MAX_ROWS = 8
+STREAM_MAX_ROWS = 16
 _stream_ok: Dict[tuple, bool] = {}
 
 
 def gemv_stream_supported(x_dtype: torch.dtype, weight: torch.Tensor, rows: int, swiglu: bool = False) -> bool:
     """The product that runs one block per SM and fetches the block's whole share of the weight ahead of its dependency
-    covers bf16 operands, up to 8 rows, and weights whose share per SM (rows / #SMs, whole rows) fits into about half an
-    SM's shared memory beside the staged activations: matrices of a few megabytes."""
+    covers bf16 operands, up to 16 rows, and weights whose share per SM (rows / #SMs, whole rows) fits into about half an
+    SM's shared memory beside the staged activations (all of it from nine rows on): matrices of a few megabytes."""
     if not (x_dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and weight.dim() == 2 and 0 < rows <= STREAM_MAX_ROWS):
         return False
-    key = (weight.shape[0], weight.shape[1], swiglu)
+    key = (weight.shape[0], weight.shape[1], swiglu, rows > 8)
     ok = _stream_ok.get(key)
     if ok is None:
-        ok = bool(_gemv_lib().cvb_gemv_stream_supported(c_int(key[0]), c_int(key[1]), c_int(2 if swiglu else 0)))
+        ok = bool(_gemv_lib().cvb_gemv_stream_supported(c_int(key[0]), c_int(key[1]), c_int(2 if swiglu else 0), c_int(rows)))
         _stream_ok[key] = ok
     return ok
 

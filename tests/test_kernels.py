@@ -601,17 +601,17 @@ def test_gemv_plain_norm_and_swiglu_forms(ops, M, N, K):
 
 
 @pytest.mark.parametrize("dependent", [True, False])
-@pytest.mark.parametrize("M", [1, 3, 8])
+@pytest.mark.parametrize("M", [1, 3, 8, 9, 13, 16])
 @pytest.mark.parametrize("N,K", [(1024, 2048), (4096, 1024), (6144, 1024), (1024, 3072), (40, 72), (1000, 3064), (3, 8), (302, 40)])
 def test_gemv_stream_forms(ops, M, N, K, dependent):
     """The product that fetches its block's weights by bulk copy ahead of its dependency (one block per SM): plain, with the
-    norm prologue and residual add, with the SwiGLU epilogue; row counts per block that are no multiple of a tile, inner
-    sizes that are no multiple of 32; twice in a row; with and without the dependent-launch attribute; against float32."""
+    norm prologue and residual add, with the SwiGLU epilogue; one and two groups of eight activation rows; row counts per
+    block that are no multiple of a tile, inner sizes that are no multiple of 32; twice in a row; with and without the dependent-launch attribute; against float32."""
     dt = torch.bfloat16
     g = torch.Generator().manual_seed(M * 37 + N + K)
     d = dev()
     W = (torch.randn(N, K, generator=g) * 0.05).to(dt).to(d)
-    assert ops.gemv_stream_supported(dt, W, M) and not ops.gemv_stream_supported(dt, W, 9)
+    assert ops.gemv_stream_supported(dt, W, M) and not ops.gemv_stream_supported(dt, W, 17)
     assert not ops.gemv_stream_supported(torch.float32, W, 1)
     assert not ops.gemv_stream_supported(dt, torch.empty(8192, 4096, dtype=dt, device="meta"), 1)    # 64 MB: not in one piece
     for rep in range(2):
