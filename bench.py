@@ -193,6 +193,38 @@ class Bench:
         flops = model_flops_prefill(self.cfg, self.cfg["num_hidden_layers"], tokens)
         return best, tokens / (best / 1e3), flops / (best / 1e3) / (pk["bf16_tflops"] * 1e12)
 
+    def portion(self, cached, tokens, pk):
+        """A portion of `tokens` tokens of a prompt whose first `cached` tokens are in the cache already, in one step:
+        (ms, tokens per second, fraction of the bf16 peak; the flops are the portion's own)."""
+        from cppvllm_b200.engine.runner import StepEntry
+        torch, r = self.torch, self.r
+        ms = []
+        budget = r.max_step_tokens
+        for it in range(1 + 3):
+            toks = self.rand_tokens(cached + tokens)
+            r.cache.admit("pp")
+            r.cache.reserve("pp", cached + tokens)
+            for a in range(0, cached, budget):
+                r.step([StepEntry("pp", toks[a:min(cached, a + budget)], a, [])])
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            t0 = time.time()
+            e0.record()
+            r.step([StepEntry("pp", toks[cached:], cached, [tokens - 1])])
+            e1.record()
+            torch.cuda.synchronize()
+            if it > 0:
+                ms.append(e0.elapsed_time(e1))
+                self.windows.append((t0, time.time()))
+            r.cache.release("pp")
+        best = min(ms)
+        c = self.cfg
+        D, H, KV, hd, I, V, L = (c["hidden_size"], c["num_attention_heads"], c["num_key_value_heads"], c["head_dim"],
+                                 c["intermediate_size"], c["vocab_size"], c["num_hidden_layers"])
+        per_token = 2 * (D * (H + 2 * KV) * hd + H * hd * D + 3 * D * I)
+        flops = L * (tokens * per_token + 4 * H * hd * tokens * (cached + (tokens + 1) / 2.0)) + 2 * D * V
+        return best, tokens / (best / 1e3), flops / (best / 1e3) / (pk["bf16_tflops"] * 1e12)
+
     def decode(self, batch, ctx, steps, warm, repeats=1):
         """`steps` decode steps of `batch` requests enqueued back to back, the last at `ctx` tokens per request, timed
         on the device (`repeats` times; the median counts).  Returns (ms per step, launches, bytes a step must read)."""
@@ -346,10 +378,14 @@ def main():
     achieved = bytes8 / (ms8 / 1e3) / 1e9
     points = {}
     if not args.no_points:
-        for b in (1, 64):
+        for b in (1, 16, 64):
             ms_b, _, nb = bench.decode(b, CTX, max(8, K // 4), W, 3)
             points[f"decode_b{b}"] = round(b / (ms_b / 1e3), 1)
             points[f"decode_b{b}_frac"] = round(nb / (ms_b / 1e3) / 1e9 / pk["hbm_gbs"], 4)
+        if CTX >= 1024:
+            # a prompt portion behind a long context: few query blocks with many key tiles each
+            _, tps_p, frac_p = bench.portion(CTX - 512, 512, pk)
+            points[f"portion_512_behind_{CTX - 512}_tok_s"], points[f"portion_512_behind_{CTX - 512}_frac"] = round(tps_p, 1), round(frac_p, 4)
 
     # ---- end to end through the public entry point --------------------------------------------------------------
     ctx0 = CTX - K - W
@@ -406,6 +442,8 @@ def main():
         points["8b_layers"], points["8b_layers_full"] = LAYERS_8B, MODEL_8B["num_hidden_layers"]
         ms_p, tps, frac = big.prefill(PREFILL_TOKENS, pk)
         points["8b_prefill_2048_tok_s"], points["8b_prefill_2048_frac"] = round(tps, 1), round(frac, 4)
+        _, tps, frac = big.portion(7680, 512, pk)
+        points["8b_portion_512_behind_7680_tok_s"], points["8b_portion_512_behind_7680_frac"] = round(tps, 1), round(frac, 4)
         for ctx in (4096, 8192):
             for b in (1, 8, 64):
                 ms_b, _, nb = big.decode(b, ctx, 16, 4, 1)
