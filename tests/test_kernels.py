@@ -475,6 +475,53 @@ def test_tcgen05_prefill_shares_the_keys_of_long_query_blocks_among_blocks(ops, 
         assert torch.isfinite(got).all() and (got[rows] - rnd(ref, dt)[rows]).abs().max() < 2e-2
 
 
+@pytest.mark.parametrize("seed", [0, 1, 2, 3, 4, 5])
+def test_tcgen05_prefill_pieces_at_random_shapes(ops, seed):
+    """Random requests (tokens in the cache, tokens in the step), heads, pages, windows, piece counts and piece lengths:
+    the rows that come out of the pieces equal, within rounding, the rows of one block per query block."""
+    import random
+    rng = random.Random(seed)
+    dt = torch.bfloat16
+    g = torch.Generator().manual_seed(100 + seed)
+    H, KV = rng.choice([(4, 2), (6, 1), (8, 8), (16, 8), (10, 2)])
+    hd, page = rng.choice([64, 128]), rng.choice([16, 32, 64])
+    window = rng.choice([0, 0, 400, 1100])
+    pieces, min_rounds = rng.randint(2, 8), rng.randint(1, 3)
+    reqs = [(rng.choice([0, rng.randint(1, 2500)]), rng.randint(2, 400)) for _ in range(rng.randint(2, 5))]
+    seqs_k = [torch.randn(c + n, KV, hd, generator=g).to(dt) for c, n in reqs]
+    seqs_v = [torch.randn(c + n, KV, hd, generator=g).to(dt) for c, n in reqs]
+    cu, positions = [0], []
+    for c, n in reqs:
+        cu.append(cu[-1] + n)
+        positions += list(range(c, c + n))
+    T = cu[-1]
+    q = (torch.randn(T, H, hd, generator=g) * 1.5).to(dt)
+    total_pages = sum((c + n + page - 1) // page for c, n in reqs) + 3
+    cache, tables = build_paged(seqs_k, seqs_v, page, total_pages, KV, hd, dt, g)
+    for s, (c, n) in enumerate(reqs):
+        if (c + n) % page:
+            cache[tables[s, (c + n - 1) // page], :, :, (c + n) % page:] = float("nan")
+        if window > 0:
+            for slot in range(max(0, c - window + 1) // page):
+                cache[tables[s, slot]] = float("nan")
+                tables[s, slot] = -1
+    d = dev()
+    scale = 1 / math.sqrt(hd)
+    q_lens = [n for _, n in reqs]
+    tiles = ops.prefill_tiles_tcgen05(q_lens, H, KV)
+    args = (q.view(T, -1).to(d), cache.to(d), tables.to(d), torch.tensor(cu, dtype=torch.int32, device=d),
+            torch.tensor(positions, dtype=torch.int32, device=d), len(reqs), tiles, H, KV, hd, page, scale)
+    whole = ops.attn_prefill_tcgen05(torch.full((T, H * hd), float("nan"), dtype=dt, device=d), *args, window=window)
+    scratch = torch.full((ops.attn_prefill_tcgen05_scratch_floats(tiles, KV, hd, pieces),), float("nan"), device=d)
+    counts = torch.full((tiles * KV,), -3, dtype=torch.int32, device=d)
+    cut = ops.attn_prefill_tcgen05(torch.full((T, H * hd), float("nan"), dtype=dt, device=d), *args, window=window,
+                                   pieces=pieces, min_rounds=min_rounds, scratch=scratch, piece_counts=counts)
+    ops.check_device_errors(d)
+    assert torch.isfinite(whole.float()).all() and torch.isfinite(cut.float()).all()
+    torch.testing.assert_close(cut.float(), whole.float(), atol=1e-2, rtol=1e-2)
+    assert int(counts.max()) <= pieces and int(counts.min()) >= 1
+
+
 @pytest.mark.parametrize("H,KV,hd,page,window,norm,rope", [(16, 8, 128, 32, 0, True, True), (6, 2, 64, 16, 0, True, True),
                                                           (16, 1, 128, 16, 0, False, True), (4, 4, 64, 64, 70, True, False)])
 def test_decode_attention_from_the_projection(ops, H, KV, hd, page, window, norm, rope):
